@@ -1,0 +1,164 @@
+// Shared device/host helpers: status codes, the canonical fp32 distance, (dist,id) keys.
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <cstdio>
+
+#include "../../include/grab_anns.h"
+
+namespace grab {
+
+constexpr uint32_t kInvalid = 0xFFFFFFFFu;  // empty graph slot / empty hash slot (reference: hashmap.cuh:15)
+constexpr uint32_t kMsb = 0x80000000u;      // "already expanded" flag on queue ids (reference: search.cu:51)
+constexpr uint64_t kMaxKey = 0xFFFFFFFFFFFFFFFFull;
+constexpr float kFltMax = 3.40282e38f;      // the reference's FLT_MAX literal (compute_distance.cuh:161)
+
+void set_last_error(const char* fmt, ...);
+
+#define GRAB_CUDA_TRY(expr)                                                              \
+  do {                                                                                   \
+    cudaError_t _e = (expr);                                                             \
+    if (_e != cudaSuccess) {                                                             \
+      ::grab::set_last_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e),     \
+                             __FILE__, __LINE__);                                        \
+      return GRAB_ERR_CUDA;                                                              \
+    }                                                                                    \
+  } while (0)
+
+#define GRAB_REQUIRE(cond, ...)              \
+  do {                                       \
+    if (!(cond)) {                           \
+      ::grab::set_last_error(__VA_ARGS__);   \
+      return GRAB_ERR_INVALID_ARGUMENT;      \
+    }                                        \
+  } while (0)
+
+// Order-preserving float -> uint32 map, so that (dist, id) pairs sort as one uint64.
+__host__ __device__ __forceinline__ uint32_t float_to_ordered(float f) {
+#ifdef __CUDA_ARCH__
+  uint32_t b = __float_as_uint(f);
+#else
+  uint32_t b;
+  memcpy(&b, &f, 4);
+#endif
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__host__ __device__ __forceinline__ float ordered_to_float(uint32_t o) {
+  uint32_t b = (o & 0x80000000u) ? (o & 0x7FFFFFFFu) : ~o;
+#ifdef __CUDA_ARCH__
+  return __uint_as_float(b);
+#else
+  float f;
+  memcpy(&f, &b, 4);
+  return f;
+#endif
+}
+__host__ __device__ __forceinline__ uint64_t make_key(float dist, uint32_t id) {
+  return (static_cast<uint64_t>(float_to_ordered(dist)) << 32) | id;
+}
+__host__ __device__ __forceinline__ float key_dist(uint64_t key) {
+  return ordered_to_float(static_cast<uint32_t>(key >> 32));
+}
+__host__ __device__ __forceinline__ uint32_t key_id(uint64_t key) {
+  return static_cast<uint32_t>(key & 0xFFFFFFFFull);
+}
+
+#ifdef __CUDACC__
+// ---------------------------------------------------------------------------------------
+// Canonical fp32 distance.  A vector is cut into float4 chunks; chunk c belongs to lane
+// (c mod 8) of a team of 8 consecutive lanes; a lane accumulates its chunks in ascending
+// order (x, y, z, w in order, one fused multiply-add each); the 8 partial sums are combined
+// by a butterfly at xor-offsets 4, 2, 1 (all 8 lanes end with the same bits).  The CPU
+// oracle evaluates exactly this expression, which is what makes ids bit-exact.
+// It replaces the reference's 32-lane scalar-load variant (compute_distance.cuh:14-139).
+// ---------------------------------------------------------------------------------------
+constexpr int kTeam = 8;
+
+template <int METRIC>
+__device__ __forceinline__ float accum4(float acc, const float4& q, const float4& x) {
+  if (METRIC == GRAB_METRIC_L2) {
+    float d;
+    d = q.x - x.x; acc = __fmaf_rn(d, d, acc);
+    d = q.y - x.y; acc = __fmaf_rn(d, d, acc);
+    d = q.z - x.z; acc = __fmaf_rn(d, d, acc);
+    d = q.w - x.w; acc = __fmaf_rn(d, d, acc);
+  } else {
+    acc = __fmaf_rn(q.x, x.x, acc);
+    acc = __fmaf_rn(q.y, x.y, acc);
+    acc = __fmaf_rn(q.z, x.z, acc);
+    acc = __fmaf_rn(q.w, x.w, acc);
+  }
+  return acc;
+}
+
+// Butterfly over the 8 lanes of a team; every lane of the warp must call it.
+template <int METRIC>
+__device__ __forceinline__ float team_reduce(float acc) {
+  acc = __fadd_rn(acc, __shfl_xor_sync(0xFFFFFFFFu, acc, 4));
+  acc = __fadd_rn(acc, __shfl_xor_sync(0xFFFFFFFFu, acc, 2));
+  acc = __fadd_rn(acc, __shfl_xor_sync(0xFFFFFFFFu, acc, 1));
+  return METRIC == GRAB_METRIC_L2 ? acc : -acc;
+}
+
+__device__ __forceinline__ float4 ldg_f4(const float* p) {
+  return __ldg(reinterpret_cast<const float4*>(p));
+}
+
+// Distance between a query held in shared memory and a dataset row, computed by one team.
+// `lane8` = lane index inside the team.  All 32 lanes of the warp must take part (lanes of
+// teams without work pass valid=false and read nothing).
+template <int METRIC>
+__device__ __forceinline__ float team_distance_smem(const float* __restrict__ q_smem,
+                                                    const float* __restrict__ row, uint32_t nchunk,
+                                                    int lane8, bool valid) {
+  float acc = 0.0f;
+  if (valid) {
+    for (uint32_t c = lane8; c < nchunk; c += kTeam) {
+      const float4 x = ldg_f4(row + 4 * c);
+      const float4 q = *reinterpret_cast<const float4*>(q_smem + 4 * c);
+      acc = accum4<METRIC>(acc, q, x);
+    }
+  }
+  return team_reduce<METRIC>(acc);
+}
+
+__device__ __forceinline__ uint32_t lane_id() { return threadIdx.x & 31u; }
+
+// Block-wide bitonic sort of `n` (power of two) uint64 keys in shared memory, ascending.
+// Every thread of the block must call it.
+__device__ __forceinline__ void block_bitonic_sort(uint64_t* keys, uint32_t n) {
+  for (uint32_t size = 2; size <= n; size <<= 1) {
+    for (uint32_t stride = size >> 1; stride > 0; stride >>= 1) {
+      for (uint32_t t = threadIdx.x; t < (n >> 1); t += blockDim.x) {
+        const uint32_t lo = ((t & ~(stride - 1)) << 1) | (t & (stride - 1));
+        const uint32_t hi = lo | stride;
+        const bool up = (lo & size) == 0;
+        const uint64_t a = keys[lo], b = keys[hi];
+        if ((a > b) == up) {
+          keys[lo] = b;
+          keys[hi] = a;
+        }
+      }
+      __syncthreads();
+    }
+  }
+}
+#endif  // __CUDACC__
+
+inline uint32_t next_pow2(uint32_t v) {
+  if (v <= 1) return 1;
+  v--;
+  v |= v >> 1; v |= v >> 2; v |= v >> 4; v |= v >> 8; v |= v >> 16;
+  return v + 1;
+}
+
+// Scratch allocation used by the stateless entry points when the caller passes no
+// workspace: plain cudaMalloc, released on scope exit.
+struct ScopedDeviceBuffer {
+  void* ptr = nullptr;
+  cudaError_t alloc(size_t bytes) { return cudaMalloc(&ptr, bytes ? bytes : 1); }
+  ~ScopedDeviceBuffer() { if (ptr) cudaFree(ptr); }
+  template <class T> T* as() { return static_cast<T*>(ptr); }
+};
+
+}  // namespace grab

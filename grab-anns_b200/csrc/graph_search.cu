@@ -1,0 +1,458 @@
+// Filtered graph search (timestamp range / bucket prefix / label mask / none).
+//
+// One kernel replaces the reference's three (src/index/search.cu:149 search_kernel, :375
+// search_kernel_bucket, :589 search_kernel_range) and its building blocks
+// (compute_distance.cuh:204-614, hashmap.cuh, the sorts of search.cu:110-144).  Same loop
+// -- keep the best `itopk`, pick up to `search_width` unexpanded parents, expand their
+// rows, repeat -- re-laid for B200:
+//   * the filter predicate runs BEFORE the visited-set insert and before any vector is
+//     fetched, so rejected neighbours cost 4+f bytes and never pollute the table
+//     (the reference inserts first: compute_distance.cuh:572-584);
+//   * survivors are compacted, then teams of 8 lanes gather one vector each with 16-byte
+//     loads, 4 vectors in flight per team (the reference: one warp, scalar loads, per
+//     neighbour);
+//   * queue entries are single uint64 (dist,id) keys; only itopk + survivors are sorted;
+//   * the visited table is cleared when half full and re-seeded from the current itopk
+//     (the reference: every 30 iterations, search.cu:692-697).
+// HBM/latency-bound by design: no tensor cores.
+#include "common.cuh"
+
+namespace grab {
+
+constexpr int kSearchThreads = 128;
+constexpr int kSearchTeams = kSearchThreads / kTeam;  // 16
+constexpr int kSearchUnroll = 4;
+
+struct SearchKernelArgs {
+  const float* data;
+  uint64_t n;
+  uint32_t dim;
+  const uint32_t* graph;
+  uint32_t deg;         // row stride
+  uint32_t active_deg;  // columns walked
+  const float* queries;
+  uint64_t nq;
+  uint32_t k, itopk, width, max_iter, hash_bitlen;
+  uint32_t num_seeds;  // seeds evaluated per query
+  const uint32_t* seeds;
+  uint32_t seeds_per_query;
+  uint64_t seed;
+  int filter_kind;
+  const uint64_t* ts;
+  const uint64_t* lo;
+  const uint64_t* hi;
+  uint64_t lo1, hi1;
+  const uint8_t* labels;
+  const uint32_t* masks;
+  uint32_t mask1;
+  const uint32_t* windows;  // [nq,4] id window per query (sorted ts), or NULL
+  uint32_t* global_hash;    // [nq, 2^bitlen] when the table does not fit shared memory
+  int64_t* out_ids;
+  float* out_dists;
+  uint64_t id_scale, id_offset;
+  unsigned long long* stats;  // grab_search_stats as 6 x u64, or NULL
+  uint32_t cand_cap, sort_cap;
+};
+
+__device__ __forceinline__ bool hash_insert(uint32_t* table, uint32_t bitlen, uint32_t key) {
+  // Open addressing, linear probe, slot = (key ^ key>>bitlen) & mask: hashmap.cuh:43-91.
+  const uint32_t mask = (1u << bitlen) - 1;
+  uint32_t idx = (key ^ (key >> bitlen)) & mask;
+  for (uint32_t i = 0; i <= mask; ++i) {
+    const uint32_t old = atomicCAS(&table[idx], kInvalid, key);
+    if (old == kInvalid) return true;
+    if (old == key) return false;
+    idx = (idx + 1) & mask;
+  }
+  return false;  // full table reads as "visited", as in the reference (hashmap.cuh:89-90)
+}
+
+__device__ __forceinline__ uint64_t mix64(uint64_t x) {  // splitmix64 finaliser
+  x ^= x >> 30; x *= 0xbf58476d1ce4e5b9ull;
+  x ^= x >> 27; x *= 0x94d049bb133111ebull;
+  x ^= x >> 31;
+  return x;
+}
+
+template <int METRIC, int CPL>
+__global__ void __launch_bounds__(kSearchThreads)
+graph_search_kernel(const SearchKernelArgs a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  uint64_t* queue = reinterpret_cast<uint64_t*>(smem_raw);                 // [sort_cap]
+  float* q_smem = reinterpret_cast<float*>(queue + a.sort_cap);            // [dim]
+  uint32_t* cand = reinterpret_cast<uint32_t*>(q_smem + a.dim);            // [cand_cap]
+  uint32_t* parents = cand + a.cand_cap;                                   // [width]
+  uint32_t* hash = parents + ((a.width + 3) & ~3u);                        // [2^bitlen] (if local)
+  __shared__ uint32_t s_ncand, s_nparents, s_hash_count;
+  __shared__ unsigned long long s_stats[6];
+
+  const uint64_t qi = blockIdx.x;
+  if (qi >= a.nq) return;
+  const uint32_t tid = threadIdx.x;
+  const int lane8 = tid & (kTeam - 1);
+  const uint32_t team = tid / kTeam;
+  const uint32_t nchunk = a.dim / 4;
+  const uint32_t hsize = 1u << a.hash_bitlen;
+  if (a.global_hash) hash = a.global_hash + qi * hsize;
+
+  for (uint32_t i = tid; i < a.dim; i += kSearchThreads) q_smem[i] = a.queries[qi * a.dim + i];
+  for (uint32_t i = tid; i < a.sort_cap; i += kSearchThreads) queue[i] = kMaxKey;
+  for (uint32_t i = tid; i < hsize; i += kSearchThreads) hash[i] = kInvalid;
+  if (tid == 0) { s_ncand = 0; s_nparents = 0; s_hash_count = 0; }
+  if (tid < 6) s_stats[tid] = 0;
+
+  uint64_t lo = 0, hi = 0;
+  uint32_t mask = 0;
+  if (a.filter_kind == GRAB_FILTER_TS_RANGE) {
+    lo = a.lo ? a.lo[qi] : a.lo1;
+    hi = a.hi ? a.hi[qi] : a.hi1;
+  } else if (a.filter_kind == GRAB_FILTER_LABELS) {
+    mask = a.masks ? a.masks[qi] : a.mask1;
+  }
+  auto passes = [&](uint32_t id) -> bool {
+    if (a.filter_kind == GRAB_FILTER_TS_RANGE) {
+      const uint64_t t = __ldg(a.ts + id);
+      return t >= lo && t < hi;
+    }
+    if (a.filter_kind == GRAB_FILTER_LABELS) return (mask >> __ldg(a.labels + id)) & 1u;
+    return true;
+  };
+  __syncthreads();
+
+  float4 qreg[CPL > 0 ? CPL : 1];
+  if (CPL > 0) {
+#pragma unroll
+    for (int c = 0; c < CPL; ++c)
+      qreg[c] = *reinterpret_cast<const float4*>(q_smem + 4 * (lane8 + kTeam * c));
+  }
+
+  // ---- seeds (compute_distance.cuh:204-269): provided ids, else pseudo-random ids ----
+  {
+    uint32_t wbeg = 0, wlen = 0;
+    if (a.windows) {
+      wbeg = a.windows[qi * 4];
+      const uint32_t wend = a.windows[qi * 4 + 1];
+      wlen = wend > wbeg ? wend - wbeg : 0;
+    }
+    const bool generated_only = (a.seeds == nullptr);
+    // without an id window a generated seed may fail the filter: allow 4 attempts per seed
+    const uint32_t attempts = (generated_only && !a.windows && a.filter_kind != GRAB_FILTER_NONE &&
+                               a.filter_kind != GRAB_FILTER_PREFIX) ? 4 * a.num_seeds : a.num_seeds;
+    for (uint32_t i = tid; i < attempts; i += kSearchThreads) {
+      uint32_t id = kInvalid;
+      if (a.seeds && i < a.seeds_per_query) id = a.seeds[qi * a.seeds_per_query + i];
+      if (id >= a.n) {
+        if (a.windows) {
+          id = wlen ? wbeg + static_cast<uint32_t>(mix64(a.seed ^ (qi * 0x9e3779b97f4a7c15ull + i)) % wlen)
+                    : kInvalid;
+        } else {
+          // reference rule: (xor_mask * (i+1)) % n, compute_distance.cuh:236-238
+          id = static_cast<uint32_t>(((a.seed | 1ull) * static_cast<uint64_t>(i + 1)) % a.n);
+        }
+      }
+      if (id < a.n && passes(id) && hash_insert(hash, a.hash_bitlen, id)) {
+        const uint32_t pos = atomicAdd(&s_ncand, 1u);
+        if (pos < a.num_seeds) cand[pos] = id;
+      }
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    if (s_ncand > a.num_seeds) s_ncand = a.num_seeds;
+    s_hash_count = s_ncand;
+    s_stats[4] += s_ncand;
+  }
+  __syncthreads();
+
+  uint32_t iter = 0;
+  bool expanded = true;  // candidates waiting in cand[0..s_ncand)
+  for (;;) {
+    // ---- distances of the compacted candidates: 16 teams x 4 vectors in flight ----
+    const uint32_t ncand = s_ncand;
+    if (expanded) {
+      for (uint32_t j0 = 0; j0 < ncand; j0 += kSearchTeams * kSearchUnroll) {
+        uint32_t id[kSearchUnroll];
+        bool ok[kSearchUnroll];
+        float acc[kSearchUnroll];
+#pragma unroll
+        for (int u = 0; u < kSearchUnroll; ++u) {
+          const uint32_t j = j0 + u * kSearchTeams + team;
+          ok[u] = j < ncand;
+          id[u] = ok[u] ? cand[j] : 0;
+          acc[u] = 0.0f;
+        }
+        if (CPL > 0) {
+          float4 x[kSearchUnroll][CPL > 0 ? CPL : 1];
+#pragma unroll
+          for (int u = 0; u < kSearchUnroll; ++u)
+#pragma unroll
+            for (int c = 0; c < CPL; ++c)
+              if (ok[u]) x[u][c] = ldg_f4(a.data + static_cast<size_t>(id[u]) * a.dim + 4 * (lane8 + kTeam * c));
+#pragma unroll
+          for (int u = 0; u < kSearchUnroll; ++u)
+#pragma unroll
+            for (int c = 0; c < CPL; ++c)
+              if (ok[u]) acc[u] = accum4<METRIC>(acc[u], qreg[c], x[u][c]);
+        } else {
+          for (uint32_t c = lane8; c < nchunk; c += kTeam) {
+            const float4 qv = *reinterpret_cast<const float4*>(q_smem + 4 * c);
+            float4 x[kSearchUnroll];
+#pragma unroll
+            for (int u = 0; u < kSearchUnroll; ++u)
+              if (ok[u]) x[u] = ldg_f4(a.data + static_cast<size_t>(id[u]) * a.dim + 4 * c);
+#pragma unroll
+            for (int u = 0; u < kSearchUnroll; ++u)
+              if (ok[u]) acc[u] = accum4<METRIC>(acc[u], qv, x[u]);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < kSearchUnroll; ++u) {
+          const float d = team_reduce<METRIC>(acc[u]);
+          if (lane8 == 0 && ok[u]) queue[a.itopk + j0 + u * kSearchTeams + team] = make_key(d, id[u]);
+        }
+      }
+      __syncthreads();
+    }
+
+    // ---- sort itopk + candidates (only as many slots as are in use) ----
+    uint32_t used = a.itopk + (expanded ? ncand : 0);
+    uint32_t padded = 64;
+    while (padded < used) padded <<= 1;
+    block_bitonic_sort(queue, padded);
+    for (uint32_t i = a.itopk + tid; i < padded; i += kSearchThreads) queue[i] = kMaxKey;
+
+    // ---- visited table half full: clear and re-seed from the current itopk ----
+    if (s_hash_count > hsize / 2) {  // uniform
+      __syncthreads();
+      for (uint32_t i = tid; i < hsize; i += kSearchThreads) hash[i] = kInvalid;
+      __syncthreads();
+      uint32_t kept = 0;
+      for (uint32_t i = tid; i < a.itopk; i += kSearchThreads) {
+        const uint64_t key = queue[i];
+        if (key != kMaxKey) { hash_insert(hash, a.hash_bitlen, key_id(key) & ~kMsb); ++kept; }
+      }
+      kept = __reduce_add_sync(0xFFFFFFFFu, kept);
+      if (tid == 0) { s_hash_count = 0; s_stats[5] += 1; }
+      __syncthreads();
+      if ((tid & 31) == 0) atomicAdd(&s_hash_count, kept);
+    }
+    if (iter >= a.max_iter) break;
+
+    // ---- pick up to `width` unexpanded parents, best first (search.cu:38-107) ----
+    if (tid < 32) {
+      uint32_t found = 0;
+      for (uint32_t j0 = 0; j0 < a.itopk && found < a.width; j0 += 32) {
+        const uint32_t j = j0 + tid;
+        uint64_t key = j < a.itopk ? queue[j] : kMaxKey;
+        const bool fresh = key != kMaxKey && (key_id(key) & kMsb) == 0;
+        const uint32_t vote = __ballot_sync(0xFFFFFFFFu, fresh);
+        if (fresh) {
+          const uint32_t rank = found + __popc(vote & ((1u << tid) - 1));
+          if (rank < a.width) {
+            parents[rank] = key_id(key);
+            queue[j] = key | kMsb;
+          }
+        }
+        found += __popc(vote);
+      }
+      if (found > a.width) found = a.width;
+      if (tid == 0) { s_nparents = found; s_ncand = 0; }
+    }
+    __syncthreads();
+    const uint32_t nparents = s_nparents;
+    if (nparents == 0) break;
+
+    // ---- expand: neighbour id -> filter -> visited set -> compacted survivor list ----
+    uint32_t my_edges = 0;
+    const uint32_t tasks = nparents * a.active_deg;
+    for (uint32_t t = tid; t < tasks; t += kSearchThreads) {
+      const uint32_t p = parents[t / a.active_deg];
+      const uint32_t nb = __ldg(a.graph + static_cast<size_t>(p) * a.deg + (t % a.active_deg));
+      if (nb < a.n) {
+        ++my_edges;
+        if (passes(nb) && hash_insert(hash, a.hash_bitlen, nb)) {
+          const uint32_t pos = atomicAdd(&s_ncand, 1u);
+          cand[pos] = nb;
+        }
+      }
+    }
+    if (a.stats) {
+      my_edges = __reduce_add_sync(0xFFFFFFFFu, my_edges);
+      if ((tid & 31) == 0) atomicAdd(&s_stats[2], static_cast<unsigned long long>(my_edges));
+    }
+    __syncthreads();
+    if (tid == 0) {
+      s_hash_count += s_ncand;
+      s_stats[0] += 1;
+      s_stats[1] += nparents;
+      s_stats[3] += s_ncand;
+    }
+    expanded = true;
+    ++iter;
+    __syncthreads();
+  }
+
+  // ---- results: ascending (dist,id); id = local*scale + offset; empty slots are -1 ----
+  __syncthreads();
+  for (uint32_t i = tid; i < a.k; i += kSearchThreads) {
+    const uint64_t key = queue[i];
+    const bool empty = key == kMaxKey;
+    a.out_ids[qi * a.k + i] =
+        empty ? -1 : static_cast<int64_t>((key_id(key) & ~kMsb) * a.id_scale + a.id_offset);
+    a.out_dists[qi * a.k + i] = empty ? kFltMax : key_dist(key);
+  }
+  if (a.stats && tid < 6) atomicAdd(&a.stats[tid], s_stats[tid]);
+}
+
+template <int METRIC>
+static cudaError_t launch_search(const SearchKernelArgs& a, size_t smem, cudaStream_t st) {
+#define GRAB_SEARCH_LAUNCH(CPL)                                                                   \
+  do {                                                                                            \
+    cudaError_t e = cudaFuncSetAttribute(graph_search_kernel<METRIC, CPL>,                        \
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    if (e != cudaSuccess) return e;                                                               \
+    graph_search_kernel<METRIC, CPL><<<(unsigned)a.nq, kSearchThreads, smem, st>>>(a);            \
+  } while (0)
+  if (a.dim == 96) GRAB_SEARCH_LAUNCH(3);
+  else if (a.dim == 128) GRAB_SEARCH_LAUNCH(4);
+  else GRAB_SEARCH_LAUNCH(0);
+#undef GRAB_SEARCH_LAUNCH
+  return cudaGetLastError();
+}
+
+__global__ void ts_window4_kernel(const uint64_t* __restrict__ ts, uint64_t n,
+                                  const uint64_t* __restrict__ lo, const uint64_t* __restrict__ hi,
+                                  uint64_t lo1, uint64_t hi1, uint64_t nq,
+                                  uint32_t* __restrict__ windows) {
+  const uint64_t qi = blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x;
+  if (qi >= nq) return;
+  const uint64_t bounds[2] = {lo ? lo[qi] : lo1, hi ? hi[qi] : hi1};
+  for (int b = 0; b < 2; ++b) {
+    uint64_t l = 0, r = n;
+    while (l < r) {
+      const uint64_t m = (l + r) >> 1;
+      if (ts[m] < bounds[b]) l = m + 1; else r = m;
+    }
+    windows[qi * 4 + b] = static_cast<uint32_t>(l);
+  }
+  windows[qi * 4 + 2] = 0;
+  windows[qi * 4 + 3] = 0;
+}
+
+// Launcher rules restated from the reference: itopk = max(k, itopk) with floor 64
+// (cagra_opt.cu:1126-1129, :1352-1355) or 128 for the bucket search (:1242-1243); seeds
+// evaluated = clamp(max(32, provided), itopk) unfiltered (:1150-1151) or min(provided, itopk)
+// filtered (:1276-1277, :1386-1387); with no seeds given a filtered search draws
+// max(32, itopk/4) of its own (the class layer's rule, cagraIndexOpt.cu:441).
+int graph_search_impl(const grab_search_args* g) {
+  GRAB_REQUIRE(g, "graph_search: null args");
+  GRAB_REQUIRE(g->d_dataset && g->d_graph && g->d_queries && g->d_out_ids && g->d_out_dists,
+               "graph_search: null pointer (the reference throws \"Graph is null!\", cagra_opt.cu:1123)");
+  GRAB_REQUIRE(g->dim >= 4 && g->dim % 4 == 0, "graph_search: dim %u must be a multiple of 4", g->dim);
+  GRAB_REQUIRE(g->n >= 1 && g->n < (1ull << 31), "graph_search: n must be in [1, 2^31)");
+  GRAB_REQUIRE(g->k >= 1 && g->k <= 1024, "graph_search: k %u outside [1,1024]", g->k);
+  GRAB_REQUIRE(g->graph_degree >= 1 && g->graph_degree <= 512, "graph_search: bad graph degree %u",
+               g->graph_degree);
+  GRAB_REQUIRE(g->metric == GRAB_METRIC_L2 || g->metric == GRAB_METRIC_IP, "graph_search: bad metric");
+  GRAB_REQUIRE(g->params.search_width >= 1 && g->params.search_width <= 64,
+               "graph_search: search_width %u outside [1,64]", g->params.search_width);
+  GRAB_REQUIRE(g->params.hash_bitlen >= 8 && g->params.hash_bitlen <= 20,
+               "graph_search: hash_bitlen %u outside [8,20]", g->params.hash_bitlen);
+  if (g->nq == 0) return GRAB_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(g->stream);
+  const grab_filter& f = g->filter;
+
+  SearchKernelArgs a{};
+  a.data = g->d_dataset; a.n = g->n; a.dim = g->dim; a.graph = g->d_graph;
+  a.deg = g->graph_degree; a.active_deg = g->graph_degree;
+  a.queries = g->d_queries; a.nq = g->nq; a.k = g->k;
+  a.width = g->params.search_width; a.max_iter = g->params.max_iterations;
+  a.hash_bitlen = g->params.hash_bitlen;
+  a.seeds = g->d_seeds; a.seeds_per_query = g->d_seeds ? g->seeds_per_query : 0;
+  a.seed = g->seed; a.filter_kind = f.kind;
+  a.out_ids = g->d_out_ids; a.out_dists = g->d_out_dists;
+  a.id_scale = g->id_scale ? g->id_scale : 1; a.id_offset = g->id_offset;
+  a.stats = reinterpret_cast<unsigned long long*>(g->d_stats);
+
+  uint32_t itopk = g->k > g->params.itopk_size ? g->k : g->params.itopk_size;
+  uint32_t floor_ = 64;
+  bool need_window = false;
+  switch (f.kind) {
+    case GRAB_FILTER_NONE: break;
+    case GRAB_FILTER_PREFIX:
+      GRAB_REQUIRE(f.active_degree >= 1 && f.active_degree <= g->graph_degree,
+                   "graph_search: active_degree %u outside [1,%u]", f.active_degree, g->graph_degree);
+      a.active_deg = f.active_degree;
+      floor_ = 128;
+      break;
+    case GRAB_FILTER_TS_RANGE:
+      GRAB_REQUIRE(f.d_ts, "graph_search: ts filter without d_ts");
+      GRAB_REQUIRE((f.d_lo == nullptr) == (f.d_hi == nullptr),
+                   "graph_search: d_lo and d_hi must both be given or both NULL");
+      a.ts = f.d_ts; a.lo = f.d_lo; a.hi = f.d_hi; a.lo1 = f.lo; a.hi1 = f.hi;
+      need_window = f.ts_sorted && !g->d_seeds;
+      break;
+    case GRAB_FILTER_LABELS:
+      GRAB_REQUIRE(f.d_labels, "graph_search: label filter without d_labels");
+      a.labels = f.d_labels; a.masks = f.d_masks; a.mask1 = f.mask;
+      break;
+    default:
+      set_last_error("graph_search: unknown filter kind %d", f.kind);
+      return GRAB_ERR_INVALID_ARGUMENT;
+  }
+  if (itopk < floor_) itopk = floor_;
+  a.itopk = itopk;
+  uint32_t nseeds;
+  if (f.kind == GRAB_FILTER_NONE) nseeds = a.seeds_per_query > 32 ? a.seeds_per_query : 32;
+  else if (g->d_seeds) nseeds = a.seeds_per_query;
+  else nseeds = itopk / 4 > 32 ? itopk / 4 : 32;
+  if (nseeds > itopk) nseeds = itopk;
+  a.num_seeds = nseeds;
+  a.cand_cap = a.width * a.deg > itopk ? a.width * a.deg : itopk;
+  a.cand_cap = (a.cand_cap + 3) & ~3u;
+  a.sort_cap = next_pow2(itopk + a.cand_cap);
+  if (a.sort_cap < 64) a.sort_cap = 64;
+
+  const bool local_hash = a.hash_bitlen <= 13;
+  const size_t hash_bytes = sizeof(uint32_t) * (size_t(1) << a.hash_bitlen);
+  size_t smem = sizeof(uint64_t) * a.sort_cap + sizeof(float) * a.dim + sizeof(uint32_t) * a.cand_cap +
+                sizeof(uint32_t) * ((a.width + 3) & ~3u) + (local_hash ? hash_bytes : 0);
+  if (smem > 200 * 1024) {
+    set_last_error("graph_search: itopk %u, width %u, degree %u, dim %u need %zu bytes of shared memory",
+                   itopk, a.width, a.deg, a.dim, smem);
+    return GRAB_ERR_UNSUPPORTED;
+  }
+  const size_t need = grab_graph_search_workspace_bytes(g->nq, a.hash_bitlen);
+  ScopedDeviceBuffer own;
+  void* ws = g->d_ws;
+  if (!ws) {
+    GRAB_CUDA_TRY(own.alloc(need));
+    ws = own.ptr;
+  } else if (g->ws_bytes < need) {
+    set_last_error("graph_search: workspace %zu < %zu bytes", g->ws_bytes, need);
+    return GRAB_ERR_WORKSPACE;
+  }
+  uint32_t* windows = static_cast<uint32_t*>(ws);
+  if (need_window) {
+    ts_window4_kernel<<<(unsigned)((g->nq + 255) / 256), 256, 0, st>>>(f.d_ts, g->n, f.d_lo, f.d_hi,
+                                                                      f.lo, f.hi, g->nq, windows);
+    GRAB_CUDA_TRY(cudaGetLastError());
+    a.windows = windows;
+  }
+  if (!local_hash)
+    a.global_hash = reinterpret_cast<uint32_t*>(static_cast<char*>(ws) +
+                                                ((sizeof(uint32_t) * 4 * g->nq + 255) / 256) * 256);
+  cudaError_t e = g->metric == GRAB_METRIC_L2 ? launch_search<GRAB_METRIC_L2>(a, smem, st)
+                                              : launch_search<GRAB_METRIC_IP>(a, smem, st);
+  GRAB_CUDA_TRY(e);
+  if (own.ptr) GRAB_CUDA_TRY(cudaStreamSynchronize(st));
+  return GRAB_OK;
+}
+
+}  // namespace grab
+
+extern "C" size_t grab_graph_search_workspace_bytes(uint64_t nq, uint32_t hash_bitlen) {
+  size_t b = ((sizeof(uint32_t) * 4 * nq + 255) / 256) * 256 + 256;
+  if (hash_bitlen > 13) b += sizeof(uint32_t) * (size_t(1) << hash_bitlen) * nq;
+  return b;
+}

@@ -1,0 +1,243 @@
+/*
+ * grab_anns.h -- C ABI of the B200-native GRAB-ANNS hot path (libgrab_anns.so).
+ *
+ * Every entry point returns an int status (GRAB_OK == 0), never exits the process and
+ * never throws.  `grab_last_error()` gives the message of the calling thread's last
+ * failure.  Unless a parameter says "host", pointers named d_* are DEVICE pointers owned
+ * by the caller; `stream` is a cudaStream_t passed as void* (NULL = default stream).
+ * Entry points that take a stream only enqueue work on it; the reference-shaped ones
+ * without a stream synchronise before returning, as the functions they replace do.
+ *
+ * Each declaration cites the reference interface it replaces (paths inside
+ * hxlou/GRAB-ANNS).  Ids are uint32 inside graphs (0xFFFFFFFF = empty slot, bit 31 is
+ * used as a flag during search, so one index holds < 2^31 vectors) and int64 in results.
+ * Distances are fp32: squared L2, or the NEGATIVE inner product, so that results are
+ * always ascending.  `dim` must be a multiple of 4.
+ */
+#ifndef GRAB_ANNS_H_
+#define GRAB_ANNS_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GRAB_ABI_VERSION 1
+
+enum grab_status {
+  GRAB_OK = 0,
+  GRAB_ERR_INVALID_ARGUMENT = 1,
+  GRAB_ERR_UNSUPPORTED = 2,
+  GRAB_ERR_CUDA = 3,
+  GRAB_ERR_WORKSPACE = 4,
+  GRAB_ERR_IO = 5,
+  GRAB_ERR_TIMEOUT = 6, /* a bounded device-side wait gave up */
+  GRAB_ERR_NCCL = 7
+};
+
+enum grab_metric { GRAB_METRIC_L2 = 0, GRAB_METRIC_IP = 1 };
+
+enum grab_filter_kind {
+  GRAB_FILTER_NONE = 0,
+  GRAB_FILTER_TS_RANGE = 1, /* lo <= ts[id] < hi          (search_kernel_range)  */
+  GRAB_FILTER_LABELS = 2,   /* bit labels[id] of mask set (no reference counterpart) */
+  GRAB_FILTER_PREFIX = 3    /* walk only the first `active_degree` columns (search_kernel_bucket) */
+};
+
+/* src/index/cagra.cuh:30-42 (BuildParams, SearchParams), same fields and defaults. */
+typedef struct grab_build_params {
+  uint32_t intermediate_degree; /* 128 */
+  uint32_t graph_degree;        /* 64  */
+} grab_build_params;
+
+typedef struct grab_search_params {
+  uint32_t itopk_size;     /* 64 */
+  uint32_t search_width;   /* 5  */
+  uint32_t min_iterations; /* 0 (carried, unused, as in the reference) */
+  uint32_t max_iterations; /* 20 */
+  uint32_t hash_bitlen;    /* 12 */
+} grab_search_params;
+
+/* Filter of one search call.  One [lo,hi) / mask per call (the reference's form) when
+ * d_lo / d_masks are NULL, else one per query. */
+typedef struct grab_filter {
+  int32_t kind;            /* grab_filter_kind */
+  int32_t ts_sorted;       /* ts is non-decreasing in id: a range is a contiguous id slice */
+  const uint64_t* d_ts;    /* [n]  kind TS_RANGE */
+  const uint64_t* d_lo;    /* [nq] or NULL */
+  const uint64_t* d_hi;    /* [nq] or NULL */
+  uint64_t lo, hi;         /* used when d_lo == NULL */
+  const uint8_t* d_labels; /* [n]  kind LABELS, values < 32 */
+  const uint32_t* d_masks; /* [nq] or NULL */
+  uint32_t mask;           /* used when d_masks == NULL */
+  uint32_t active_degree;  /* kind PREFIX */
+} grab_filter;
+
+/* Per-launch counters of the graph search (all queries summed), the inputs of the
+ * algorithmic-bytes figure: bytes = 4*dim*(nq + seeds + distances) + 4*deg*parents
+ * + f*edges + 12*k*nq. */
+typedef struct grab_search_stats {
+  uint64_t iterations;
+  uint64_t parents;   /* graph rows read */
+  uint64_t edges;     /* valid neighbour ids examined (before filter / visited test) */
+  uint64_t distances; /* neighbour vectors read and distance-evaluated */
+  uint64_t seeds;     /* seed vectors evaluated */
+  uint64_t hash_resets;
+} grab_search_stats;
+
+int grab_abi_version(void);
+const char* grab_status_string(int status);
+const char* grab_last_error(void);
+
+/* ------------------------------------------------------------------------------------ */
+/* Exact filtered brute force on the GPU: tests/test_cagra_auto.cu:57-89                 */
+/* (compute_ground_truth_range) with ties broken by the lower id.  Canonical fp32 order. */
+/* Missing results: id -1, dist 3.40282e38.  d_ws may be NULL (scratch is then allocated */
+/* and freed inside the call).                                                           */
+/* ------------------------------------------------------------------------------------ */
+size_t grab_exact_search_workspace_bytes(uint64_t n, uint64_t nq, uint32_t k);
+int grab_exact_search(const float* d_dataset, uint64_t n, uint32_t dim, int metric,
+                      const grab_filter* filter, const float* d_queries, uint64_t nq, uint32_t k,
+                      int64_t* d_out_ids, float* d_out_dists, void* d_ws, size_t ws_bytes,
+                      void* stream);
+
+/* ------------------------------------------------------------------------------------ */
+/* Filtered graph search.  One entry point for the reference's three launchers           */
+/* (src/index/cagra_opt.cuh:33-80: search_opt, search_bucket_opt, search_bucket_range;   */
+/* src/index/cagra.cuh:121-134: search) and their kernels (src/index/search.cu:149,      */
+/* :375, :589).  itopk floor, seed-count and queue rules follow cagra_opt.cu:1108-1442.  */
+/* d_seeds [nq, seeds_per_query] uint32 or NULL (pseudo-random seeds inside the filter   */
+/* when the filter allows it).  id_scale/id_offset: result id = local*id_scale+id_offset */
+/* (striped shards; 1/0 for a single index).  d_stats may be NULL.                       */
+/* ------------------------------------------------------------------------------------ */
+typedef struct grab_search_args {
+  const float* d_dataset;
+  uint64_t n;
+  uint32_t dim;
+  int32_t metric;
+  const uint32_t* d_graph;
+  uint32_t graph_degree; /* row stride */
+  const float* d_queries;
+  uint64_t nq;
+  uint32_t k;
+  grab_search_params params;
+  grab_filter filter;
+  const uint32_t* d_seeds;
+  uint32_t seeds_per_query;
+  uint64_t seed; /* replaces the reference's std::random_device xor mask */
+  int64_t* d_out_ids;
+  float* d_out_dists;
+  uint64_t id_scale, id_offset;
+  grab_search_stats* d_stats;
+  void* d_ws;
+  size_t ws_bytes;
+  void* stream;
+} grab_search_args;
+
+size_t grab_graph_search_workspace_bytes(uint64_t nq, uint32_t hash_bitlen);
+int grab_graph_search(const grab_search_args* args);
+
+/* Reference-shaped wrappers (same argument order as the functions they replace, int
+ * status instead of void).  They synchronise before returning. */
+int grab_search(const float* d_dataset, uint32_t dim, uint64_t num_dataset, const uint32_t* d_graph,
+                uint32_t graph_degree, const float* d_queries, int64_t num_queries, int64_t k,
+                grab_search_params params, int64_t* d_out_indices, float* d_out_dists,
+                const uint32_t* d_seeds, uint32_t num_seeds_per_query,
+                void* stream); /* cagra_opt.cuh:33-46 search_opt */
+int grab_search_bucket(const float* d_dataset, uint32_t dim, uint64_t num_dataset,
+                       const uint32_t* d_graph, uint32_t total_degree, uint32_t local_degree,
+                       const float* d_queries, int64_t num_queries, int64_t k,
+                       grab_search_params params, int64_t* d_out_indices, float* d_out_dists,
+                       const uint32_t* d_seeds, uint32_t num_seeds_per_query,
+                       void* stream); /* cagra_opt.cuh:48-62 search_bucket_opt */
+int grab_search_range(const float* d_dataset, uint32_t dim, uint64_t num_dataset,
+                      const uint32_t* d_graph, const uint64_t* d_ts, uint32_t total_degree,
+                      uint32_t local_degree, const float* d_queries, int64_t num_queries, int64_t k,
+                      uint64_t start_bucket, uint64_t end_bucket, grab_search_params params,
+                      int64_t* d_out_indices, float* d_out_dists, const uint32_t* d_seeds,
+                      uint32_t num_seeds_per_query); /* cagra_opt.cuh:64-80 search_bucket_range */
+
+/* ------------------------------------------------------------------------------------ */
+/* kNN graph.                                                                            */
+/* grab_knn_graph_blocks: exact kNN inside each contiguous id block (self dropped, short */
+/* rows padded with 0xFFFFFFFF, GLOBAL ids) -- src/index/raft_help.cuh:74-172            */
+/* build_batch_knn_graphs plus the offsetting of cagra_opt.cu:1038-1044.                 */
+/* h_block_offsets: host array [num_blocks+1].  mode 0: own block; mode 1: every vector  */
+/* EXCEPT those of the own block (candidates for cross-bucket edges, the role of the     */
+/* IVF-PQ self-search of cagra_opt.cu:813-856).  Output ascending exact distance.        */
+/* grab_generate_knn_graph: src/index/cagra.cuh:59-63 (device dataset, HOST output).     */
+/* ------------------------------------------------------------------------------------ */
+int grab_knn_graph_blocks(const float* d_dataset, uint64_t n, uint32_t dim, int metric,
+                          const uint64_t* h_block_offsets, uint32_t num_blocks, uint32_t k,
+                          int mode, uint32_t* d_out_knn, float* d_out_dists, void* stream);
+int grab_generate_knn_graph(const float* d_dataset, uint64_t num_dataset, uint32_t dim, uint32_t k,
+                            uint32_t* h_knn_graph);
+
+/* ------------------------------------------------------------------------------------ */
+/* Graph optimisation.  *_device variants take device graphs and a stream; the           */
+/* reference-shaped ones take HOST graphs as src/index/cagra.cuh:72-107 do.              */
+/* prune: cagra.cu:219-276 + 367-392.  reverse: cagra.cu:418-444, 455-548 (slot order =  */
+/* column, then ascending source id).  merge: cagra.cu:574-650.                          */
+/* ------------------------------------------------------------------------------------ */
+int grab_optimize_prune_device(const uint32_t* d_knn, uint32_t* d_out, uint64_t n,
+                               uint32_t input_degree, uint32_t output_degree,
+                               uint8_t* d_detour_or_null, void* stream);
+int grab_optimize_reverse_graph_device(const uint32_t* d_graph, uint32_t* d_rev,
+                                       uint32_t* d_rev_counts, uint64_t n, uint32_t degree,
+                                       void* stream);
+int grab_optimize_merge_graphs_device(uint32_t* d_graph, const uint32_t* d_rev,
+                                      const uint32_t* d_rev_counts, uint64_t n, uint32_t degree,
+                                      void* stream);
+int grab_optimize_prune(const uint32_t* h_knn_graph, uint32_t* h_new_graph, uint64_t num_dataset,
+                        uint32_t input_degree, uint32_t output_degree);
+int grab_optimize_create_reverse_graph(const uint32_t* h_input_graph, uint32_t* h_rev_graph,
+                                       uint32_t* h_rev_counts, uint64_t num_dataset,
+                                       uint32_t degree);
+int grab_optimize_merge_graphs(uint32_t* h_graph, const uint32_t* h_rev_graph,
+                               const uint32_t* h_rev_counts, uint64_t num_dataset, uint32_t degree);
+/* cagra.cuh:109-119 build: raw kNN graph (device) -> prune/reverse/merge -> a cudaMalloc'd
+ * graph the caller frees with cudaFree. */
+int grab_build(const float* d_dataset, uint64_t num_dataset, const uint32_t* d_raw_knn_graph,
+               grab_build_params params, uint32_t** d_constructed_graph);
+
+/* Cross-bucket edges: cagra_opt.cu:209-303 (selection) and :457-600, :739-790 (reverse
+ * injection).  d_cand [n, gk] is consumed.  d_bucket [n]: bucket id per vector. */
+int grab_remote_edges_device(uint32_t* d_graph, const uint64_t* d_bucket, uint32_t* d_cand,
+                             uint64_t n, uint32_t total_degree, uint32_t local_degree, uint32_t gk,
+                             void* stream);
+int grab_inject_reverse_remote_device(uint32_t* d_graph, uint64_t n, uint32_t total_degree,
+                                      uint32_t local_degree, uint32_t max_rev, void* stream);
+/* cagra_opt.cuh:21-31 build_time_partitioned_graph: per-bucket local graphs of width
+ * total_degree, then cross-bucket edges over columns >= local_degree.  h_bucket_sizes: host. */
+int grab_build_time_partitioned_graph(const float* d_dataset, uint64_t total_num, uint32_t dim,
+                                      int metric, uint32_t* d_graph, const uint64_t* d_bucket,
+                                      const uint64_t* h_bucket_sizes, uint32_t num_buckets,
+                                      uint32_t total_degree, uint32_t local_degree);
+
+/* ------------------------------------------------------------------------------------ */
+/* Insert: topology updates.  v1: src/index/insert.cuh:62-72 (insert.cu:225-440).        */
+/* opt: src/index/insert.cuh:96-116 (insert.cu:448-765, 1398-1573); mailbox order is     */
+/* ascending new id, then column.                                                        */
+/* ------------------------------------------------------------------------------------ */
+int grab_update_topology_v1(uint32_t* d_graph, const int64_t* d_search_indices,
+                            uint64_t num_existing, uint64_t num_new, uint32_t graph_degree,
+                            uint32_t search_k, void* stream);
+int grab_update_topology_opt(uint32_t* d_graph, const uint64_t* d_bucket, int64_t* d_local_knn,
+                             int64_t* d_global_knn, uint64_t num_existing, uint64_t num_new,
+                             uint64_t target_bucket, uint32_t total_degree, uint32_t local_degree,
+                             uint32_t k_local, uint32_t k_global, void* stream);
+
+/* ------------------------------------------------------------------------------------ */
+/* Merge of `parts` ascending top-k lists per query into one (the exchange step of the   */
+/* id-sharded multi-GPU search; also merges the splits of the exact scan).  No reference */
+/* counterpart (the reference is single-GPU).  Lists [nq, parts, k]; ids < 0 are empty.  */
+/* ------------------------------------------------------------------------------------ */
+int grab_merge_topk(const float* d_dists, const int64_t* d_ids, uint64_t nq, uint32_t parts,
+                    uint32_t k, int64_t* d_out_ids, float* d_out_dists, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GRAB_ANNS_H_ */
