@@ -42,6 +42,8 @@ def parse():
     ap.add_argument("--width", type=int, default=4)
     ap.add_argument("--max-iter", type=int, default=32)
     ap.add_argument("--hash-bitlen", type=int, default=12)
+    ap.add_argument("--knn-precision", type=int, default=1,
+                    help="0 exact scan, 1 bf16 tensor cores (exact for integer-valued data), 2 split bf16")
     ap.add_argument("--cpu-sample", type=int, default=0, help="queries in the CPU sample (0 = auto)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
@@ -208,7 +210,8 @@ def main():
     d_bucket = torch.from_numpy((w["ts"] // np.uint64(bsize)).view(np.int64)).cuda()
     torch.cuda.synchronize()
     t0 = time.perf_counter()
-    graph = grab.build_time_partitioned_graph(d_base, d_bucket, sizes, deg, args.local_degree, metric=w["metric"])
+    graph = grab.build_time_partitioned_graph(d_base, d_bucket, sizes, deg, args.local_degree, metric=w["metric"],
+                                              knn_precision=args.knn_precision)
     torch.cuda.synchronize()
     build_s = time.perf_counter() - t0
 
@@ -303,7 +306,7 @@ def main():
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic", "config": workload_config(args, w),
             "recall_at_10": recall, "results_in_range": in_range,
-            "build": {"seconds": build_s, "mvec_per_s": n / build_s / 1e6},
+            "build": {"seconds": build_s, "mvec_per_s": n / build_s / 1e6, "knn_precision": args.knn_precision},
             "e2e": {"value": world * nq / (ms_e2e / 1e3), "unit": "queries/s",
                     "h2d_bytes_per_step": int(h_q.numel() * 4 + 16 * nq), "d2h_bytes_per_step": int(12 * nq * k)},
             "gpu_launches": 2 * args.steps,

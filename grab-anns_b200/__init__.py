@@ -17,6 +17,7 @@ LIB_PATH = os.path.join(HERE, "libgrab_anns.so")
 
 METRIC_L2, METRIC_IP = 0, 1
 FILTER_NONE, FILTER_TS_RANGE, FILTER_LABELS, FILTER_PREFIX = 0, 1, 2, 3
+KNN_EXACT_SCAN, KNN_TC_BF16, KNN_TC_SPLIT = 0, 1, 2
 
 
 class GrabError(RuntimeError):
@@ -128,6 +129,8 @@ def make_filter(kind=FILTER_NONE, ts=None, lo=None, hi=None, ts_sorted=False, la
     elif masks is not None:
         f.mask = int(masks)
     f.active_degree = active_degree
+    # the struct only holds raw pointers: keep the tensors alive as long as the filter is
+    f._keepalive = (ts, lo, hi, labels, masks)
     return f
 
 
@@ -187,7 +190,8 @@ def graph_search(dataset, graph, queries, k, params: SearchParams, metric=METRIC
     return ids, dists
 
 
-def knn_graph_blocks(dataset, block_offsets, k, mode=0, metric=METRIC_L2, want_dists=False):
+def knn_graph_blocks(dataset, block_offsets, k, mode=0, metric=METRIC_L2, want_dists=False,
+                     precision=KNN_EXACT_SCAN):
     import numpy as np
     import torch
     n, dim = dataset.shape
@@ -196,12 +200,12 @@ def knn_graph_blocks(dataset, block_offsets, k, mode=0, metric=METRIC_L2, want_d
     dists = torch.empty((n, k), dtype=torch.float32, device=dataset.device) if want_dists else None
     check(lib().grab_knn_graph_blocks(_p(dataset), C.c_uint64(n), C.c_uint32(dim), C.c_int(metric),
                                       _p(offs), C.c_uint32(len(offs) - 1), C.c_uint32(k),
-                                      C.c_int(mode), _p(out), _p(dists), _stream()))
+                                      C.c_int(mode), C.c_int(precision), _p(out), _p(dists), _stream()))
     return (out, dists) if want_dists else out
 
 
 def build_time_partitioned_graph(dataset, bucket, bucket_sizes, total_degree, local_degree,
-                                 metric=METRIC_L2):
+                                 metric=METRIC_L2, knn_precision=KNN_TC_SPLIT):
     import numpy as np
     import torch
     n, dim = dataset.shape
@@ -211,7 +215,7 @@ def build_time_partitioned_graph(dataset, bucket, bucket_sizes, total_degree, lo
     check(lib().grab_build_time_partitioned_graph(_p(dataset), C.c_uint64(n), C.c_uint32(dim),
                                                   C.c_int(metric), _p(graph), _p(bucket), _p(sizes),
                                                   C.c_uint32(len(sizes)), C.c_uint32(total_degree),
-                                                  C.c_uint32(local_degree)))
+                                                  C.c_uint32(local_degree), C.c_int(knn_precision)))
     return graph
 
 

@@ -21,6 +21,8 @@ int exact_search_impl(const float*, uint64_t, uint32_t, int, const grab_filter*,
                       uint32_t, int64_t*, float*, void*, size_t, cudaStream_t);
 int knn_blocks_impl(const float*, uint64_t, uint32_t, int, const uint64_t*, uint32_t, uint32_t, int,
                     uint32_t*, float*, cudaStream_t);
+int knn_tc_impl(const float*, uint64_t, uint32_t, int, const uint64_t*, uint32_t, uint32_t, int, int, uint32_t*,
+                float*, cudaStream_t);
 int merge_topk_impl(const float*, const int64_t*, uint64_t, uint32_t, uint32_t, int64_t*, float*,
                     cudaStream_t);
 int graph_search_impl(const grab_search_args*);
@@ -39,6 +41,18 @@ int update_topology_opt_impl(uint32_t*, const uint64_t*, int64_t*, int64_t*, uin
     int _rc = (expr);             \
     if (_rc != GRAB_OK) return _rc; \
   } while (0)
+
+// kNN stage: exact SIMT scan, or tensor-core candidates + exact re-rank
+static int knn_dispatch(const float* d_dataset, uint64_t n, uint32_t dim, int metric, const uint64_t* offs,
+                        uint32_t nb, uint32_t k, int mode, int precision, uint32_t* out, float* out_d,
+                        cudaStream_t st) {
+  if (precision == GRAB_KNN_EXACT_SCAN)
+    return knn_blocks_impl(d_dataset, n, dim, metric, offs, nb, k, mode, out, out_d, st);
+  if (precision == GRAB_KNN_TC_BF16 || precision == GRAB_KNN_TC_SPLIT)
+    return knn_tc_impl(d_dataset, n, dim, metric, offs, nb, k, mode, precision, out, out_d, st);
+  set_last_error("knn: unknown precision %d", precision);
+  return GRAB_ERR_INVALID_ARGUMENT;
+}
 
 // prune -> reverse -> merge over a device kNN graph (cagra.cu:665-711 without the host hops)
 static int optimize_pipeline(const uint32_t* d_knn, uint32_t* d_graph, uint64_t n, uint32_t in_deg,
@@ -146,9 +160,9 @@ int grab_search_range(const float* d_dataset, uint32_t dim, uint64_t num_dataset
 
 int grab_knn_graph_blocks(const float* d_dataset, uint64_t n, uint32_t dim, int metric,
                           const uint64_t* h_block_offsets, uint32_t num_blocks, uint32_t k, int mode,
-                          uint32_t* d_out_knn, float* d_out_dists, void* stream) {
-  return knn_blocks_impl(d_dataset, n, dim, metric, h_block_offsets, num_blocks, k, mode, d_out_knn,
-                         d_out_dists, static_cast<cudaStream_t>(stream));
+                          int precision, uint32_t* d_out_knn, float* d_out_dists, void* stream) {
+  return knn_dispatch(d_dataset, n, dim, metric, h_block_offsets, num_blocks, k, mode, precision, d_out_knn,
+                      d_out_dists, static_cast<cudaStream_t>(stream));
 }
 
 int grab_generate_knn_graph(const float* d_dataset, uint64_t num_dataset, uint32_t dim, uint32_t k,
@@ -157,8 +171,9 @@ int grab_generate_knn_graph(const float* d_dataset, uint64_t num_dataset, uint32
   ScopedDeviceBuffer out;
   GRAB_CUDA_TRY(out.alloc(sizeof(uint32_t) * num_dataset * k));
   const uint64_t offs[2] = {0, num_dataset};
-  GRAB_TRY(knn_blocks_impl(d_dataset, num_dataset, dim, GRAB_METRIC_L2, offs, 1, k, 0, out.as<uint32_t>(),
-                           nullptr, nullptr));
+  // tensor-core candidates (split precision) + exact re-rank; wide rows fall back to the scan
+  GRAB_TRY(knn_dispatch(d_dataset, num_dataset, dim, GRAB_METRIC_L2, offs, 1, k, 0,
+                        k <= 204 ? GRAB_KNN_TC_SPLIT : GRAB_KNN_EXACT_SCAN, out.as<uint32_t>(), nullptr, nullptr));
   GRAB_CUDA_TRY(cudaMemcpy(h_knn_graph, out.ptr, sizeof(uint32_t) * num_dataset * k, cudaMemcpyDeviceToHost));
   return GRAB_OK;
 }
@@ -247,7 +262,7 @@ int grab_inject_reverse_remote_device(uint32_t* d_graph, uint64_t n, uint32_t to
 int grab_build_time_partitioned_graph(const float* d_dataset, uint64_t total_num, uint32_t dim, int metric,
                                       uint32_t* d_graph, const uint64_t* d_bucket,
                                       const uint64_t* h_bucket_sizes, uint32_t num_buckets,
-                                      uint32_t total_degree, uint32_t local_degree) {
+                                      uint32_t total_degree, uint32_t local_degree, int knn_precision) {
   GRAB_REQUIRE(d_dataset && d_graph && d_bucket && h_bucket_sizes, "build_time_partitioned_graph: null pointer");
   GRAB_REQUIRE(num_buckets >= 1, "build_time_partitioned_graph: no buckets");
   GRAB_REQUIRE(total_degree >= 4 && total_degree <= 256 && local_degree >= 1 && local_degree <= total_degree,
@@ -263,8 +278,8 @@ int grab_build_time_partitioned_graph(const float* d_dataset, uint64_t total_num
   {
     ScopedDeviceBuffer knn;
     GRAB_CUDA_TRY(knn.alloc(sizeof(uint32_t) * total_num * inter));
-    GRAB_TRY(knn_blocks_impl(d_dataset, total_num, dim, metric, offs.data(), num_buckets, inter, 0,
-                             knn.as<uint32_t>(), nullptr, nullptr));
+    GRAB_TRY(knn_dispatch(d_dataset, total_num, dim, metric, offs.data(), num_buckets, inter, 0,
+                          inter <= 204 ? knn_precision : GRAB_KNN_EXACT_SCAN, knn.as<uint32_t>(), nullptr, nullptr));
     GRAB_TRY(optimize_pipeline(knn.as<uint32_t>(), d_graph, total_num, inter, total_degree, nullptr));
   }
   if (local_degree == total_degree || num_buckets == 1) return GRAB_OK;
@@ -278,8 +293,8 @@ int grab_build_time_partitioned_graph(const float* d_dataset, uint64_t total_num
   {
     ScopedDeviceBuffer cand;
     GRAB_CUDA_TRY(cand.alloc(sizeof(uint32_t) * total_num * gk));
-    GRAB_TRY(knn_blocks_impl(d_dataset, total_num, dim, metric, offs.data(), num_buckets, gk, 1,
-                             cand.as<uint32_t>(), nullptr, nullptr));
+    GRAB_TRY(knn_dispatch(d_dataset, total_num, dim, metric, offs.data(), num_buckets, gk, 1,
+                          gk <= 204 ? knn_precision : GRAB_KNN_EXACT_SCAN, cand.as<uint32_t>(), nullptr, nullptr));
     GRAB_TRY(remote_edges_impl(d_graph, d_bucket, cand.as<uint32_t>(), total_num, total_degree, local_degree,
                                gk, nullptr));
     GRAB_TRY(inject_reverse_impl(d_graph, total_num, total_degree, local_degree, 32, nullptr));

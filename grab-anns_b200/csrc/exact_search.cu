@@ -7,6 +7,7 @@
 // Top-k: keys (dist,id) below the running k-th key are appended to a shared-memory buffer
 // that is bitonic-sorted into the top-k when it fills.
 #include "common.cuh"
+#include "windows.cuh"
 
 namespace grab {
 
@@ -21,10 +22,6 @@ struct ScanFilter {
   uint32_t mask1;
 };
 
-// Per-query scan window [begin,end) and excluded id interval [xbegin,xend).
-struct ScanWindow {
-  uint32_t begin, end, xbegin, xend;
-};
 
 constexpr int kScanThreads = 256;
 constexpr int kScanTeams = kScanThreads / kTeam;  // 32
@@ -236,32 +233,6 @@ __global__ void ts_window_kernel(const uint64_t* __restrict__ ts, uint64_t n,
   w.xbegin = 0;
   w.xend = 0;
   windows[qi] = w;
-}
-
-// kNN windows: query row r (global id) scans its own block minus itself (mode 0) or
-// everything except its own block (mode 1).
-__global__ void knn_window_kernel(const uint64_t* __restrict__ block_offsets, uint32_t num_blocks,
-                                  uint64_t n, int mode, ScanWindow* __restrict__ windows) {
-  const uint64_t r = blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x;
-  if (r >= n) return;
-  uint32_t l = 0, h = num_blocks;  // find block b with offsets[b] <= r < offsets[b+1]
-  while (h - l > 1) {
-    const uint32_t m = (l + h) >> 1;
-    if (block_offsets[m] <= r) l = m; else h = m;
-  }
-  ScanWindow w;
-  if (mode == 0) {
-    w.begin = static_cast<uint32_t>(block_offsets[l]);
-    w.end = static_cast<uint32_t>(block_offsets[l + 1]);
-    w.xbegin = static_cast<uint32_t>(r);
-    w.xend = static_cast<uint32_t>(r + 1);
-  } else {
-    w.begin = 0;
-    w.end = static_cast<uint32_t>(n);
-    w.xbegin = static_cast<uint32_t>(block_offsets[l]);
-    w.xend = static_cast<uint32_t>(block_offsets[l + 1]);
-  }
-  windows[r] = w;
 }
 
 template <int METRIC>

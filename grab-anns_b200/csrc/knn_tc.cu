@@ -1,0 +1,622 @@
+// All-pairs kNN candidates on the 5th-generation tensor cores (tcgen05 + TMEM + TMA),
+// with a fused per-row running top-KC in the epilogue and an exact fp32 re-rank.
+//
+// This is the dense contraction of the build: it replaces the reference's per-bucket RAFT
+// brute force (src/index/raft_help.cuh:74-172) and its FAISS IVF-PQ candidate searches
+// (src/index/cagra.cu:76-131, cagra_opt.cu:813-847), followed -- as there
+// (cagra.cu:138, cagra_opt.cu:48-148) -- by exact distances over the candidates.
+//
+//   d(x,y) = |y|^2 - 2 x.y  (+|x|^2, constant per row, dropped for ranking)
+//
+// x.y runs as bf16 x bf16 -> fp32 MMAs, M=128 rows x N=128 columns per tile, K = 64 per
+// pipeline stage.  "Split" precision stores every value as hi+lo bf16 and concatenates
+// [hi,lo,hi].[hi,hi,lo] along K, which recovers ~fp32 products at 3x the MMA work.
+//
+// One persistent CTA per SM, 6 warps:
+//   warp 0   TMA producer   (cp.async.bulk.tensor 2D, 128B swizzle, 4-stage ring, mbarriers)
+//   warp 1   MMA issuer     (one lane issues tcgen05.mma; tcgen05.commit frees ring stages and
+//                            publishes the accumulator; owns the TMEM allocation)
+//   warps 2-5 epilogue      (tcgen05.ld of a double-buffered 128x128 fp32 accumulator; thread r
+//                            owns row r: threshold test, append to the row's candidate buffer;
+//                            a full buffer is bitonic-sorted by the warp and cut back to KC)
+// Every mbarrier wait is bounded; on expiry the kernel raises a flag, all roles leave their
+// loops, TMEM is released and the host sees GRAB_ERR_TIMEOUT.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+#include "windows.cuh"
+
+namespace grab {
+
+namespace tc {
+
+constexpr int BM = 128, BN = 128, BK = 64;  // BK bf16 = one 128-byte swizzle row
+constexpr int STAGES = 4;
+constexpr int STAGE_BYTES = (BM + BN) * BK * 2;  // 32 KB
+constexpr int THREADS = 192;
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false when the limit expired or another role raised the abort flag.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 255u) == 255u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int32_t x,
+                                            int32_t y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols));
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols));
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128
+// bytes, 8-row groups 1024 bytes apart (stride byte offset), descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((addr & 0x3FFFFu) >> 4);  // start address   [0,14)
+  d |= static_cast<uint64_t>(1) << 16;                 // leading offset  [16,30) (unused with swizzle)
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;         // stride offset   [32,46)
+  d |= static_cast<uint64_t>(1) << 46;                 // version         [46,48)
+  d |= static_cast<uint64_t>(2) << 61;                 // SWIZZLE_128B    [61,64)
+  return d;
+}
+// Instruction descriptor: D fp32, A/B bf16, both K-major, N=128, M=128.
+constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((BN >> 3) << 17) | ((BM >> 4) << 24);
+
+// ------------------------------------------------------------------ epilogue helpers
+template <int NREG>
+__device__ __forceinline__ void warp_bitonic_sort_u64(uint64_t (&k)[NREG], uint32_t lane) {
+  // element g = j*32 + lane; ascending over all 32*NREG elements
+  constexpr uint32_t total = 32 * NREG;
+#pragma unroll
+  for (uint32_t size = 2; size <= total; size <<= 1) {
+#pragma unroll
+    for (uint32_t stride = size >> 1; stride > 0; stride >>= 1) {
+      if (stride >= 32) {
+        const uint32_t js = stride >> 5;
+#pragma unroll
+        for (uint32_t j = 0; j < NREG; ++j) {
+          if ((j & js) == 0) {
+            const uint32_t g = j * 32 + lane;
+            const bool up = (g & size) == 0;
+            const uint64_t a = k[j], b = k[j | js];
+            if ((a > b) == up) { k[j] = b; k[j | js] = a; }
+          }
+        }
+      } else {
+#pragma unroll
+        for (uint32_t j = 0; j < NREG; ++j) {
+          const uint64_t other = __shfl_xor_sync(0xFFFFFFFFu, k[j], stride);
+          const uint32_t g = j * 32 + lane;
+          const bool up = (g & size) == 0;
+          const bool lower = (lane & stride) == 0;
+          const bool keep_min = (lower == up);
+          const uint64_t mn = k[j] < other ? k[j] : other;
+          const uint64_t mx = k[j] < other ? other : k[j];
+          k[j] = keep_min ? mn : mx;
+        }
+      }
+    }
+  }
+}
+
+struct TileRange {
+  uint32_t row0, rows;       // rows of this tile that exist
+  uint32_t jb, je;           // column tiles [jb, je)
+  uint32_t skip_lo, skip_hi; // column tiles fully inside every row's exclusion are skipped
+  uint32_t safe_lo, safe_hi; // columns inside every row's window ...
+  uint32_t ex_lo, ex_hi;     // ... and outside [ex_lo, ex_hi) need no per-element mask
+};
+
+__device__ __forceinline__ TileRange tile_range(const ScanWindow* windows, uint64_t n, uint32_t rt) {
+  TileRange t;
+  t.row0 = rt * BM;
+  const uint64_t last = (t.row0 + BM <= n ? t.row0 + BM : n) - 1;
+  t.rows = static_cast<uint32_t>(last - t.row0 + 1);
+  const ScanWindow a = windows[t.row0], b = windows[last];
+  // windows are monotone in the row id (blocks are contiguous id ranges)
+  t.jb = a.begin / BN;
+  t.je = (b.end + BN - 1) / BN;
+  t.skip_lo = a.xbegin > b.xbegin ? a.xbegin : b.xbegin;
+  t.skip_hi = a.xend < b.xend ? a.xend : b.xend;
+  t.safe_lo = b.begin;
+  t.safe_hi = a.end;
+  t.ex_lo = a.xbegin;
+  t.ex_hi = b.xend;
+  return t;
+}
+__device__ __forceinline__ bool tile_skipped(const TileRange& t, uint32_t j) {
+  const uint32_t c0 = j * BN;
+  return c0 >= t.skip_lo && c0 + BN <= t.skip_hi;
+}
+
+struct SharedCtl {
+  uint64_t full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  float ynorm[4][BN];  // one staging row per epilogue warp
+};
+
+template <int KC>
+__global__ void __launch_bounds__(THREADS, 1)
+knn_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+              const float* __restrict__ ynorm, const ScanWindow* __restrict__ windows, uint64_t n,
+              uint32_t kblocks, uint32_t num_row_tiles, uint64_t* __restrict__ scratch,
+              uint64_t* __restrict__ out_keys, int* __restrict__ status) {
+  constexpr uint32_t CAP = 2 * KC;
+  constexpr int NREG = CAP / 32;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  // stage s: A tile at s*STAGE_BYTES, B tile 16 KB after it; control block after the ring
+  unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  SharedCtl* ctl = reinterpret_cast<SharedCtl*>(ring + STAGES * STAGE_BYTES);
+  volatile int* abort_flag = &ctl->abort_flag;
+
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&ctl->full[s]), 1);
+      mbar_init(smem_u32(&ctl->empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&ctl->tmem_full[a]), 1);
+      mbar_init(smem_u32(&ctl->tmem_empty[a]), 4);
+    }
+    ctl->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&ctl->tmem_base), 2 * BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+
+  if (warp == 0) {
+    // ============================ TMA producer ============================
+    if (lane == 0) {
+      uint32_t it = 0;
+      uint32_t issued_phase[STAGES];
+      bool issued[STAGES];
+      for (int s = 0; s < STAGES; ++s) { issued[s] = false; issued_phase[s] = 0; }
+      bool ok = true;
+      for (uint32_t rt = blockIdx.x; rt < num_row_tiles && ok; rt += gridDim.x) {
+        const TileRange t = tile_range(windows, n, rt);
+        for (uint32_t j = t.jb; j < t.je && ok; ++j) {
+          if (tile_skipped(t, j)) continue;
+          for (uint32_t kb = 0; kb < kblocks; ++kb, ++it) {
+            const uint32_t s = it % STAGES, phase = (it / STAGES) & 1;
+            if (!mbar_wait(smem_u32(&ctl->empty[s]), phase ^ 1, abort_flag)) { ok = false; break; }
+            const uint32_t bar = smem_u32(&ctl->full[s]);
+            mbar_expect_tx(bar, STAGE_BYTES);
+            const uint32_t dst = smem_u32(ring + s * STAGE_BYTES);
+            tma_load_2d(dst, &map_a, bar, static_cast<int32_t>(kb * BK), static_cast<int32_t>(t.row0));
+            tma_load_2d(dst + BM * BK * 2, &map_b, bar, static_cast<int32_t>(kb * BK), static_cast<int32_t>(j * BN));
+            issued[s] = true;
+            issued_phase[s] = phase;
+          }
+        }
+      }
+      if (!ok) {
+        // leaving early: give copies already in flight a bounded time to land
+        for (int s = 0; s < STAGES; ++s)
+          if (issued[s])
+            for (uint32_t i = 0; i < (1u << 16); ++i)
+              if (mbar_try_wait(smem_u32(&ctl->full[s]), issued_phase[s])) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ============================ MMA issuer ============================
+    if (lane == 0) {
+      uint32_t it = 0, tile = 0;
+      bool ok = true;
+      for (uint32_t rt = blockIdx.x; rt < num_row_tiles && ok; rt += gridDim.x) {
+        const TileRange t = tile_range(windows, n, rt);
+        for (uint32_t j = t.jb; j < t.je && ok; ++j) {
+          if (tile_skipped(t, j)) continue;
+          const uint32_t acc = tile & 1, acc_phase = (tile >> 1) & 1;
+          if (!mbar_wait(smem_u32(&ctl->tmem_empty[acc]), acc_phase ^ 1, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + acc * BN;
+          for (uint32_t kb = 0; kb < kblocks; ++kb, ++it) {
+            const uint32_t s = it % STAGES, phase = (it / STAGES) & 1;
+            if (!mbar_wait(smem_u32(&ctl->full[s]), phase, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t a_addr = smem_u32(ring + s * STAGE_BYTES);
+            const uint64_t da = smem_desc_sw128(a_addr);
+            const uint64_t db = smem_desc_sw128(a_addr + BM * BK * 2);
+#pragma unroll
+            for (uint32_t kk = 0; kk < BK / 16; ++kk) {
+              // 16 bf16 = 32 bytes further along K inside the swizzled row: +2 in 16-byte units
+              tc_mma_bf16(d_tmem, da + 2 * kk, db + 2 * kk, kIdesc, (kb | kk) != 0 ? 1u : 0u);
+            }
+            tc_commit(smem_u32(&ctl->empty[s]));  // stage reusable once these MMAs have read it
+          }
+          if (!ok) break;
+          tc_commit(smem_u32(&ctl->tmem_full[acc]));  // accumulator complete
+          ++tile;
+        }
+      }
+    }
+  } else {
+    // ============================ epilogue (warps 2..5) ============================
+    const uint32_t quarter = warp & 3;          // TMEM lane quarter this warp may read
+    const uint32_t r_local = quarter * 32 + lane;
+    uint64_t* warp_buf = scratch + (static_cast<uint64_t>(blockIdx.x) * BM + quarter * 32) * CAP;
+    uint64_t* my_buf = warp_buf + static_cast<uint64_t>(lane) * CAP;
+    uint32_t tile = 0;
+    bool ok = true;
+
+    auto compress = [&](uint32_t& cnt, float& thr, bool force) {
+      __syncwarp();
+      uint32_t need = __ballot_sync(0xFFFFFFFFu, force || cnt > CAP - 32);
+      while (need) {
+        const int src = __ffs(need) - 1;
+        need &= need - 1;
+        const uint32_t c_src = __shfl_sync(0xFFFFFFFFu, cnt, src);
+        uint64_t* rb = warp_buf + static_cast<uint64_t>(src) * CAP;
+        uint64_t k[NREG];
+#pragma unroll
+        for (int j = 0; j < NREG; ++j) {
+          const uint32_t g = j * 32 + lane;
+          k[j] = g < c_src ? rb[g] : kMaxKey;
+        }
+        warp_bitonic_sort_u64<NREG>(k, lane);
+#pragma unroll
+        for (int j = 0; j < KC / 32; ++j) rb[j * 32 + lane] = k[j];
+        const uint64_t kth = __shfl_sync(0xFFFFFFFFu, k[KC / 32 - 1], 31);
+        if (static_cast<int>(lane) == src) {
+          cnt = c_src < KC ? c_src : KC;
+          thr = c_src >= KC ? key_dist(kth) : __int_as_float(0x7f800000);
+        }
+      }
+      __syncwarp();
+    };
+
+    for (uint32_t rt = blockIdx.x; rt < num_row_tiles && ok; rt += gridDim.x) {
+      const TileRange t = tile_range(windows, n, rt);
+      const bool row_valid = r_local < t.rows;
+      ScanWindow w{0, 0, 0, 0};
+      if (row_valid) w = windows[t.row0 + r_local];
+      uint32_t cnt = 0;
+      float thr = __int_as_float(0x7f800000);  // +inf
+      for (uint32_t j = t.jb; j < t.je && ok; ++j) {
+        if (tile_skipped(t, j)) continue;
+        const uint32_t acc = tile & 1, acc_phase = (tile >> 1) & 1;
+        const uint32_t c0 = j * BN;
+        // column norms of this tile, staged per warp (no cross-warp barrier in the epilogue)
+        float* yn = ctl->ynorm[warp - 2];
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < BN / 32; ++i) {
+          const uint64_t c = static_cast<uint64_t>(c0) + i * 32 + lane;
+          yn[i * 32 + lane] = c < n ? __ldg(ynorm + c) : 0.0f;
+        }
+        __syncwarp();
+        if (!mbar_wait(smem_u32(&ctl->tmem_full[acc]), acc_phase, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const bool need_mask = !(c0 >= t.safe_lo && c0 + BN <= t.safe_hi && (c0 + BN <= t.ex_lo || c0 >= t.ex_hi));
+#pragma unroll 1
+        for (uint32_t chunk = 0; chunk < BN / 32; ++chunk) {
+          uint32_t v[32];
+          tmem_ld32(tmem_base + ((quarter * 32) << 16) + acc * BN + chunk * 32, v);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const uint32_t c = c0 + chunk * 32 + i;
+            const float d = __fmaf_rn(-2.0f, __uint_as_float(v[i]), yn[chunk * 32 + i]);
+            bool take = row_valid && d < thr;
+            if (need_mask) take = take && c >= w.begin && c < w.end && !(c >= w.xbegin && c < w.xend);
+            if (take) my_buf[cnt++] = make_key(d, c);
+          }
+          compress(cnt, thr, false);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&ctl->tmem_empty[acc]));
+        ++tile;
+      }
+      if (!ok) break;
+      // final cut of this row tile: sorted candidates out, padded with empty keys
+      compress(cnt, thr, true);
+      for (uint32_t r = 0; r < 32; ++r) {
+        const uint32_t c_r = __shfl_sync(0xFFFFFFFFu, cnt, r);
+        const uint32_t row = t.row0 + quarter * 32 + r;
+        if (row >= n) continue;  // uniform across the warp
+        const uint64_t* rb = warp_buf + static_cast<uint64_t>(r) * CAP;
+        for (uint32_t i = lane; i < KC; i += 32) out_keys[static_cast<uint64_t>(row) * KC + i] = i < c_r ? rb[i] : kMaxKey;
+      }
+      __syncwarp();
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, 2 * BN);
+  if (threadIdx.x == 0 && ctl->abort_flag) *status = GRAB_ERR_TIMEOUT;
+}
+
+// ------------------------------------------------------------------ operand preparation
+// Deterministic column means: fixed row chunks, fixed summation order.
+constexpr int kMeanChunk = 4096;
+__global__ void mean_partial_kernel(const float* __restrict__ x, uint64_t n, uint32_t dim, float* __restrict__ partial) {
+  const uint64_t r0 = static_cast<uint64_t>(blockIdx.x) * kMeanChunk;
+  const uint64_t r1 = r0 + kMeanChunk < n ? r0 + kMeanChunk : n;
+  for (uint32_t d = threadIdx.x; d < dim; d += blockDim.x) {
+    float s = 0.0f;
+    for (uint64_t r = r0; r < r1; ++r) s += x[r * dim + d];
+    partial[static_cast<uint64_t>(blockIdx.x) * dim + d] = s;
+  }
+}
+__global__ void mean_final_kernel(const float* __restrict__ partial, uint32_t nchunks, uint32_t dim, uint64_t n,
+                                  float* __restrict__ mean) {
+  const uint32_t d = blockIdx.x * blockDim.x + threadIdx.x;
+  if (d >= dim) return;
+  float s = 0.0f;
+  for (uint32_t c = 0; c < nchunks; ++c) s += partial[static_cast<uint64_t>(c) * dim + d];
+  mean[d] = s / static_cast<float>(n);
+}
+
+// fp32 rows -> bf16 operands.  split == 0: A = B = bf16(x - mean), K = dim.
+// split == 1: hi = bf16(v), lo = bf16(v - hi); A = [hi, lo, hi], B = [hi, hi, lo], K = 3*dim.
+// norm[r] = sum (x - mean)^2 (L2) or 0 (inner product).  One warp per row.
+__global__ void prep_operands_kernel(const float* __restrict__ x, uint64_t n, uint32_t dim, const float* __restrict__ mean,
+                                     int split, int metric, uint32_t kp, __nv_bfloat16* __restrict__ a,
+                                     __nv_bfloat16* __restrict__ b, float* __restrict__ norm) {
+  const uint64_t r = (blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x) >> 5;
+  const uint32_t lane = threadIdx.x & 31;
+  if (r >= n) return;
+  float s = 0.0f;
+  for (uint32_t d = lane; d < dim; d += 32) {
+    const float v = x[r * dim + d] - (mean ? mean[d] : 0.0f);
+    s = __fmaf_rn(v, v, s);
+    const __nv_bfloat16 hi = __float2bfloat16_rn(v);
+    if (!split) {
+      a[r * kp + d] = hi;
+    } else {
+      const __nv_bfloat16 lo = __float2bfloat16_rn(v - __bfloat162float(hi));
+      a[r * kp + d] = hi; a[r * kp + dim + d] = lo; a[r * kp + 2 * dim + d] = hi;
+      b[r * kp + d] = hi; b[r * kp + dim + d] = hi; b[r * kp + 2 * dim + d] = lo;
+    }
+  }
+  const uint32_t used = split ? 3 * dim : dim;
+  for (uint32_t d = used + lane; d < kp; d += 32) {
+    a[r * kp + d] = __float2bfloat16_rn(0.0f);
+    if (split) b[r * kp + d] = __float2bfloat16_rn(0.0f);
+  }
+  for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, off);
+  if (lane == 0) norm[r] = metric == GRAB_METRIC_L2 ? s : 0.0f;
+}
+
+// ------------------------------------------------------------------ exact re-rank
+// One CTA per row: canonical fp32 distances of the KC candidates, sorted by (dist, id).
+constexpr int kRerankThreads = 128;
+template <int METRIC>
+__global__ void __launch_bounds__(kRerankThreads)
+rerank_kernel(const float* __restrict__ data, uint32_t dim, const uint64_t* __restrict__ cand_keys, uint32_t kc,
+              uint32_t k, uint32_t* __restrict__ out_ids, float* __restrict__ out_dists) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  uint64_t* keys = reinterpret_cast<uint64_t*>(smem_raw);
+  float* q_smem = reinterpret_cast<float*>(keys + kc);
+  const uint64_t row = blockIdx.x;
+  const uint32_t tid = threadIdx.x;
+  const int lane8 = tid & (kTeam - 1);
+  const uint32_t team = tid / kTeam;
+  constexpr uint32_t teams = kRerankThreads / kTeam;
+  const uint32_t nchunk = dim / 4;
+  for (uint32_t i = tid; i < dim; i += kRerankThreads) q_smem[i] = data[row * dim + i];
+  __syncthreads();
+  for (uint32_t j0 = 0; j0 < kc; j0 += teams) {
+    const uint32_t j = j0 + team;
+    const uint64_t ck = j < kc ? cand_keys[row * kc + j] : kMaxKey;
+    const bool valid = ck != kMaxKey;
+    const uint32_t id = key_id(ck);
+    const float d = team_distance_smem<METRIC>(q_smem, data + static_cast<size_t>(id) * dim, nchunk, lane8, valid);
+    if (lane8 == 0 && j < kc) keys[j] = valid ? make_key(d, id) : kMaxKey;
+  }
+  __syncthreads();
+  block_bitonic_sort(keys, kc);
+  for (uint32_t i = tid; i < k; i += kRerankThreads) {
+    const uint64_t key = i < kc ? keys[i] : kMaxKey;
+    out_ids[row * k + i] = key == kMaxKey ? kInvalid : key_id(key);
+    if (out_dists) out_dists[row * k + i] = key == kMaxKey ? kFltMax : key_dist(key);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+static int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint32_t kp) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) {
+    set_last_error("knn_tc: cuTensorMapEncodeTiled is not available from the driver");
+    return GRAB_ERR_CUDA;
+  }
+  const cuuint64_t dims[2] = {kp, rows};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(kp) * 2};
+  const cuuint32_t box[2] = {BK, BM};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_last_error("knn_tc: cuTensorMapEncodeTiled failed with %d", static_cast<int>(r));
+    return GRAB_ERR_CUDA;
+  }
+  return GRAB_OK;
+}
+
+}  // namespace tc
+
+// precision 1: bf16 operands; 2: split bf16 (hi+lo), close to fp32 products.
+int knn_tc_impl(const float* d_dataset, uint64_t n, uint32_t dim, int metric, const uint64_t* h_block_offsets,
+                uint32_t num_blocks, uint32_t k, int mode, int precision, uint32_t* d_out_knn,
+                float* d_out_dists, cudaStream_t st) {
+  using namespace tc;
+  GRAB_REQUIRE(d_dataset && h_block_offsets && d_out_knn, "knn_tc: null pointer");
+  GRAB_REQUIRE(dim >= 4 && dim % 4 == 0, "knn_tc: dim %u must be a multiple of 4", dim);
+  GRAB_REQUIRE(n >= 1 && n < (1ull << 31) && num_blocks >= 1, "knn_tc: bad sizes");
+  GRAB_REQUIRE(h_block_offsets[0] == 0 && h_block_offsets[num_blocks] == n, "knn_tc: block offsets must span [0,n]");
+  GRAB_REQUIRE(mode == 0 || mode == 1, "knn_tc: mode must be 0 or 1");
+  GRAB_REQUIRE(precision == 1 || precision == 2, "knn_tc: precision must be 1 (bf16) or 2 (split bf16)");
+  const uint32_t want = k + k / 4 + 1;  // over-fetch: the exact re-rank picks the final k
+  GRAB_REQUIRE(k >= 1 && want <= 256, "knn_tc: k %u too large for the tensor-core path (max 204)", k);
+  const uint32_t kc = want <= 128 ? 128 : 256;
+  const int split = precision == 2;
+  const uint32_t kused = split ? 3 * dim : dim;
+  const uint32_t kp = (kused + BK - 1) / BK * BK;
+  const uint32_t kblocks = kp / BK;
+  const uint32_t num_row_tiles = static_cast<uint32_t>((n + BM - 1) / BM);
+  int dev = 0, sms = 0;
+  GRAB_CUDA_TRY(cudaGetDevice(&dev));
+  GRAB_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const uint32_t grid = num_row_tiles < static_cast<uint32_t>(sms) ? num_row_tiles : static_cast<uint32_t>(sms);
+
+  ScopedDeviceBuffer offs, wins, a_op, b_op, norm, mean, partial, scratch, keys, status;
+  GRAB_CUDA_TRY(offs.alloc(sizeof(uint64_t) * (num_blocks + 1)));
+  GRAB_CUDA_TRY(wins.alloc(sizeof(ScanWindow) * n));
+  GRAB_CUDA_TRY(a_op.alloc(sizeof(__nv_bfloat16) * n * kp));
+  if (split) GRAB_CUDA_TRY(b_op.alloc(sizeof(__nv_bfloat16) * n * kp));
+  GRAB_CUDA_TRY(norm.alloc(sizeof(float) * n));
+  GRAB_CUDA_TRY(scratch.alloc(sizeof(uint64_t) * static_cast<uint64_t>(grid) * BM * 2 * kc));
+  GRAB_CUDA_TRY(keys.alloc(sizeof(uint64_t) * n * kc));
+  GRAB_CUDA_TRY(status.alloc(sizeof(int)));
+  GRAB_CUDA_TRY(cudaMemsetAsync(status.ptr, 0, sizeof(int), st));
+  GRAB_CUDA_TRY(cudaMemcpyAsync(offs.ptr, h_block_offsets, sizeof(uint64_t) * (num_blocks + 1), cudaMemcpyHostToDevice, st));
+  knn_window_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(offs.as<uint64_t>(), num_blocks, n, mode, wins.as<ScanWindow>());
+  GRAB_CUDA_TRY(cudaGetLastError());
+
+  const float* d_mean = nullptr;
+  if (metric == GRAB_METRIC_L2) {  // distances are translation invariant: centring shrinks |x|^2
+    const uint32_t nchunks = static_cast<uint32_t>((n + kMeanChunk - 1) / kMeanChunk);
+    GRAB_CUDA_TRY(mean.alloc(sizeof(float) * dim));
+    GRAB_CUDA_TRY(partial.alloc(sizeof(float) * static_cast<uint64_t>(nchunks) * dim));
+    mean_partial_kernel<<<nchunks, 128, 0, st>>>(d_dataset, n, dim, partial.as<float>());
+    mean_final_kernel<<<(dim + 127) / 128, 128, 0, st>>>(partial.as<float>(), nchunks, dim, n, mean.as<float>());
+    GRAB_CUDA_TRY(cudaGetLastError());
+    d_mean = mean.as<float>();
+  }
+  __nv_bfloat16* pa = a_op.as<__nv_bfloat16>();
+  __nv_bfloat16* pb = split ? b_op.as<__nv_bfloat16>() : pa;
+  prep_operands_kernel<<<(unsigned)((n * 32 + 255) / 256), 256, 0, st>>>(d_dataset, n, dim, d_mean, split, metric, kp, pa,
+                                                                      pb, norm.as<float>());
+  GRAB_CUDA_TRY(cudaGetLastError());
+
+  CUtensorMap map_a, map_b;
+  int rc = make_map(&map_a, pa, n, kp);
+  if (rc != GRAB_OK) return rc;
+  rc = make_map(&map_b, pb, n, kp);
+  if (rc != GRAB_OK) return rc;
+
+  const size_t smem = STAGES * STAGE_BYTES + sizeof(SharedCtl) + 1024;
+  if (kc == 128) {
+    GRAB_CUDA_TRY(cudaFuncSetAttribute(knn_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    knn_tc_kernel<128><<<grid, THREADS, smem, st>>>(map_a, map_b, norm.as<float>(), wins.as<ScanWindow>(), n, kblocks,
+                                                   num_row_tiles, scratch.as<uint64_t>(), keys.as<uint64_t>(),
+                                                   status.as<int>());
+  } else {
+    GRAB_CUDA_TRY(cudaFuncSetAttribute(knn_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    knn_tc_kernel<256><<<grid, THREADS, smem, st>>>(map_a, map_b, norm.as<float>(), wins.as<ScanWindow>(), n, kblocks,
+                                                   num_row_tiles, scratch.as<uint64_t>(), keys.as<uint64_t>(),
+                                                   status.as<int>());
+  }
+  GRAB_CUDA_TRY(cudaGetLastError());
+  const size_t rsmem = sizeof(uint64_t) * kc + sizeof(float) * dim;
+  if (metric == GRAB_METRIC_L2)
+    rerank_kernel<GRAB_METRIC_L2><<<(unsigned)n, kRerankThreads, rsmem, st>>>(d_dataset, dim, keys.as<uint64_t>(), kc, k,
+                                                                           d_out_knn, d_out_dists);
+  else
+    rerank_kernel<GRAB_METRIC_IP><<<(unsigned)n, kRerankThreads, rsmem, st>>>(d_dataset, dim, keys.as<uint64_t>(), kc, k,
+                                                                           d_out_knn, d_out_dists);
+  GRAB_CUDA_TRY(cudaGetLastError());
+  int h_status = 0;
+  GRAB_CUDA_TRY(cudaMemcpyAsync(&h_status, status.ptr, sizeof(int), cudaMemcpyDeviceToHost, st));
+  GRAB_CUDA_TRY(cudaStreamSynchronize(st));
+  if (h_status != 0) {
+    set_last_error("knn_tc: a bounded device-side wait expired (pipeline stalled)");
+    return GRAB_ERR_TIMEOUT;
+  }
+  return GRAB_OK;
+}
+
+}  // namespace grab

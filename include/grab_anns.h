@@ -167,11 +167,17 @@ int grab_search_range(const float* d_dataset, uint32_t dim, uint64_t num_dataset
 /* h_block_offsets: host array [num_blocks+1].  mode 0: own block; mode 1: every vector  */
 /* EXCEPT those of the own block (candidates for cross-bucket edges, the role of the     */
 /* IVF-PQ self-search of cagra_opt.cu:813-856).  Output ascending exact distance.        */
+/* precision: GRAB_KNN_EXACT_SCAN = every pair in canonical fp32 (SIMT scan);            */
+/* GRAB_KNN_TC_BF16 / GRAB_KNN_TC_SPLIT = all-pairs tile on the tcgen05 tensor cores     */
+/* (bf16, or hi+lo split bf16 ~ fp32 products), fused per-row top-(k+k/4) and an exact   */
+/* fp32 re-rank of those candidates (k <= 204).                                          */
 /* grab_generate_knn_graph: src/index/cagra.cuh:59-63 (device dataset, HOST output).     */
 /* ------------------------------------------------------------------------------------ */
+enum grab_knn_precision { GRAB_KNN_EXACT_SCAN = 0, GRAB_KNN_TC_BF16 = 1, GRAB_KNN_TC_SPLIT = 2 };
 int grab_knn_graph_blocks(const float* d_dataset, uint64_t n, uint32_t dim, int metric,
                           const uint64_t* h_block_offsets, uint32_t num_blocks, uint32_t k,
-                          int mode, uint32_t* d_out_knn, float* d_out_dists, void* stream);
+                          int mode, int precision, uint32_t* d_out_knn, float* d_out_dists,
+                          void* stream);
 int grab_generate_knn_graph(const float* d_dataset, uint64_t num_dataset, uint32_t dim, uint32_t k,
                             uint32_t* h_knn_graph);
 
@@ -214,7 +220,8 @@ int grab_inject_reverse_remote_device(uint32_t* d_graph, uint64_t n, uint32_t to
 int grab_build_time_partitioned_graph(const float* d_dataset, uint64_t total_num, uint32_t dim,
                                       int metric, uint32_t* d_graph, const uint64_t* d_bucket,
                                       const uint64_t* h_bucket_sizes, uint32_t num_buckets,
-                                      uint32_t total_degree, uint32_t local_degree);
+                                      uint32_t total_degree, uint32_t local_degree,
+                                      int knn_precision);
 
 /* ------------------------------------------------------------------------------------ */
 /* Insert: topology updates.  v1: src/index/insert.cuh:62-72 (insert.cu:225-440).        */

@@ -164,7 +164,8 @@ def test_prune_reverse_merge_bit_exact(grab, oracle):
     knn_p[::7, 20:] = 0xFFFFFFFF
     knn_p[::11, 5] = knn_p[::11, 2]
     out2 = torch.empty((n, deg), dtype=torch.int32, device="cuda")
-    grab.check(L.grab_optimize_prune_device(grab._p(_t(knn_p.view(np.int32))), grab._p(out2),
+    knn_pt = _t(knn_p.view(np.int32))          # keep alive: the C ABI only sees raw pointers
+    grab.check(L.grab_optimize_prune_device(grab._p(knn_pt), grab._p(out2),
                                             grab.C.c_uint64(n), 32, deg, None, None))
     torch.cuda.synchronize()
     assert np.array_equal(_u32(out2), oracle.prune(knn_p, deg))
@@ -218,8 +219,8 @@ def test_insert_topology_bit_exact(grab, oracle):
     found = np.stack([rng.choice(ne // 10, size=sk, replace=False) for _ in range(nn)]).astype(np.int64)
     found[::9, -3:] = -1
     go = oracle.insert_v1(g, found, ne, sk)
-    gt = _t(g.view(np.int32))
-    grab.check(L.grab_update_topology_v1(grab._p(gt), grab._p(_t(found)), grab.C.c_uint64(ne),
+    gt, ft = _t(g.view(np.int32)), _t(found)
+    grab.check(L.grab_update_topology_v1(grab._p(gt), grab._p(ft), grab.C.c_uint64(ne),
                                          grab.C.c_uint64(nn), deg, sk, None))
     assert np.array_equal(_u32(gt), go)
     # time-partitioned
@@ -234,9 +235,9 @@ def test_insert_topology_bit_exact(grab, oracle):
                    for _ in range(nn)]).astype(np.int64)
     gkn = np.stack([rng.choice(ne, size=kg, replace=False) for _ in range(nn)]).astype(np.int64)
     go = oracle.insert_opt(g, bucket, lk, gkn, ne, nbk - 1, local)
-    gt = _t(g.view(np.int32))
-    grab.check(L.grab_update_topology_opt(grab._p(gt), grab._p(_t(bucket.view(np.int64))), grab._p(_t(lk)),
-                                          grab._p(_t(gkn)), grab.C.c_uint64(ne), grab.C.c_uint64(nn),
+    gt, bt, lkt, gkt = _t(g.view(np.int32)), _t(bucket.view(np.int64)), _t(lk), _t(gkn)
+    grab.check(L.grab_update_topology_opt(grab._p(gt), grab._p(bt), grab._p(lkt),
+                                          grab._p(gkt), grab.C.c_uint64(ne), grab.C.c_uint64(nn),
                                           grab.C.c_uint64(nbk - 1), total, local, kl, kg, None))
     assert np.array_equal(_u32(gt), go)
 
@@ -387,7 +388,8 @@ def test_time_partitioned_build_end_to_end(grab, oracle):
     n, dim, nb, total, local = 16000, 64, 8, 32, 24
     data = clustered(n, dim, 40, 1.0, 41)
     bucket = np.repeat(np.arange(nb, dtype=np.uint64), n // nb)
-    graph = grab.build_time_partitioned_graph(_t(data), _t(bucket.view(np.int64)), [n // nb] * nb, total, local)
+    graph = grab.build_time_partitioned_graph(_t(data), _t(bucket.view(np.int64)), [n // nb] * nb, total, local,
+                                              knn_precision=grab.KNN_EXACT_SCAN)
     g = _u32(graph)
     blk = np.arange(n) // (n // nb)
     loc = g[:, :local]
@@ -414,3 +416,76 @@ def test_time_partitioned_build_end_to_end(grab, oracle):
     gi, _ = grab.graph_search(_t(data), graph, _t(q), 10,
                               grab.SearchParams(64, 4, 0, 40, 13), flt=f)
     assert oracle.recall(gi.cpu().numpy(), gt) > 0.9
+
+
+# ------------------------------------------------------------------ tensor-core kNN (tcgen05)
+def _row_recall(a, b):
+    hit = sum(len(set(x[x != 0xFFFFFFFF]).intersection(y[y != 0xFFFFFFFF])) for x, y in zip(a, b))
+    return hit / max(1, int((b != 0xFFFFFFFF).sum()))
+
+
+@pytest.mark.parametrize("dim,metric", [(128, 0), (96, 0), (768, 1)])
+def test_knn_tensor_core_matches_exact(grab, dim, metric):
+    """All-pairs tile on tcgen05 + fused top-k + exact re-rank against the exact fp32 scan."""
+    n, k = 20000, 64
+    data = clustered(n, dim, 40, 1.0, 50 + dim)
+    if metric == 1:
+        data /= np.linalg.norm(data, axis=1, keepdims=True)
+    offs = np.array([0, 7000, 7100, n], dtype=np.uint64)      # ragged blocks, one tiny
+    d = _t(data)
+    exact, exact_d = grab.knn_graph_blocks(d, offs, k, mode=0, metric=metric, want_dists=True)
+    exact = _u32(exact)
+    for prec, floor in [(grab.KNN_TC_SPLIT, 0.999), (grab.KNN_TC_BF16, 0.97)]:
+        got, got_d = grab.knn_graph_blocks(d, offs, k, mode=0, metric=metric, want_dists=True, precision=prec)
+        got = _u32(got)
+        assert not (got == np.arange(n, dtype=np.uint32)[:, None]).any()          # no self loops
+        blk = np.searchsorted(offs, np.arange(n), side="right") - 1
+        gb = np.searchsorted(offs, np.where(got == 0xFFFFFFFF, 0, got), side="right") - 1
+        assert ((gb == blk[:, None]) | (got == 0xFFFFFFFF)).all()                  # stays inside its block
+        assert _row_recall(got, exact) >= floor, (prec, _row_recall(got, exact))
+        gd = got_d.cpu().numpy()
+        assert np.all(np.diff(gd, axis=1) >= 0)                                    # exact distances, ascending
+        same = got == exact
+        assert np.array_equal(gd[same], exact_d.cpu().numpy()[same])               # re-rank is the canonical fp32
+    # candidates from OTHER blocks
+    ex1 = _u32(grab.knn_graph_blocks(d, offs, 32, mode=1, metric=metric))
+    tc1 = _u32(grab.knn_graph_blocks(d, offs, 32, mode=1, metric=metric, precision=grab.KNN_TC_SPLIT))
+    assert _row_recall(tc1, ex1) >= 0.999
+    blk = np.searchsorted(offs, np.arange(n), side="right") - 1
+    assert (np.searchsorted(offs, tc1, side="right") - 1 != blk[:, None]).all()
+
+
+def test_knn_tensor_core_integer_data_is_exact(grab, datasets):
+    """Descriptor-like data (integers 0..255) is exactly representable in bf16 and the fp32
+    accumulation is exact, so the tensor-core path must reproduce the exact rows bit for bit."""
+    base, _ = datasets.descriptor_like(30000, 128, 100, 77)
+    d = _t(base)
+    offs = np.array([0, 10000, 20000, 30000], dtype=np.uint64)
+    exact = _u32(grab.knn_graph_blocks(d, offs, 96, mode=0))
+    tc = _u32(grab.knn_graph_blocks(d, offs, 96, mode=0, precision=grab.KNN_TC_BF16))
+    assert _row_recall(tc, exact) >= 0.9999
+
+
+def test_knn_constant_vector_known_answer_tensor_core(grab):
+    # tests/test_knn_build.cu (N 10 000, dim 1024, K 10, vector i = constant i*0.001) through
+    # the reference-shaped entry point grab_generate_knn_graph (split precision + exact re-rank)
+    n, dim, k = 10000, 1024, 10
+    data = (np.arange(n, dtype=np.float32) * np.float32(0.001))[:, None].repeat(dim, 1)
+    d = _t(data)
+    out = np.empty((n, k), dtype=np.uint32)
+    grab.check(grab.lib().grab_generate_knn_graph(grab._p(d), grab.C.c_uint64(n), dim, k, grab._p(out)))
+    idx = np.arange(n)[:, None]
+    assert not (out == idx).any()                       # 0 self loops
+    lo = np.clip(idx - 5, 0, n - 11)
+    assert ((out >= lo) & (out <= lo + 10)).mean() > 0.99   # recall > 99 % (test_knn_build.cu:111)
+
+
+def test_time_partitioned_build_tensor_core(grab, oracle):
+    n, dim, nb, total, local = 16000, 64, 8, 32, 24
+    data = clustered(n, dim, 40, 1.0, 41)
+    bucket = np.repeat(np.arange(nb, dtype=np.uint64), n // nb)
+    g_ex = _u32(grab.build_time_partitioned_graph(_t(data), _t(bucket.view(np.int64)), [n // nb] * nb, total, local,
+                                                  knn_precision=grab.KNN_EXACT_SCAN))
+    g_tc = _u32(grab.build_time_partitioned_graph(_t(data), _t(bucket.view(np.int64)), [n // nb] * nb, total, local,
+                                                  knn_precision=grab.KNN_TC_SPLIT))
+    assert (g_ex == g_tc).mean() > 0.98
