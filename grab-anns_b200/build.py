@@ -24,7 +24,7 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fopenmp",
     "--expt-relaxed-constexpr",
     "-I", INCLUDE, "-I", CSRC, "-I", HOST,
-]
+] + os.environ.get("GRAB_EXTRA_NVCC_FLAGS", "").split()
 
 
 def _sources():

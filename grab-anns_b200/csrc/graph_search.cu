@@ -11,7 +11,10 @@
 //   * survivors are compacted, then teams of 8 lanes gather one vector each with 16-byte
 //     loads, 4 vectors in flight per team (the reference: one warp, scalar loads, per
 //     neighbour);
-//   * queue entries are single uint64 (dist,id) keys; only itopk + survivors are sorted;
+//   * queue entries are single uint64 (dist,id) keys; a candidate enters the merge only if it
+//     beats the current worst of the itopk list; one warp sorts those few keys and folds them
+//     into the sorted itopk with a bitonic merge (the reference re-sorts the whole queue with
+//     one warp every iteration, search.cu:702-716);
 //   * the visited table is cleared when half full and re-seeded from the current itopk
 //     (the reference: every 30 iterations, search.cu:692-697).
 // HBM/latency-bound by design: no tensor cores.
@@ -21,7 +24,15 @@ namespace grab {
 
 constexpr int kSearchThreads = 128;
 constexpr int kSearchTeams = kSearchThreads / kTeam;  // 16
-constexpr int kSearchUnroll = 4;
+// vectors in flight per team and resident CTAs per SM the register budget is capped for
+#ifndef GRAB_SEARCH_UNROLL
+#define GRAB_SEARCH_UNROLL 2
+#endif
+#ifndef GRAB_SEARCH_CTAS_PER_SM
+#define GRAB_SEARCH_CTAS_PER_SM 8
+#endif
+constexpr int kSearchUnroll = GRAB_SEARCH_UNROLL;
+constexpr int kSearchCtasPerSm = GRAB_SEARCH_CTAS_PER_SM;
 
 struct SearchKernelArgs {
   const float* data;
@@ -51,7 +62,8 @@ struct SearchKernelArgs {
   float* out_dists;
   uint64_t id_scale, id_offset;
   unsigned long long* stats;  // grab_search_stats as 6 x u64, or NULL
-  uint32_t cand_cap, sort_cap;
+  uint32_t ckeys_cap;
+  uint32_t cand_cap, sort_cap;  // survivor list capacity; sort_cap = itopk rounded up to a power of two
 };
 
 __device__ __forceinline__ bool hash_insert(uint32_t* table, uint32_t bitlen, uint32_t key) {
@@ -67,6 +79,14 @@ __device__ __forceinline__ bool hash_insert(uint32_t* table, uint32_t bitlen, ui
   return false;  // full table reads as "visited", as in the reference (hashmap.cuh:89-90)
 }
 
+// Search-queue keys: [ordered dist : 32 | id : 31 | expanded flag : 1].  Raising the flag of an
+// entry cannot move it past another entry (ids are unique), so the list stays sorted.
+__device__ __forceinline__ uint64_t make_skey(float d, uint32_t id) {
+  return (static_cast<uint64_t>(float_to_ordered(d)) << 32) | (static_cast<uint64_t>(id) << 1);
+}
+__device__ __forceinline__ uint32_t skey_id(uint64_t key) { return static_cast<uint32_t>(key & 0xFFFFFFFFull) >> 1; }
+__device__ __forceinline__ bool skey_expanded(uint64_t key) { return (key & 1ull) != 0; }
+
 __device__ __forceinline__ uint64_t mix64(uint64_t x) {  // splitmix64 finaliser
   x ^= x >> 30; x *= 0xbf58476d1ce4e5b9ull;
   x ^= x >> 27; x *= 0x94d049bb133111ebull;
@@ -74,16 +94,55 @@ __device__ __forceinline__ uint64_t mix64(uint64_t x) {  // splitmix64 finaliser
   return x;
 }
 
+// Ascending bitonic sort of n (power of two, >= 32) keys in shared memory by ONE warp.
+__device__ __forceinline__ void warp_bitonic_sort_smem(uint64_t* keys, uint32_t n, uint32_t lane) {
+  for (uint32_t size = 2; size <= n; size <<= 1) {
+    for (uint32_t stride = size >> 1; stride > 0; stride >>= 1) {
+      for (uint32_t t = lane; t < (n >> 1); t += 32) {
+        const uint32_t lo = ((t & ~(stride - 1)) << 1) | (t & (stride - 1));
+        const uint32_t hi = lo | stride;
+        const bool up = (lo & size) == 0;
+        const uint64_t a = keys[lo], b = keys[hi];
+        if ((a > b) == up) { keys[lo] = b; keys[hi] = a; }
+      }
+      __syncwarp();
+    }
+  }
+}
+
+// Fold `ncand` sorted candidate keys into the sorted list top[0..m) (m a power of two), keeping
+// the m smallest: top[m-1-i] = min(top[m-1-i], cand[i]) leaves a bitonic sequence, which one
+// pass of bitonic merge stages sorts again.  One warp.
+__device__ __forceinline__ void warp_merge_into_topk(uint64_t* top, uint32_t m, const uint64_t* cand,
+                                                     uint32_t ncand, uint32_t lane) {
+  const uint32_t lim = ncand < m ? ncand : m;
+  for (uint32_t i = lane; i < lim; i += 32) {
+    const uint64_t a = top[m - 1 - i], b = cand[i];
+    if (b < a) top[m - 1 - i] = b;
+  }
+  __syncwarp();
+  for (uint32_t stride = m >> 1; stride > 0; stride >>= 1) {
+    for (uint32_t t = lane; t < (m >> 1); t += 32) {
+      const uint32_t lo = ((t & ~(stride - 1)) << 1) | (t & (stride - 1));
+      const uint32_t hi = lo | stride;
+      const uint64_t a = top[lo], b = top[hi];
+      if (a > b) { top[lo] = b; top[hi] = a; }
+    }
+    __syncwarp();
+  }
+}
+
 template <int METRIC, int CPL>
-__global__ void __launch_bounds__(kSearchThreads)
+__global__ void __launch_bounds__(kSearchThreads, kSearchCtasPerSm)
 graph_search_kernel(const SearchKernelArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  uint64_t* queue = reinterpret_cast<uint64_t*>(smem_raw);                 // [sort_cap]
-  float* q_smem = reinterpret_cast<float*>(queue + a.sort_cap);            // [dim]
-  uint32_t* cand = reinterpret_cast<uint32_t*>(q_smem + a.dim);            // [cand_cap]
+  uint64_t* queue = reinterpret_cast<uint64_t*>(smem_raw);                 // [sort_cap] sorted itopk list
+  uint64_t* ckeys = queue + a.sort_cap;                                    // [cand_cap pow2] kept candidates
+  float* q_smem = reinterpret_cast<float*>(ckeys + a.ckeys_cap);           // [dim]
+  uint32_t* cand = reinterpret_cast<uint32_t*>(q_smem + a.dim);            // [cand_cap] survivor ids
   uint32_t* parents = cand + a.cand_cap;                                   // [width]
   uint32_t* hash = parents + ((a.width + 3) & ~3u);                        // [2^bitlen] (if local)
-  __shared__ uint32_t s_ncand, s_nparents, s_hash_count;
+  __shared__ uint32_t s_ncand, s_nparents, s_hash_count, s_nkeep;
   __shared__ unsigned long long s_stats[6];
 
   const uint64_t qi = blockIdx.x;
@@ -98,7 +157,7 @@ graph_search_kernel(const SearchKernelArgs a) {
   for (uint32_t i = tid; i < a.dim; i += kSearchThreads) q_smem[i] = a.queries[qi * a.dim + i];
   for (uint32_t i = tid; i < a.sort_cap; i += kSearchThreads) queue[i] = kMaxKey;
   for (uint32_t i = tid; i < hsize; i += kSearchThreads) hash[i] = kInvalid;
-  if (tid == 0) { s_ncand = 0; s_nparents = 0; s_hash_count = 0; }
+  if (tid == 0) { s_ncand = 0; s_nparents = 0; s_hash_count = 0; s_nkeep = 0; }
   if (tid < 6) s_stats[tid] = 0;
 
   uint64_t lo = 0, hi = 0;
@@ -165,61 +224,71 @@ graph_search_kernel(const SearchKernelArgs a) {
   __syncthreads();
 
   uint32_t iter = 0;
-  bool expanded = true;  // candidates waiting in cand[0..s_ncand)
   for (;;) {
-    // ---- distances of the compacted candidates: 16 teams x 4 vectors in flight ----
+    // ---- distances of the compacted candidates: 16 teams, vectors gathered with 16-byte loads;
+    //      a key is kept only if it beats the current worst entry of the itopk list ----
     const uint32_t ncand = s_ncand;
-    if (expanded) {
-      for (uint32_t j0 = 0; j0 < ncand; j0 += kSearchTeams * kSearchUnroll) {
-        uint32_t id[kSearchUnroll];
-        bool ok[kSearchUnroll];
-        float acc[kSearchUnroll];
+    const uint64_t worst = queue[a.sort_cap - 1];
+    for (uint32_t j0 = 0; j0 < ncand; j0 += kSearchTeams * kSearchUnroll) {
+      uint32_t id[kSearchUnroll];
+      bool ok[kSearchUnroll];
+      float acc[kSearchUnroll];
 #pragma unroll
-        for (int u = 0; u < kSearchUnroll; ++u) {
-          const uint32_t j = j0 + u * kSearchTeams + team;
-          ok[u] = j < ncand;
-          id[u] = ok[u] ? cand[j] : 0;
-          acc[u] = 0.0f;
-        }
-        if (CPL > 0) {
-          float4 x[kSearchUnroll][CPL > 0 ? CPL : 1];
+      for (int u = 0; u < kSearchUnroll; ++u) {
+        const uint32_t j = j0 + u * kSearchTeams + team;
+        ok[u] = j < ncand;
+        id[u] = ok[u] ? cand[j] : 0;
+        acc[u] = 0.0f;
+      }
+      if (CPL > 0) {
+        float4 x[kSearchUnroll][CPL > 0 ? CPL : 1];
+#pragma unroll
+        for (int u = 0; u < kSearchUnroll; ++u)
+#pragma unroll
+          for (int c = 0; c < CPL; ++c)
+            if (ok[u]) x[u][c] = ldg_f4(a.data + static_cast<size_t>(id[u]) * a.dim + 4 * (lane8 + kTeam * c));
+#pragma unroll
+        for (int u = 0; u < kSearchUnroll; ++u)
+#pragma unroll
+          for (int c = 0; c < CPL; ++c)
+            if (ok[u]) acc[u] = accum4<METRIC>(acc[u], qreg[c], x[u][c]);
+      } else {
+        for (uint32_t c = lane8; c < nchunk; c += kTeam) {
+          const float4 qv = *reinterpret_cast<const float4*>(q_smem + 4 * c);
+          float4 x[kSearchUnroll];
 #pragma unroll
           for (int u = 0; u < kSearchUnroll; ++u)
-#pragma unroll
-            for (int c = 0; c < CPL; ++c)
-              if (ok[u]) x[u][c] = ldg_f4(a.data + static_cast<size_t>(id[u]) * a.dim + 4 * (lane8 + kTeam * c));
+            if (ok[u]) x[u] = ldg_f4(a.data + static_cast<size_t>(id[u]) * a.dim + 4 * c);
 #pragma unroll
           for (int u = 0; u < kSearchUnroll; ++u)
-#pragma unroll
-            for (int c = 0; c < CPL; ++c)
-              if (ok[u]) acc[u] = accum4<METRIC>(acc[u], qreg[c], x[u][c]);
-        } else {
-          for (uint32_t c = lane8; c < nchunk; c += kTeam) {
-            const float4 qv = *reinterpret_cast<const float4*>(q_smem + 4 * c);
-            float4 x[kSearchUnroll];
-#pragma unroll
-            for (int u = 0; u < kSearchUnroll; ++u)
-              if (ok[u]) x[u] = ldg_f4(a.data + static_cast<size_t>(id[u]) * a.dim + 4 * c);
-#pragma unroll
-            for (int u = 0; u < kSearchUnroll; ++u)
-              if (ok[u]) acc[u] = accum4<METRIC>(acc[u], qv, x[u]);
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < kSearchUnroll; ++u) {
-          const float d = team_reduce<METRIC>(acc[u]);
-          if (lane8 == 0 && ok[u]) queue[a.itopk + j0 + u * kSearchTeams + team] = make_key(d, id[u]);
+            if (ok[u]) acc[u] = accum4<METRIC>(acc[u], qv, x[u]);
         }
       }
-      __syncthreads();
+#pragma unroll
+      for (int u = 0; u < kSearchUnroll; ++u) {
+        const float d = team_reduce<METRIC>(acc[u]);
+        if (lane8 == 0 && ok[u]) {
+          const uint64_t key = make_skey(d, id[u]);
+          if (key < worst) ckeys[atomicAdd(&s_nkeep, 1u)] = key;
+        }
+      }
     }
+    __syncthreads();
 
-    // ---- sort itopk + candidates (only as many slots as are in use) ----
-    uint32_t used = a.itopk + (expanded ? ncand : 0);
-    uint32_t padded = 64;
-    while (padded < used) padded <<= 1;
-    block_bitonic_sort(queue, padded);
-    for (uint32_t i = a.itopk + tid; i < padded; i += kSearchThreads) queue[i] = kMaxKey;
+    // ---- warp 0: sort the kept candidates and fold them into the sorted itopk list ----
+    if (tid < 32) {
+      const uint32_t nkeep = s_nkeep;
+      if (nkeep > 0) {
+        uint32_t padded = 32;
+        while (padded < nkeep) padded <<= 1;
+        for (uint32_t i = nkeep + tid; i < padded; i += 32) ckeys[i] = kMaxKey;
+        __syncwarp();
+        warp_bitonic_sort_smem(ckeys, padded, tid);
+        warp_merge_into_topk(queue, a.sort_cap, ckeys, nkeep, tid);
+      }
+      if (tid == 0) s_nkeep = 0;
+    }
+    __syncthreads();
 
     // ---- visited table half full: clear and re-seed from the current itopk ----
     if (s_hash_count > hsize / 2) {  // uniform
@@ -227,9 +296,9 @@ graph_search_kernel(const SearchKernelArgs a) {
       for (uint32_t i = tid; i < hsize; i += kSearchThreads) hash[i] = kInvalid;
       __syncthreads();
       uint32_t kept = 0;
-      for (uint32_t i = tid; i < a.itopk; i += kSearchThreads) {
+      for (uint32_t i = tid; i < a.sort_cap; i += kSearchThreads) {
         const uint64_t key = queue[i];
-        if (key != kMaxKey) { hash_insert(hash, a.hash_bitlen, key_id(key) & ~kMsb); ++kept; }
+        if (key != kMaxKey) { hash_insert(hash, a.hash_bitlen, skey_id(key)); ++kept; }
       }
       kept = __reduce_add_sync(0xFFFFFFFFu, kept);
       if (tid == 0) { s_hash_count = 0; s_stats[5] += 1; }
@@ -241,16 +310,16 @@ graph_search_kernel(const SearchKernelArgs a) {
     // ---- pick up to `width` unexpanded parents, best first (search.cu:38-107) ----
     if (tid < 32) {
       uint32_t found = 0;
-      for (uint32_t j0 = 0; j0 < a.itopk && found < a.width; j0 += 32) {
+      for (uint32_t j0 = 0; j0 < a.sort_cap && found < a.width; j0 += 32) {
         const uint32_t j = j0 + tid;
-        uint64_t key = j < a.itopk ? queue[j] : kMaxKey;
-        const bool fresh = key != kMaxKey && (key_id(key) & kMsb) == 0;
+        uint64_t key = j < a.sort_cap ? queue[j] : kMaxKey;
+        const bool fresh = key != kMaxKey && !skey_expanded(key);
         const uint32_t vote = __ballot_sync(0xFFFFFFFFu, fresh);
         if (fresh) {
           const uint32_t rank = found + __popc(vote & ((1u << tid) - 1));
           if (rank < a.width) {
-            parents[rank] = key_id(key);
-            queue[j] = key | kMsb;
+            parents[rank] = skey_id(key);
+            queue[j] = key | 1ull;
           }
         }
         found += __popc(vote);
@@ -287,7 +356,6 @@ graph_search_kernel(const SearchKernelArgs a) {
       s_stats[1] += nparents;
       s_stats[3] += s_ncand;
     }
-    expanded = true;
     ++iter;
     __syncthreads();
   }
@@ -298,7 +366,7 @@ graph_search_kernel(const SearchKernelArgs a) {
     const uint64_t key = queue[i];
     const bool empty = key == kMaxKey;
     a.out_ids[qi * a.k + i] =
-        empty ? -1 : static_cast<int64_t>((key_id(key) & ~kMsb) * a.id_scale + a.id_offset);
+        empty ? -1 : static_cast<int64_t>(static_cast<uint64_t>(skey_id(key)) * a.id_scale + a.id_offset);
     a.out_dists[qi * a.k + i] = empty ? kFltMax : key_dist(key);
   }
   if (a.stats && tid < 6) atomicAdd(&a.stats[tid], s_stats[tid]);
@@ -410,12 +478,14 @@ int graph_search_impl(const grab_search_args* g) {
   a.num_seeds = nseeds;
   a.cand_cap = a.width * a.deg > itopk ? a.width * a.deg : itopk;
   a.cand_cap = (a.cand_cap + 3) & ~3u;
-  a.sort_cap = next_pow2(itopk + a.cand_cap);
+  a.sort_cap = next_pow2(itopk);  // the itopk list is kept at a power-of-two length (>= the requested itopk)
   if (a.sort_cap < 64) a.sort_cap = 64;
+  a.ckeys_cap = next_pow2(a.cand_cap);
+  if (a.ckeys_cap < 32) a.ckeys_cap = 32;
 
   const bool local_hash = a.hash_bitlen <= 13;
   const size_t hash_bytes = sizeof(uint32_t) * (size_t(1) << a.hash_bitlen);
-  size_t smem = sizeof(uint64_t) * a.sort_cap + sizeof(float) * a.dim + sizeof(uint32_t) * a.cand_cap +
+  size_t smem = sizeof(uint64_t) * (a.sort_cap + a.ckeys_cap) + sizeof(float) * a.dim + sizeof(uint32_t) * a.cand_cap +
                 sizeof(uint32_t) * ((a.width + 3) & ~3u) + (local_hash ? hash_bytes : 0);
   if (smem > 200 * 1024) {
     set_last_error("graph_search: itopk %u, width %u, degree %u, dim %u need %zu bytes of shared memory",
