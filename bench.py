@@ -243,7 +243,7 @@ def main():
     recall = hit / max(denom, 1)
     in_range = bool(np.all(((res >= w["lo"][:, None].astype(np.int64)) & (res < w["hi"][:, None].astype(np.int64)))
                            | (res < 0)))
-    alg_bytes = grab.search_bytes(stats, nq, dim, deg, k, 8)
+    alg_bytes = grab.search_bytes(stats, nq, dim, deg, k, 0)  # sorted timestamps: id-window predicate, no gather
 
     def step():
         grab.graph_search(d_base, graph, d_q, k, params, metric=w["metric"], flt=flt, out=(out_ids, out_d), ws=ws)

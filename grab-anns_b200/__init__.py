@@ -233,6 +233,7 @@ def merge_topk(dists, ids, k):
 def search_bytes(stats: SearchStats, nq: int, dim: int, deg: int, k: int, filter_bytes: int) -> int:
     """Algorithmic bytes of one search launch: vectors that had to be read (queries, seeds,
     distance-evaluated neighbours), graph rows of expanded parents, filter values of examined
-    neighbours, results written."""
+    neighbours (filter_bytes = 8 for gathered uint64 timestamps, 1 for labels, 0 when sorted
+    timestamps make the range an id window), results written."""
     return (4 * dim * (nq + stats.seeds + stats.distances) + 4 * deg * stats.parents +
             filter_bytes * stats.edges + 12 * k * nq)

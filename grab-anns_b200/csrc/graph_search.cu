@@ -22,14 +22,17 @@
 
 namespace grab {
 
-constexpr int kSearchThreads = 128;
+#ifndef GRAB_SEARCH_THREADS
+#define GRAB_SEARCH_THREADS 128
+#endif
+constexpr int kSearchThreads = GRAB_SEARCH_THREADS;
 constexpr int kSearchTeams = kSearchThreads / kTeam;  // 16
 // vectors in flight per team and resident CTAs per SM the register budget is capped for
 #ifndef GRAB_SEARCH_UNROLL
 #define GRAB_SEARCH_UNROLL 2
 #endif
 #ifndef GRAB_SEARCH_CTAS_PER_SM
-#define GRAB_SEARCH_CTAS_PER_SM 8
+#define GRAB_SEARCH_CTAS_PER_SM 6
 #endif
 constexpr int kSearchUnroll = GRAB_SEARCH_UNROLL;
 constexpr int kSearchCtasPerSm = GRAB_SEARCH_CTAS_PER_SM;
@@ -168,7 +171,17 @@ graph_search_kernel(const SearchKernelArgs a) {
   } else if (a.filter_kind == GRAB_FILTER_LABELS) {
     mask = a.masks ? a.masks[qi] : a.mask1;
   }
+  // Timestamps that are non-decreasing in the id turn a range into an id window: the
+  // predicate then reads nothing (the reference gathers d_ts[nbr], compute_distance.cuh:580).
+  uint32_t wbeg = 0, wend = 0;
+  const bool by_window = a.windows != nullptr && a.filter_kind == GRAB_FILTER_TS_RANGE;
+  if (a.windows) {
+    wbeg = a.windows[qi * 4];
+    wend = a.windows[qi * 4 + 1];
+    if (wend < wbeg) wend = wbeg;
+  }
   auto passes = [&](uint32_t id) -> bool {
+    if (by_window) return id >= wbeg && id < wend;
     if (a.filter_kind == GRAB_FILTER_TS_RANGE) {
       const uint64_t t = __ldg(a.ts + id);
       return t >= lo && t < hi;
@@ -187,12 +200,7 @@ graph_search_kernel(const SearchKernelArgs a) {
 
   // ---- seeds (compute_distance.cuh:204-269): provided ids, else pseudo-random ids ----
   {
-    uint32_t wbeg = 0, wlen = 0;
-    if (a.windows) {
-      wbeg = a.windows[qi * 4];
-      const uint32_t wend = a.windows[qi * 4 + 1];
-      wlen = wend > wbeg ? wend - wbeg : 0;
-    }
+    const uint32_t wlen = wend - wbeg;
     const bool generated_only = (a.seeds == nullptr);
     // without an id window a generated seed may fail the filter: allow 4 attempts per seed
     const uint32_t attempts = (generated_only && !a.windows && a.filter_kind != GRAB_FILTER_NONE &&
@@ -458,7 +466,7 @@ int graph_search_impl(const grab_search_args* g) {
       GRAB_REQUIRE((f.d_lo == nullptr) == (f.d_hi == nullptr),
                    "graph_search: d_lo and d_hi must both be given or both NULL");
       a.ts = f.d_ts; a.lo = f.d_lo; a.hi = f.d_hi; a.lo1 = f.lo; a.hi1 = f.hi;
-      need_window = f.ts_sorted && !g->d_seeds;
+      need_window = f.ts_sorted != 0;
       break;
     case GRAB_FILTER_LABELS:
       GRAB_REQUIRE(f.d_labels, "graph_search: label filter without d_labels");

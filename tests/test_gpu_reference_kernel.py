@@ -25,7 +25,7 @@ def ref():
 @pytest.fixture(scope="module")
 def setup(oracle):
     n, dim, deg = 20000, 128, 32
-    data = clustered(n, dim, 40, 1.0, 61)
+    data = clustered(n, dim, 8, 1.0, 61)      # few clusters: 32 random seeds reach every cluster
     knn = oracle.knn_block(data, 2 * deg)
     g = oracle.prune(knn, deg)
     rev, cnt = oracle.reverse_graph(g)
