@@ -36,12 +36,12 @@ def parse():
     ap.add_argument("--workload", default="C2")
     ap.add_argument("--scale", type=float, default=1.0, help="shrink the workload (tests / profiling)")
     ap.add_argument("--selectivity", type=float, default=0.10)
-    ap.add_argument("--buckets", type=int, default=100)
+    ap.add_argument("--buckets", type=int, default=20)
     ap.add_argument("--local-degree", type=int, default=48)
     ap.add_argument("--itopk", type=int, default=64)
-    ap.add_argument("--width", type=int, default=4)
-    ap.add_argument("--max-iter", type=int, default=32)
-    ap.add_argument("--hash-bitlen", type=int, default=12)
+    ap.add_argument("--width", type=int, default=3)
+    ap.add_argument("--max-iter", type=int, default=20)
+    ap.add_argument("--hash-bitlen", type=int, default=11)
     ap.add_argument("--knn-precision", type=int, default=1,
                     help="0 exact scan, 1 bf16 tensor cores (exact for integer-valued data), 2 split bf16")
     ap.add_argument("--cpu-sample", type=int, default=0, help="queries in the CPU sample (0 = auto)")

@@ -9,8 +9,10 @@
 //     fetched, so rejected neighbours cost 4+f bytes and never pollute the table
 //     (the reference inserts first: compute_distance.cuh:572-584);
 //   * survivors are compacted, then teams of 8 lanes gather one vector each with 16-byte
-//     loads, 4 vectors in flight per team (the reference: one warp, scalar loads, per
+//     loads, 2 vectors in flight per team (the reference: one warp, scalar loads, per
 //     neighbour);
+//   * small CTAs (2 warps) and many of them per SM: the phases of one query (expand, gather,
+//     merge) overlap with the phases of the others, which is what hides the gather latency;
 //   * queue entries are single uint64 (dist,id) keys; a candidate enters the merge only if it
 //     beats the current worst of the itopk list; one warp sorts those few keys and folds them
 //     into the sorted itopk with a bitonic merge (the reference re-sorts the whole queue with
@@ -23,7 +25,7 @@
 namespace grab {
 
 #ifndef GRAB_SEARCH_THREADS
-#define GRAB_SEARCH_THREADS 128
+#define GRAB_SEARCH_THREADS 64
 #endif
 constexpr int kSearchThreads = GRAB_SEARCH_THREADS;
 constexpr int kSearchTeams = kSearchThreads / kTeam;  // 16
@@ -32,7 +34,7 @@ constexpr int kSearchTeams = kSearchThreads / kTeam;  // 16
 #define GRAB_SEARCH_UNROLL 2
 #endif
 #ifndef GRAB_SEARCH_CTAS_PER_SM
-#define GRAB_SEARCH_CTAS_PER_SM 6
+#define GRAB_SEARCH_CTAS_PER_SM 12
 #endif
 constexpr int kSearchUnroll = GRAB_SEARCH_UNROLL;
 constexpr int kSearchCtasPerSm = GRAB_SEARCH_CTAS_PER_SM;

@@ -1,0 +1,183 @@
+// Batched insert: neighbour search for the new vectors, then the topology update.
+//
+// v1  : src/index/cagra.cu:938-1015 (cagra::insert) = find_near_nodes (insert.cu:140-219:
+//       search over the old nodes with search_k = 2*degree, exact distances, sorted) +
+//       update_topology_gpu_v1.
+// opt : src/index/cagra_opt.cu:1674-1981 (time-partitioned cagra::insert) = global search
+//       over the old nodes + bucket search from in-bucket seeds + exact kNN inside the batch
+//       (the reference asks RAFT), the two "local" lists merged by distance
+//       (merge_topk_kernel, cagra_opt.cu:1476-1652), then update_topology_gpu_opt.
+// The searches return canonical exact fp32 distances already sorted, so the reference's
+// separate refine / sort kernels (insert.cu:24-137) have no counterpart here.
+#include "common.cuh"
+
+namespace grab {
+
+int graph_search_impl(const grab_search_args*);
+int knn_blocks_impl(const float*, uint64_t, uint32_t, int, const uint64_t*, uint32_t, uint32_t, int, uint32_t*,
+                    float*, cudaStream_t);
+int update_topology_v1_impl(uint32_t*, const int64_t*, uint64_t, uint64_t, uint32_t, uint32_t, cudaStream_t);
+int update_topology_opt_impl(uint32_t*, const uint64_t*, int64_t*, int64_t*, uint64_t, uint64_t, uint64_t,
+                             uint32_t, uint32_t, uint32_t, uint32_t, cudaStream_t);
+
+#define GRAB_TRY(expr)              \
+  do {                              \
+    int _rc = (expr);               \
+    if (_rc != GRAB_OK) return _rc; \
+  } while (0)
+
+__global__ void fill_empty_kernel(int64_t* ids, float* dists, uint64_t total) {
+  const uint64_t i = blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x;
+  if (i >= total) return;
+  ids[i] = -1;
+  dists[i] = kFltMax;
+}
+
+// Per new vector: merge the bucket-search list [ka] with the intra-batch kNN list [kb] (local
+// ids + id_offset), keep the ka best by (dist, id).  cagra_opt.cu:1476-1652.
+__global__ void merge_two_lists_kernel(int64_t* __restrict__ ids_a, float* __restrict__ dists_a, uint32_t ka,
+                                       const uint32_t* __restrict__ ids_b, const float* __restrict__ dists_b,
+                                       uint32_t kb, uint64_t id_offset, uint32_t padded) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  uint64_t* keys = reinterpret_cast<uint64_t*>(smem_raw);
+  const uint64_t row = blockIdx.x;
+  for (uint32_t i = threadIdx.x; i < padded; i += blockDim.x) {
+    uint64_t key = kMaxKey;
+    if (i < ka) {
+      const int64_t id = ids_a[row * ka + i];
+      if (id >= 0) key = make_key(dists_a[row * ka + i], static_cast<uint32_t>(id));
+    } else if (i < ka + kb) {
+      const uint32_t id = ids_b[row * kb + (i - ka)];
+      if (id != kInvalid) key = make_key(dists_b[row * kb + (i - ka)], static_cast<uint32_t>(id + id_offset));
+    }
+    keys[i] = key;
+  }
+  __syncthreads();
+  block_bitonic_sort(keys, padded);
+  for (uint32_t i = threadIdx.x; i < ka; i += blockDim.x) {
+    const uint64_t key = keys[i];
+    ids_a[row * ka + i] = key == kMaxKey ? -1 : static_cast<int64_t>(key_id(key));
+    dists_a[row * ka + i] = key == kMaxKey ? kFltMax : key_dist(key);
+  }
+}
+
+static grab_search_args insert_search_args(const float* d_dataset, uint32_t dim, uint64_t n, const uint32_t* d_graph,
+                                           uint32_t deg, const float* d_queries, uint64_t nq, uint32_t k,
+                                           grab_search_params params, int64_t* ids, float* dists, int metric) {
+  grab_search_args a;
+  memset(&a, 0, sizeof(a));
+  a.d_dataset = d_dataset; a.n = n; a.dim = dim; a.metric = metric;
+  a.d_graph = d_graph; a.graph_degree = deg;
+  a.d_queries = d_queries; a.nq = nq; a.k = k; a.params = params;
+  a.seed = 0x51ED270B3A4D9C35ull + n;
+  a.d_out_ids = ids; a.d_out_dists = dists; a.id_scale = 1;
+  return a;
+}
+
+int insert_v1_impl(const float* d_dataset, uint64_t num_existing, uint64_t num_new, const float* d_new_vectors,
+                   uint32_t* d_graph, uint32_t dim, uint32_t degree, grab_search_params params, int metric) {
+  GRAB_REQUIRE(d_dataset && d_new_vectors && d_graph, "insert: null pointer");
+  if (num_new == 0) return GRAB_OK;
+  GRAB_REQUIRE(num_existing >= 1, "insert: the index is empty (build it first)");
+  const uint32_t search_k = 2 * degree;  // cagra.cu:958
+  ScopedDeviceBuffer ids, dists;
+  GRAB_CUDA_TRY(ids.alloc(sizeof(int64_t) * num_new * search_k));
+  GRAB_CUDA_TRY(dists.alloc(sizeof(float) * num_new * search_k));
+  grab_search_args a = insert_search_args(d_dataset, dim, num_existing, d_graph, degree, d_new_vectors, num_new,
+                                          search_k, params, ids.as<int64_t>(), dists.as<float>(), metric);
+  a.filter.kind = GRAB_FILTER_NONE;
+  GRAB_TRY(graph_search_impl(&a));
+  GRAB_TRY(update_topology_v1_impl(d_graph, ids.as<int64_t>(), num_existing, num_new, degree, search_k, nullptr));
+  GRAB_CUDA_TRY(cudaDeviceSynchronize());
+  return GRAB_OK;
+}
+
+int insert_opt_impl(const float* d_dataset, uint32_t* d_graph, const uint64_t* d_bucket, const uint32_t* d_seeds,
+                    uint64_t num_existing, uint64_t num_new, uint64_t target_bucket, const float* d_queries,
+                    uint32_t dim, uint32_t total_degree, uint32_t local_degree, grab_search_params params,
+                    uint32_t num_seeds_per_query, int metric) {
+  GRAB_REQUIRE(d_dataset && d_graph && d_bucket && d_queries, "insert: null pointer");
+  if (num_new == 0) return GRAB_OK;
+  GRAB_REQUIRE(num_existing >= 1, "insert: the index is empty (build it first)");
+  const uint32_t search_k = params.itopk_size;  // cagra_opt.cu:1691
+  GRAB_REQUIRE(search_k >= 2 && search_k <= 512, "insert: itopk_size %u outside [2,512]", search_k);
+  ScopedDeviceBuffer ig, dg, il, dl;
+  GRAB_CUDA_TRY(ig.alloc(sizeof(int64_t) * num_new * search_k));
+  GRAB_CUDA_TRY(dg.alloc(sizeof(float) * num_new * search_k));
+  GRAB_CUDA_TRY(il.alloc(sizeof(int64_t) * num_new * search_k));
+  GRAB_CUDA_TRY(dl.alloc(sizeof(float) * num_new * search_k));
+  const uint64_t total = num_new * search_k;
+  // global search over the old nodes, all columns, self-drawn seeds (cagra_opt.cu:1725-1740)
+  {
+    grab_search_args a = insert_search_args(d_dataset, dim, num_existing, d_graph, total_degree, d_queries, num_new,
+                                            search_k, params, ig.as<int64_t>(), dg.as<float>(), metric);
+    a.filter.kind = GRAB_FILTER_NONE;
+    GRAB_TRY(graph_search_impl(&a));
+  }
+  // bucket search from in-bucket seeds, local columns only (cagra_opt.cu:1779-1795)
+  if (d_seeds && num_seeds_per_query > 0) {
+    grab_search_args a = insert_search_args(d_dataset, dim, num_existing, d_graph, total_degree, d_queries, num_new,
+                                            search_k, params, il.as<int64_t>(), dl.as<float>(), metric);
+    a.filter.kind = GRAB_FILTER_PREFIX;
+    a.filter.active_degree = local_degree;
+    a.d_seeds = d_seeds;
+    a.seeds_per_query = num_seeds_per_query;
+    GRAB_TRY(graph_search_impl(&a));
+  } else {
+    fill_empty_kernel<<<(unsigned)((total + 255) / 256), 256>>>(il.as<int64_t>(), dl.as<float>(), total);
+    GRAB_CUDA_TRY(cudaGetLastError());
+  }
+  // exact kNN inside the batch, tmp = min(n, search_k/2) wide (cagra_opt.cu:1877-1928)
+  const uint32_t tmp = static_cast<uint32_t>(num_new < search_k / 2 ? num_new : search_k / 2);
+  if (num_new >= 2 && tmp >= 1) {
+    ScopedDeviceBuffer bi, bd;
+    GRAB_CUDA_TRY(bi.alloc(sizeof(uint32_t) * num_new * tmp));
+    GRAB_CUDA_TRY(bd.alloc(sizeof(float) * num_new * tmp));
+    const uint64_t offs[2] = {0, num_new};
+    GRAB_TRY(knn_blocks_impl(d_queries, num_new, dim, metric, offs, 1, tmp, 0, bi.as<uint32_t>(), bd.as<float>(), nullptr));
+    const uint32_t padded = next_pow2(search_k + tmp);
+    merge_two_lists_kernel<<<(unsigned)num_new, 128, sizeof(uint64_t) * padded>>>(
+        il.as<int64_t>(), dl.as<float>(), search_k, bi.as<uint32_t>(), bd.as<float>(), tmp, num_existing, padded);
+    GRAB_CUDA_TRY(cudaGetLastError());
+    GRAB_CUDA_TRY(cudaDeviceSynchronize());
+  }
+  GRAB_TRY(update_topology_opt_impl(d_graph, d_bucket, il.as<int64_t>(), ig.as<int64_t>(), num_existing, num_new,
+                                    target_bucket, total_degree, local_degree, search_k, search_k, nullptr));
+  GRAB_CUDA_TRY(cudaDeviceSynchronize());
+  return GRAB_OK;
+}
+
+}  // namespace grab
+
+using namespace grab;
+
+extern "C" {
+
+int grab_find_near_nodes(const float* d_dataset, uint64_t num_existing, const float* d_queries, uint64_t num_queries,
+                         const uint32_t* d_graph, uint32_t dim, uint32_t graph_degree, uint32_t search_k,
+                         grab_search_params params, int64_t* d_out_indices, float* d_out_dists) {
+  GRAB_REQUIRE(d_dataset && d_queries && d_graph && d_out_indices && d_out_dists, "find_near_nodes: null pointer");
+  grab_search_args a = insert_search_args(d_dataset, dim, num_existing, d_graph, graph_degree, d_queries, num_queries,
+                                          search_k, params, d_out_indices, d_out_dists, GRAB_METRIC_L2);
+  a.filter.kind = GRAB_FILTER_NONE;
+  GRAB_TRY(graph_search_impl(&a));
+  GRAB_CUDA_TRY(cudaDeviceSynchronize());
+  return GRAB_OK;
+}
+
+int grab_insert(const float* d_dataset, uint64_t num_existing, uint64_t num_new, const float* d_new_vectors,
+                uint32_t* d_graph, uint32_t dim, uint32_t graph_degree, grab_search_params params) {
+  return insert_v1_impl(d_dataset, num_existing, num_new, d_new_vectors, d_graph, dim, graph_degree, params,
+                        GRAB_METRIC_L2);
+}
+
+int grab_insert_opt(const float* d_dataset, uint32_t* d_graph, const uint64_t* d_ts, const uint32_t* d_seeds,
+                    uint64_t num_existing, uint64_t num_new, int use_heuristic, uint64_t target_ts,
+                    const float* d_queries, uint32_t dim, uint32_t total_degree, uint32_t local_degree,
+                    grab_search_params params, uint32_t num_seeds_per_query) {
+  (void)use_heuristic;  // the reference compiles a heuristic variant but never runs it (insert.cu:1425)
+  return insert_opt_impl(d_dataset, d_graph, d_ts, d_seeds, num_existing, num_new, target_ts, d_queries, dim,
+                         total_degree, local_degree, params, num_seeds_per_query, GRAB_METRIC_L2);
+}
+
+}  // extern "C"

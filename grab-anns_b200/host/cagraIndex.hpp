@@ -1,0 +1,72 @@
+// cagra::CagraIndex -- same public surface as the reference class (src/cagraIndex.hpp:12-119):
+// host pointers in and out, int64 ids, ascending distances.  Everything underneath goes
+// through the C ABI of libgrab_anns (include/grab_anns.h) to hand-written sm_100a kernels.
+// Failures surface as std::runtime_error (the reference exits the process on CUDA errors,
+// src/index/cagra.cuh:9-17, and throws for file / allocator errors).
+#pragma once
+#include <cstdint>
+#include <map>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "device_buffer.hpp"
+#include "grab_anns.h"
+
+namespace cagra {
+
+using BuildParams = grab_build_params;
+using SearchParams = grab_search_params;
+
+class CagraIndex {
+ public:
+  CagraIndex(uint32_t dim, uint32_t graph_degree = 64, size_t vmm_max_bytes = 20ULL * 1024 * 1024 * 1024);
+  ~CagraIndex();
+
+  void add(size_t num_vectors, const float* add_vectors, const uint64_t* add_timestamps = nullptr);
+  void build();
+  void insert(size_t new_vectors, const float* insert_vectors, const uint64_t* insert_timestamps = nullptr);
+  void query(const float* host_queries, size_t num_queries, int k, int64_t* host_indices, float* host_dists,
+             uint32_t* seeds = nullptr, size_t num_seeds_per_query = 0);
+  void query_range(const float* host_queries, size_t num_queries, int k, float range_radius, uint64_t start_ts,
+                   uint64_t end_ts, int64_t* host_indices, float* host_dists, uint32_t* seeds = nullptr,
+                   size_t num_seeds_per_query = 0);
+
+  void setBuildParams(uint32_t inter_degree, uint32_t graph_degree) {
+    build_params_.intermediate_degree = inter_degree;
+    build_params_.graph_degree = graph_degree;
+  }
+  void setQueryParams(uint32_t itopk_size, uint32_t search_width, uint32_t min_iterations, uint32_t max_iterations,
+                      uint32_t hash_bitlen) {
+    search_params_ = {itopk_size, search_width, min_iterations, max_iterations, hash_bitlen};
+  }
+  void* get_data() { return h_data_.data(); }
+  const uint32_t* get_graph();
+  void save(const std::string& filepath);
+  void load(const std::string& filepath);
+  size_t size() const { return h_data_.size() / dim_; }
+
+  // additions (not in the reference): metric, kNN precision of build(), reproducible seeds
+  void setMetric(int metric) { metric_ = metric; }
+  void setKnnPrecision(int precision) { knn_precision_ = precision; }
+  void setSeed(uint64_t seed) { seed_ = seed; }
+  void setInsertBatch(size_t batch) { insert_batch_ = batch ? batch : 64; }
+
+ private:
+  void upload_timestamps();
+  uint32_t dim_, graph_degree_;
+  size_t current_size_ = 0;
+  std::vector<float> h_data_;
+  std::vector<uint32_t> h_graph_;
+  std::map<uint64_t, std::vector<uint32_t>> ts_to_ids_;
+  std::vector<uint64_t> h_timestamps_;
+  bool ts_sorted_ = true;
+  std::unique_ptr<grab::DeviceBuffer> d_ts_, d_data_, d_graph_;
+  BuildParams build_params_;
+  SearchParams search_params_, insert_params_;
+  int metric_ = GRAB_METRIC_L2, knn_precision_ = GRAB_KNN_TC_SPLIT;
+  uint64_t seed_ = 0x9E3779B97F4A7C15ull;
+  size_t insert_batch_ = 64;  // the reference's batch (src/cagraIndex.cu:165)
+};
+
+}  // namespace cagra

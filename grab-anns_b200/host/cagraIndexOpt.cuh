@@ -1,0 +1,86 @@
+// cagra::CagraIndexOpt -- the time-partitioned index, same public surface as the reference
+// class (src/cagraIndexOpt.cuh:13-155): add / build / insert / query / query_local
+// (search_bucket) / query_range (search_range) / save / load.
+//
+// The reference equates "timestamp" with "bucket id" (one bucket per distinct timestamp,
+// src/cagraIndexOpt.cu:168-184).  Here the filter predicate runs on the raw timestamps and the
+// graph layout uses bucket = timestamp / bucket_width; with the default width 1 both coincide
+// with the reference.  query_range_batch takes one range per query (the reference takes one per
+// call).
+#pragma once
+#include <cstdint>
+#include <map>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "device_buffer.hpp"
+#include "grab_anns.h"
+
+namespace cagra {
+
+class CagraIndexOpt {
+ public:
+  CagraIndexOpt(uint32_t dim, uint32_t graph_degree = 32, uint32_t local_degree = 16,
+                size_t vmm_max_bytes = 20ULL * 1024 * 1024 * 1024);
+  ~CagraIndexOpt();
+
+  void add(size_t num_vectors, const float* add_vectors, const uint64_t* add_timestamps);
+  void build();
+  void insert(size_t new_vectors, const float* insert_vectors, const uint64_t* insert_timestamps);
+  void query(const float* host_queries, size_t num_queries, int k, uint64_t min_ts, uint64_t max_ts,
+             int64_t* host_indices, float* host_dists, const uint32_t* seeds = nullptr,
+             size_t num_seeds_per_query = 0);
+  void query_local(const float* host_queries, size_t num_queries, int k, uint64_t target_timestamp,
+                   int64_t* host_indices, float* host_dists, uint32_t local_degree);
+  void query_range(const float* host_queries, size_t num_queries, int k, uint64_t start_bucket, uint64_t end_bucket,
+                   int64_t* host_indices, float* host_dists, uint32_t local_degree);
+  // one [start, end) per query; timestamps, not bucket ids
+  void query_range_batch(const float* host_queries, size_t num_queries, int k, const uint64_t* start_ts,
+                         const uint64_t* end_ts, int64_t* host_indices, float* host_dists);
+
+  void setBuildParams(uint32_t inter_degree, uint32_t graph_degree) {
+    build_params_.intermediate_degree = inter_degree;
+    build_params_.graph_degree = graph_degree;
+  }
+  void setQueryParams(uint32_t itopk_size, uint32_t search_width, uint32_t min_iterations, uint32_t max_iterations,
+                      uint32_t hash_bitlen) {
+    search_params_ = {itopk_size, search_width, min_iterations, max_iterations, hash_bitlen};
+  }
+  const float* get_data() const { return h_data_.data(); }
+  uint32_t* get_graph();
+  std::vector<uint32_t> get_ids_by_timestamp(uint64_t ts) const;
+  size_t size() const { return current_size_; }
+  std::vector<uint32_t> sample_seeds_by_time(uint64_t min_ts, uint64_t max_ts, size_t num) const;
+  void save(const std::string& filepath);
+  void load(const std::string& filepath);
+
+  // additions (not in the reference)
+  void setBucketWidth(uint64_t width) { bucket_width_ = width ? width : 1; }
+  void setMetric(int metric) { metric_ = metric; }
+  void setKnnPrecision(int precision) { knn_precision_ = precision; }
+  void setSeed(uint64_t seed) { seed_ = seed; }
+  void setInsertBatch(size_t batch) { insert_batch_ = batch ? batch : 32; }
+
+ private:
+  uint64_t bucket_of(uint64_t ts) const { return ts / bucket_width_; }
+  void range_search(const float* host_queries, size_t nq, int k, const uint64_t* lo, const uint64_t* hi,
+                    uint64_t lo1, uint64_t hi1, int64_t* ids, float* dists);
+  uint32_t dim_, graph_degree_;
+  size_t current_size_ = 0;
+  std::vector<float> h_data_;
+  std::vector<uint32_t> h_graph_;
+  std::unique_ptr<grab::DeviceBuffer> d_data_, d_graph_, d_ts_, d_bucket_;
+  std::map<uint64_t, std::vector<uint32_t>> ts_to_ids_;  // bucket id -> ids
+  std::vector<uint64_t> h_timestamps_;
+  bool ts_sorted_ = true;
+  grab_build_params build_params_;
+  grab_search_params search_params_;
+  size_t local_degree_;
+  uint64_t bucket_width_ = 1;
+  int metric_ = GRAB_METRIC_L2, knn_precision_ = GRAB_KNN_TC_SPLIT;
+  uint64_t seed_ = 0x9E3779B97F4A7C15ull;
+  size_t insert_batch_ = 32;  // the reference's batch (src/cagraIndexOpt.cu:590)
+};
+
+}  // namespace cagra

@@ -236,6 +236,26 @@ int grab_update_topology_opt(uint32_t* d_graph, const uint64_t* d_bucket, int64_
                              uint64_t target_bucket, uint32_t total_degree, uint32_t local_degree,
                              uint32_t k_local, uint32_t k_global, void* stream);
 
+/* Neighbour search for new vectors over the first num_existing nodes: insert.cuh:38-60
+ * find_near_nodes (exact distances, ascending). */
+int grab_find_near_nodes(const float* d_dataset, uint64_t num_existing, const float* d_queries,
+                         uint64_t num_queries, const uint32_t* d_graph, uint32_t dim,
+                         uint32_t graph_degree, uint32_t search_k, grab_search_params params,
+                         int64_t* d_out_indices, float* d_out_dists);
+/* cagra.cuh:136-146 insert (v1): search_k = 2*degree search + v1 topology update.  The new
+ * vectors are rows [num_existing, num_existing+num_new) of d_dataset / d_graph. */
+int grab_insert(const float* d_dataset, uint64_t num_existing, uint64_t num_new,
+                const float* d_new_vectors, uint32_t* d_graph, uint32_t dim, uint32_t graph_degree,
+                grab_search_params params);
+/* cagra_opt.cuh:82-93 insert (time-partitioned): global search + bucket search from d_seeds
+ * [num_new, num_seeds_per_query] + exact kNN inside the batch, then the opt topology update.
+ * All new vectors belong to bucket target_ts; d_ts holds the bucket id of every vector. */
+int grab_insert_opt(const float* d_dataset, uint32_t* d_graph, const uint64_t* d_ts,
+                    const uint32_t* d_seeds, uint64_t num_existing, uint64_t num_new,
+                    int use_heuristic, uint64_t target_ts, const float* d_queries, uint32_t dim,
+                    uint32_t total_degree, uint32_t local_degree, grab_search_params params,
+                    uint32_t num_seeds_per_query);
+
 /* ------------------------------------------------------------------------------------ */
 /* Merge of `parts` ascending top-k lists per query into one (the exchange step of the   */
 /* id-sharded multi-GPU search; also merges the splits of the exact scan).  No reference */
