@@ -1,0 +1,125 @@
+// C handles over the index classes (include/grab_index.h).
+#include <cstring>
+#include <exception>
+
+#include "cagraIndex.hpp"
+#include "cagraIndexOpt.cuh"
+#include "common.cuh"
+#include "grab_index.h"
+#include "timeStampIndex.cuh"
+
+namespace {
+template <class F>
+int guarded(F&& f) {
+  try {
+    f();
+    return GRAB_OK;
+  } catch (const std::exception& e) {
+    grab::set_last_error("%s", e.what());
+    return GRAB_ERR_INVALID_ARGUMENT;
+  } catch (...) {
+    grab::set_last_error("unknown exception");
+    return GRAB_ERR_INVALID_ARGUMENT;
+  }
+}
+cagra::CagraIndexOpt* O(void* h) { return static_cast<cagra::CagraIndexOpt*>(h); }
+cagra::CagraIndex* I(void* h) { return static_cast<cagra::CagraIndex*>(h); }
+timestamp::TimeStampIndex* T(void* h) { return static_cast<timestamp::TimeStampIndex*>(h); }
+}  // namespace
+
+extern "C" {
+
+void* grab_index_opt_create(uint32_t dim, uint32_t graph_degree, uint32_t local_degree, size_t vmm_max_bytes) {
+  void* out = nullptr;
+  guarded([&] { out = new cagra::CagraIndexOpt(dim, graph_degree, local_degree, vmm_max_bytes); });
+  return out;
+}
+void grab_index_opt_destroy(void* h) { delete O(h); }
+int grab_index_opt_configure(void* h, uint64_t bucket_width, int metric, int knn_precision, uint64_t seed,
+                             size_t insert_batch) {
+  return guarded([&] {
+    O(h)->setBucketWidth(bucket_width); O(h)->setMetric(metric); O(h)->setKnnPrecision(knn_precision);
+    O(h)->setSeed(seed); O(h)->setInsertBatch(insert_batch);
+  });
+}
+int grab_index_opt_set_query_params(void* h, uint32_t itopk, uint32_t width, uint32_t min_iter, uint32_t max_iter,
+                                    uint32_t hash_bitlen) {
+  return guarded([&] { O(h)->setQueryParams(itopk, width, min_iter, max_iter, hash_bitlen); });
+}
+int grab_index_opt_add(void* h, size_t n, const float* v, const uint64_t* ts) { return guarded([&] { O(h)->add(n, v, ts); }); }
+int grab_index_opt_build(void* h) { return guarded([&] { O(h)->build(); }); }
+int grab_index_opt_insert(void* h, size_t n, const float* v, const uint64_t* ts) { return guarded([&] { O(h)->insert(n, v, ts); }); }
+int grab_index_opt_query(void* h, const float* q, size_t nq, int k, int64_t* ids, float* dists) {
+  return guarded([&] { O(h)->query(q, nq, k, 0, 0, ids, dists); });
+}
+int grab_index_opt_query_local(void* h, const float* q, size_t nq, int k, uint64_t target, int64_t* ids, float* dists) {
+  return guarded([&] { O(h)->query_local(q, nq, k, target, ids, dists, 0); });
+}
+int grab_index_opt_query_range(void* h, const float* q, size_t nq, int k, uint64_t s, uint64_t e, int64_t* ids, float* dists) {
+  return guarded([&] { O(h)->query_range(q, nq, k, s, e, ids, dists, 0); });
+}
+int grab_index_opt_query_range_batch(void* h, const float* q, size_t nq, int k, const uint64_t* s, const uint64_t* e,
+                                     int64_t* ids, float* dists) {
+  return guarded([&] { O(h)->query_range_batch(q, nq, k, s, e, ids, dists); });
+}
+int grab_index_opt_get_graph(void* h, uint32_t* out, size_t cap) {
+  return guarded([&] {
+    const uint32_t* g = O(h)->get_graph();
+    (void)g;
+    // the graph width is not stored in the handle API: copy what fits
+    memcpy(out, g, cap * sizeof(uint32_t));
+  });
+}
+size_t grab_index_opt_size(void* h) { return O(h)->size(); }
+int grab_index_opt_save(void* h, const char* p) { return guarded([&] { O(h)->save(p); }); }
+int grab_index_opt_load(void* h, const char* p) { return guarded([&] { O(h)->load(p); }); }
+
+void* grab_index_create(uint32_t dim, uint32_t graph_degree, size_t vmm_max_bytes) {
+  void* out = nullptr;
+  guarded([&] { out = new cagra::CagraIndex(dim, graph_degree, vmm_max_bytes); });
+  return out;
+}
+void grab_index_destroy(void* h) { delete I(h); }
+int grab_index_configure(void* h, int metric, int knn_precision, uint64_t seed, size_t insert_batch) {
+  return guarded([&] { I(h)->setMetric(metric); I(h)->setKnnPrecision(knn_precision); I(h)->setSeed(seed); I(h)->setInsertBatch(insert_batch); });
+}
+int grab_index_set_query_params(void* h, uint32_t itopk, uint32_t width, uint32_t min_iter, uint32_t max_iter,
+                                uint32_t hash_bitlen) {
+  return guarded([&] { I(h)->setQueryParams(itopk, width, min_iter, max_iter, hash_bitlen); });
+}
+int grab_index_add(void* h, size_t n, const float* v, const uint64_t* ts) { return guarded([&] { I(h)->add(n, v, ts); }); }
+int grab_index_build(void* h) { return guarded([&] { I(h)->build(); }); }
+int grab_index_insert(void* h, size_t n, const float* v, const uint64_t* ts) { return guarded([&] { I(h)->insert(n, v, ts); }); }
+int grab_index_query(void* h, const float* q, size_t nq, int k, int64_t* ids, float* dists) {
+  return guarded([&] { I(h)->query(q, nq, k, ids, dists); });
+}
+int grab_index_query_range(void* h, const float* q, size_t nq, int k, float radius, uint64_t s, uint64_t e, int64_t* ids,
+                           float* dists) {
+  return guarded([&] { I(h)->query_range(q, nq, k, radius, s, e, ids, dists); });
+}
+int grab_index_get_graph(void* h, uint32_t* out, size_t cap) {
+  return guarded([&] { memcpy(out, I(h)->get_graph(), cap * sizeof(uint32_t)); });
+}
+size_t grab_index_size(void* h) { return I(h)->size(); }
+int grab_index_save(void* h, const char* p) { return guarded([&] { I(h)->save(p); }); }
+int grab_index_load(void* h, const char* p) { return guarded([&] { I(h)->load(p); }); }
+
+void* grab_tsindex_create(uint32_t dim, uint32_t degree, size_t cluster_ratio) {
+  void* out = nullptr;
+  guarded([&] { out = new timestamp::TimeStampIndex(dim, degree, cluster_ratio); });
+  return out;
+}
+void grab_tsindex_destroy(void* h) { delete T(h); }
+int grab_tsindex_insert(void* h, const float* v, const uint64_t* ts, size_t n, uint64_t* first_id) {
+  return guarded([&] { const uint64_t id = T(h)->insert(v, ts, n); if (first_id) *first_id = id; });
+}
+int grab_tsindex_build_virtual_index(void* h) { return guarded([&] { T(h)->build_virtual_index(); }); }
+int grab_tsindex_query(void* h, const float* q, size_t topk, int64_t* ids, float* dists, int probe) {
+  return guarded([&] { T(h)->query(q, topk, ids, dists, probe); });
+}
+int grab_tsindex_query_by_timestamp(void* h, const float* q, size_t topk, uint64_t ts, int64_t* ids, float* dists) {
+  return guarded([&] { T(h)->query_by_timestamp(q, topk, ts, ids, dists); });
+}
+size_t grab_tsindex_size(void* h) { return T(h)->size(); }
+
+}  // extern "C"
