@@ -46,6 +46,9 @@ def parse():
                     help="0 exact scan, 1 bf16 tensor cores (exact for integer-valued data), 2 split bf16")
     ap.add_argument("--cpu-sample", type=int, default=0, help="queries in the CPU sample (0 = auto)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sharded", action="store_true",
+                    help="stripe the index by id across the ranks (all_gather + device merge of the per-shard "
+                         "top-k) instead of replicating it")
     return ap.parse_args()
 
 
@@ -172,7 +175,9 @@ def workload_config(args, w):
             "buckets": args.buckets, "selectivity": args.selectivity, "itopk": args.itopk,
             "search_width": args.width, "max_iterations": args.max_iter, "hash_bitlen": args.hash_bitlen,
             "l2": "inputs (dataset + graph, 768 MB at full size) exceed the 126 MB L2",
-            "parallelism": "one process per GPU, index replica per rank, queries partitioned"}
+            "parallelism": ("one process per GPU, index striped by id across the ranks, queries broadcast, "
+                            "all_gather + device merge of per-shard top-k") if getattr(args, "sharded", False) else
+                           "one process per GPU, index replica per rank, queries partitioned"}
 
 
 def main():
@@ -196,8 +201,14 @@ def main():
     base, queries = w["base"], w["queries"]
     n, dim = base.shape
     k, deg = w["k"], w["degree"]
+    sharded = importlib.import_module("grab-anns_b200.sharded")
+    if args.sharded:
+        # id-striped shard of this rank; the same queries on every rank
+        base = np.ascontiguousarray(sharded.stripe(base, rank, world))
+        w["ts"] = np.ascontiguousarray(sharded.stripe(w["ts"], rank, world))
+        n = base.shape[0]
     # each rank answers its own, different slice of the query stream (same size on every rank)
-    if world > 1:
+    if world > 1 and not args.sharded:
         ds = importlib.import_module("grab-anns_b200.datasets")
         queries = np.roll(queries, rank * 997, axis=0)
         w["lo"], w["hi"] = ds.range_queries(queries.shape[0], n, max(1, int(n * args.selectivity)), 2003 + rank)
@@ -205,9 +216,11 @@ def main():
 
     d_base = torch.from_numpy(base).cuda()
     d_ts = torch.from_numpy(w["ts"].view(np.int64)).cuda()
-    bsize = (n + args.buckets - 1) // args.buckets
-    sizes = [min(bsize, n - b * bsize) for b in range(args.buckets) if b * bsize < n]
-    d_bucket = torch.from_numpy((w["ts"] // np.uint64(bsize)).view(np.int64)).cuda()
+    n_total = n * world if args.sharded else n
+    bsize = (n_total + args.buckets - 1) // args.buckets       # bucket width in timestamps
+    h_bucket = w["ts"] // np.uint64(bsize)
+    sizes = np.bincount(h_bucket.astype(np.int64)).tolist()    # timestamps are sorted: buckets are id runs
+    d_bucket = torch.from_numpy(h_bucket.view(np.int64)).cuda()
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     graph = grab.build_time_partitioned_graph(d_base, d_bucket, sizes, deg, args.local_degree, metric=w["metric"],
@@ -228,10 +241,20 @@ def main():
     ws = torch.empty(grab.lib().grab_graph_search_workspace_bytes(nq, args.hash_bitlen), dtype=torch.uint8,
                      device="cuda")
 
+    id_scale, id_offset = (world, rank) if args.sharded else (1, 0)
+    merge = lambda d, i, kk: grab.merge_topk(d, i, kk)
     # ground truth from the exact filtered kernel (bit-exact against the CPU oracle in tests/)
-    gt_ids, _ = grab.exact_search(d_base, d_q, k, metric=w["metric"], flt=flt)
-    ids, _, stats = grab.graph_search(d_base, graph, d_q, k, params, metric=w["metric"], flt=flt, stats=True,
-                                      out=(out_ids, out_d), ws=ws)
+    gt_ids, gt_d = grab.exact_search(d_base, d_q, k, metric=w["metric"], flt=flt)
+    ids, dd, stats = grab.graph_search(d_base, graph, d_q, k, params, metric=w["metric"], flt=flt, stats=True,
+                                       out=(out_ids, out_d), ws=ws, id_scale=id_scale, id_offset=id_offset)
+    if args.sharded:
+        gt_ids = torch.where(gt_ids >= 0, gt_ids * world + rank, gt_ids)
+        gt_ids, _ = sharded.gather_and_merge(gt_d, gt_ids, k, merge)
+        ids, _ = sharded.gather_and_merge(dd, ids, k, merge)
+        st = torch.tensor([stats.iterations, stats.parents, stats.edges, stats.distances, stats.seeds,
+                           stats.hash_resets], device="cuda", dtype=torch.int64)
+        dist.all_reduce(st) if dist is not None else None
+        stats = grab.SearchStats(*st.cpu().tolist())
     gt = gt_ids.cpu().numpy()
     res = ids.cpu().numpy()
     hit = 0
@@ -241,12 +264,17 @@ def main():
         hit += np.intersect1d(r, g).size
         denom += g.size
     recall = hit / max(denom, 1)
+    # timestamps equal global ids in this workload
     in_range = bool(np.all(((res >= w["lo"][:, None].astype(np.int64)) & (res < w["hi"][:, None].astype(np.int64)))
                            | (res < 0)))
-    alg_bytes = grab.search_bytes(stats, nq, dim, deg, k, 0)  # sorted timestamps: id-window predicate, no gather
+    # sorted timestamps: id-window predicate, no gather (f = 0); sharded: every rank reads every query
+    alg_bytes = grab.search_bytes(stats, nq * (world if args.sharded else 1), dim, deg, k, 0)
 
     def step():
-        grab.graph_search(d_base, graph, d_q, k, params, metric=w["metric"], flt=flt, out=(out_ids, out_d), ws=ws)
+        grab.graph_search(d_base, graph, d_q, k, params, metric=w["metric"], flt=flt, out=(out_ids, out_d), ws=ws,
+                          id_scale=id_scale, id_offset=id_offset)
+        if args.sharded:
+            sharded.gather_and_merge(out_d, out_ids, k, merge)
 
     def e2e_step():
         d_q.copy_(h_q, non_blocking=True)
@@ -301,15 +329,16 @@ def main():
         peak = float(peaks.get("hbm_gbs", 6650.0))
         achieved = alg_bytes / (ms / 1e3) / 1e9
         line = {
-            "metric": "filtered QPS at recall@10>=0.95", "value": world * nq / (ms / 1e3), "unit": "queries/s",
+            "metric": "filtered QPS at recall@10>=0.95",
+            "value": (1 if args.sharded else world) * nq / (ms / 1e3), "unit": "queries/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic", "config": workload_config(args, w),
+            "higher_is_better": True, "scaling": "strong" if args.sharded else "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "config": workload_config(args, w),
             "recall_at_10": recall, "results_in_range": in_range,
             "build": {"seconds": build_s, "mvec_per_s": n / build_s / 1e6, "knn_precision": args.knn_precision},
-            "e2e": {"value": world * nq / (ms_e2e / 1e3), "unit": "queries/s",
+            "e2e": {"value": (1 if args.sharded else world) * nq / (ms_e2e / 1e3), "unit": "queries/s",
                     "h2d_bytes_per_step": int(h_q.numel() * 4 + 16 * nq), "d2h_bytes_per_step": int(12 * nq * k)},
-            "gpu_launches": 2 * args.steps,
+            "gpu_launches": (4 if args.sharded and world > 1 else 2) * args.steps,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": None,
                          "peak_source": "measured" if peaks else "fallback",
