@@ -103,6 +103,18 @@ int grab_exact_search(const float* d_dataset, uint64_t n, uint32_t dim, int metr
                       int64_t* d_out_ids, float* d_out_dists, void* d_ws, size_t ws_bytes,
                       void* stream);
 
+/* Same scan for callers that must not allocate (a serving loop that cannot afford the device
+ * synchronisation of cudaMalloc/cudaFree, a host whose memory pool already owns the GPU): the
+ * scratch is a fixed GRAB_NOALLOC_SCRATCH_BYTES array inside the library, held by every GPU that
+ * loads it.  Requests needing more (grab_exact_search_workspace_bytes) fail with
+ * GRAB_ERR_WORKSPACE.  All calls on a device share the array: calls that overlap on the GPU
+ * race.  The first call on a device resolves the array's address; make it before any stream
+ * capture.  This entry point has no counterpart in the reference. */
+#define GRAB_NOALLOC_SCRATCH_BYTES (8u << 20)
+int grab_exact_search_noalloc(const float* d_dataset, uint64_t n, uint32_t dim, int metric,
+                              const grab_filter* filter, const float* d_queries, uint64_t nq,
+                              uint32_t k, int64_t* d_out_ids, float* d_out_dists, void* stream);
+
 /* ------------------------------------------------------------------------------------ */
 /* Filtered graph search.  One entry point for the reference's three launchers           */
 /* (src/index/cagra_opt.cuh:33-80: search_opt, search_bucket_opt, search_bucket_range;   */
