@@ -1,5 +1,7 @@
 // extern "C" entry points of libgrab_anns.so and the build orchestration behind them.
+#include <chrono>
 #include <cstdarg>
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -14,6 +16,32 @@ void set_last_error(const char* fmt, ...) {
   va_start(ap, fmt);
   vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
   va_end(ap);
+}
+
+static int g_trace = -1;
+int trace_level() {
+  if (g_trace < 0) {
+    const char* e = getenv("GRAB_TRACE");
+    g_trace = e ? atoi(e) : 0;
+  }
+  return g_trace;
+}
+static double now_s() {
+  return std::chrono::duration<double>(std::chrono::steady_clock::now().time_since_epoch()).count();
+}
+StageTimer::StageTimer(const char* s) : scope(s) {
+  if (trace_level() > 0) {
+    cudaDeviceSynchronize();
+    t0 = now_s();
+  }
+}
+void StageTimer::mark(const char* stage) {
+  if (trace_level() > 0) {
+    cudaDeviceSynchronize();
+    const double t = now_s();
+    fprintf(stderr, "[grab trace] %-28s %-22s %9.3f ms\n", scope, stage, (t - t0) * 1e3);
+    t0 = t;
+  }
 }
 
 // implemented in the kernel translation units
@@ -57,13 +85,17 @@ static int knn_dispatch(const float* d_dataset, uint64_t n, uint32_t dim, int me
 // prune -> reverse -> merge over a device kNN graph (cagra.cu:665-711 without the host hops)
 static int optimize_pipeline(const uint32_t* d_knn, uint32_t* d_graph, uint64_t n, uint32_t in_deg,
                              uint32_t deg, cudaStream_t st) {
+  StageTimer tm("optimize");
   ScopedDeviceBuffer rev, cnt;
   GRAB_CUDA_TRY(rev.alloc(sizeof(uint32_t) * n * deg));
   GRAB_CUDA_TRY(cnt.alloc(sizeof(uint32_t) * n));
   GRAB_TRY(prune_device_impl(d_knn, d_graph, n, in_deg, deg, nullptr, st));
+  tm.mark("prune");
   GRAB_TRY(reverse_device_impl(d_graph, rev.as<uint32_t>(), cnt.as<uint32_t>(), n, deg, st));
+  tm.mark("reverse");
   GRAB_TRY(merge_device_impl(d_graph, rev.as<uint32_t>(), cnt.as<uint32_t>(), n, deg, st));
   GRAB_CUDA_TRY(cudaStreamSynchronize(st));
+  tm.mark("merge");
   return GRAB_OK;
 }
 
@@ -74,6 +106,7 @@ using namespace grab;
 extern "C" {
 
 int grab_abi_version(void) { return GRAB_ABI_VERSION; }
+void grab_set_trace(int level) { g_trace = level; }
 
 const char* grab_status_string(int status) {
   switch (status) {
@@ -275,12 +308,15 @@ int grab_build_time_partitioned_graph(const float* d_dataset, uint64_t total_num
   // prune / reverse / merge to total_degree.  Edges never leave a bucket, so one pass over
   // all N is the same as the reference's per-bucket passes.
   const uint32_t inter = 2 * total_degree;
+  StageTimer tm("time_partitioned_build");
   {
     ScopedDeviceBuffer knn;
     GRAB_CUDA_TRY(knn.alloc(sizeof(uint32_t) * total_num * inter));
     GRAB_TRY(knn_dispatch(d_dataset, total_num, dim, metric, offs.data(), num_buckets, inter, 0,
                           inter <= 204 ? knn_precision : GRAB_KNN_EXACT_SCAN, knn.as<uint32_t>(), nullptr, nullptr));
+    tm.mark("local kNN");
     GRAB_TRY(optimize_pipeline(knn.as<uint32_t>(), d_graph, total_num, inter, total_degree, nullptr));
+    tm.mark("prune+reverse+merge");
   }
   if (local_degree == total_degree || num_buckets == 1) return GRAB_OK;
   // Global phase (cagra_opt.cu:796-907): candidates from other buckets, ascending exact
@@ -295,9 +331,11 @@ int grab_build_time_partitioned_graph(const float* d_dataset, uint64_t total_num
     GRAB_CUDA_TRY(cand.alloc(sizeof(uint32_t) * total_num * gk));
     GRAB_TRY(knn_dispatch(d_dataset, total_num, dim, metric, offs.data(), num_buckets, gk, 1,
                           gk <= 204 ? knn_precision : GRAB_KNN_EXACT_SCAN, cand.as<uint32_t>(), nullptr, nullptr));
+    tm.mark("global candidates");
     GRAB_TRY(remote_edges_impl(d_graph, d_bucket, cand.as<uint32_t>(), total_num, total_degree, local_degree,
                                gk, nullptr));
     GRAB_TRY(inject_reverse_impl(d_graph, total_num, total_degree, local_degree, 32, nullptr));
+    tm.mark("remote edges + inject");
   }
   GRAB_CUDA_TRY(cudaDeviceSynchronize());
   return GRAB_OK;

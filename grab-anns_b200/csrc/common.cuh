@@ -152,6 +152,18 @@ inline uint32_t next_pow2(uint32_t v) {
   return v + 1;
 }
 
+// Stage timing for the multi-stage host pipelines (build, insert).  Off by default; enabled by
+// grab_set_trace(1) or the environment variable GRAB_TRACE=1.  Each mark synchronises the
+// device and prints the time since the previous mark to stderr.  The reference has
+// std::chrono stage timers of the same kind (cagra_opt.cu:1700,1848,1935,1962-1972).
+int trace_level();
+struct StageTimer {
+  const char* scope;
+  double t0 = 0.0;
+  explicit StageTimer(const char* s);
+  void mark(const char* stage);
+};
+
 // Scratch allocation used by the stateless entry points when the caller passes no
 // workspace: plain cudaMalloc, released on scope exit.
 struct ScopedDeviceBuffer {

@@ -552,6 +552,7 @@ int knn_tc_impl(const float* d_dataset, uint64_t n, uint32_t dim, int metric, co
   GRAB_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   const uint32_t grid = num_row_tiles < static_cast<uint32_t>(sms) ? num_row_tiles : static_cast<uint32_t>(sms);
 
+  StageTimer tm(mode == 0 ? "knn_tc (own block)" : "knn_tc (other blocks)");
   ScopedDeviceBuffer offs, wins, a_op, b_op, norm, mean, partial, scratch, keys, status;
   GRAB_CUDA_TRY(offs.alloc(sizeof(uint64_t) * (num_blocks + 1)));
   GRAB_CUDA_TRY(wins.alloc(sizeof(ScanWindow) * n));
@@ -582,6 +583,7 @@ int knn_tc_impl(const float* d_dataset, uint64_t n, uint32_t dim, int metric, co
                                                                       pb, norm.as<float>());
   GRAB_CUDA_TRY(cudaGetLastError());
 
+  tm.mark("alloc + operands");
   CUtensorMap map_a, map_b;
   int rc = make_map(&map_a, pa, n, kp);
   if (rc != GRAB_OK) return rc;
@@ -601,6 +603,7 @@ int knn_tc_impl(const float* d_dataset, uint64_t n, uint32_t dim, int metric, co
                                                    status.as<int>());
   }
   GRAB_CUDA_TRY(cudaGetLastError());
+  tm.mark("tcgen05 all-pairs + top-k");
   const size_t rsmem = sizeof(uint64_t) * kc + sizeof(float) * dim;
   if (metric == GRAB_METRIC_L2)
     rerank_kernel<GRAB_METRIC_L2><<<(unsigned)n, kRerankThreads, rsmem, st>>>(d_dataset, dim, keys.as<uint64_t>(), kc, k,
@@ -609,6 +612,7 @@ int knn_tc_impl(const float* d_dataset, uint64_t n, uint32_t dim, int metric, co
     rerank_kernel<GRAB_METRIC_IP><<<(unsigned)n, kRerankThreads, rsmem, st>>>(d_dataset, dim, keys.as<uint64_t>(), kc, k,
                                                                            d_out_knn, d_out_dists);
   GRAB_CUDA_TRY(cudaGetLastError());
+  tm.mark("exact re-rank");
   int h_status = 0;
   GRAB_CUDA_TRY(cudaMemcpyAsync(&h_status, status.ptr, sizeof(int), cudaMemcpyDeviceToHost, st));
   GRAB_CUDA_TRY(cudaStreamSynchronize(st));

@@ -90,6 +90,9 @@ typedef struct grab_search_stats {
 int grab_abi_version(void);
 const char* grab_status_string(int status);
 const char* grab_last_error(void);
+/* Stage timers of the build / insert pipelines to stderr (also GRAB_TRACE=1 in the environment);
+ * the reference prints std::chrono stage times the same way (cagra_opt.cu:1962-1972). */
+void grab_set_trace(int level);
 
 /* ------------------------------------------------------------------------------------ */
 /* Exact filtered brute force on the GPU: tests/test_cagra_auto.cu:57-89                 */
