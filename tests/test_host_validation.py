@@ -1,0 +1,76 @@
+"""Failure paths that never reach the GPU: every entry point validates its arguments on the host
+and answers with a status and a message instead of exiting (the reference calls exit(1) on CUDA
+errors, src/index/cagra.cuh:9-17, and prints from the device for unsupported shapes)."""
+import ctypes as C
+import importlib
+
+import numpy as np
+import pytest
+
+
+@pytest.fixture(scope="module")
+def lib():
+    grab = importlib.import_module("grab-anns_b200")
+    grab.build()
+    return grab.lib()
+
+
+def _err(lib):
+    return lib.grab_last_error().decode()
+
+
+def test_null_and_shape_errors_return_status(lib):
+    null = None
+    one = C.c_void_p(16)          # a non-null dummy: validation fails before it is dereferenced
+    assert lib.grab_exact_search(null, C.c_uint64(10), 8, 0, null, null, C.c_uint64(1), 1, null, null, null,
+                                 C.c_size_t(0), null) == 1
+    assert "null pointer" in _err(lib)
+    assert lib.grab_exact_search(one, C.c_uint64(10), 6, 0, null, one, C.c_uint64(1), 1, one, one, null,
+                                 C.c_size_t(0), null) == 1
+    assert "multiple of 4" in _err(lib)
+    assert lib.grab_exact_search(one, C.c_uint64(10), 8, 0, null, one, C.c_uint64(1), 5000, one, one, null,
+                                 C.c_size_t(0), null) == 1
+    assert lib.grab_exact_search(one, C.c_uint64(10), 8, 7, null, one, C.c_uint64(1), 5, one, one, null,
+                                 C.c_size_t(0), null) == 1
+    assert "metric" in _err(lib)
+    assert lib.grab_graph_search(null) == 1
+    assert lib.grab_optimize_prune_device(null, null, C.c_uint64(4), 8, 4, null, null) == 1
+    assert lib.grab_optimize_prune_device(one, one, C.c_uint64(4), 600, 4, null, null) == 1     # > 512, as the reference
+    assert "512" in _err(lib)
+    assert lib.grab_optimize_prune_device(one, one, C.c_uint64(4), 8, 9, null, null) == 1       # out > in
+    assert lib.grab_merge_topk(one, one, C.c_uint64(4), 100, 100, one, one, null) == 1          # parts*k > 8192
+    assert lib.grab_update_topology_opt(one, one, one, one, C.c_uint64(4), C.c_uint64(1), C.c_uint64(0), 8, 8, 4, 4,
+                                        null) == 1
+    offs = np.array([0, 5], dtype=np.uint64)
+    assert lib.grab_knn_graph_blocks(one, C.c_uint64(10), 8, 0, C.c_void_p(offs.ctypes.data), 1, 4, 0, 0, one, null,
+                                     null) == 1
+    assert "span" in _err(lib)
+    assert lib.grab_knn_graph_blocks(one, C.c_uint64(5), 8, 0, C.c_void_p(offs.ctypes.data), 1, 300, 0, 1, one, null,
+                                     null) == 1                                                 # k too wide for the tensor-core path
+    assert lib.grab_build_time_partitioned_graph(one, C.c_uint64(10), 8, 0, one, one, C.c_void_p(offs.ctypes.data), 2,
+                                                 2, 2, 0) == 1
+    assert lib.grab_exact_search_noalloc(one, C.c_uint64(10), 8, 0, null, one, C.c_uint64(10**7), 10, one, one,
+                                         null) == 4                                             # scratch too small
+    assert lib.grab_status_string(4) == b"workspace too small"
+
+
+def test_search_argument_checks(lib):
+    grab = importlib.import_module("grab-anns_b200")
+    a = grab.SearchArgs()
+    a.d_dataset = a.d_graph = a.d_queries = a.d_out_ids = a.d_out_dists = 16
+    a.n, a.dim, a.graph_degree, a.nq, a.k = 100, 8, 4, 1, 2
+    a.params = grab.SearchParams(64, 4, 0, 10, 30)
+    assert lib.grab_graph_search(C.byref(a)) == 1 and "hash_bitlen" in _err(lib)
+    a.params = grab.SearchParams(64, 0, 0, 10, 12)
+    assert lib.grab_graph_search(C.byref(a)) == 1 and "search_width" in _err(lib)
+    a.params = grab.SearchParams(64, 4, 0, 10, 12)
+    a.filter.kind = grab.FILTER_TS_RANGE
+    assert lib.grab_graph_search(C.byref(a)) == 1 and "d_ts" in _err(lib)
+    a.filter.kind = grab.FILTER_PREFIX
+    a.filter.active_degree = 9
+    assert lib.grab_graph_search(C.byref(a)) == 1 and "active_degree" in _err(lib)
+    a.filter.kind = 42
+    assert lib.grab_graph_search(C.byref(a)) == 1
+    a.filter.kind = grab.FILTER_NONE
+    a.n = 1 << 31
+    assert lib.grab_graph_search(C.byref(a)) == 1 and "2^31" in _err(lib)
