@@ -12,13 +12,15 @@
 // pipeline stage.  "Split" precision stores every value as hi+lo bf16 and concatenates
 // [hi,lo,hi].[hi,hi,lo] along K, which recovers ~fp32 products at 3x the MMA work.
 //
-// One persistent CTA per SM, 6 warps:
-//   warp 0   TMA producer   (cp.async.bulk.tensor 2D, 128B swizzle, 4-stage ring, mbarriers)
+// Persistent CTAs, two per SM, 6 warps each:
+//   warp 0   TMA producer   (cp.async.bulk.tensor 2D, 128B swizzle, 3-stage ring, mbarriers)
 //   warp 1   MMA issuer     (one lane issues tcgen05.mma; tcgen05.commit frees ring stages and
 //                            publishes the accumulator; owns the TMEM allocation)
-//   warps 2-5 epilogue      (tcgen05.ld of a double-buffered 128x128 fp32 accumulator; thread r
-//                            owns row r: threshold test, append to the row's candidate buffer;
-//                            a full buffer is bitonic-sorted by the warp and cut back to KC)
+//   warps 2-5 epilogue      (tcgen05.ld of a double-buffered 128x128 fp32 accumulator, the next
+//                            32 columns in flight while the current 32 are tested; thread r owns
+//                            row r: branch-free threshold mask, rare appends to the row's
+//                            candidate buffer; a full buffer is cut back to its KC smallest by a
+//                            warp-cooperative radix select -- no sort)
 // Every mbarrier wait is bounded; on expiry the kernel raises a flag, all roles leave their
 // loops, TMEM is released and the host sees GRAB_ERR_TIMEOUT.
 #include <cuda.h>
@@ -32,7 +34,8 @@ namespace grab {
 namespace tc {
 
 constexpr int BM = 128, BN = 128, BK = 64;  // BK bf16 = one 128-byte swizzle row
-constexpr int STAGES = 4;
+constexpr int STAGES = 3;
+constexpr int CTAS_PER_SM = 2;
 constexpr int STAGE_BYTES = (BM + BN) * BK * 2;  // 32 KB
 constexpr int THREADS = 192;
 constexpr uint32_t kSpinLimit = 1u << 22;
@@ -100,7 +103,9 @@ __device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t desc_a, ui
       ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+// Asynchronous TMEM load of 32 columns x 32 lanes; the registers are valid only after
+// tmem_ld_wait on the same array.
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&v)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -111,7 +116,17 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
         "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
       : "r"(taddr)
       : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+// Waits for all TMEM loads of this thread; naming the registers as in/out operands keeps
+// the compiler from moving their uses above the wait.
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&v)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
+                 "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]),
+                 "+r"(v[16]), "+r"(v[17]), "+r"(v[18]), "+r"(v[19]), "+r"(v[20]), "+r"(v[21]), "+r"(v[22]), "+r"(v[23]),
+                 "+r"(v[24]), "+r"(v[25]), "+r"(v[26]), "+r"(v[27]), "+r"(v[28]), "+r"(v[29]), "+r"(v[30]), "+r"(v[31])
+               :
+               : "memory");
 }
 
 // Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128
@@ -129,40 +144,15 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
 constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((BN >> 3) << 17) | ((BM >> 4) << 24);
 
 // ------------------------------------------------------------------ epilogue helpers
-template <int NREG>
-__device__ __forceinline__ void warp_bitonic_sort_u64(uint64_t (&k)[NREG], uint32_t lane) {
-  // element g = j*32 + lane; ascending over all 32*NREG elements
-  constexpr uint32_t total = 32 * NREG;
-#pragma unroll
-  for (uint32_t size = 2; size <= total; size <<= 1) {
-#pragma unroll
-    for (uint32_t stride = size >> 1; stride > 0; stride >>= 1) {
-      if (stride >= 32) {
-        const uint32_t js = stride >> 5;
-#pragma unroll
-        for (uint32_t j = 0; j < NREG; ++j) {
-          if ((j & js) == 0) {
-            const uint32_t g = j * 32 + lane;
-            const bool up = (g & size) == 0;
-            const uint64_t a = k[j], b = k[j | js];
-            if ((a > b) == up) { k[j] = b; k[j | js] = a; }
-          }
-        }
-      } else {
-#pragma unroll
-        for (uint32_t j = 0; j < NREG; ++j) {
-          const uint64_t other = __shfl_xor_sync(0xFFFFFFFFu, k[j], stride);
-          const uint32_t g = j * 32 + lane;
-          const bool up = (g & size) == 0;
-          const bool lower = (lane & stride) == 0;
-          const bool keep_min = (lower == up);
-          const uint64_t mn = k[j] < other ? k[j] : other;
-          const uint64_t mx = k[j] < other ? other : k[j];
-          k[j] = keep_min ? mn : mx;
-        }
-      }
-    }
-  }
+// Bits i of a 32-column chunk starting at `cbase` whose column lies in [lo, hi).
+__device__ __forceinline__ uint32_t range_bits(uint32_t cbase, uint32_t lo, uint32_t hi) {
+  uint32_t a = lo > cbase ? lo - cbase : 0u, b = hi > cbase ? hi - cbase : 0u;
+  if (a > 32u) a = 32u;
+  if (b > 32u) b = 32u;
+  if (b <= a) return 0u;
+  const uint32_t upto_b = b >= 32u ? 0xFFFFFFFFu : ((1u << b) - 1u);
+  const uint32_t upto_a = (1u << a) - 1u;  // a < 32 here
+  return upto_b & ~upto_a;
 }
 
 struct TileRange {
@@ -199,11 +189,12 @@ struct SharedCtl {
   uint64_t full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2];
   uint32_t tmem_base;
   int abort_flag;
-  float ynorm[4][BN];  // one staging row per epilogue warp
+  float ynorm[4][BN];       // one staging row per epilogue warp
+  uint32_t hist[4][256];    // radix-select histogram per epilogue warp
 };
 
 template <int KC>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS, CTAS_PER_SM)
 knn_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
               const float* __restrict__ ynorm, const ScanWindow* __restrict__ windows, uint64_t n,
               uint32_t kblocks, uint32_t num_row_tiles, uint64_t* __restrict__ scratch,
@@ -313,9 +304,17 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     uint32_t tile = 0;
     bool ok = true;
 
+    uint32_t* hist = ctl->hist[warp - 2];
+    const uint32_t lt_mask = (1u << lane) - 1u;
+
+    // Cut the buffers of the rows that are (nearly) full back to their KC smallest keys and
+    // tighten the rows' thresholds.  Warp-cooperative, one row at a time: the row's keys sit in
+    // registers (element g = j*32 + lane), a 4-pass radix select on the ordered distance finds
+    // the KC-th smallest value, a ballot compaction writes the survivors back.  No ordering is
+    // produced: the exact re-rank sorts later.
     auto compress = [&](uint32_t& cnt, float& thr, bool force) {
       __syncwarp();
-      uint32_t need = __ballot_sync(0xFFFFFFFFu, force || cnt > CAP - 32);
+      uint32_t need = __ballot_sync(0xFFFFFFFFu, force ? (cnt > KC) : (cnt > CAP - 32));
       while (need) {
         const int src = __ffs(need) - 1;
         need &= need - 1;
@@ -327,13 +326,63 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
           const uint32_t g = j * 32 + lane;
           k[j] = g < c_src ? rb[g] : kMaxKey;
         }
-        warp_bitonic_sort_u64<NREG>(k, lane);
+        uint32_t prefix = 0, hi_mask = 0, want = KC;
+#pragma unroll 1
+        for (int pass = 0; pass < 4; ++pass) {
+          const uint32_t shift = 24 - 8 * pass;
+          for (uint32_t b = lane; b < 256; b += 32) hist[b] = 0;
+          __syncwarp();
 #pragma unroll
-        for (int j = 0; j < KC / 32; ++j) rb[j * 32 + lane] = k[j];
-        const uint64_t kth = __shfl_sync(0xFFFFFFFFu, k[KC / 32 - 1], 31);
+          for (int j = 0; j < NREG; ++j) {
+            const uint32_t o = static_cast<uint32_t>(k[j] >> 32);
+            if (j * 32 + lane < c_src && ((o ^ prefix) & hi_mask) == 0) atomicAdd(&hist[(o >> shift) & 255u], 1u);
+          }
+          __syncwarp();
+          uint32_t local[8], sum = 0;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) { local[i] = hist[lane * 8 + i]; sum += local[i]; }
+          uint32_t incl = sum;
+#pragma unroll
+          for (int off = 1; off < 32; off <<= 1) {
+            const uint32_t t = __shfl_up_sync(0xFFFFFFFFu, incl, off);
+            if (static_cast<int>(lane) >= off) incl += t;
+          }
+          const uint32_t excl = incl - sum;
+          const bool mine = excl < want && want <= incl;
+          uint32_t digit = 0, before = 0;
+          if (mine) {
+            uint32_t run = excl;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              if (run + local[i] >= want) { digit = lane * 8 + i; before = run; break; }
+              run += local[i];
+            }
+          }
+          const uint32_t owner = __ffs(__ballot_sync(0xFFFFFFFFu, mine)) - 1;  // exactly one lane: want <= c_src
+          digit = __shfl_sync(0xFFFFFFFFu, digit, owner & 31);
+          before = __shfl_sync(0xFFFFFFFFu, before, owner & 31);
+          want -= before;
+          prefix |= digit << shift;
+          hi_mask |= 0xFFu << shift;
+          __syncwarp();
+        }
+        // `prefix` = ordered distance of the KC-th smallest key, `want` of the keys equal to it stay
+        uint32_t base = 0, eq_seen = 0;
+#pragma unroll
+        for (int j = 0; j < NREG; ++j) {
+          const uint32_t o = static_cast<uint32_t>(k[j] >> 32);
+          const bool valid = j * 32 + lane < c_src;
+          const bool eq = valid && o == prefix;
+          const uint32_t eqm = __ballot_sync(0xFFFFFFFFu, eq);
+          const bool take = (valid && o < prefix) || (eq && eq_seen + __popc(eqm & lt_mask) < want);
+          eq_seen += __popc(eqm);
+          const uint32_t tm = __ballot_sync(0xFFFFFFFFu, take);
+          if (take) rb[base + __popc(tm & lt_mask)] = k[j];
+          base += __popc(tm);
+        }
         if (static_cast<int>(lane) == src) {
-          cnt = c_src < KC ? c_src : KC;
-          thr = c_src >= KC ? key_dist(kth) : __int_as_float(0x7f800000);
+          cnt = KC;
+          thr = ordered_to_float(prefix);
         }
       }
       __syncwarp();
@@ -362,27 +411,61 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         if (!mbar_wait(smem_u32(&ctl->tmem_full[acc]), acc_phase, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const bool need_mask = !(c0 >= t.safe_lo && c0 + BN <= t.safe_hi && (c0 + BN <= t.ex_lo || c0 >= t.ex_hi));
-#pragma unroll 1
-        for (uint32_t chunk = 0; chunk < BN / 32; ++chunk) {
-          uint32_t v[32];
-          tmem_ld32(tmem_base + ((quarter * 32) << 16) + acc * BN + chunk * 32, v);
+        const uint32_t taddr = tmem_base + ((quarter * 32) << 16) + acc * BN;
+
+        // one 32-column chunk: branch-free threshold mask, then the (rare) appends
+        auto process = [&](uint32_t (&v)[32], uint32_t chunk) {
+          const uint32_t cbase = c0 + chunk * 32;
+          const float4* yn4 = reinterpret_cast<const float4*>(yn + chunk * 32);
+          uint32_t m = 0;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const uint32_t c = c0 + chunk * 32 + i;
-            const float d = __fmaf_rn(-2.0f, __uint_as_float(v[i]), yn[chunk * 32 + i]);
-            bool take = row_valid && d < thr;
-            if (need_mask) take = take && c >= w.begin && c < w.end && !(c >= w.xbegin && c < w.xend);
-            if (take) my_buf[cnt++] = make_key(d, c);
+          for (int i4 = 0; i4 < 8; ++i4) {
+            const float4 y = yn4[i4];
+            const float d0 = __fmaf_rn(-2.0f, __uint_as_float(v[4 * i4 + 0]), y.x);
+            const float d1 = __fmaf_rn(-2.0f, __uint_as_float(v[4 * i4 + 1]), y.y);
+            const float d2 = __fmaf_rn(-2.0f, __uint_as_float(v[4 * i4 + 2]), y.z);
+            const float d3 = __fmaf_rn(-2.0f, __uint_as_float(v[4 * i4 + 3]), y.w);
+            v[4 * i4 + 0] = __float_as_uint(d0);
+            v[4 * i4 + 1] = __float_as_uint(d1);
+            v[4 * i4 + 2] = __float_as_uint(d2);
+            v[4 * i4 + 3] = __float_as_uint(d3);
+            m |= (d0 < thr ? 1u : 0u) << (4 * i4 + 0);
+            m |= (d1 < thr ? 1u : 0u) << (4 * i4 + 1);
+            m |= (d2 < thr ? 1u : 0u) << (4 * i4 + 2);
+            m |= (d3 < thr ? 1u : 0u) << (4 * i4 + 3);
+          }
+          uint32_t allowed = row_valid ? 0xFFFFFFFFu : 0u;
+          if (need_mask) allowed &= range_bits(cbase, w.begin, w.end) & ~range_bits(cbase, w.xbegin, w.xend);
+          m &= allowed;
+          if (m) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (m & (1u << i)) my_buf[cnt++] = make_key(__uint_as_float(v[i]), cbase + i);
           }
           compress(cnt, thr, false);
-        }
+        };
+
+        uint32_t va[32], vb[32];
+        tmem_ld32_issue(taddr, va);
+        tmem_ld_wait(va);
+        tmem_ld32_issue(taddr + 32, vb);
+        process(va, 0);
+        tmem_ld_wait(vb);
+        tmem_ld32_issue(taddr + 64, va);
+        process(vb, 1);
+        tmem_ld_wait(va);
+        tmem_ld32_issue(taddr + 96, vb);
+        process(va, 2);
+        tmem_ld_wait(vb);
+        process(vb, 3);
+
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&ctl->tmem_empty[acc]));
         ++tile;
       }
       if (!ok) break;
-      // final cut of this row tile: sorted candidates out, padded with empty keys
+      // final cut of this row tile: at most KC candidates per row (unordered; the re-rank sorts)
       compress(cnt, thr, true);
       for (uint32_t r = 0; r < 32; ++r) {
         const uint32_t c_r = __shfl_sync(0xFFFFFFFFu, cnt, r);
@@ -550,7 +633,8 @@ int knn_tc_impl(const float* d_dataset, uint64_t n, uint32_t dim, int metric, co
   int dev = 0, sms = 0;
   GRAB_CUDA_TRY(cudaGetDevice(&dev));
   GRAB_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  const uint32_t grid = num_row_tiles < static_cast<uint32_t>(sms) ? num_row_tiles : static_cast<uint32_t>(sms);
+  const uint32_t max_ctas = static_cast<uint32_t>(sms) * CTAS_PER_SM;
+  const uint32_t grid = num_row_tiles < max_ctas ? num_row_tiles : max_ctas;
 
   StageTimer tm(mode == 0 ? "knn_tc (own block)" : "knn_tc (other blocks)");
   ScopedDeviceBuffer offs, wins, a_op, b_op, norm, mean, partial, scratch, keys, status;
