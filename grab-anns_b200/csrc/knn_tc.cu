@@ -189,7 +189,7 @@ struct SharedCtl {
   uint64_t full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2];
   uint32_t tmem_base;
   int abort_flag;
-  float ynorm[4][BN];       // one staging row per epilogue warp
+  alignas(16) float ynorm[4][BN];  // one staging row per epilogue warp, read as float4
   uint32_t hist[4][256];    // radix-select histogram per epilogue warp
 };
 
