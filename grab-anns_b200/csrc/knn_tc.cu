@@ -155,6 +155,108 @@ __device__ __forceinline__ uint32_t range_bits(uint32_t cbase, uint32_t lo, uint
   return upto_b & ~upto_a;
 }
 
+// Cut the candidate buffers of the rows that are (nearly) full back to their KC smallest keys
+// and tighten the rows' thresholds.  Warp-cooperative, one row at a time: the row's keys sit in
+// registers (element g = j*32 + lane), a 4-pass radix select on the ordered distance finds the
+// KC-th smallest value, a ballot compaction writes the survivors back.  No ordering is produced:
+// the exact re-rank sorts later.  Kept out of line: it runs rarely and would otherwise bloat
+// the hot loop's instruction footprint.
+template <int KC>
+__device__ __noinline__ uint2 compress_rows(uint64_t* warp_buf, uint32_t* hist, uint32_t lane, uint32_t cnt,
+                                            float thr, bool force) {
+  constexpr uint32_t CAP = 2 * KC;
+  constexpr int NREG = CAP / 32;
+  const uint32_t lt_mask = (1u << lane) - 1u;
+  __syncwarp();
+  uint32_t need = __ballot_sync(0xFFFFFFFFu, force ? (cnt > KC) : (cnt > CAP - 32));
+  while (need) {
+    const int src = __ffs(need) - 1;
+    need &= need - 1;
+    const uint32_t c_src = __shfl_sync(0xFFFFFFFFu, cnt, src);
+    uint64_t* rb = warp_buf + static_cast<uint64_t>(src) * CAP;
+    uint64_t k[NREG];
+#pragma unroll
+    for (int j = 0; j < NREG; ++j) {
+      const uint32_t g = j * 32 + lane;
+      k[j] = g < c_src ? rb[g] : kMaxKey;
+    }
+    uint32_t prefix = 0, hi_mask = 0, want = KC;
+#pragma unroll 1
+    for (int pass = 0; pass < 4; ++pass) {
+      const uint32_t shift = 24 - 8 * pass;
+      for (uint32_t b = lane; b < 256; b += 32) hist[b] = 0;
+      __syncwarp();
+#pragma unroll
+      for (int j = 0; j < NREG; ++j) {
+        const uint32_t o = static_cast<uint32_t>(k[j] >> 32);
+        if (j * 32 + lane < c_src && ((o ^ prefix) & hi_mask) == 0) atomicAdd(&hist[(o >> shift) & 255u], 1u);
+      }
+      __syncwarp();
+      uint32_t local[8], sum = 0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { local[i] = hist[lane * 8 + i]; sum += local[i]; }
+      uint32_t incl = sum;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const uint32_t t = __shfl_up_sync(0xFFFFFFFFu, incl, off);
+        if (static_cast<int>(lane) >= off) incl += t;
+      }
+      const uint32_t excl = incl - sum;
+      const bool mine = excl < want && want <= incl;
+      uint32_t digit = 0, before = 0;
+      if (mine) {
+        uint32_t run = excl;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          if (run + local[i] >= want) { digit = lane * 8 + i; before = run; break; }
+          run += local[i];
+        }
+      }
+      const uint32_t owner = __ffs(__ballot_sync(0xFFFFFFFFu, mine)) - 1;  // exactly one lane: want <= c_src
+      digit = __shfl_sync(0xFFFFFFFFu, digit, owner & 31);
+      before = __shfl_sync(0xFFFFFFFFu, before, owner & 31);
+      want -= before;
+      prefix |= digit << shift;
+      hi_mask |= 0xFFu << shift;
+      __syncwarp();
+    }
+    // `prefix` = ordered distance of the KC-th smallest key, `want` of the keys equal to it stay
+    uint32_t base = 0, eq_seen = 0;
+#pragma unroll
+    for (int j = 0; j < NREG; ++j) {
+      const uint32_t o = static_cast<uint32_t>(k[j] >> 32);
+      const bool valid = j * 32 + lane < c_src;
+      const bool eq = valid && o == prefix;
+      const uint32_t eqm = __ballot_sync(0xFFFFFFFFu, eq);
+      const bool take = (valid && o < prefix) || (eq && eq_seen + __popc(eqm & lt_mask) < want);
+      eq_seen += __popc(eqm);
+      const uint32_t tm = __ballot_sync(0xFFFFFFFFu, take);
+      if (take) rb[base + __popc(tm & lt_mask)] = k[j];
+      base += __popc(tm);
+    }
+    if (static_cast<int>(lane) == src) {
+      cnt = KC;
+      thr = ordered_to_float(prefix);
+    }
+  }
+  __syncwarp();
+  return make_uint2(cnt, __float_as_uint(thr));
+}
+
+// v[i] for a run-time i without spilling the array: a 5-level select tree.
+__device__ __forceinline__ uint32_t pick32(const uint32_t (&v)[32], uint32_t i) {
+  uint32_t a[16], b[8], c[4], d[2];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) a[j] = (i & 1u) ? v[2 * j + 1] : v[2 * j];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) b[j] = (i & 2u) ? a[2 * j + 1] : a[2 * j];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) c[j] = (i & 4u) ? b[2 * j + 1] : b[2 * j];
+#pragma unroll
+  for (int j = 0; j < 2; ++j) d[j] = (i & 8u) ? c[2 * j + 1] : c[2 * j];
+  return (i & 16u) ? d[1] : d[0];
+}
+
 struct TileRange {
   uint32_t row0, rows;       // rows of this tile that exist
   uint32_t jb, je;           // column tiles [jb, je)
@@ -305,88 +407,6 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     bool ok = true;
 
     uint32_t* hist = ctl->hist[warp - 2];
-    const uint32_t lt_mask = (1u << lane) - 1u;
-
-    // Cut the buffers of the rows that are (nearly) full back to their KC smallest keys and
-    // tighten the rows' thresholds.  Warp-cooperative, one row at a time: the row's keys sit in
-    // registers (element g = j*32 + lane), a 4-pass radix select on the ordered distance finds
-    // the KC-th smallest value, a ballot compaction writes the survivors back.  No ordering is
-    // produced: the exact re-rank sorts later.
-    auto compress = [&](uint32_t& cnt, float& thr, bool force) {
-      __syncwarp();
-      uint32_t need = __ballot_sync(0xFFFFFFFFu, force ? (cnt > KC) : (cnt > CAP - 32));
-      while (need) {
-        const int src = __ffs(need) - 1;
-        need &= need - 1;
-        const uint32_t c_src = __shfl_sync(0xFFFFFFFFu, cnt, src);
-        uint64_t* rb = warp_buf + static_cast<uint64_t>(src) * CAP;
-        uint64_t k[NREG];
-#pragma unroll
-        for (int j = 0; j < NREG; ++j) {
-          const uint32_t g = j * 32 + lane;
-          k[j] = g < c_src ? rb[g] : kMaxKey;
-        }
-        uint32_t prefix = 0, hi_mask = 0, want = KC;
-#pragma unroll 1
-        for (int pass = 0; pass < 4; ++pass) {
-          const uint32_t shift = 24 - 8 * pass;
-          for (uint32_t b = lane; b < 256; b += 32) hist[b] = 0;
-          __syncwarp();
-#pragma unroll
-          for (int j = 0; j < NREG; ++j) {
-            const uint32_t o = static_cast<uint32_t>(k[j] >> 32);
-            if (j * 32 + lane < c_src && ((o ^ prefix) & hi_mask) == 0) atomicAdd(&hist[(o >> shift) & 255u], 1u);
-          }
-          __syncwarp();
-          uint32_t local[8], sum = 0;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) { local[i] = hist[lane * 8 + i]; sum += local[i]; }
-          uint32_t incl = sum;
-#pragma unroll
-          for (int off = 1; off < 32; off <<= 1) {
-            const uint32_t t = __shfl_up_sync(0xFFFFFFFFu, incl, off);
-            if (static_cast<int>(lane) >= off) incl += t;
-          }
-          const uint32_t excl = incl - sum;
-          const bool mine = excl < want && want <= incl;
-          uint32_t digit = 0, before = 0;
-          if (mine) {
-            uint32_t run = excl;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              if (run + local[i] >= want) { digit = lane * 8 + i; before = run; break; }
-              run += local[i];
-            }
-          }
-          const uint32_t owner = __ffs(__ballot_sync(0xFFFFFFFFu, mine)) - 1;  // exactly one lane: want <= c_src
-          digit = __shfl_sync(0xFFFFFFFFu, digit, owner & 31);
-          before = __shfl_sync(0xFFFFFFFFu, before, owner & 31);
-          want -= before;
-          prefix |= digit << shift;
-          hi_mask |= 0xFFu << shift;
-          __syncwarp();
-        }
-        // `prefix` = ordered distance of the KC-th smallest key, `want` of the keys equal to it stay
-        uint32_t base = 0, eq_seen = 0;
-#pragma unroll
-        for (int j = 0; j < NREG; ++j) {
-          const uint32_t o = static_cast<uint32_t>(k[j] >> 32);
-          const bool valid = j * 32 + lane < c_src;
-          const bool eq = valid && o == prefix;
-          const uint32_t eqm = __ballot_sync(0xFFFFFFFFu, eq);
-          const bool take = (valid && o < prefix) || (eq && eq_seen + __popc(eqm & lt_mask) < want);
-          eq_seen += __popc(eqm);
-          const uint32_t tm = __ballot_sync(0xFFFFFFFFu, take);
-          if (take) rb[base + __popc(tm & lt_mask)] = k[j];
-          base += __popc(tm);
-        }
-        if (static_cast<int>(lane) == src) {
-          cnt = KC;
-          thr = ordered_to_float(prefix);
-        }
-      }
-      __syncwarp();
-    };
 
     for (uint32_t rt = blockIdx.x; rt < num_row_tiles && ok; rt += gridDim.x) {
       const TileRange t = tile_range(windows, n, rt);
@@ -395,19 +415,38 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
       if (row_valid) w = windows[t.row0 + r_local];
       uint32_t cnt = 0;
       float thr = __int_as_float(0x7f800000);  // +inf
+      float ynext[BN / 32];
+      {
+        uint32_t j0 = t.jb;
+        while (j0 < t.je && tile_skipped(t, j0)) ++j0;
+#pragma unroll
+        for (int i = 0; i < BN / 32; ++i) {
+          const uint64_t c = static_cast<uint64_t>(j0) * BN + i * 32 + lane;
+          ynext[i] = (j0 < t.je && c < n) ? __ldg(ynorm + c) : 0.0f;
+        }
+      }
       for (uint32_t j = t.jb; j < t.je && ok; ++j) {
         if (tile_skipped(t, j)) continue;
         const uint32_t acc = tile & 1, acc_phase = (tile >> 1) & 1;
         const uint32_t c0 = j * BN;
-        // column norms of this tile, staged per warp (no cross-warp barrier in the epilogue)
+        // column norms of this tile: prefetched into registers while the previous tile was
+        // processed, staged per warp in shared memory (no cross-warp barrier in the epilogue)
         float* yn = ctl->ynorm[warp - 2];
         __syncwarp();
 #pragma unroll
-        for (int i = 0; i < BN / 32; ++i) {
-          const uint64_t c = static_cast<uint64_t>(c0) + i * 32 + lane;
-          yn[i * 32 + lane] = c < n ? __ldg(ynorm + c) : 0.0f;
-        }
+        for (int i = 0; i < BN / 32; ++i) yn[i * 32 + lane] = ynext[i];
         __syncwarp();
+        {
+          uint32_t jn = j + 1;  // next tile this CTA will visit in this row tile
+          while (jn < t.je && tile_skipped(t, jn)) ++jn;
+          if (jn < t.je) {
+#pragma unroll
+            for (int i = 0; i < BN / 32; ++i) {
+              const uint64_t c = static_cast<uint64_t>(jn) * BN + i * 32 + lane;
+              ynext[i] = c < n ? __ldg(ynorm + c) : 0.0f;
+            }
+          }
+        }
         if (!mbar_wait(smem_u32(&ctl->tmem_full[acc]), acc_phase, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const bool need_mask = !(c0 >= t.safe_lo && c0 + BN <= t.safe_hi && (c0 + BN <= t.ex_lo || c0 >= t.ex_hi));
@@ -437,27 +476,30 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
           uint32_t allowed = row_valid ? 0xFFFFFFFFu : 0u;
           if (need_mask) allowed &= range_bits(cbase, w.begin, w.end) & ~range_bits(cbase, w.xbegin, w.xend);
           m &= allowed;
-          if (m) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (m & (1u << i)) my_buf[cnt++] = make_key(__uint_as_float(v[i]), cbase + i);
+          while (m) {  // rare once the threshold has tightened
+            const uint32_t i = __ffs(m) - 1;
+            m &= m - 1;
+            my_buf[cnt++] = make_key(__uint_as_float(pick32(v, i)), cbase + i);
           }
-          compress(cnt, thr, false);
+          if (__any_sync(0xFFFFFFFFu, cnt > CAP - 32)) {
+            const uint2 r = compress_rows<KC>(warp_buf, hist, lane, cnt, thr, false);
+            cnt = r.x;
+            thr = __uint_as_float(r.y);
+          }
         };
 
         uint32_t va[32], vb[32];
         tmem_ld32_issue(taddr, va);
         tmem_ld_wait(va);
-        tmem_ld32_issue(taddr + 32, vb);
-        process(va, 0);
-        tmem_ld_wait(vb);
-        tmem_ld32_issue(taddr + 64, va);
-        process(vb, 1);
-        tmem_ld_wait(va);
-        tmem_ld32_issue(taddr + 96, vb);
-        process(va, 2);
-        tmem_ld_wait(vb);
-        process(vb, 3);
+#pragma unroll 1
+        for (uint32_t pair = 0; pair < BN / 64; ++pair) {
+          tmem_ld32_issue(taddr + pair * 64 + 32, vb);
+          process(va, 2 * pair);
+          tmem_ld_wait(vb);
+          if (pair + 1 < BN / 64) tmem_ld32_issue(taddr + pair * 64 + 64, va);
+          process(vb, 2 * pair + 1);
+          if (pair + 1 < BN / 64) tmem_ld_wait(va);
+        }
 
         tc_fence_before();
         __syncwarp();
@@ -466,7 +508,11 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
       }
       if (!ok) break;
       // final cut of this row tile: at most KC candidates per row (unordered; the re-rank sorts)
-      compress(cnt, thr, true);
+      {
+        const uint2 r = compress_rows<KC>(warp_buf, hist, lane, cnt, thr, true);
+        cnt = r.x;
+        thr = __uint_as_float(r.y);
+      }
       for (uint32_t r = 0; r < 32; ++r) {
         const uint32_t c_r = __shfl_sync(0xFFFFFFFFu, cnt, r);
         const uint32_t row = t.row0 + quarter * 32 + r;
