@@ -201,6 +201,34 @@ __global__ void merge_keys_kernel(const uint64_t* __restrict__ part_keys, uint32
   }
 }
 
+// Merge `parts` ascending (dist, int64 id) lists per query straight from the pair arrays: the
+// keys are built in shared memory, so the exchange step of the sharded search needs no scratch
+// and no extra pass.  Ids must be < 2^32.
+__global__ void merge_pairs_kernel(const float* __restrict__ dists, const int64_t* __restrict__ ids, uint32_t parts,
+                                   uint32_t k, uint32_t padded, int64_t* __restrict__ out_ids,
+                                   float* __restrict__ out_dists) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  uint64_t* keys = reinterpret_cast<uint64_t*>(smem_raw);
+  const uint64_t qi = blockIdx.x;
+  const uint32_t m = parts * k;
+  for (uint32_t i = threadIdx.x; i < padded; i += blockDim.x) {
+    uint64_t key = kMaxKey;
+    if (i < m) {
+      const int64_t id = ids[qi * m + i];
+      if (id >= 0) key = make_key(dists[qi * m + i], static_cast<uint32_t>(id));
+    }
+    keys[i] = key;
+  }
+  __syncthreads();
+  block_bitonic_sort(keys, padded);
+  for (uint32_t i = threadIdx.x; i < k; i += blockDim.x) {
+    const uint64_t key = keys[i];
+    const bool empty = key == kMaxKey;
+    out_ids[qi * k + i] = empty ? -1 : static_cast<int64_t>(key_id(key));
+    out_dists[qi * k + i] = empty ? kFltMax : key_dist(key);
+  }
+}
+
 // (dist, int64 id) lists -> keys (ids must be < 2^32), for the public merge entry point.
 __global__ void pack_keys_kernel(const float* __restrict__ dists, const int64_t* __restrict__ ids,
                                  uint64_t total, uint64_t* __restrict__ keys) {
@@ -375,21 +403,13 @@ int merge_topk_impl(const float* d_dists, const int64_t* d_ids, uint64_t nq, uin
   GRAB_REQUIRE(parts >= 1 && k >= 1 && (uint64_t)parts * k <= 8192,
                "merge_topk: parts*k = %llu exceeds 8192", (unsigned long long)parts * k);
   if (nq == 0) return GRAB_OK;
-  ScopedDeviceBuffer keys;
-  const uint64_t total = nq * parts * k;
-  GRAB_CUDA_TRY(keys.alloc(sizeof(uint64_t) * total));
-  pack_keys_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(d_dists, d_ids, total,
-                                                                   keys.as<uint64_t>());
-  GRAB_CUDA_TRY(cudaGetLastError());
   const uint32_t padded = next_pow2(parts * k);
   const size_t smem = sizeof(uint64_t) * padded;
-  GRAB_CUDA_TRY(cudaFuncSetAttribute(merge_keys_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)smem));
-  merge_keys_kernel<<<(unsigned)nq, 256, smem, st>>>(keys.as<uint64_t>(), parts, k, padded,
-                                                    d_out_ids, d_out_dists);
+  const uint32_t threads = padded >= 512 ? 256 : (padded >= 128 ? 64 : 32);
+  GRAB_CUDA_TRY(cudaFuncSetAttribute(merge_pairs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  merge_pairs_kernel<<<(unsigned)nq, threads, smem, st>>>(d_dists, d_ids, parts, k, padded, d_out_ids, d_out_dists);
   GRAB_CUDA_TRY(cudaGetLastError());
-  GRAB_CUDA_TRY(cudaStreamSynchronize(st));
-  return GRAB_OK;
+  return GRAB_OK;  // stream-ordered: nothing allocated, nothing synchronised
 }
 
 }  // namespace grab

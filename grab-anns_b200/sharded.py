@@ -33,14 +33,17 @@ def gather_and_merge(dists, ids, k: int, merge_fn, dist_mod=None, group=None):
     world = dist_mod.get_world_size(group) if dist_mod.is_initialized() else 1
     if world == 1:
         return merge_fn(dists.unsqueeze(1).contiguous(), ids.unsqueeze(1).contiguous(), k)
-    all_d = [torch.empty_like(dists) for _ in range(world)]
-    all_i = [torch.empty_like(ids) for _ in range(world)]
-    dist_mod.all_gather(all_d, dists.contiguous(), group=group)
-    dist_mod.all_gather(all_i, ids.contiguous(), group=group)
+    nq = dists.shape[0]
+    all_d = torch.empty((world, nq, k), dtype=dists.dtype, device=dists.device)
+    all_i = torch.empty((world, nq, k), dtype=ids.dtype, device=ids.device)
+    if dists.is_cuda:  # NCCL: one collective per buffer, straight into the gather tensor
+        dist_mod.all_gather_into_tensor(all_d, dists.contiguous(), group=group)
+        dist_mod.all_gather_into_tensor(all_i, ids.contiguous(), group=group)
+    else:              # gloo (CPU ranks in the tests) takes a list of per-rank views
+        dist_mod.all_gather(list(all_d.unbind(0)), dists.contiguous(), group=group)
+        dist_mod.all_gather(list(all_i.unbind(0)), ids.contiguous(), group=group)
     # [G, nq, k] -> [nq, G, k]: one ascending run per shard and query
-    d = torch.stack(all_d, dim=1).contiguous()
-    i = torch.stack(all_i, dim=1).contiguous()
-    return merge_fn(d, i, k)
+    return merge_fn(all_d.transpose(0, 1).contiguous(), all_i.transpose(0, 1).contiguous(), k)
 
 
 def sharded_search(search_fn, merge_fn, k: int, rank: int, world: int, dist_mod=None, group=None):
