@@ -46,6 +46,7 @@ def parse():
                     help="0 exact scan, 1 bf16 tensor cores (exact for integer-valued data), 2 split bf16")
     ap.add_argument("--cpu-sample", type=int, default=0, help="queries in the CPU sample (0 = auto)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-hnsw", action="store_true", help="reference arm: skip the CPU HNSW harness")
     ap.add_argument("--sharded", action="store_true",
                     help="stripe the index by id across the ranks (all_gather + device merge of the per-shard "
                          "top-k) instead of replicating it")
@@ -137,6 +138,50 @@ def auto_cpu_sample(w, target_s=12.0):
     return int(max(probe, min(w["queries"].shape[0], qps * target_s)))
 
 
+def hnsw_harness(w, base_n=50_000, add_n=50_000, batches=10, batch=32):
+    """The reference's CPU baseline harness (tests/test_faiss_hnsw_insert.cpp:69-204) with its own sizes
+    and parameters on the first vectors of the workload: HNSW M 32, efConstruction 128, efSearch 64; build
+    on `base_n`, timed add of `add_n` -> vectors/s, `batches` x `batch` queries -> QPS and recall@10
+    against the exact scan.  Unfiltered like the harness, plus a post-filtered variant for the range
+    predicate (over-fetch k / selectivity).  HNSW restatement, not FAISS: parity unpinned."""
+    import oracle
+    n = min(base_n + add_n, w["base"].shape[0])
+    base_n = n // 2
+    data = np.ascontiguousarray(w["base"][:n])
+    h = oracle.HNSW(data, M=32, ef_construction=128)
+    t0 = time.perf_counter(); h.add(base_n); t1 = time.perf_counter()
+    h.add(n - base_n); t2 = time.perf_counter()
+    nq = min(batches * batch, w["queries"].shape[0])
+    q = w["queries"][:nq]
+    k = w["k"]
+    t3 = time.perf_counter()
+    for b in range(0, nq, batch):
+        ids_b, _ = h.search(q[b:b + batch], k, ef=64)
+        ids = ids_b if b == 0 else np.concatenate([ids, ids_b])
+    t4 = time.perf_counter()
+    gt, _ = oracle.exact_search(data, q, k, canonical=False)
+    out = {"kind": "HNSW restatement (not FAISS), parity unpinned", "vectors": int(n), "cores": oracle.num_threads(),
+           "build_s": t1 - t0, "insert_vectors_per_s": (n - base_n) / (t2 - t1),
+           "qps_unfiltered": nq / (t4 - t3), "recall_at_10_unfiltered": oracle.recall(ids, gt)}
+    if "ts" in w:  # range predicate by post-filtering an over-fetched result
+        width = max(1, n // 10)
+        rng = np.random.default_rng(7)
+        lo = rng.integers(0, n - width + 1, nq).astype(np.uint64)
+        hi = lo + np.uint64(width)
+        fetch = min(n, 16 * k)
+        t5 = time.perf_counter()
+        ids_f, _ = h.search(q, fetch, ef=max(64, 2 * fetch))
+        res = np.full((nq, k), -1, dtype=np.int64)
+        for i in range(nq):
+            keep = ids_f[i][(ids_f[i] >= lo[i]) & (ids_f[i] < hi[i])][:k]
+            res[i, :keep.size] = keep
+        t6 = time.perf_counter()
+        gtf, _ = oracle.exact_search(data, q, k, ts=np.arange(n, dtype=np.uint64), lo=lo, hi=hi, canonical=False)
+        out.update({"qps_range_10pct_postfilter": nq / (t6 - t5), "recall_at_10_range": oracle.recall(res, gtf),
+                    "overfetch": int(fetch)})
+    return out
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -164,6 +209,8 @@ def run_reference(args):
                                           "routine restated (FAISS-HNSW is not installed on this box)"},
         "e2e": {"value": qps, "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
+    if not args.no_hnsw:
+        line["hnsw_harness"] = hnsw_harness(w)
     print(json.dumps(line), flush=True)
 
 

@@ -201,3 +201,34 @@ def recall(result_ids, gt_ids):
         tot += len(g.intersection(int(x) for x in r)) / len(g)
         cnt += 1
     return tot / max(cnt, 1)
+
+
+class HNSW:
+    """CPU HNSW baseline (oracle/hnsw_baseline.c): the published algorithm with the parameters of
+    the reference's FAISS harness (tests/test_faiss_hnsw_insert.cpp: M 32, efConstruction 128,
+    efSearch 64).  Not FAISS; parity unpinned."""
+
+    def __init__(self, data, M=32, ef_construction=128, seed=1):
+        self.data = _f32(data)            # the index borrows this array: keep it alive
+        n, dim = self.data.shape
+        L = lib()
+        L.orc_hnsw_new.restype = C.c_void_p
+        self.h = L.orc_hnsw_new(_p(self.data), C.c_uint64(n), C.c_uint32(dim), C.c_uint32(M),
+                                C.c_uint32(ef_construction), C.c_uint64(seed))
+        self.dim = dim
+
+    def add(self, count):
+        lib().orc_hnsw_add(C.c_void_p(self.h), C.c_uint64(count))
+
+    def search(self, queries, k, ef=64):
+        q = _f32(queries)
+        ids = np.empty((q.shape[0], k), dtype=np.int64)
+        d = np.empty((q.shape[0], k), dtype=np.float32)
+        lib().orc_hnsw_search(C.c_void_p(self.h), _p(q), C.c_uint64(q.shape[0]), C.c_uint32(k), C.c_uint32(ef),
+                              _p(ids), _p(d))
+        return ids, d
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            lib().orc_hnsw_free(C.c_void_p(self.h))
+            self.h = None

@@ -206,3 +206,20 @@ def test_insert_v1_restatement(oracle):
         assert 6 in out[old] or 7 in out[old]
     # protected first half is rarely touched, the row keeps its width
     assert out.shape == g.shape
+
+
+def test_hnsw_baseline_restatement(oracle):
+    # the CPU baseline harness of tests/test_faiss_hnsw_insert.cpp in miniature: build on the first
+    # half, add the second half, search with efSearch 64, recall@10 against the exact scan
+    from conftest import clustered
+    n, dim = 6000, 32
+    data = clustered(n, dim, 20, 1.0, 91)
+    h = oracle.HNSW(data, M=32, ef_construction=128)
+    h.add(n // 2)
+    h.add(n - n // 2)
+    rng = np.random.default_rng(92)
+    q = data[rng.integers(0, n, 64)] + 0.05 * rng.standard_normal((64, dim)).astype(np.float32)
+    ids, d = h.search(q, 10, ef=64)
+    gt, _ = oracle.exact_search(data, q, 10)
+    assert oracle.recall(ids, gt) > 0.95
+    assert np.all(np.diff(d, axis=1) >= 0) and (ids >= 0).all()
