@@ -375,6 +375,12 @@ def main():
             pass
         peak = float(peaks.get("hbm_gbs", 6650.0))
         achieved = alg_bytes / (ms / 1e3) / 1e9
+        # dram__bytes_read.sum + dram__bytes_write.sum of one search launch at the default full-size
+        # configuration (ncu capture summarised in profiles/graph_search_kernel_C2.md)
+        default_cfg = (args.workload == "C2" and args.scale == 1.0 and args.buckets == 20 and args.itopk == 64 and
+                       args.width == 3 and args.max_iter == 20 and args.hash_bitlen == 11 and
+                       args.selectivity == 0.10 and not args.sharded)
+        traffic = 4141677056 + 1401856 if default_cfg else None
         line = {
             "metric": "filtered QPS at recall@10>=0.95",
             "value": (1 if args.sharded else world) * nq / (ms / 1e3), "unit": "queries/s",
@@ -387,7 +393,7 @@ def main():
                     "h2d_bytes_per_step": int(h_q.numel() * 4 + 16 * nq), "d2h_bytes_per_step": int(12 * nq * k)},
             "gpu_launches": (4 if args.sharded and world > 1 else 2) * args.steps,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": None,
+                         "frac": achieved / peak, "traffic": traffic,
                          "peak_source": "measured" if peaks else "fallback",
                          "algorithmic_bytes_per_launch": int(alg_bytes),
                          "counters": {"seeds": stats.seeds, "parents": stats.parents, "edges": stats.edges,
