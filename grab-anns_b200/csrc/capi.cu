@@ -3,6 +3,7 @@
 #include <cstdarg>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <vector>
 
 #include "common.cuh"
@@ -42,6 +43,34 @@ void StageTimer::mark(const char* stage) {
     fprintf(stderr, "[grab trace] %-28s %-22s %9.3f ms\n", scope, stage, (t - t0) * 1e3);
     t0 = t;
   }
+}
+
+namespace {
+struct PoolEntry { void* ptr = nullptr; size_t bytes = 0; };
+PoolEntry g_pool[16][kPoolSlots];
+std::mutex g_pool_mutex;
+}  // namespace
+
+void* pool_get(int slot, size_t bytes, bool zeroed) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return nullptr;
+  std::lock_guard<std::mutex> lock(g_pool_mutex);
+  PoolEntry& e = g_pool[dev][slot];
+  if (e.bytes < bytes) {
+    if (e.ptr) cudaFree(e.ptr);
+    e.ptr = nullptr;
+    e.bytes = 0;
+    const size_t want = bytes + bytes / 2 + 256;  // headroom: the index grows with every batch
+    if (cudaMalloc(&e.ptr, want) != cudaSuccess) {
+      cudaGetLastError();
+      if (cudaMalloc(&e.ptr, bytes) != cudaSuccess) { e.ptr = nullptr; return nullptr; }
+      e.bytes = bytes;
+    } else {
+      e.bytes = want;
+    }
+    if (zeroed) cudaMemset(e.ptr, 0, e.bytes);
+  }
+  return e.ptr;
 }
 
 // implemented in the kernel translation units

@@ -164,6 +164,17 @@ struct StageTimer {
   void mark(const char* stage);
 };
 
+// Grow-only device scratch that survives across calls (per device, per slot), for pipelines
+// that run thousands of small batches (insert): no cudaMalloc / cudaFree per batch.  `zeroed`
+// slots are cleared when (re)allocated and the kernels that use them leave them all-zero
+// again.  Not for concurrent callers: one insert pipeline at a time per device.
+enum PoolSlot {
+  kPoolMailCountsL = 0, kPoolMailCountsR, kPoolMailCursor, kPoolMailOffsets, kPoolMailTouched, kPoolMailCsr,
+  kPoolMailMeta, kPoolInsIdsG, kPoolInsDistG, kPoolInsIdsL, kPoolInsDistL, kPoolInsBatchIds, kPoolInsBatchDist,
+  kPoolSearchWs, kPoolSlots
+};
+void* pool_get(int slot, size_t bytes, bool zeroed);
+
 // Scratch allocation used by the stateless entry points when the caller passes no
 // workspace: plain cudaMalloc, released on scope exit.
 struct ScopedDeviceBuffer {

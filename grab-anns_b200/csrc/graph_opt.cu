@@ -712,36 +712,74 @@ __global__ void opt_fill_kernel(uint32_t* __restrict__ graph, const uint64_t* __
   }
 }
 
-__global__ void opt_apply_kernel(uint32_t* __restrict__ graph, const uint64_t* __restrict__ bucket,
-                                 const uint32_t* __restrict__ lcnt, const uint32_t* __restrict__ llist,
-                                 uint32_t lmax, const uint32_t* __restrict__ rcnt,
-                                 const uint32_t* __restrict__ rlist, uint32_t rmax, uint64_t num_existing,
-                                 uint32_t total_deg, uint32_t local_deg) {
-  const uint64_t t = blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x;
-  if (t >= num_existing) return;
-  uint32_t lc = lcnt[t], rc = rcnt[t];
-  if (lc == 0 && rc == 0) return;
-  uint32_t* row = graph + t * total_deg;
-  uint32_t rng = wang_hash(static_cast<uint32_t>(t));
-  if (lc > 0) {
+// ---------------------------------------------------------------------------------------
+// Sparse mailboxes for the batched insert: only the old nodes that actually receive mail are
+// visited (the reference clears and walks O(N) mailboxes for every batch of 32,
+// insert.cu:1462-1560).  Per pass (local columns, then remote columns):
+//   count   every edge of the new rows bumps counts[dest]; the first toucher appends dest to a list
+//   offsets every touched dest claims a segment of the request array
+//   fill    every edge writes its key (src, column) into its dest's segment
+//   apply   one warp per touched dest sorts its segment, takes the first `cap` sources in
+//           ascending (src, column) order and rewrites slots exactly as insert.cu:653-765 does
+// counts / cursor live in pooled scratch that is all-zero between batches.
+// ---------------------------------------------------------------------------------------
+struct MailMeta {
+  uint32_t n_touched;
+  uint32_t csr_cursor;
+};
+
+__global__ void mail_count_kernel(EdgeSource e, uint64_t total, uint32_t* __restrict__ counts,
+                                  uint32_t* __restrict__ touched, MailMeta* __restrict__ meta) {
+  const uint64_t idx = blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x;
+  if (idx >= total) return;
+  uint32_t d, s; uint64_t key;
+  if (edge_at(e, idx, &d, &key, &s) && atomicAdd(&counts[d], 1u) == 0) touched[atomicAdd(&meta->n_touched, 1u)] = d;
+}
+
+__global__ void mail_offsets_kernel(const uint32_t* __restrict__ touched, MailMeta* __restrict__ meta,
+                                    const uint32_t* __restrict__ counts, uint32_t* __restrict__ offsets) {
+  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= meta->n_touched) return;
+  const uint32_t d = touched[i];
+  offsets[d] = atomicAdd(&meta->csr_cursor, counts[d]);
+}
+
+template <int REMOTE>
+__global__ void __launch_bounds__(kSelWarps * 32)
+mail_apply_kernel(uint32_t* __restrict__ graph, const uint64_t* __restrict__ bucket,
+                  const uint32_t* __restrict__ touched, const MailMeta* __restrict__ meta,
+                  uint32_t* __restrict__ counts, const uint32_t* __restrict__ counts_local,
+                  const uint32_t* __restrict__ offsets, uint32_t* __restrict__ cursor,
+                  const uint64_t* __restrict__ csr, uint32_t cap, uint32_t lmax, uint32_t total_deg,
+                  uint32_t local_deg) {
+  __shared__ uint64_t sbuf[kSelWarps][kSelSort];
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t i = blockIdx.x * kSelWarps + warp;
+  if (i >= meta->n_touched) return;
+  const uint32_t t = touched[i];
+  const uint32_t len = counts[t];
+  const uint64_t* seg = csr + offsets[t];
+  uint32_t* row = graph + static_cast<size_t>(t) * total_deg;
+  const uint32_t take = len < cap ? len : cap;
+
+  uint32_t rng = wang_hash(t);
+  if (REMOTE) {  // the local pass of this node advanced the generator twice per applied request
+    uint32_t lc = counts_local[t];
     if (lc > lmax) lc = lmax;
-    const uint32_t half = local_deg / 2, strong = half, weak = local_deg - half;
-    for (uint32_t i = 0; i < lc; ++i) {
-      const uint32_t c = llist[t * lmax + i];
+    for (uint32_t r = 0; r < 2 * lc; ++r) rng = wang_hash(rng);
+  }
+  auto apply = [&](uint32_t c) {  // executed by lane 0 only
+    if (!REMOTE) {
+      const uint32_t half = local_deg / 2, weak = local_deg - half;
       rng = wang_hash(rng);
       const bool atk = (rng % 100) < 10;
-      const uint32_t ts = atk ? 0 : half, tl = atk ? strong : weak;
+      const uint32_t ts = atk ? 0 : half, tl = atk ? half : weak;
       if (tl > 0) {
         rng = wang_hash(rng);
         row[ts + (rng % tl)] = c;
       }
-    }
-  }
-  if (rc > 0) {
-    if (rc > rmax) rc = rmax;
-    const uint32_t rd = total_deg - local_deg;
-    for (uint32_t i = 0; i < rc; ++i) {
-      const uint32_t c = rlist[t * rmax + i];
+    } else {
+      const uint32_t rd = total_deg - local_deg;
       const int64_t mt = static_cast<int64_t>(bucket[t]), ct = static_cast<int64_t>(bucket[c]);
       const bool near = (ct >= mt - 20) && (ct <= mt + 20);
       const uint32_t nlen = rd / 3;
@@ -752,7 +790,55 @@ __global__ void opt_apply_kernel(uint32_t* __restrict__ graph, const uint64_t* _
         row[ts + (rng % tl)] = c;
       }
     }
+  };
+
+  if (len <= kSelSort) {
+    uint64_t* keys = sbuf[warp];
+    uint32_t padded = 32;
+    while (padded < len) padded <<= 1;
+    for (uint32_t j = lane; j < padded; j += 32) keys[j] = j < len ? seg[j] : kMaxKey;
+    __syncwarp();
+    for (uint32_t size = 2; size <= padded; size <<= 1)
+      for (uint32_t stride = size >> 1; stride > 0; stride >>= 1) {
+        for (uint32_t x = lane; x < (padded >> 1); x += 32) {
+          const uint32_t lo = ((x & ~(stride - 1)) << 1) | (x & (stride - 1));
+          const uint32_t hi = lo | stride;
+          const bool up = (lo & size) == 0;
+          const uint64_t a = keys[lo], b = keys[hi];
+          if ((a > b) == up) { keys[lo] = b; keys[hi] = a; }
+        }
+        __syncwarp();
+      }
+    if (lane == 0)
+      for (uint32_t r = 0; r < take; ++r) apply(static_cast<uint32_t>(keys[r] >> 32));
+  } else {
+    uint64_t last = 0;
+    for (uint32_t r = 0; r < take; ++r) {
+      uint64_t best = kMaxKey;
+      for (uint32_t j = lane; j < len; j += 32) {
+        const uint64_t key = seg[j];
+        if ((r == 0 || key > last) && key < best) best = key;
+      }
+      for (int off = 16; off > 0; off >>= 1) {
+        const uint64_t o = __shfl_xor_sync(0xFFFFFFFFu, best, off);
+        best = o < best ? o : best;
+      }
+      if (lane == 0) apply(static_cast<uint32_t>(best >> 32));
+      last = best;
+    }
   }
+  // leave the pooled arrays all-zero for the next batch (the local counts are still needed by
+  // the remote pass and are cleared by mail_clear_kernel afterwards)
+  if (lane == 0) {
+    cursor[t] = 0;
+    if (REMOTE) counts[t] = 0;
+  }
+}
+
+__global__ void mail_clear_kernel(const uint32_t* __restrict__ touched, const MailMeta* __restrict__ meta,
+                                  uint32_t* __restrict__ counts) {
+  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < meta->n_touched) counts[touched[i]] = 0;
 }
 
 int update_topology_opt_impl(uint32_t* d_graph, const uint64_t* d_bucket, int64_t* d_local_knn,
@@ -767,25 +853,49 @@ int update_topology_opt_impl(uint32_t* d_graph, const uint64_t* d_bucket, int64_
       d_graph, d_bucket, d_local_knn, d_global_knn, num_existing, num_new, total_deg, local_deg, k_local,
       k_global);
   GRAB_CUDA_TRY(cudaGetLastError());
+  if (num_existing == 0) return GRAB_OK;
   const uint64_t ntot = num_existing + num_new;
   const uint32_t lmax = local_deg / 2, rmax = (total_deg - local_deg) / 2;
-  ScopedDeviceBuffer llist, lcnt, rlist, rcnt;
-  GRAB_CUDA_TRY(llist.alloc(sizeof(uint32_t) * ntot * lmax));
-  GRAB_CUDA_TRY(lcnt.alloc(sizeof(uint32_t) * ntot));
-  GRAB_CUDA_TRY(rlist.alloc(sizeof(uint32_t) * ntot * rmax));
-  GRAB_CUDA_TRY(rcnt.alloc(sizeof(uint32_t) * ntot));
+  const uint64_t max_edges = num_new * (local_deg > total_deg - local_deg ? local_deg : total_deg - local_deg);
+  GRAB_REQUIRE(max_edges < (1ull << 31), "update_topology_opt: batch too large");
+  uint32_t* counts_l = static_cast<uint32_t*>(pool_get(kPoolMailCountsL, sizeof(uint32_t) * num_existing, true));
+  uint32_t* counts_r = static_cast<uint32_t*>(pool_get(kPoolMailCountsR, sizeof(uint32_t) * num_existing, true));
+  uint32_t* cursor = static_cast<uint32_t*>(pool_get(kPoolMailCursor, sizeof(uint32_t) * num_existing, true));
+  uint32_t* offsets = static_cast<uint32_t*>(pool_get(kPoolMailOffsets, sizeof(uint32_t) * num_existing, false));
+  uint32_t* touched = static_cast<uint32_t*>(pool_get(kPoolMailTouched, sizeof(uint32_t) * 2 * max_edges, false));
+  uint64_t* csr = static_cast<uint64_t*>(pool_get(kPoolMailCsr, sizeof(uint64_t) * max_edges, false));
+  MailMeta* meta = static_cast<MailMeta*>(pool_get(kPoolMailMeta, sizeof(MailMeta) * 2, false));
+  if (!counts_l || !counts_r || !cursor || !offsets || !touched || !csr || !meta) {
+    set_last_error("update_topology_opt: out of device memory for the mailbox scratch");
+    return GRAB_ERR_CUDA;
+  }
+  GRAB_CUDA_TRY(cudaMemsetAsync(meta, 0, sizeof(MailMeta) * 2, st));
+  uint32_t* touched_l = touched;
+  uint32_t* touched_r = touched + max_edges;
   EdgeSource e{};
-  e.graph = d_graph; e.deg = total_deg; e.row0 = num_existing; e.row1 = ntot; e.n_dest = ntot;
+  e.graph = d_graph; e.deg = total_deg; e.row0 = num_existing; e.row1 = ntot;
+  e.n_dest = num_existing;  // mail for nodes of the batch itself is never applied (insert.cu:653-668)
   e.col_major_key = 0;
-  e.c0 = 0; e.c1 = local_deg;
-  int rc = grouped_lists(e, lmax, llist.as<uint32_t>(), lcnt.as<uint32_t>(), st);
-  if (rc != GRAB_OK) return rc;
-  e.c0 = local_deg; e.c1 = total_deg; e.bucket = d_bucket; e.skip_bucket = target_bucket; e.use_skip = 1;
-  rc = grouped_lists(e, rmax, rlist.as<uint32_t>(), rcnt.as<uint32_t>(), st);
-  if (rc != GRAB_OK) return rc;
-  opt_apply_kernel<<<(unsigned)((num_existing + 255) / 256), 256, 0, st>>>(
-      d_graph, d_bucket, lcnt.as<uint32_t>(), llist.as<uint32_t>(), lmax, rcnt.as<uint32_t>(),
-      rlist.as<uint32_t>(), rmax, num_existing, total_deg, local_deg);
+  for (int pass = 0; pass < 2; ++pass) {
+    if (pass == 0) { e.c0 = 0; e.c1 = local_deg; e.use_skip = 0; }
+    else { e.c0 = local_deg; e.c1 = total_deg; e.bucket = d_bucket; e.skip_bucket = target_bucket; e.use_skip = 1; }
+    const uint64_t total = num_new * (e.c1 - e.c0);
+    uint32_t* counts = pass == 0 ? counts_l : counts_r;
+    uint32_t* tl = pass == 0 ? touched_l : touched_r;
+    const unsigned eg = (unsigned)((total + 255) / 256);
+    mail_count_kernel<<<eg, 256, 0, st>>>(e, total, counts, tl, meta + pass);
+    mail_offsets_kernel<<<eg, 256, 0, st>>>(tl, meta + pass, counts, offsets);
+    group_fill_kernel<<<eg, 256, 0, st>>>(e, total, offsets, cursor, csr);
+    const unsigned ag = (unsigned)((total + kSelWarps - 1) / kSelWarps);  // upper bound on touched nodes
+    if (pass == 0)
+      mail_apply_kernel<0><<<ag, kSelWarps * 32, 0, st>>>(d_graph, d_bucket, tl, meta + pass, counts, counts_l, offsets,
+                                                          cursor, csr, lmax, lmax, total_deg, local_deg);
+    else
+      mail_apply_kernel<1><<<ag, kSelWarps * 32, 0, st>>>(d_graph, d_bucket, tl, meta + pass, counts, counts_l, offsets,
+                                                          cursor, csr, rmax, lmax, total_deg, local_deg);
+    GRAB_CUDA_TRY(cudaGetLastError());
+  }
+  mail_clear_kernel<<<(unsigned)((num_new * local_deg + 255) / 256), 256, 0, st>>>(touched_l, meta, counts_l);
   GRAB_CUDA_TRY(cudaGetLastError());
   GRAB_CUDA_TRY(cudaStreamSynchronize(st));
   return GRAB_OK;

@@ -101,19 +101,29 @@ int insert_opt_impl(const float* d_dataset, uint32_t* d_graph, const uint64_t* d
   GRAB_REQUIRE(num_existing >= 1, "insert: the index is empty (build it first)");
   const uint32_t search_k = params.itopk_size;  // cagra_opt.cu:1691
   GRAB_REQUIRE(search_k >= 2 && search_k <= 512, "insert: itopk_size %u outside [2,512]", search_k);
-  ScopedDeviceBuffer ig, dg, il, dl;
-  GRAB_CUDA_TRY(ig.alloc(sizeof(int64_t) * num_new * search_k));
-  GRAB_CUDA_TRY(dg.alloc(sizeof(float) * num_new * search_k));
-  GRAB_CUDA_TRY(il.alloc(sizeof(int64_t) * num_new * search_k));
-  GRAB_CUDA_TRY(dl.alloc(sizeof(float) * num_new * search_k));
+  StageTimer tm("insert_opt batch");
+  // pooled scratch: thousands of batches must not pay cudaMalloc / cudaFree each
+  struct Buf { void* ptr; template <class T> T* as() { return static_cast<T*>(ptr); } };
+  Buf ig{pool_get(kPoolInsIdsG, sizeof(int64_t) * num_new * search_k, false)};
+  Buf dg{pool_get(kPoolInsDistG, sizeof(float) * num_new * search_k, false)};
+  Buf il{pool_get(kPoolInsIdsL, sizeof(int64_t) * num_new * search_k, false)};
+  Buf dl{pool_get(kPoolInsDistL, sizeof(float) * num_new * search_k, false)};
+  const size_t ws_bytes = grab_graph_search_workspace_bytes(num_new, params.hash_bitlen);
+  void* ws = pool_get(kPoolSearchWs, ws_bytes, false);
+  if (!ig.ptr || !dg.ptr || !il.ptr || !dl.ptr || !ws) {
+    set_last_error("insert: out of device memory for the batch scratch");
+    return GRAB_ERR_CUDA;
+  }
   const uint64_t total = num_new * search_k;
   // global search over the old nodes, all columns, self-drawn seeds (cagra_opt.cu:1725-1740)
   {
     grab_search_args a = insert_search_args(d_dataset, dim, num_existing, d_graph, total_degree, d_queries, num_new,
                                             search_k, params, ig.as<int64_t>(), dg.as<float>(), metric);
     a.filter.kind = GRAB_FILTER_NONE;
+    a.d_ws = ws; a.ws_bytes = ws_bytes;
     GRAB_TRY(graph_search_impl(&a));
   }
+  tm.mark("global search");
   // bucket search from in-bucket seeds, local columns only (cagra_opt.cu:1779-1795)
   if (d_seeds && num_seeds_per_query > 0) {
     grab_search_args a = insert_search_args(d_dataset, dim, num_existing, d_graph, total_degree, d_queries, num_new,
@@ -122,17 +132,22 @@ int insert_opt_impl(const float* d_dataset, uint32_t* d_graph, const uint64_t* d
     a.filter.active_degree = local_degree;
     a.d_seeds = d_seeds;
     a.seeds_per_query = num_seeds_per_query;
+    a.d_ws = ws; a.ws_bytes = ws_bytes;
     GRAB_TRY(graph_search_impl(&a));
   } else {
     fill_empty_kernel<<<(unsigned)((total + 255) / 256), 256>>>(il.as<int64_t>(), dl.as<float>(), total);
     GRAB_CUDA_TRY(cudaGetLastError());
   }
+  tm.mark("bucket search");
   // exact kNN inside the batch, tmp = min(n, search_k/2) wide (cagra_opt.cu:1877-1928)
   const uint32_t tmp = static_cast<uint32_t>(num_new < search_k / 2 ? num_new : search_k / 2);
   if (num_new >= 2 && tmp >= 1) {
-    ScopedDeviceBuffer bi, bd;
-    GRAB_CUDA_TRY(bi.alloc(sizeof(uint32_t) * num_new * tmp));
-    GRAB_CUDA_TRY(bd.alloc(sizeof(float) * num_new * tmp));
+    Buf bi{pool_get(kPoolInsBatchIds, sizeof(uint32_t) * num_new * tmp, false)};
+    Buf bd{pool_get(kPoolInsBatchDist, sizeof(float) * num_new * tmp, false)};
+    if (!bi.ptr || !bd.ptr) {
+      set_last_error("insert: out of device memory for the batch scratch");
+      return GRAB_ERR_CUDA;
+    }
     const uint64_t offs[2] = {0, num_new};
     GRAB_TRY(knn_blocks_impl(d_queries, num_new, dim, metric, offs, 1, tmp, 0, bi.as<uint32_t>(), bd.as<float>(), nullptr));
     const uint32_t padded = next_pow2(search_k + tmp);
@@ -141,9 +156,11 @@ int insert_opt_impl(const float* d_dataset, uint32_t* d_graph, const uint64_t* d
     GRAB_CUDA_TRY(cudaGetLastError());
     GRAB_CUDA_TRY(cudaDeviceSynchronize());
   }
+  tm.mark("batch kNN + merge");
   GRAB_TRY(update_topology_opt_impl(d_graph, d_bucket, il.as<int64_t>(), ig.as<int64_t>(), num_existing, num_new,
                                     target_bucket, total_degree, local_degree, search_k, search_k, nullptr));
   GRAB_CUDA_TRY(cudaDeviceSynchronize());
+  tm.mark("topology update");
   return GRAB_OK;
 }
 

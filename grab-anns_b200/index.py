@@ -41,9 +41,12 @@ class _Base:
         _g.check(getattr(_lib(), self._prefix + name)(C.c_void_p(self.h), *args))
 
     def __del__(self):
-        if getattr(self, "h", None):
-            getattr(_lib(), self._prefix + "destroy")(C.c_void_p(self.h))
-            self.h = None
+        try:
+            if getattr(self, "h", None):
+                getattr(_lib(), self._prefix + "destroy")(C.c_void_p(self.h))
+                self.h = None
+        except Exception:      # interpreter shutdown: the library module may already be gone
+            pass
 
     def _out(self, nq, k):
         return np.empty((nq, k), dtype=np.int64), np.empty((nq, k), dtype=np.float32)
