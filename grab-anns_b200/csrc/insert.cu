@@ -26,6 +26,12 @@ int update_topology_opt_impl(uint32_t*, const uint64_t*, int64_t*, int64_t*, uin
     if (_rc != GRAB_OK) return _rc; \
   } while (0)
 
+// view of a pooled scratch buffer
+struct Buf {
+  void* ptr;
+  template <class T> T* as() { return static_cast<T*>(ptr); }
+};
+
 __global__ void fill_empty_kernel(int64_t* ids, float* dists, uint64_t total) {
   const uint64_t i = blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x;
   if (i >= total) return;
@@ -103,7 +109,6 @@ int insert_opt_impl(const float* d_dataset, uint32_t* d_graph, const uint64_t* d
   GRAB_REQUIRE(search_k >= 2 && search_k <= 512, "insert: itopk_size %u outside [2,512]", search_k);
   StageTimer tm("insert_opt batch");
   // pooled scratch: thousands of batches must not pay cudaMalloc / cudaFree each
-  struct Buf { void* ptr; template <class T> T* as() { return static_cast<T*>(ptr); } };
   Buf ig{pool_get(kPoolInsIdsG, sizeof(int64_t) * num_new * search_k, false)};
   Buf dg{pool_get(kPoolInsDistG, sizeof(float) * num_new * search_k, false)};
   Buf il{pool_get(kPoolInsIdsL, sizeof(int64_t) * num_new * search_k, false)};
