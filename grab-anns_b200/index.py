@@ -70,7 +70,7 @@ class CagraIndexOpt(_Base):
     _prefix = "grab_index_opt_"
 
     def __init__(self, dim, graph_degree=32, local_degree=16, vmm_max_bytes=4 << 30, bucket_width=1, metric=0,
-                 knn_precision=2, seed=0x9E3779B97F4A7C15, insert_batch=32):
+                 knn_precision=2, seed=0x9E3779B97F4A7C15, insert_batch=1024):
         self.dim, self.graph_degree = dim, graph_degree
         self.h = _lib().grab_index_opt_create(C.c_uint32(dim), C.c_uint32(graph_degree), C.c_uint32(local_degree),
                                               C.c_size_t(vmm_max_bytes))
