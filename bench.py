@@ -40,7 +40,13 @@ def parse():
     ap.add_argument("--local-degree", type=int, default=48)
     ap.add_argument("--itopk", type=int, default=64)
     ap.add_argument("--width", type=int, default=3)
-    ap.add_argument("--max-iter", type=int, default=20)
+    ap.add_argument("--max-iter", type=int, default=0,
+                    help="0 = 6 with the entry-point router, 20 without")
+    ap.add_argument("--router-centroids", type=int, default=1024,
+                    help="centroids of the entry-point router that draws the seeds (0 = seeds drawn "
+                         "uniformly inside the filter by the search kernel)")
+    ap.add_argument("--probes", type=int, default=4, help="nearest centroids the seeds are taken from")
+    ap.add_argument("--seeds", type=int, default=32, help="routed seeds per query")
     ap.add_argument("--hash-bitlen", type=int, default=11)
     ap.add_argument("--knn-precision", type=int, default=1,
                     help="0 exact scan, 1 bf16 tensor cores (exact for integer-valued data), 2 split bf16")
@@ -60,6 +66,12 @@ def workload(args):
     if "ts" in w:
         width = max(1, int(n * args.selectivity))
         w["lo"], w["hi"] = ds.range_queries(w["queries"].shape[0], n, width, 2003)
+    else:
+        # label workloads: vectors grouped by label (ids are arbitrary), one bucket per label
+        order = np.argsort(w["labels"], kind="stable")
+        w["base"] = np.ascontiguousarray(w["base"][order])
+        w["labels"] = np.ascontiguousarray(w["labels"][order])
+        w["label_offsets"] = np.searchsorted(w["labels"], np.arange(33), side="left").astype(np.uint32)
     return w
 
 
@@ -215,12 +227,14 @@ def run_reference(args):
 
 
 def workload_config(args, w):
+    filt = f"timestamp-range filter {args.selectivity:.0%}" if "ts" in w else "label filter (1-3 of 16 Zipf labels)"
     return {"workload": f"{args.workload}: {w['base'].shape[0]}x{w['dim']} fp32, {w['queries'].shape[0]} queries, "
-                        f"timestamp-range filter {args.selectivity:.0%}, k {w['k']}, degree {w['degree']}",
+                        f"{filt}, k {w['k']}, degree {w['degree']}",
             "n": int(w["base"].shape[0]), "dim": int(w["dim"]), "queries": int(w["queries"].shape[0]),
             "k": int(w["k"]), "graph_degree": int(w["degree"]), "local_degree": args.local_degree,
-            "buckets": args.buckets, "selectivity": args.selectivity, "itopk": args.itopk,
+            "buckets": args.buckets if "ts" in w else 16, "selectivity": args.selectivity, "itopk": args.itopk,
             "search_width": args.width, "max_iterations": args.max_iter, "hash_bitlen": args.hash_bitlen,
+            "router_centroids": args.router_centroids, "probes": args.probes, "routed_seeds": args.seeds,
             "l2": "inputs (dataset + graph, 768 MB at full size) exceed the 126 MB L2",
             "parallelism": ("one process per GPU, index striped by id across the ranks, queries broadcast, "
                             "all_gather + device merge of per-shard top-k") if getattr(args, "sharded", False) else
@@ -229,6 +243,8 @@ def workload_config(args, w):
 
 def main():
     args = parse()
+    if args.max_iter == 0:
+        args.max_iter = 6 if args.router_centroids else 20
     if args.impl == "reference":
         return run_reference(args)
 
@@ -262,11 +278,17 @@ def main():
     nq = queries.shape[0]
 
     d_base = torch.from_numpy(base).cuda()
-    d_ts = torch.from_numpy(w["ts"].view(np.int64)).cuda()
-    n_total = n * world if args.sharded else n
-    bsize = (n_total + args.buckets - 1) // args.buckets       # bucket width in timestamps
-    h_bucket = w["ts"] // np.uint64(bsize)
-    sizes = np.bincount(h_bucket.astype(np.int64)).tolist()    # timestamps are sorted: buckets are id runs
+    by_labels = "ts" not in w
+    if by_labels:
+        if args.sharded:
+            raise SystemExit("--sharded is implemented for the timestamp workloads")
+        h_bucket = w["labels"].astype(np.uint64)               # one bucket per label
+    else:
+        d_ts = torch.from_numpy(w["ts"].view(np.int64)).cuda()
+        n_total = n * world if args.sharded else n
+        bsize = (n_total + args.buckets - 1) // args.buckets   # bucket width in timestamps
+        h_bucket = w["ts"] // np.uint64(bsize)
+    sizes = np.bincount(h_bucket.astype(np.int64)).tolist()    # sorted keys: buckets are id runs
     d_bucket = torch.from_numpy(h_bucket.view(np.int64)).cuda()
     torch.cuda.synchronize()
     t0 = time.perf_counter()
@@ -274,12 +296,27 @@ def main():
                                               knn_precision=args.knn_precision)
     torch.cuda.synchronize()
     build_s = time.perf_counter() - t0
+    router, router_s = None, 0.0
+    if args.router_centroids:
+        t0 = time.perf_counter()
+        router = grab.router_build(d_base, min(args.router_centroids, n), metric=w["metric"])
+        torch.cuda.synchronize()
+        router_s = time.perf_counter() - t0
 
     h_q = torch.from_numpy(queries).pin_memory()
-    h_lo = torch.from_numpy(w["lo"].view(np.int64)).pin_memory()
-    h_hi = torch.from_numpy(w["hi"].view(np.int64)).pin_memory()
-    d_q, d_lo, d_hi = h_q.cuda(), h_lo.cuda(), h_hi.cuda()
-    flt = grab.make_filter(grab.FILTER_TS_RANGE, ts=d_ts, lo=d_lo, hi=d_hi, ts_sorted=True)
+    d_q = h_q.cuda()
+    if by_labels:
+        h_lo = torch.from_numpy(w["masks"].view(np.int32)).pin_memory()    # per-query label masks
+        h_hi = h_lo
+        d_lo = d_hi = h_lo.cuda()
+        d_labels = torch.from_numpy(w["labels"]).cuda()
+        d_offs = torch.from_numpy(w["label_offsets"].view(np.int32)).cuda()
+        flt = grab.make_filter(grab.FILTER_LABELS, labels=d_labels, masks=d_lo, label_offsets=d_offs)
+    else:
+        h_lo = torch.from_numpy(w["lo"].view(np.int64)).pin_memory()
+        h_hi = torch.from_numpy(w["hi"].view(np.int64)).pin_memory()
+        d_lo, d_hi = h_lo.cuda(), h_hi.cuda()
+        flt = grab.make_filter(grab.FILTER_TS_RANGE, ts=d_ts, lo=d_lo, hi=d_hi, ts_sorted=True)
     params = grab.SearchParams(args.itopk, args.width, 0, args.max_iter, args.hash_bitlen)
     out_ids = torch.empty((nq, k), dtype=torch.int64, device="cuda")
     out_d = torch.empty((nq, k), dtype=torch.float32, device="cuda")
@@ -288,12 +325,25 @@ def main():
     ws = torch.empty(grab.lib().grab_graph_search_workspace_bytes(nq, args.hash_bitlen), dtype=torch.uint8,
                      device="cuda")
 
+    seeds = route_ws = None
+    if router is not None:
+        seeds = torch.empty((nq, args.seeds), dtype=torch.int32, device="cuda")
+        route_ws = torch.empty(grab.lib().grab_route_seeds_workspace_bytes(nq, args.probes), dtype=torch.uint8,
+                               device="cuda")
+
+    def route():
+        if router is not None:
+            grab.route_seeds(router, d_q, n, flt, probes=args.probes, seeds_per_query=args.seeds, out=seeds,
+                             ws=route_ws)
+
     id_scale, id_offset = (world, rank) if args.sharded else (1, 0)
     merge = lambda d, i, kk: grab.merge_topk(d, i, kk)
     # ground truth from the exact filtered kernel (bit-exact against the CPU oracle in tests/)
     gt_ids, gt_d = grab.exact_search(d_base, d_q, k, metric=w["metric"], flt=flt)
+    route()
     ids, dd, stats = grab.graph_search(d_base, graph, d_q, k, params, metric=w["metric"], flt=flt, stats=True,
-                                       out=(out_ids, out_d), ws=ws, id_scale=id_scale, id_offset=id_offset)
+                                       seeds=seeds, out=(out_ids, out_d), ws=ws, id_scale=id_scale,
+                                       id_offset=id_offset)
     if args.sharded:
         gt_ids = torch.where(gt_ids >= 0, gt_ids * world + rank, gt_ids)
         gt_ids, _ = sharded.gather_and_merge(gt_d, gt_ids, k, merge)
@@ -311,22 +361,31 @@ def main():
         hit += np.intersect1d(r, g).size
         denom += g.size
     recall = hit / max(denom, 1)
-    # timestamps equal global ids in this workload
-    in_range = bool(np.all(((res >= w["lo"][:, None].astype(np.int64)) & (res < w["hi"][:, None].astype(np.int64)))
-                           | (res < 0)))
-    # sorted timestamps: id-window predicate, no gather (f = 0); sharded: every rank reads every query
-    alg_bytes = grab.search_bytes(stats, nq * (world if args.sharded else 1), dim, deg, k, 0)
+    if by_labels:
+        lab = w["labels"][np.clip(res, 0, n - 1)]
+        in_range = bool(np.all((((w["masks"][:, None] >> lab) & 1) == 1) | (res < 0)))
+    else:  # timestamps equal global ids in this workload
+        in_range = bool(np.all(((res >= w["lo"][:, None].astype(np.int64)) &
+                                (res < w["hi"][:, None].astype(np.int64))) | (res < 0)))
+    # sorted timestamps: id-window predicate, no gather (f = 0); labels: one byte per examined edge;
+    # sharded: every rank reads every query
+    alg_bytes = grab.search_bytes(stats, nq * (world if args.sharded else 1), dim, deg, k, 1 if by_labels else 0)
+
+    def search_only():
+        grab.graph_search(d_base, graph, d_q, k, params, metric=w["metric"], flt=flt, seeds=seeds,
+                          out=(out_ids, out_d), ws=ws, id_scale=id_scale, id_offset=id_offset)
 
     def step():
-        grab.graph_search(d_base, graph, d_q, k, params, metric=w["metric"], flt=flt, out=(out_ids, out_d), ws=ws,
-                          id_scale=id_scale, id_offset=id_offset)
+        route()
+        search_only()
         if args.sharded:
             sharded.gather_and_merge(out_d, out_ids, k, merge)
 
     def e2e_step():
         d_q.copy_(h_q, non_blocking=True)
         d_lo.copy_(h_lo, non_blocking=True)
-        d_hi.copy_(h_hi, non_blocking=True)
+        if not by_labels:
+            d_hi.copy_(h_hi, non_blocking=True)
         step()
         h_ids.copy_(out_ids, non_blocking=True)
         h_d.copy_(out_d, non_blocking=True)
@@ -357,6 +416,8 @@ def main():
     ms = timed(step, args.steps, max(args.warmup, 3))
     clocks = sampler.stop()
     ms_e2e = timed(e2e_step, args.steps, max(args.warmup, 3))
+    # the dominant kernel alone (the search launch with the routed seeds already written), for the roofline
+    ms_search = timed(search_only, args.steps, max(args.warmup, 3)) if router is not None or args.sharded else ms
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -374,12 +435,12 @@ def main():
         except Exception:
             pass
         peak = float(peaks.get("hbm_gbs", 6650.0))
-        achieved = alg_bytes / (ms / 1e3) / 1e9
+        achieved = alg_bytes / (ms_search / 1e3) / 1e9
         # dram__bytes_read.sum + dram__bytes_write.sum of one search launch at the default full-size
         # configuration (ncu capture summarised in profiles/graph_search_kernel_C2.md)
         default_cfg = (args.workload == "C2" and args.scale == 1.0 and args.buckets == 20 and args.itopk == 64 and
                        args.width == 3 and args.max_iter == 20 and args.hash_bitlen == 11 and
-                       args.selectivity == 0.10 and not args.sharded)
+                       args.selectivity == 0.10 and not args.sharded and router is None)
         traffic = 4141677056 + 1401856 if default_cfg else None
         line = {
             "metric": "filtered QPS at recall@10>=0.95",
@@ -388,10 +449,15 @@ def main():
             "higher_is_better": True, "scaling": "strong" if args.sharded else "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic", "config": workload_config(args, w),
             "recall_at_10": recall, "results_in_range": in_range,
-            "build": {"seconds": build_s, "mvec_per_s": n / build_s / 1e6, "knn_precision": args.knn_precision},
+            "build": {"seconds": build_s, "mvec_per_s": n / build_s / 1e6, "knn_precision": args.knn_precision,
+                      "router_seconds": router_s},
+            "ms_search_kernel": ms_search, "ms_router": ms - ms_search if router is not None and not args.sharded else None,
             "e2e": {"value": (1 if args.sharded else world) * nq / (ms_e2e / 1e3), "unit": "queries/s",
-                    "h2d_bytes_per_step": int(h_q.numel() * 4 + 16 * nq), "d2h_bytes_per_step": int(12 * nq * k)},
-            "gpu_launches": (4 if args.sharded and world > 1 else 2) * args.steps,
+                    "h2d_bytes_per_step": int(h_q.numel() * 4 + (4 if by_labels else 16) * nq), "d2h_bytes_per_step": int(12 * nq * k)},
+            # per step: nearest-centroids + seed picking (router), id windows (sorted timestamps), search,
+            # and the merge after the all_gather when sharded
+            "gpu_launches": ((2 if router is not None else 0) + (1 if by_labels else 2) +
+                             (2 if args.sharded and world > 1 else 0)) * args.steps,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": traffic,
                          "peak_source": "measured" if peaks else "fallback",

@@ -45,7 +45,7 @@ class Filter(C.Structure):
     _fields_ = [("kind", C.c_int32), ("ts_sorted", C.c_int32), ("d_ts", C.c_void_p),
                 ("d_lo", C.c_void_p), ("d_hi", C.c_void_p), ("lo", C.c_uint64), ("hi", C.c_uint64),
                 ("d_labels", C.c_void_p), ("d_masks", C.c_void_p), ("mask", C.c_uint32),
-                ("active_degree", C.c_uint32)]
+                ("active_degree", C.c_uint32), ("d_label_offsets", C.c_void_p)]
 
 
 class SearchStats(C.Structure):
@@ -62,6 +62,12 @@ class SearchArgs(C.Structure):
                 ("d_out_dists", C.c_void_p), ("id_scale", C.c_uint64), ("id_offset", C.c_uint64),
                 ("d_stats", C.c_void_p), ("d_ws", C.c_void_p), ("ws_bytes", C.c_size_t),
                 ("stream", C.c_void_p)]
+
+
+class RouterStruct(C.Structure):
+    _fields_ = [("num_centroids", C.c_uint32), ("dim", C.c_uint32), ("metric", C.c_int32),
+                ("d_centroids", C.c_void_p), ("d_centroid_norms", C.c_void_p),
+                ("d_member_offsets", C.c_void_p), ("d_members", C.c_void_p)]
 
 
 _lib = None
@@ -90,6 +96,8 @@ def lib() -> C.CDLL:
         _lib.grab_exact_search_workspace_bytes.argtypes = [C.c_uint64, C.c_uint64, C.c_uint32]
         _lib.grab_graph_search_workspace_bytes.restype = C.c_size_t
         _lib.grab_graph_search_workspace_bytes.argtypes = [C.c_uint64, C.c_uint32]
+        _lib.grab_route_seeds_workspace_bytes.restype = C.c_size_t
+        _lib.grab_route_seeds_workspace_bytes.argtypes = [C.c_uint64, C.c_uint32]
     return _lib
 
 
@@ -114,7 +122,7 @@ def _stream():
 
 
 def make_filter(kind=FILTER_NONE, ts=None, lo=None, hi=None, ts_sorted=False, labels=None,
-                masks=None, active_degree=0) -> Filter:
+                masks=None, active_degree=0, label_offsets=None) -> Filter:
     f = Filter()
     f.kind = kind
     f.ts_sorted = int(ts_sorted)
@@ -129,8 +137,9 @@ def make_filter(kind=FILTER_NONE, ts=None, lo=None, hi=None, ts_sorted=False, la
     elif masks is not None:
         f.mask = int(masks)
     f.active_degree = active_degree
+    f.d_label_offsets = _p(label_offsets)
     # the struct only holds raw pointers: keep the tensors alive as long as the filter is
-    f._keepalive = (ts, lo, hi, labels, masks)
+    f._keepalive = (ts, lo, hi, labels, masks, label_offsets)
     return f
 
 
@@ -228,6 +237,55 @@ def merge_topk(dists, ids, k):
     check(lib().grab_merge_topk(_p(dists), _p(ids), C.c_uint64(nq), C.c_uint32(parts), C.c_uint32(k),
                                 _p(out_ids), _p(out_d), _stream()))
     return out_ids, out_d
+
+
+class Router:
+    """Entry-point router (grab_router): centroids plus the ids grouped by nearest centroid."""
+
+    def __init__(self, centroids, norms, offsets, members, metric):
+        self.centroids, self.norms, self.offsets, self.members, self.metric = centroids, norms, offsets, members, metric
+        self.struct = RouterStruct(centroids.shape[0], centroids.shape[1], metric, _p(centroids), _p(norms),
+                                   _p(offsets), _p(members))
+
+
+def router_build(dataset, num_centroids, metric=METRIC_L2, iterations=10, max_sample=0, centroids=None, norms=None):
+    """grab_router_build; with `centroids`/`norms` given and iterations=0 only re-assigns."""
+    import torch
+    n, dim = dataset.shape
+    dev = dataset.device
+    if centroids is None:
+        centroids = torch.empty((num_centroids, dim), dtype=torch.float32, device=dev)
+        norms = torch.empty(num_centroids, dtype=torch.float32, device=dev)
+    offsets = torch.empty(num_centroids + 1, dtype=torch.int32, device=dev)
+    members = torch.empty(n, dtype=torch.int32, device=dev)
+    check(lib().grab_router_build(_p(dataset), C.c_uint32(dim), C.c_uint64(n), C.c_int(metric),
+                                  C.c_uint32(num_centroids), C.c_uint32(iterations), C.c_uint64(max_sample),
+                                  _p(centroids), _p(norms), _p(offsets), _p(members), _stream()))
+    return Router(centroids, norms, offsets, members, metric)
+
+
+def nearest_centroids(router: Router, rows, probes=1):
+    import torch
+    out = torch.empty((rows.shape[0], probes), dtype=torch.int32, device=rows.device)
+    check(lib().grab_nearest_centroids(C.byref(router.struct), _p(rows), C.c_uint64(rows.shape[0]),
+                                       C.c_uint32(probes), _p(out), _stream()))
+    return out
+
+
+def route_seeds(router: Router, queries, n, flt: Filter | None = None, probes=4, seeds_per_query=32,
+                seed=0x1234ABCD, out=None, ws=None):
+    """grab_route_seeds: int32 tensor [nq, seeds_per_query] (-1 = no seed found) for `seeds=`."""
+    import torch
+    nq = queries.shape[0]
+    if out is None:
+        out = torch.empty((nq, seeds_per_query), dtype=torch.int32, device=queries.device)
+    if ws is None:
+        ws = torch.empty(lib().grab_route_seeds_workspace_bytes(nq, probes), dtype=torch.uint8, device=queries.device)
+    check(lib().grab_route_seeds(C.byref(router.struct), _p(queries), C.c_uint64(nq), C.c_uint64(n),
+                                 C.byref(flt) if flt is not None else None, C.c_uint32(probes),
+                                 C.c_uint32(seeds_per_query), C.c_uint64(seed), _p(out), _p(ws),
+                                 C.c_size_t(ws.numel()), _stream()))
+    return out
 
 
 def search_bytes(stats: SearchStats, nq: int, dim: int, deg: int, k: int, filter_bytes: int) -> int:

@@ -80,6 +80,11 @@ int knn_blocks_impl(const float*, uint64_t, uint32_t, int, const uint64_t*, uint
                     uint32_t*, float*, cudaStream_t);
 int knn_tc_impl(const float*, uint64_t, uint32_t, int, const uint64_t*, uint32_t, uint32_t, int, int, uint32_t*,
                 float*, cudaStream_t);
+int router_build_impl(const float*, uint32_t, uint64_t, int, uint32_t, uint32_t, uint64_t, float*, float*, uint32_t*,
+                      uint32_t*, cudaStream_t);
+int route_seeds_impl(const grab_router*, const float*, uint64_t, uint64_t, const grab_filter*, uint32_t, uint32_t,
+                     uint64_t, uint32_t*, void*, size_t, cudaStream_t);
+int nearest_centroids_impl(const grab_router*, const float*, uint64_t, uint32_t, uint32_t*, cudaStream_t);
 int merge_topk_impl(const float*, const int64_t*, uint64_t, uint32_t, uint32_t, int64_t*, float*,
                     cudaStream_t);
 int graph_search_impl(const grab_search_args*);
@@ -387,6 +392,25 @@ int grab_update_topology_opt(uint32_t* d_graph, const uint64_t* d_bucket, int64_
 int grab_merge_topk(const float* d_dists, const int64_t* d_ids, uint64_t nq, uint32_t parts, uint32_t k,
                     int64_t* d_out_ids, float* d_out_dists, void* stream) {
   return merge_topk_impl(d_dists, d_ids, nq, parts, k, d_out_ids, d_out_dists, static_cast<cudaStream_t>(stream));
+}
+
+int grab_router_build(const float* d_dataset, uint32_t dim, uint64_t n, int metric, uint32_t num_centroids,
+                      uint32_t iterations, uint64_t max_sample, float* d_centroids, float* d_centroid_norms,
+                      uint32_t* d_member_offsets, uint32_t* d_members, void* stream) {
+  return router_build_impl(d_dataset, dim, n, metric, num_centroids, iterations, max_sample, d_centroids,
+                           d_centroid_norms, d_member_offsets, d_members, static_cast<cudaStream_t>(stream));
+}
+
+int grab_nearest_centroids(const grab_router* router, const float* d_rows, uint64_t m, uint32_t probes,
+                           uint32_t* d_out, void* stream) {
+  return nearest_centroids_impl(router, d_rows, m, probes, d_out, static_cast<cudaStream_t>(stream));
+}
+
+int grab_route_seeds(const grab_router* router, const float* d_queries, uint64_t nq, uint64_t n,
+                     const grab_filter* filter, uint32_t probes, uint32_t seeds_per_query, uint64_t seed,
+                     uint32_t* d_seeds, void* d_ws, size_t ws_bytes, void* stream) {
+  return route_seeds_impl(router, d_queries, nq, n, filter, probes, seeds_per_query, seed, d_seeds, d_ws, ws_bytes,
+                          static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

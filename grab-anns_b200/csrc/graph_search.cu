@@ -61,6 +61,7 @@ struct SearchKernelArgs {
   const uint8_t* labels;
   const uint32_t* masks;
   uint32_t mask1;
+  const uint32_t* label_offsets;  // [33] id range per label (vectors grouped by label), or NULL
   const uint32_t* windows;  // [nq,4] id window per query (sorted ts), or NULL
   uint32_t* global_hash;    // [nq, 2^bitlen] when the table does not fit shared memory
   int64_t* out_ids;
@@ -204,8 +205,10 @@ graph_search_kernel(const SearchKernelArgs a) {
   {
     const uint32_t wlen = wend - wbeg;
     const bool generated_only = (a.seeds == nullptr);
+    const bool by_label_range = a.filter_kind == GRAB_FILTER_LABELS && a.label_offsets != nullptr && mask != 0;
+    const uint32_t nlab = __popc(mask);
     // without an id window a generated seed may fail the filter: allow 4 attempts per seed
-    const uint32_t attempts = (generated_only && !a.windows && a.filter_kind != GRAB_FILTER_NONE &&
+    const uint32_t attempts = (generated_only && !a.windows && !by_label_range && a.filter_kind != GRAB_FILTER_NONE &&
                                a.filter_kind != GRAB_FILTER_PREFIX) ? 4 * a.num_seeds : a.num_seeds;
     for (uint32_t i = tid; i < attempts; i += kSearchThreads) {
       uint32_t id = kInvalid;
@@ -214,6 +217,14 @@ graph_search_kernel(const SearchKernelArgs a) {
         if (a.windows) {
           id = wlen ? wbeg + static_cast<uint32_t>(mix64(a.seed ^ (qi * 0x9e3779b97f4a7c15ull + i)) % wlen)
                     : kInvalid;
+        } else if (by_label_range) {
+          // round-robin over the query's labels, a pseudo-random member of the label's id range
+          uint32_t m = mask;
+          for (uint32_t skip = i % nlab; skip > 0; --skip) m &= m - 1;
+          const uint32_t lab = __ffs(m) - 1;
+          const uint32_t lb = a.label_offsets[lab], le = a.label_offsets[lab + 1];
+          id = le > lb ? lb + static_cast<uint32_t>(mix64(a.seed ^ (qi * 0x9e3779b97f4a7c15ull + i)) % (le - lb))
+                       : kInvalid;
         } else {
           // reference rule: (xor_mask * (i+1)) % n, compute_distance.cuh:236-238
           id = static_cast<uint32_t>(((a.seed | 1ull) * static_cast<uint64_t>(i + 1)) % a.n);
@@ -473,6 +484,7 @@ int graph_search_impl(const grab_search_args* g) {
     case GRAB_FILTER_LABELS:
       GRAB_REQUIRE(f.d_labels, "graph_search: label filter without d_labels");
       a.labels = f.d_labels; a.masks = f.d_masks; a.mask1 = f.mask;
+      a.label_offsets = f.d_label_offsets;  // also fills holes (ids >= n) in a provided seed list
       break;
     default:
       set_last_error("graph_search: unknown filter kind %d", f.kind);

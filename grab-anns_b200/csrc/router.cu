@@ -1,0 +1,538 @@
+// Entry-point router: filter-aware search seeds close to the query.
+//
+// The reference samples search seeds on the host, uniformly among the ids that pass the filter
+// (cagraIndexOpt.cu:441-511 for query_range, :313-336 for query_local, cagraIndex.cu:267-296),
+// and its two-level index routes a query through k-means centroids, each with a few entry
+// points (timeStampIndex.cu:141-238 build_virtual_index, :240-419 query).  This file is the
+// device version of both ideas in one structure:
+//
+//   build : Lloyd's k-means over a strided sample of the dataset (every step deterministic),
+//           then every vector is assigned to its nearest centroid and the ids are grouped by
+//           centroid, ascending inside each group (a CSR list).
+//   route : per query the `probes` nearest centroids (one tiled fp32 GEMM-with-selection
+//           kernel), then for every (centroid, filter window) pair a few members of the
+//           centroid's id list that fall inside the window -- found by binary search because
+//           the list is sorted by id and a sorted-timestamp range or a label range is an id
+//           range.  Filters without id windows draw members and test the predicate.
+//
+// The result is the [nq, seeds_per_query] uint32 seed array every search entry point takes
+// (d_seeds); slots that found nothing hold 0xFFFFFFFF and the search kernel fills them with
+// its own pseudo-random draws.
+#include "common.cuh"
+
+namespace grab {
+namespace {
+
+constexpr int kRtBM = 64;        // rows (queries or vectors) per CTA
+constexpr int kRtBN = 64;        // centroids per tile
+constexpr int kRtBK = 16;        // dimensions per shared-memory stage
+constexpr int kRtThreads = 256;  // 16 x 16 threads, 4 x 4 outputs each
+constexpr uint32_t kMaxProbes = 16;
+
+__device__ __forceinline__ uint64_t rt_mix64(uint64_t x) {  // splitmix64 finaliser
+  x ^= x >> 30; x *= 0xbf58476d1ce4e5b9ull;
+  x ^= x >> 27; x *= 0x94d049bb133111ebull;
+  x ^= x >> 31;
+  return x;
+}
+
+// ---------------------------------------------------------------------------------------
+// Nearest centroids.  score(x, c) = |c|^2 - 2 x.c (L2, the |x|^2 term is the same for all
+// centroids) or -x.c (inner product); x.c is ONE fused-multiply-add chain over the dimensions
+// in ascending order, so a CPU loop reproduces the bits.  Each row keeps its `P` best
+// (score, centroid) keys, ties to the lower centroid id.
+// ---------------------------------------------------------------------------------------
+template <int METRIC>
+__global__ void __launch_bounds__(kRtThreads)
+nearest_centroids_kernel(const float* __restrict__ X, uint64_t m, uint32_t dim,
+                         const float* __restrict__ cen, const float* __restrict__ cnorm, uint32_t C,
+                         uint32_t P, uint32_t* __restrict__ out) {
+  __shared__ __align__(16) float As[kRtBK][kRtBM + 4];
+  __shared__ __align__(16) float Bs[kRtBK][kRtBN + 4];
+  __shared__ float S[kRtBM][kRtBN + 1];
+  __shared__ uint64_t top[kMaxProbes][kRtBM];
+
+  const uint32_t tid = threadIdx.x;
+  const uint32_t tx = tid & 15u, ty = tid >> 4;
+  const uint64_t row0 = static_cast<uint64_t>(blockIdx.x) * kRtBM;
+  const uint32_t lrow = tid >> 2, lk = (tid & 3u) * 4;  // this thread's float4 of a 64 x 16 stage
+
+  for (uint32_t j = tid; j < kMaxProbes * kRtBM; j += kRtThreads) (&top[0][0])[j] = kMaxKey;
+
+  for (uint32_t c0 = 0; c0 < C; c0 += kRtBN) {
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+
+    for (uint32_t k0 = 0; k0 < dim; k0 += kRtBK) {
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+      if (k0 + lk < dim) {
+        if (row0 + lrow < m) a = ldg_f4(X + (row0 + lrow) * dim + k0 + lk);
+        if (c0 + lrow < C) b = ldg_f4(cen + static_cast<uint64_t>(c0 + lrow) * dim + k0 + lk);
+      }
+      __syncthreads();  // the previous stage (and the previous tile's row scan) is done
+      As[lk + 0][lrow] = a.x; As[lk + 1][lrow] = a.y; As[lk + 2][lrow] = a.z; As[lk + 3][lrow] = a.w;
+      Bs[lk + 0][lrow] = b.x; Bs[lk + 1][lrow] = b.y; Bs[lk + 2][lrow] = b.z; Bs[lk + 3][lrow] = b.w;
+      __syncthreads();
+#pragma unroll
+      for (int kk = 0; kk < kRtBK; ++kk) {
+        const float4 av = *reinterpret_cast<const float4*>(&As[kk][ty * 4]);
+        const float4 bv = *reinterpret_cast<const float4*>(&Bs[kk][tx * 4]);
+        const float ar[4] = {av.x, av.y, av.z, av.w};
+        const float br[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[i][j] = __fmaf_rn(ar[i], br[j], acc[i][j]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t c = c0 + tx * 4 + j;
+      const float cn = (METRIC == GRAB_METRIC_L2 && c < C) ? __ldg(cnorm + c) : 0.0f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        S[ty * 4 + i][tx * 4 + j] = METRIC == GRAB_METRIC_L2 ? __fmaf_rn(-2.0f, acc[i][j], cn) : -acc[i][j];
+    }
+    __syncthreads();
+    if (tid < kRtBM && row0 + tid < m) {  // one thread per row folds the tile into the row's list
+      uint64_t worst = top[P - 1][tid];
+      const uint32_t ncol = C - c0 < kRtBN ? C - c0 : kRtBN;
+      for (uint32_t col = 0; col < ncol; ++col) {
+        const uint64_t key = make_key(S[tid][col], c0 + col);
+        if (key < worst) {
+          uint32_t j = P - 1;
+          while (j > 0 && top[j - 1][tid] > key) {
+            top[j][tid] = top[j - 1][tid];
+            --j;
+          }
+          top[j][tid] = key;
+          worst = top[P - 1][tid];
+        }
+      }
+    }
+  }
+  __syncthreads();
+  for (uint32_t j = tid; j < kRtBM * P; j += kRtThreads) {
+    const uint32_t r = j / P, p = j % P;
+    if (row0 + r < m) {
+      const uint64_t key = top[p][r];
+      out[(row0 + r) * P + p] = key == kMaxKey ? kInvalid : key_id(key);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Grouping ids by centroid, ascending inside each group, without a sort and without atomics
+// on positions: ids are cut into chunks of consecutive ids; counts[chunk][c] is turned into
+// the chunk's first slot inside group c by a column scan; one warp then walks its chunk in id
+// order and hands out slots (lanes with the same centroid are ranked by lane index).
+// ---------------------------------------------------------------------------------------
+constexpr uint32_t kChunk = 2048;
+
+__global__ void chunk_count_kernel(const uint32_t* __restrict__ assign, uint64_t n, uint32_t C,
+                                   uint32_t* __restrict__ counts) {
+  const uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const uint32_t c = assign[i];
+  if (c < C) atomicAdd(&counts[(i / kChunk) * C + c], 1u);
+}
+
+__global__ void column_scan_kernel(uint32_t* __restrict__ counts, uint32_t nchunks, uint32_t C,
+                                   uint32_t* __restrict__ totals) {
+  const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  uint32_t run = 0;
+  for (uint32_t ch = 0; ch < nchunks; ++ch) {
+    const uint32_t v = counts[static_cast<uint64_t>(ch) * C + c];
+    counts[static_cast<uint64_t>(ch) * C + c] = run;
+    run += v;
+  }
+  totals[c] = run;
+}
+
+// offsets[0..C] = exclusive scan of totals; one CTA of 1024 threads.
+__global__ void offsets_kernel(const uint32_t* __restrict__ totals, uint32_t C, uint32_t* __restrict__ offsets) {
+  __shared__ uint32_t part[1024];
+  const uint32_t t = threadIdx.x;
+  const uint32_t per = (C + 1023) / 1024;
+  const uint32_t b = t * per, e = b + per < C ? b + per : C;
+  uint32_t s = 0;
+  for (uint32_t c = b; c < e; ++c) s += totals[c];
+  part[t] = s;
+  __syncthreads();
+  if (t == 0) {
+    uint32_t run = 0;
+    for (uint32_t j = 0; j < 1024; ++j) {
+      const uint32_t v = part[j];
+      part[j] = run;
+      run += v;
+    }
+    offsets[C] = run;
+  }
+  __syncthreads();
+  uint32_t run = part[t];
+  for (uint32_t c = b; c < e; ++c) {
+    offsets[c] = run;
+    run += totals[c];
+  }
+}
+
+__global__ void chunk_fill_kernel(const uint32_t* __restrict__ assign, uint64_t n, uint32_t C,
+                                  uint32_t* __restrict__ counts, const uint32_t* __restrict__ offsets,
+                                  uint32_t* __restrict__ members) {
+  const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const uint32_t lane = threadIdx.x & 31u;
+  const uint64_t begin = static_cast<uint64_t>(warp) * kChunk;
+  if (begin >= n) return;
+  const uint64_t end = begin + kChunk < n ? begin + kChunk : n;
+  uint32_t* row = counts + static_cast<uint64_t>(warp) * C;  // private to this warp
+  for (uint64_t i0 = begin; i0 < end; i0 += 32) {
+    const uint64_t i = i0 + lane;
+    const uint32_t c = i < end ? assign[i] : kInvalid;
+    const bool valid = c < C;
+    const uint32_t mask = __match_any_sync(0xFFFFFFFFu, c);
+    const uint32_t rank = __popc(mask & ((1u << lane) - 1u));
+    const int leader = __ffs(mask) - 1;
+    uint32_t base = 0;
+    if (valid && static_cast<int>(lane) == leader) {
+      base = row[c];
+      row[c] = base + __popc(mask);
+    }
+    base = __shfl_sync(0xFFFFFFFFu, base, leader);
+    if (valid) members[offsets[c] + base + rank] = static_cast<uint32_t>(i);
+    __syncwarp();
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// k-means pieces.  Sample row s is dataset row floor(s * n / m).
+// ---------------------------------------------------------------------------------------
+__global__ void gather_rows_kernel(const float* __restrict__ X, uint64_t n, uint32_t dim, uint64_t m,
+                                   uint64_t out_rows, float* __restrict__ out) {
+  // out row r = X row floor((r * m / out_rows) * n / m): out_rows == m gives the sample itself,
+  // out_rows == C gives C sample rows spread evenly (the initial centroids)
+  const uint32_t nchunk = dim / 4;
+  const uint64_t idx = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= out_rows * nchunk) return;
+  const uint64_t r = idx / nchunk, c = idx % nchunk;
+  const uint64_t s = r * m / out_rows;
+  const uint64_t src = s * n / m;  // s < m <= n < 2^31: no overflow
+  reinterpret_cast<float4*>(out)[r * nchunk + c] = ldg_f4(X + src * dim + 4 * c);
+}
+
+// Squared norm of a row held by one warp: lane l takes dimensions l, l+32, ... ascending
+// (fused multiply-add), then a butterfly over xor 16, 8, 4, 2, 1.
+__device__ __forceinline__ float warp_sqnorm(const float* v, uint32_t dim, uint32_t lane) {
+  float acc = 0.0f;
+  for (uint32_t k = lane; k < dim; k += 32) acc = __fmaf_rn(v[k], v[k], acc);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xFFFFFFFFu, acc, o));
+  return acc;
+}
+
+// One CTA per centroid: mean of its sample members, summed in ascending sample order with
+// plain fp32 adds; empty groups keep the old centroid.  For the inner-product metric the mean
+// is scaled to unit length (spherical k-means).  Also writes |c|^2.
+__global__ void __launch_bounds__(128)
+centroid_update_kernel(const float* __restrict__ sample, uint32_t dim, const uint32_t* __restrict__ offsets,
+                       const uint32_t* __restrict__ members, int metric, float* __restrict__ cen,
+                       float* __restrict__ cnorm) {
+  extern __shared__ float v[];  // dim floats
+  __shared__ float s_norm;
+  const uint32_t c = blockIdx.x;
+  const uint32_t b = offsets[c], e = offsets[c + 1];
+  float* out = cen + static_cast<uint64_t>(c) * dim;
+  for (uint32_t k = threadIdx.x; k < dim; k += blockDim.x) {
+    float val = out[k];
+    if (e > b) {
+      float s = 0.0f;
+      for (uint32_t j = b; j < e; ++j) s = __fadd_rn(s, __ldg(sample + static_cast<uint64_t>(members[j]) * dim + k));
+      val = __fdiv_rn(s, static_cast<float>(e - b));
+    }
+    v[k] = val;
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    const float n2 = warp_sqnorm(v, dim, threadIdx.x);
+    if (threadIdx.x == 0) s_norm = n2;
+  }
+  __syncthreads();
+  if (metric == GRAB_METRIC_IP && e > b && s_norm > 0.0f) {
+    const float len = __fsqrt_rn(s_norm);
+    for (uint32_t k = threadIdx.x; k < dim; k += blockDim.x) v[k] = __fdiv_rn(v[k], len);
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      const float n2 = warp_sqnorm(v, dim, threadIdx.x);
+      if (threadIdx.x == 0) s_norm = n2;
+    }
+    __syncthreads();
+  }
+  for (uint32_t k = threadIdx.x; k < dim; k += blockDim.x) out[k] = v[k];
+  if (threadIdx.x == 0) cnorm[c] = s_norm;
+}
+
+// ---------------------------------------------------------------------------------------
+// Seeds.  One warp per query.  Slot s: probe j = s mod p, t = s div p, window w = t mod nwin,
+// pick r = t div nwin.  The members of centroid probes[j] inside window w form a sub-run of
+// length L of the centroid's sorted id list; pick r takes element (start + r * step) mod L
+// with step = max(1, L / per), per = ceil(S / (p * nwin)), start pseudo-random: picks of one
+// pair are distinct, pairs are disjoint, so a query never gets the same seed twice.
+// ---------------------------------------------------------------------------------------
+struct RouteArgs {
+  const uint32_t* probes;  // [nq, p]
+  uint32_t p, S, C;
+  uint64_t nq, n, seed;
+  const uint32_t* offsets;
+  const uint32_t* members;
+  int filter_kind, ts_sorted;
+  const uint64_t* ts; const uint64_t* lo; const uint64_t* hi; uint64_t lo1, hi1;
+  const uint8_t* labels; const uint32_t* masks; uint32_t mask1; const uint32_t* label_offsets;
+  uint32_t* seeds;  // [nq, S]
+};
+
+__device__ __forceinline__ uint32_t lower_bound_u32(const uint32_t* a, uint32_t b, uint32_t e, uint32_t x) {
+  while (b < e) {  // first position in [b,e) with a[pos] >= x
+    const uint32_t mid = (b + e) >> 1;
+    if (a[mid] < x) b = mid + 1; else e = mid;
+  }
+  return b;
+}
+
+__global__ void __launch_bounds__(256) route_seeds_kernel(RouteArgs a) {
+  const uint64_t q = (static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const uint32_t lane = threadIdx.x & 31u;
+  if (q >= a.nq) return;
+  const uint32_t n32 = static_cast<uint32_t>(a.n);
+
+  // the query's id windows
+  uint32_t nwin = 1, wlo = 0, whi = n32, mask = 0;
+  bool check = false;  // no id window: test the predicate on every pick
+  uint64_t tlo = 0, thi = 0;
+  if (a.filter_kind == GRAB_FILTER_TS_RANGE || (a.filter_kind == GRAB_FILTER_PREFIX && a.ts)) {
+    tlo = a.lo ? a.lo[q] : a.lo1;
+    thi = a.hi ? a.hi[q] : a.hi1;
+    if (a.ts_sorted) {
+      uint32_t b = 0, e = n32;
+      while (b < e) { const uint32_t mid = (b + e) >> 1; if (a.ts[mid] < tlo) b = mid + 1; else e = mid; }
+      wlo = b;
+      e = n32;
+      while (b < e) { const uint32_t mid = (b + e) >> 1; if (a.ts[mid] < thi) b = mid + 1; else e = mid; }
+      whi = b;
+      if (whi <= wlo) nwin = 0;
+    } else {
+      check = true;
+      if (thi <= tlo) nwin = 0;
+    }
+  } else if (a.filter_kind == GRAB_FILTER_LABELS) {
+    mask = a.masks ? a.masks[q] : a.mask1;
+    if (a.label_offsets) nwin = __popc(mask);
+    else { check = true; if (mask == 0) nwin = 0; }
+  }
+  const uint32_t p = a.p;
+  const uint32_t pairs = p * (nwin ? nwin : 1);
+  const uint32_t per = (a.S + pairs - 1) / pairs;
+
+  for (uint32_t s = lane; s < a.S; s += 32) {
+    uint32_t id = kInvalid;
+    if (nwin) {
+      const uint32_t j = s % p, t = s / p, w = t % nwin, r = t / nwin;
+      const uint32_t c = a.probes[q * p + j];
+      if (c < a.C) {
+        uint32_t lo_id = wlo, hi_id = whi;
+        if (a.filter_kind == GRAB_FILTER_LABELS && a.label_offsets) {
+          uint32_t mm = mask;
+          for (uint32_t skip = w; skip > 0; --skip) mm &= mm - 1;
+          const uint32_t lab = __ffs(mm) - 1;
+          lo_id = a.label_offsets[lab];
+          hi_id = a.label_offsets[lab + 1];
+        }
+        const uint32_t rb = a.offsets[c], re = a.offsets[c + 1];
+        const uint32_t b = lower_bound_u32(a.members, rb, re, lo_id);
+        const uint32_t e = lower_bound_u32(a.members, b, re, hi_id);
+        const uint32_t L = e - b;
+        if (r < L) {
+          const uint32_t step = L / per > 1 ? L / per : 1;
+          const uint32_t start = static_cast<uint32_t>(
+              rt_mix64(a.seed ^ (q * 0x9e3779b97f4a7c15ull + (static_cast<uint64_t>(c) << 8) + w)) % L);
+          const uint32_t pos = static_cast<uint32_t>((start + static_cast<uint64_t>(r) * step) % L);
+          if (!check) {
+            id = a.members[b + pos];
+          } else {
+            // a pick that fails the predicate is replaced by the next members of the run (4 tries);
+            // tries of different picks may meet, the search kernel drops duplicate seeds
+            for (uint32_t tr = 0; tr < 4 && tr < L; ++tr) {
+              const uint32_t cand = a.members[b + (pos + tr) % L];
+              bool ok;
+              if (a.filter_kind == GRAB_FILTER_LABELS) ok = ((mask >> (a.labels[cand] & 31u)) & 1u) != 0;
+              else { const uint64_t tv = a.ts[cand]; ok = tv >= tlo && tv < thi; }
+              if (ok) { id = cand; break; }
+            }
+          }
+        }
+      }
+    }
+    a.seeds[q * a.S + s] = id;
+  }
+}
+
+template <int METRIC>
+cudaError_t launch_nearest(const float* X, uint64_t m, uint32_t dim, const float* cen, const float* cnorm,
+                           uint32_t C, uint32_t P, uint32_t* out, cudaStream_t st) {
+  if (m == 0) return cudaSuccess;
+  nearest_centroids_kernel<METRIC><<<static_cast<unsigned>((m + kRtBM - 1) / kRtBM), kRtThreads, 0, st>>>(
+      X, m, dim, cen, cnorm, C, P, out);
+  return cudaGetLastError();
+}
+
+cudaError_t nearest(int metric, const float* X, uint64_t m, uint32_t dim, const float* cen, const float* cnorm,
+                    uint32_t C, uint32_t P, uint32_t* out, cudaStream_t st) {
+  return metric == GRAB_METRIC_L2 ? launch_nearest<GRAB_METRIC_L2>(X, m, dim, cen, cnorm, C, P, out, st)
+                                  : launch_nearest<GRAB_METRIC_IP>(X, m, dim, cen, cnorm, C, P, out, st);
+}
+
+// assign[m] -> offsets[C+1], members[m]; counts is scratch of ceil(m/kChunk) * C words
+int group_by_centroid(const uint32_t* assign, uint64_t m, uint32_t C, uint32_t* counts, uint32_t* totals,
+                      uint32_t* offsets, uint32_t* members, cudaStream_t st) {
+  const uint32_t nchunks = static_cast<uint32_t>((m + kChunk - 1) / kChunk);
+  GRAB_CUDA_TRY(cudaMemsetAsync(counts, 0, sizeof(uint32_t) * static_cast<size_t>(nchunks) * C, st));
+  chunk_count_kernel<<<static_cast<unsigned>((m + 255) / 256), 256, 0, st>>>(assign, m, C, counts);
+  column_scan_kernel<<<(C + 255) / 256, 256, 0, st>>>(counts, nchunks, C, totals);
+  offsets_kernel<<<1, 1024, 0, st>>>(totals, C, offsets);
+  chunk_fill_kernel<<<(nchunks * 32 + 255) / 256, 256, 0, st>>>(assign, m, C, counts, offsets, members);
+  GRAB_CUDA_TRY(cudaGetLastError());
+  return GRAB_OK;
+}
+
+}  // namespace
+
+int router_build_impl(const float* d_dataset, uint32_t dim, uint64_t n, int metric, uint32_t C, uint32_t iterations,
+                      uint64_t max_sample, float* d_centroids, float* d_cnorm, uint32_t* d_offsets,
+                      uint32_t* d_members, cudaStream_t st) {
+  GRAB_REQUIRE(d_dataset && d_centroids && d_cnorm && d_offsets && d_members, "router_build: null pointer");
+  GRAB_REQUIRE(dim >= 4 && dim % 4 == 0, "router_build: dim %u must be a multiple of 4", dim);
+  GRAB_REQUIRE(n >= 1 && n < (1ull << 31), "router_build: n must be in [1, 2^31)");
+  GRAB_REQUIRE(C >= 1 && C <= 65536 && C <= n, "router_build: num_centroids %u outside [1, min(n, 65536)]", C);
+  GRAB_REQUIRE(metric == GRAB_METRIC_L2 || metric == GRAB_METRIC_IP, "router_build: bad metric");
+  GRAB_REQUIRE(dim * sizeof(float) <= 48 * 1024, "router_build: dim %u too large", dim);
+  StageTimer timer("router_build");
+  uint64_t m = max_sample ? max_sample : 64ull * C;  // k-means sample size
+  if (m > n) m = n;
+  if (m < C) m = C;
+  const uint64_t big = n > m ? n : m;
+  const uint32_t nchunks = static_cast<uint32_t>((big + kChunk - 1) / kChunk);
+  ScopedDeviceBuffer sample, assign, counts, totals, soffs, smembers;
+  if (iterations > 0) GRAB_CUDA_TRY(sample.alloc(sizeof(float) * m * dim));
+  GRAB_CUDA_TRY(assign.alloc(sizeof(uint32_t) * big));
+  GRAB_CUDA_TRY(counts.alloc(sizeof(uint32_t) * static_cast<size_t>(nchunks) * C));
+  GRAB_CUDA_TRY(totals.alloc(sizeof(uint32_t) * C));
+  const uint32_t nchunk4 = dim / 4;
+  if (iterations > 0) {
+    GRAB_CUDA_TRY(soffs.alloc(sizeof(uint32_t) * (C + 1)));
+    GRAB_CUDA_TRY(smembers.alloc(sizeof(uint32_t) * m));
+    gather_rows_kernel<<<static_cast<unsigned>((m * nchunk4 + 255) / 256), 256, 0, st>>>(
+        d_dataset, n, dim, m, m, sample.as<float>());
+    gather_rows_kernel<<<static_cast<unsigned>((static_cast<uint64_t>(C) * nchunk4 + 255) / 256), 256, 0, st>>>(
+        d_dataset, n, dim, m, C, d_centroids);
+    GRAB_CUDA_TRY(cudaGetLastError());
+    // norms of the initial centroids: an update with empty groups keeps the rows and writes |c|^2
+    GRAB_CUDA_TRY(cudaMemsetAsync(soffs.ptr, 0, sizeof(uint32_t) * (C + 1), st));
+    centroid_update_kernel<<<C, 128, dim * sizeof(float), st>>>(sample.as<float>(), dim, soffs.as<uint32_t>(),
+                                                                 smembers.as<uint32_t>(), GRAB_METRIC_L2, d_centroids,
+                                                                 d_cnorm);
+    for (uint32_t it = 0; it < iterations; ++it) {
+      GRAB_CUDA_TRY(nearest(metric, sample.as<float>(), m, dim, d_centroids, d_cnorm, C, 1, assign.as<uint32_t>(), st));
+      int rc = group_by_centroid(assign.as<uint32_t>(), m, C, counts.as<uint32_t>(), totals.as<uint32_t>(),
+                                 soffs.as<uint32_t>(), smembers.as<uint32_t>(), st);
+      if (rc != GRAB_OK) return rc;
+      centroid_update_kernel<<<C, 128, dim * sizeof(float), st>>>(sample.as<float>(), dim, soffs.as<uint32_t>(),
+                                                                   smembers.as<uint32_t>(), metric, d_centroids, d_cnorm);
+      GRAB_CUDA_TRY(cudaGetLastError());
+    }
+    timer.mark("k-means on the sample");
+  }
+  GRAB_CUDA_TRY(nearest(metric, d_dataset, n, dim, d_centroids, d_cnorm, C, 1, assign.as<uint32_t>(), st));
+  timer.mark("assignment");
+  int rc = group_by_centroid(assign.as<uint32_t>(), n, C, counts.as<uint32_t>(), totals.as<uint32_t>(), d_offsets,
+                             d_members, st);
+  if (rc != GRAB_OK) return rc;
+  GRAB_CUDA_TRY(cudaStreamSynchronize(st));  // the scratch buffers are released on return
+  timer.mark("member lists");
+  return GRAB_OK;
+}
+
+int route_seeds_impl(const grab_router* r, const float* d_queries, uint64_t nq, uint64_t n, const grab_filter* f,
+                     uint32_t probes, uint32_t S, uint64_t seed, uint32_t* d_seeds, void* d_ws, size_t ws_bytes,
+                     cudaStream_t st) {
+  GRAB_REQUIRE(r && r->d_centroids && r->d_centroid_norms && r->d_member_offsets && r->d_members,
+               "route_seeds: incomplete router");
+  GRAB_REQUIRE(d_queries && d_seeds, "route_seeds: null pointer");
+  GRAB_REQUIRE(r->dim >= 4 && r->dim % 4 == 0, "route_seeds: dim %u must be a multiple of 4", r->dim);
+  GRAB_REQUIRE(r->num_centroids >= 1, "route_seeds: router without centroids");
+  GRAB_REQUIRE(n >= 1 && n < (1ull << 31), "route_seeds: n must be in [1, 2^31)");
+  GRAB_REQUIRE(probes >= 1 && probes <= kMaxProbes, "route_seeds: probes %u outside [1,%u]", probes, kMaxProbes);
+  GRAB_REQUIRE(S >= 1 && S <= 1024, "route_seeds: seeds_per_query %u outside [1,1024]", S);
+  GRAB_REQUIRE(r->metric == GRAB_METRIC_L2 || r->metric == GRAB_METRIC_IP, "route_seeds: bad metric");
+  if (nq == 0) return GRAB_OK;
+  if (probes > r->num_centroids) probes = r->num_centroids;
+  RouteArgs a{};
+  a.p = probes; a.S = S; a.C = r->num_centroids; a.nq = nq; a.n = n; a.seed = seed;
+  a.offsets = r->d_member_offsets; a.members = r->d_members; a.seeds = d_seeds;
+  a.filter_kind = GRAB_FILTER_NONE;
+  if (f) {
+    a.filter_kind = f->kind;
+    switch (f->kind) {
+      case GRAB_FILTER_NONE: break;
+      case GRAB_FILTER_PREFIX:
+      case GRAB_FILTER_TS_RANGE:
+        if (f->kind == GRAB_FILTER_TS_RANGE) GRAB_REQUIRE(f->d_ts, "route_seeds: ts filter without d_ts");
+        GRAB_REQUIRE((f->d_lo == nullptr) == (f->d_hi == nullptr),
+                     "route_seeds: d_lo and d_hi must both be given or both NULL");
+        a.ts = f->d_ts; a.lo = f->d_lo; a.hi = f->d_hi; a.lo1 = f->lo; a.hi1 = f->hi; a.ts_sorted = f->ts_sorted;
+        break;
+      case GRAB_FILTER_LABELS:
+        GRAB_REQUIRE(f->d_labels, "route_seeds: label filter without d_labels");
+        a.labels = f->d_labels; a.masks = f->d_masks; a.mask1 = f->mask; a.label_offsets = f->d_label_offsets;
+        break;
+      default:
+        set_last_error("route_seeds: unknown filter kind %d", f->kind);
+        return GRAB_ERR_INVALID_ARGUMENT;
+    }
+  }
+  const size_t need = grab_route_seeds_workspace_bytes(nq, probes);
+  ScopedDeviceBuffer own;
+  void* ws = d_ws;
+  if (!ws) {
+    GRAB_CUDA_TRY(own.alloc(need));
+    ws = own.ptr;
+  } else if (ws_bytes < need) {
+    set_last_error("route_seeds: workspace %zu < %zu bytes", ws_bytes, need);
+    return GRAB_ERR_WORKSPACE;
+  }
+  uint32_t* d_probes = static_cast<uint32_t*>(ws);
+  GRAB_CUDA_TRY(nearest(r->metric, d_queries, nq, r->dim, r->d_centroids, r->d_centroid_norms, r->num_centroids,
+                        probes, d_probes, st));
+  a.probes = d_probes;
+  route_seeds_kernel<<<static_cast<unsigned>((nq * 32 + 255) / 256), 256, 0, st>>>(a);
+  GRAB_CUDA_TRY(cudaGetLastError());
+  if (own.ptr) GRAB_CUDA_TRY(cudaStreamSynchronize(st));
+  return GRAB_OK;
+}
+
+int nearest_centroids_impl(const grab_router* r, const float* d_rows, uint64_t m, uint32_t probes, uint32_t* d_out,
+                           cudaStream_t st) {
+  GRAB_REQUIRE(r && r->d_centroids && r->d_centroid_norms && d_rows && d_out, "nearest_centroids: null pointer");
+  GRAB_REQUIRE(probes >= 1 && probes <= kMaxProbes, "nearest_centroids: probes %u outside [1,%u]", probes, kMaxProbes);
+  GRAB_REQUIRE(r->dim >= 4 && r->dim % 4 == 0, "nearest_centroids: dim %u must be a multiple of 4", r->dim);
+  GRAB_CUDA_TRY(nearest(r->metric, d_rows, m, r->dim, r->d_centroids, r->d_centroid_norms, r->num_centroids, probes,
+                        d_out, st));
+  return GRAB_OK;
+}
+
+}  // namespace grab
+
+extern "C" size_t grab_route_seeds_workspace_bytes(uint64_t nq, uint32_t probes) {
+  return ((sizeof(uint32_t) * nq * (probes ? probes : 1) + 255) / 256) * 256;
+}

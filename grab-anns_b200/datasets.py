@@ -37,13 +37,25 @@ def descriptor_like(n, dim, n_centres, seed, centres=None):
     return _mixture(n, dim, centres, np.float32(12.0), rng, post=post), centres
 
 
-def normalised_mixture(n, dim, n_centres, sigma, seed, centres=None):
-    """Embedding-like: Gaussian mixture, L2-normalised rows (inner-product metric)."""
+def normalised_mixture(n, dim, n_centres, sigma, seed, centres=None, isotropic=False):
+    """Embedding-like: Gaussian mixture, L2-normalised rows (inner-product metric).
+
+    Within a cluster the noise has a 1/j variance spectrum over the dimensions (same total
+    energy dim * sigma^2 as the isotropic case; participation ratio about 32 at dim 768), the
+    shape trained embeddings have.  `isotropic=True` gives equal variance in every dimension:
+    then all cluster mates are almost equidistant (intrinsic dimension = dim), nearest
+    neighbours inside a cluster are close to random, and the recall of any graph index equals
+    the fraction of the cluster it scans -- kept as a stress case."""
     rng = np.random.Generator(np.random.PCG64(seed))
     if centres is None:
         centres = rng.standard_normal((n_centres, dim), dtype=np.float32)
+    if isotropic:
+        sig = np.float32(sigma)
+    else:
+        lam = 1.0 / np.arange(1, dim + 1)
+        sig = (sigma * np.sqrt(dim * lam / lam.sum())).astype(np.float32)
     post = lambda x: (x / np.linalg.norm(x, axis=1, keepdims=True)).astype(np.float32)
-    return _mixture(n, dim, centres, np.float32(sigma), rng, post=post), centres
+    return _mixture(n, dim, centres, sig, rng, post=post), centres
 
 
 def zipf_labels(n, n_labels, s, seed):
@@ -70,7 +82,7 @@ def range_queries(nq, n, width, seed):
     return lo, lo + np.uint64(width)
 
 
-def config(name, scale=1.0):
+def config(name, scale=1.0, isotropic=False):
     """Workload of one benchmark config ('C1'..'C4'), optionally scaled down for tests."""
     if name == "C1":
         n, nq = int(100_000 * scale), max(8, int(1000 * scale))
@@ -88,8 +100,8 @@ def config(name, scale=1.0):
                     degree=64, itopk=64, metric=0, dim=128)
     if name == "C3":
         n, nq = int(1_000_000 * scale), max(8, int(10_000 * scale))
-        base, cen = normalised_mixture(n, 768, 256, 0.3, 3001)
-        q, _ = normalised_mixture(nq, 768, 256, 0.3, 3002, centres=cen)
+        base, cen = normalised_mixture(n, 768, 256, 0.3, 3001, isotropic=isotropic)
+        q, _ = normalised_mixture(nq, 768, 256, 0.3, 3002, centres=cen, isotropic=isotropic)
         return dict(base=base, queries=q, labels=zipf_labels(n, 16, 1.1, 3003),
                     masks=label_masks(nq, 16, 3004), k=10, degree=64, itopk=64, metric=1, dim=768)
     if name == "C4":

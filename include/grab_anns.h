@@ -73,6 +73,10 @@ typedef struct grab_filter {
   const uint32_t* d_masks; /* [nq] or NULL */
   uint32_t mask;           /* used when d_masks == NULL */
   uint32_t active_degree;  /* kind PREFIX */
+  /* kind LABELS, optional: when the vectors are grouped by label (ids of label l are
+   * [d_label_offsets[l], d_label_offsets[l+1])), 33 offsets on the device let the search draw its
+   * own seeds inside the query's labels */
+  const uint32_t* d_label_offsets;
 } grab_filter;
 
 /* Per-launch counters of the graph search (all queries summed), the inputs of the
@@ -278,6 +282,44 @@ int grab_insert_opt(const float* d_dataset, uint32_t* d_graph, const uint64_t* d
 /* ------------------------------------------------------------------------------------ */
 int grab_merge_topk(const float* d_dists, const int64_t* d_ids, uint64_t nq, uint32_t parts,
                     uint32_t k, int64_t* d_out_ids, float* d_out_dists, void* stream);
+
+/* ------------------------------------------------------------------------------------ */
+/* Entry-point router: search seeds that pass the filter AND lie close to the query.     */
+/* Device version of the reference's host seed sampling (cagraIndexOpt.cu:441-511 for    */
+/* query_range, :313-336 for query_local; cagraIndex.cu:267-296) combined with the       */
+/* k-means routing of its two-level index (timeStampIndex.cu:141-238 build_virtual_index,*/
+/* :240-419 query).  The seed array it writes is the d_seeds / num_seeds_per_query input */
+/* of grab_search, grab_search_bucket, grab_search_range and grab_graph_search.          */
+/* ------------------------------------------------------------------------------------ */
+typedef struct grab_router {
+  uint32_t num_centroids;
+  uint32_t dim;
+  int metric;                       /* grab_metric the centroids were trained for */
+  const float* d_centroids;         /* [num_centroids, dim] */
+  const float* d_centroid_norms;    /* [num_centroids] squared norms */
+  const uint32_t* d_member_offsets; /* [num_centroids + 1] */
+  const uint32_t* d_members;        /* [n] ids grouped by nearest centroid, ascending inside a group */
+} grab_router;
+
+/* Trains `num_centroids` centroids (Lloyd, `iterations` rounds over a strided sample of
+ * max_sample rows; 0 = 64 per centroid), assigns all n vectors and writes the four arrays a
+ * grab_router points to (caller-allocated: [C,dim], [C], [C+1], [n]).  iterations == 0 keeps
+ * the centroids and norms found in d_centroids / d_centroid_norms and only re-assigns (after
+ * inserts).  Deterministic; synchronises the stream before returning. */
+int grab_router_build(const float* d_dataset, uint32_t dim, uint64_t n, int metric, uint32_t num_centroids,
+                      uint32_t iterations, uint64_t max_sample, float* d_centroids, float* d_centroid_norms,
+                      uint32_t* d_member_offsets, uint32_t* d_members, void* stream);
+/* The `probes` (1..16) nearest centroids of m rows, best first: d_out u32[m, probes]. */
+int grab_nearest_centroids(const grab_router* router, const float* d_rows, uint64_t m, uint32_t probes,
+                           uint32_t* d_out, void* stream);
+size_t grab_route_seeds_workspace_bytes(uint64_t nq, uint32_t probes);
+/* d_seeds u32[nq, seeds_per_query]: members of the `probes` nearest centroids that pass
+ * `filter` (NULL = no filter; id windows for sorted timestamps and for labels with
+ * d_label_offsets, predicate tests otherwise); 0xFFFFFFFF where nothing was found.  n = number
+ * of indexed vectors.  d_ws may be NULL (then the call allocates and synchronises). */
+int grab_route_seeds(const grab_router* router, const float* d_queries, uint64_t nq, uint64_t n,
+                     const grab_filter* filter, uint32_t probes, uint32_t seeds_per_query, uint64_t seed,
+                     uint32_t* d_seeds, void* d_ws, size_t ws_bytes, void* stream);
 
 #ifdef __cplusplus
 }

@@ -879,3 +879,164 @@ void orc_merge_topk(const float* dists, const int64_t* ids, uint64_t nq, uint32_
     free(keys);
   }
 }
+
+/* ------------------------------------------------------------------------- */
+/* Entry-point router (device form of the reference's host seed sampling,     */
+/* cagraIndexOpt.cu:441-511, and of the k-means routing of its two-level      */
+/* index, timeStampIndex.cu:141-238 and :240-419).  Restated step by step in  */
+/* the arithmetic order the product fixes, so every output is bit-exact.      */
+/* ------------------------------------------------------------------------- */
+
+/* The P nearest centroids of every row, best first.  x.c is one fused multiply-add chain
+ * over ascending dimensions; score = fma(-2, x.c, |c|^2) (L2) or -(x.c) (inner product);
+ * ties go to the lower centroid id; missing entries are 0xFFFFFFFF. */
+void orc_nearest_centroids(const float* X, uint64_t m, uint32_t dim, const float* cen, const float* cnorm,
+                           uint32_t C, int metric, uint32_t P, uint32_t* out) {
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < (int64_t)m; ++r) {
+    uint64_t* keys = (uint64_t*)malloc(sizeof(uint64_t) * C);
+    for (uint32_t c = 0; c < C; ++c) {
+      float acc = 0.0f;
+      for (uint32_t k = 0; k < dim; ++k) acc = fmaf(X[r * dim + k], cen[(uint64_t)c * dim + k], acc);
+      float s = metric == 0 ? fmaf(-2.0f, acc, cnorm[c]) : -acc;
+      keys[c] = orc_make_key(s, c);
+    }
+    qsort(keys, C, sizeof(uint64_t), cmp_u64);
+    for (uint32_t p = 0; p < P; ++p) out[r * P + p] = p < C ? (uint32_t)(keys[p] & 0xFFFFFFFFu) : 0xFFFFFFFFu;
+    free(keys);
+  }
+}
+
+/* ids 0..m-1 grouped by assign[], ascending inside each group. */
+void orc_group_by_centroid(const uint32_t* assign, uint64_t m, uint32_t C, uint32_t* offsets, uint32_t* members) {
+  uint32_t* cur = (uint32_t*)calloc(C + 1, sizeof(uint32_t));
+  for (uint64_t i = 0; i < m; ++i) if (assign[i] < C) cur[assign[i] + 1]++;
+  for (uint32_t c = 0; c < C; ++c) cur[c + 1] += cur[c];
+  memcpy(offsets, cur, sizeof(uint32_t) * (C + 1));
+  for (uint64_t i = 0; i < m; ++i) if (assign[i] < C) members[cur[assign[i]]++] = (uint32_t)i;
+  free(cur);
+}
+
+static float sqnorm_32lanes(const float* v, uint32_t dim) {
+  float lane[32];
+  for (uint32_t l = 0; l < 32; ++l) {
+    float acc = 0.0f;
+    for (uint32_t k = l; k < dim; k += 32) acc = fmaf(v[k], v[k], acc);
+    lane[l] = acc;
+  }
+  for (uint32_t o = 16; o > 0; o >>= 1) {
+    float nxt[32];
+    for (uint32_t l = 0; l < 32; ++l) nxt[l] = lane[l] + lane[l ^ o];
+    memcpy(lane, nxt, sizeof(lane));
+  }
+  return lane[0];
+}
+
+/* One Lloyd update: centroid = mean of its sample members (sequential fp32 sum in list
+ * order, one division), empty groups keep the old row; inner product: scaled to unit length;
+ * cnorm = squared norm (32 strided partial sums, butterfly 16..1). */
+void orc_centroid_update(const float* sample, uint32_t dim, const uint32_t* offsets, const uint32_t* members,
+                         int metric, uint32_t C, float* cen, float* cnorm) {
+  for (uint32_t c = 0; c < C; ++c) {
+    float* v = cen + (uint64_t)c * dim;
+    const uint32_t b = offsets[c], e = offsets[c + 1];
+    if (e > b)
+      for (uint32_t k = 0; k < dim; ++k) {
+        float s = 0.0f;
+        for (uint32_t j = b; j < e; ++j) s = s + sample[(uint64_t)members[j] * dim + k];
+        v[k] = s / (float)(e - b);
+      }
+    float n2 = sqnorm_32lanes(v, dim);
+    if (metric == 1 && e > b && n2 > 0.0f) {
+      const float len = sqrtf(n2);
+      for (uint32_t k = 0; k < dim; ++k) v[k] = v[k] / len;
+      n2 = sqnorm_32lanes(v, dim);
+    }
+    cnorm[c] = n2;
+  }
+}
+
+static uint64_t mix64(uint64_t x) {
+  x ^= x >> 30; x *= 0xbf58476d1ce4e5b9ull;
+  x ^= x >> 27; x *= 0x94d049bb133111ebull;
+  x ^= x >> 31;
+  return x;
+}
+
+static uint32_t lower_bound_u32(const uint32_t* a, uint32_t b, uint32_t e, uint32_t x) {
+  while (b < e) { uint32_t mid = (b + e) >> 1; if (a[mid] < x) b = mid + 1; else e = mid; }
+  return b;
+}
+
+/* Seeds of one batch.  filter_kind 0 none, 1 timestamp range, 2 labels (3 = prefix: a range
+ * when ts is given).  lo/hi and masks are per query (NULL -> lo1/hi1/mask1). */
+void orc_route_seeds(const uint32_t* probes, uint32_t p, uint64_t nq, uint64_t n, uint32_t C,
+                     const uint32_t* offsets, const uint32_t* members, int filter_kind, int ts_sorted,
+                     const uint64_t* ts, const uint64_t* lo, const uint64_t* hi, uint64_t lo1, uint64_t hi1,
+                     const uint8_t* labels, const uint32_t* masks, uint32_t mask1, const uint32_t* label_offsets,
+                     uint32_t S, uint64_t seed, uint32_t* seeds) {
+  for (uint64_t q = 0; q < nq; ++q) {
+    uint32_t nwin = 1, wlo = 0, whi = (uint32_t)n, mask = 0;
+    int check = 0;
+    uint64_t tlo = 0, thi = 0;
+    if (filter_kind == 1 || (filter_kind == 3 && ts)) {
+      tlo = lo ? lo[q] : lo1;
+      thi = hi ? hi[q] : hi1;
+      if (ts_sorted) {
+        uint32_t b = 0, e = (uint32_t)n;
+        while (b < e) { uint32_t mid = (b + e) >> 1; if (ts[mid] < tlo) b = mid + 1; else e = mid; }
+        wlo = b; e = (uint32_t)n;
+        while (b < e) { uint32_t mid = (b + e) >> 1; if (ts[mid] < thi) b = mid + 1; else e = mid; }
+        whi = b;
+        if (whi <= wlo) nwin = 0;
+      } else {
+        check = 1;
+        if (thi <= tlo) nwin = 0;
+      }
+    } else if (filter_kind == 2) {
+      mask = masks ? masks[q] : mask1;
+      if (label_offsets) nwin = (uint32_t)__builtin_popcount(mask);
+      else { check = 1; if (mask == 0) nwin = 0; }
+    }
+    const uint32_t pairs = p * (nwin ? nwin : 1);
+    const uint32_t per = (S + pairs - 1) / pairs;
+    for (uint32_t s = 0; s < S; ++s) {
+      uint32_t id = 0xFFFFFFFFu;
+      if (nwin) {
+        const uint32_t j = s % p, t = s / p, w = t % nwin, r = t / nwin;
+        const uint32_t c = probes[q * p + j];
+        if (c < C) {
+          uint32_t lo_id = wlo, hi_id = whi;
+          if (filter_kind == 2 && label_offsets) {
+            uint32_t mm = mask;
+            for (uint32_t skip = w; skip > 0; --skip) mm &= mm - 1;
+            const uint32_t lab = (uint32_t)__builtin_ctz(mm);
+            lo_id = label_offsets[lab];
+            hi_id = label_offsets[lab + 1];
+          }
+          const uint32_t rb = offsets[c], re = offsets[c + 1];
+          const uint32_t b = lower_bound_u32(members, rb, re, lo_id);
+          const uint32_t e = lower_bound_u32(members, b, re, hi_id);
+          const uint32_t L = e - b;
+          if (r < L) {
+            const uint32_t step = L / per > 1 ? L / per : 1;
+            const uint32_t start = (uint32_t)(mix64(seed ^ (q * 0x9e3779b97f4a7c15ull + ((uint64_t)c << 8) + w)) % L);
+            const uint32_t pos = (uint32_t)((start + (uint64_t)r * step) % L);
+            if (!check) {
+              id = members[b + pos];
+            } else {
+              for (uint32_t tr = 0; tr < 4 && tr < L; ++tr) {
+                const uint32_t cand = members[b + (pos + tr) % L];
+                int ok;
+                if (filter_kind == 2) ok = ((mask >> (labels[cand] & 31u)) & 1u) != 0;
+                else ok = ts[cand] >= tlo && ts[cand] < thi;
+                if (ok) { id = cand; break; }
+              }
+            }
+          }
+        }
+      }
+      seeds[q * S + s] = id;
+    }
+  }
+}

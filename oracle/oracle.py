@@ -232,3 +232,81 @@ class HNSW:
         if getattr(self, "h", None):
             lib().orc_hnsw_free(C.c_void_p(self.h))
             self.h = None
+
+
+# ------------------------------------------------------------------ entry-point router
+def nearest_centroids(rows, cen, cnorm, metric=0, probes=1):
+    rows, cen, cnorm = _f32(rows), _f32(cen), _f32(cnorm)
+    m, dim = rows.shape
+    out = np.empty((m, probes), dtype=np.uint32)
+    lib().orc_nearest_centroids(_p(rows), C.c_uint64(m), C.c_uint32(dim), _p(cen), _p(cnorm),
+                                C.c_uint32(cen.shape[0]), C.c_int(metric), C.c_uint32(probes), _p(out))
+    return out
+
+
+def group_by_centroid(assign, num_centroids):
+    assign = np.ascontiguousarray(assign, dtype=np.uint32).reshape(-1)
+    offsets = np.empty(num_centroids + 1, dtype=np.uint32)
+    members = np.empty(assign.shape[0], dtype=np.uint32)
+    lib().orc_group_by_centroid(_p(assign), C.c_uint64(assign.shape[0]), C.c_uint32(num_centroids),
+                                _p(offsets), _p(members))
+    return offsets, members
+
+
+def router_build(data, num_centroids, metric=0, iterations=10, max_sample=0):
+    """k-means on the strided sample, then assignment and member lists: (cen, cnorm, offsets, members)."""
+    data = _f32(data)
+    n, dim = data.shape
+    nc = num_centroids
+    m = min(n, max_sample if max_sample else 64 * nc)
+    m = max(m, nc)
+    sample = np.ascontiguousarray(data[(np.arange(m, dtype=np.uint64) * np.uint64(n)) // np.uint64(m)])
+    cen = np.ascontiguousarray(sample[(np.arange(nc, dtype=np.uint64) * np.uint64(m)) // np.uint64(nc)]).copy()
+    cnorm = np.empty(nc, dtype=np.float32)
+    empty = np.zeros(nc + 1, dtype=np.uint32)
+    none = np.zeros(1, dtype=np.uint32)
+    L = lib()
+    L.orc_centroid_update(_p(sample), C.c_uint32(dim), _p(empty), _p(none), C.c_int(0), C.c_uint32(nc), _p(cen),
+                          _p(cnorm))
+    for _ in range(iterations):
+        a = nearest_centroids(sample, cen, cnorm, metric, 1)
+        offs, mem = group_by_centroid(a, nc)
+        L.orc_centroid_update(_p(sample), C.c_uint32(dim), _p(offs), _p(mem), C.c_int(metric), C.c_uint32(nc),
+                              _p(cen), _p(cnorm))
+    a = nearest_centroids(data, cen, cnorm, metric, 1)
+    offs, mem = group_by_centroid(a, nc)
+    return cen, cnorm, offs, mem
+
+
+def route_seeds(probes, n, offsets, members, seeds_per_query, seed=0x1234ABCD, ts=None, lo=None, hi=None,
+                ts_sorted=True, labels=None, masks=None, label_offsets=None):
+    """Seeds [nq, seeds_per_query] (0xFFFFFFFF = none); lo/hi and masks scalar or per query."""
+    probes = np.ascontiguousarray(probes, dtype=np.uint32)
+    nq, p = probes.shape
+    offsets = np.ascontiguousarray(offsets, dtype=np.uint32)
+    members = np.ascontiguousarray(members, dtype=np.uint32)
+    kind, lo1, hi1, mask1 = 0, 0, 0, 0
+    lo_a = hi_a = masks_a = None
+    if ts is not None:
+        kind = 1
+        ts = np.ascontiguousarray(ts, dtype=np.uint64)
+        if np.ndim(lo) == 0:
+            lo1, hi1 = int(lo), int(hi)
+        else:
+            lo_a = np.ascontiguousarray(lo, dtype=np.uint64)
+            hi_a = np.ascontiguousarray(hi, dtype=np.uint64)
+    elif labels is not None:
+        kind = 2
+        labels = np.ascontiguousarray(labels, dtype=np.uint8)
+        if np.ndim(masks) == 0:
+            mask1 = int(masks)
+        else:
+            masks_a = np.ascontiguousarray(masks, dtype=np.uint32)
+        if label_offsets is not None:
+            label_offsets = np.ascontiguousarray(label_offsets, dtype=np.uint32)
+    out = np.empty((nq, seeds_per_query), dtype=np.uint32)
+    lib().orc_route_seeds(_p(probes), C.c_uint32(p), C.c_uint64(nq), C.c_uint64(n), C.c_uint32(offsets.shape[0] - 1),
+                          _p(offsets), _p(members), C.c_int(kind), C.c_int(1 if ts_sorted else 0), _p(ts), _p(lo_a),
+                          _p(hi_a), C.c_uint64(lo1), C.c_uint64(hi1), _p(labels), _p(masks_a), C.c_uint32(mask1),
+                          _p(label_offsets), C.c_uint32(seeds_per_query), C.c_uint64(seed), _p(out))
+    return out

@@ -367,6 +367,33 @@ def test_graph_search_labels_ip_and_sharded_ids(grab, oracle):
     assert oracle.recall(loc, gt) > 0.8
 
 
+def test_graph_search_label_partitioned_seeds(grab, oracle):
+    """Vectors grouped by label, one bucket per label: seeds drawn from the id ranges of the query's
+    labels find a rare label (2 % of the data) that uniform seeds would mostly miss."""
+    rng = np.random.default_rng(37)
+    n, dim, total, local, nq, k = 12000, 64, 32, 24, 200, 10
+    data = clustered(n, dim, 24, 1.0, 38)
+    sizes = [6000, 3000, 1800, 960, 240]
+    labels = np.repeat(np.arange(5, dtype=np.uint8), sizes)
+    offsets = np.zeros(33, np.uint32)
+    offsets[1:6] = np.cumsum(sizes)
+    offsets[6:] = n
+    bucket = labels.astype(np.uint64)
+    graph = grab.build_time_partitioned_graph(_t(data), _t(bucket.view(np.int64)), sizes, total, local,
+                                              knn_precision=grab.KNN_EXACT_SCAN)
+    q = data[rng.integers(0, n, nq)].copy() + 0.01
+    masks = np.full(nq, 1 << 4, np.uint32)                     # the rare label alone ...
+    masks[nq // 2:] = (1 << 4) | (1 << 1)                      # ... or together with a common one
+    gt, _ = oracle.exact_search(data, q, k, labels=labels, masks=masks)
+    d_labels, d_masks, d_offs = _t(labels), _t(masks.view(np.int32)), _t(offsets.view(np.int32))
+    f = grab.make_filter(grab.FILTER_LABELS, labels=d_labels, masks=d_masks, label_offsets=d_offs)
+    gi, gd = grab.graph_search(_t(data), graph, _t(q), k, grab.SearchParams(64, 4, 0, 40, 12), flt=f)
+    gi = gi.cpu().numpy()
+    assert (((masks[:, None] >> labels[np.clip(gi, 0, n - 1)]) & 1) == 1)[gi >= 0].all()
+    assert (gi[: nq // 2] >= offsets[4]).all() and (gi[: nq // 2] >= 0).all()
+    assert oracle.recall(gi, gt) > 0.9, oracle.recall(gi, gt)
+
+
 def test_graph_search_empty_range_and_global_hash(grab, oracle, small_graph):
     data, g = small_graph
     n, dim = data.shape
