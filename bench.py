@@ -439,9 +439,10 @@ def main():
         # dram__bytes_read.sum + dram__bytes_write.sum of one search launch at the default full-size
         # configuration (ncu capture summarised in profiles/graph_search_kernel_C2.md)
         default_cfg = (args.workload == "C2" and args.scale == 1.0 and args.buckets == 20 and args.itopk == 64 and
-                       args.width == 3 and args.max_iter == 20 and args.hash_bitlen == 11 and
-                       args.selectivity == 0.10 and not args.sharded and router is None)
-        traffic = 4141677056 + 1401856 if default_cfg else None
+                       args.width == 3 and args.max_iter == 6 and args.hash_bitlen == 11 and
+                       args.selectivity == 0.10 and not args.sharded and args.router_centroids == 1024 and
+                       args.probes == 4 and args.seeds == 32 and args.local_degree == 48)
+        traffic = 1488718336 + 1193216 if default_cfg else None
         line = {
             "metric": "filtered QPS at recall@10>=0.95",
             "value": (1 if args.sharded else world) * nq / (ms / 1e3), "unit": "queries/s",

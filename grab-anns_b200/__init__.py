@@ -18,6 +18,7 @@ LIB_PATH = os.path.join(HERE, "libgrab_anns.so")
 METRIC_L2, METRIC_IP = 0, 1
 FILTER_NONE, FILTER_TS_RANGE, FILTER_LABELS, FILTER_PREFIX = 0, 1, 2, 3
 KNN_EXACT_SCAN, KNN_TC_BF16, KNN_TC_SPLIT = 0, 1, 2
+ROUTER_EXACT_SCAN = 1
 
 
 class GrabError(RuntimeError):
@@ -67,7 +68,7 @@ class SearchArgs(C.Structure):
 class RouterStruct(C.Structure):
     _fields_ = [("num_centroids", C.c_uint32), ("dim", C.c_uint32), ("metric", C.c_int32),
                 ("d_centroids", C.c_void_p), ("d_centroid_norms", C.c_void_p),
-                ("d_member_offsets", C.c_void_p), ("d_members", C.c_void_p)]
+                ("d_member_offsets", C.c_void_p), ("d_members", C.c_void_p), ("flags", C.c_uint32)]
 
 
 _lib = None
@@ -242,10 +243,15 @@ def merge_topk(dists, ids, k):
 class Router:
     """Entry-point router (grab_router): centroids plus the ids grouped by nearest centroid."""
 
-    def __init__(self, centroids, norms, offsets, members, metric):
+    def __init__(self, centroids, norms, offsets, members, metric, exact_scan=False):
         self.centroids, self.norms, self.offsets, self.members, self.metric = centroids, norms, offsets, members, metric
         self.struct = RouterStruct(centroids.shape[0], centroids.shape[1], metric, _p(centroids), _p(norms),
-                                   _p(offsets), _p(members))
+                                   _p(offsets), _p(members), ROUTER_EXACT_SCAN if exact_scan else 0)
+
+    def exact(self, on=True):
+        """Rank centroids with the exact fp32 scan (True) or on the tensor cores (False)."""
+        self.struct.flags = ROUTER_EXACT_SCAN if on else 0
+        return self
 
 
 def router_build(dataset, num_centroids, metric=METRIC_L2, iterations=10, max_sample=0, centroids=None, norms=None):

@@ -124,6 +124,26 @@ __device__ __forceinline__ float team_distance_smem(const float* __restrict__ q_
 
 __device__ __forceinline__ uint32_t lane_id() { return threadIdx.x & 31u; }
 
+// First index in [0, n) whose value is >= x (n if none) in a non-decreasing array, found by a
+// whole warp: every round the 32 lanes probe 32 evenly spaced positions, so 2^20 entries take
+// four dependent loads instead of twenty.  All lanes must call it and get the same result.
+__device__ __forceinline__ uint32_t warp_lower_bound_u64(const uint64_t* __restrict__ a, uint32_t n, uint64_t x) {
+  const uint32_t lane = lane_id();
+  uint32_t b = 0, e = n;  // the answer lies in [b, e]
+  while (e - b > 32) {
+    const uint32_t span = e - b;
+    const uint32_t pos = b + static_cast<uint32_t>((static_cast<uint64_t>(lane + 1) * span) / 33);  // b < pos < e
+    const uint32_t below = __ballot_sync(0xFFFFFFFFu, __ldg(a + pos) < x);  // a prefix of the lanes
+    const uint32_t k = __popc(below);
+    const uint32_t nb = k > 0 ? b + static_cast<uint32_t>((static_cast<uint64_t>(k) * span) / 33) + 1 : b;
+    const uint32_t ne = k < 32 ? b + static_cast<uint32_t>((static_cast<uint64_t>(k + 1) * span) / 33) : e;
+    b = nb;
+    e = ne;
+  }
+  const uint32_t below = __ballot_sync(0xFFFFFFFFu, b + lane < e && __ldg(a + b + lane) < x);
+  return b + __popc(below);
+}
+
 // Block-wide bitonic sort of `n` (power of two) uint64 keys in shared memory, ascending.
 // Every thread of the block must call it.
 __device__ __forceinline__ void block_bitonic_sort(uint64_t* keys, uint32_t n) {

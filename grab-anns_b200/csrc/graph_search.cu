@@ -409,23 +409,16 @@ static cudaError_t launch_search(const SearchKernelArgs& a, size_t smem, cudaStr
   return cudaGetLastError();
 }
 
+// One warp per query: id window [first id with ts >= lo, first id with ts >= hi).
 __global__ void ts_window4_kernel(const uint64_t* __restrict__ ts, uint64_t n,
                                   const uint64_t* __restrict__ lo, const uint64_t* __restrict__ hi,
                                   uint64_t lo1, uint64_t hi1, uint64_t nq,
                                   uint32_t* __restrict__ windows) {
-  const uint64_t qi = blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x;
-  if (qi >= nq) return;
-  const uint64_t bounds[2] = {lo ? lo[qi] : lo1, hi ? hi[qi] : hi1};
-  for (int b = 0; b < 2; ++b) {
-    uint64_t l = 0, r = n;
-    while (l < r) {
-      const uint64_t m = (l + r) >> 1;
-      if (ts[m] < bounds[b]) l = m + 1; else r = m;
-    }
-    windows[qi * 4 + b] = static_cast<uint32_t>(l);
-  }
-  windows[qi * 4 + 2] = 0;
-  windows[qi * 4 + 3] = 0;
+  const uint64_t qi = (blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x) >> 5;
+  if (qi >= nq) return;  // whole warps leave together
+  const uint32_t wb = warp_lower_bound_u64(ts, static_cast<uint32_t>(n), lo ? lo[qi] : lo1);
+  const uint32_t we = warp_lower_bound_u64(ts, static_cast<uint32_t>(n), hi ? hi[qi] : hi1);
+  if (lane_id() == 0) *reinterpret_cast<uint4*>(windows + qi * 4) = make_uint4(wb, we, 0u, 0u);
 }
 
 // Launcher rules restated from the reference: itopk = max(k, itopk) with floor 64
@@ -526,8 +519,8 @@ int graph_search_impl(const grab_search_args* g) {
   }
   uint32_t* windows = static_cast<uint32_t*>(ws);
   if (need_window) {
-    ts_window4_kernel<<<(unsigned)((g->nq + 255) / 256), 256, 0, st>>>(f.d_ts, g->n, f.d_lo, f.d_hi,
-                                                                      f.lo, f.hi, g->nq, windows);
+    ts_window4_kernel<<<(unsigned)((g->nq * 32 + 255) / 256), 256, 0, st>>>(f.d_ts, g->n, f.d_lo, f.d_hi,
+                                                                           f.lo, f.hi, g->nq, windows);
     GRAB_CUDA_TRY(cudaGetLastError());
     a.windows = windows;
   }

@@ -27,6 +27,7 @@
 #include <cuda_bf16.h>
 
 #include "common.cuh"
+#include "tcgen05.cuh"
 #include "windows.cuh"
 
 namespace grab {
@@ -38,123 +39,10 @@ constexpr int STAGES = 3;
 constexpr int CTAS_PER_SM = 2;
 constexpr int STAGE_BYTES = (BM + BN) * BK * 2;  // 32 KB
 constexpr int THREADS = 192;
-constexpr uint32_t kSpinLimit = 1u << 22;
-
-// ------------------------------------------------------------------ PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.b32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait: false when the limit expired or another role raised the abort flag.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 255u) == 255u && *abort_flag) return false;
-  }
-  *abort_flag = 1;
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int32_t x,
-                                            int32_t y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols));
-}
-__device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols));
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                            uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// Asynchronous TMEM load of 32 columns x 32 lanes; the registers are valid only after
-// tmem_ld_wait on the same array.
-__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&v)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-      : "r"(taddr)
-      : "memory");
-}
-// Waits for all TMEM loads of this thread; naming the registers as in/out operands keeps
-// the compiler from moving their uses above the wait.
-__device__ __forceinline__ void tmem_ld_wait(uint32_t (&v)[32]) {
-  asm volatile("tcgen05.wait::ld.sync.aligned;"
-               : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
-                 "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]),
-                 "+r"(v[16]), "+r"(v[17]), "+r"(v[18]), "+r"(v[19]), "+r"(v[20]), "+r"(v[21]), "+r"(v[22]), "+r"(v[23]),
-                 "+r"(v[24]), "+r"(v[25]), "+r"(v[26]), "+r"(v[27]), "+r"(v[28]), "+r"(v[29]), "+r"(v[30]), "+r"(v[31])
-               :
-               : "memory");
-}
-
-// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128
-// bytes, 8-row groups 1024 bytes apart (stride byte offset), descriptor version 1 (sm_100).
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((addr & 0x3FFFFu) >> 4);  // start address   [0,14)
-  d |= static_cast<uint64_t>(1) << 16;                 // leading offset  [16,30) (unused with swizzle)
-  d |= static_cast<uint64_t>(1024 >> 4) << 32;         // stride offset   [32,46)
-  d |= static_cast<uint64_t>(1) << 46;                 // version         [46,48)
-  d |= static_cast<uint64_t>(2) << 61;                 // SWIZZLE_128B    [61,64)
-  return d;
-}
 // Instruction descriptor: D fp32, A/B bf16, both K-major, N=128, M=128.
 constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((BN >> 3) << 17) | ((BM >> 4) << 24);
 
 // ------------------------------------------------------------------ epilogue helpers
-// Bits i of a 32-column chunk starting at `cbase` whose column lies in [lo, hi).
-__device__ __forceinline__ uint32_t range_bits(uint32_t cbase, uint32_t lo, uint32_t hi) {
-  uint32_t a = lo > cbase ? lo - cbase : 0u, b = hi > cbase ? hi - cbase : 0u;
-  if (a > 32u) a = 32u;
-  if (b > 32u) b = 32u;
-  if (b <= a) return 0u;
-  const uint32_t upto_b = b >= 32u ? 0xFFFFFFFFu : ((1u << b) - 1u);
-  const uint32_t upto_a = (1u << a) - 1u;  // a < 32 here
-  return upto_b & ~upto_a;
-}
-
 // Cut the candidate buffers of the rows that are (nearly) full back to their KC smallest keys
 // and tighten the rows' thresholds.  Warp-cooperative, one row at a time: the row's keys sit in
 // registers (element g = j*32 + lane), a 4-pass radix select on the ordered distance finds the
@@ -241,20 +129,6 @@ __device__ __noinline__ uint2 compress_rows(uint64_t* warp_buf, uint32_t* hist, 
   }
   __syncwarp();
   return make_uint2(cnt, __float_as_uint(thr));
-}
-
-// v[i] for a run-time i without spilling the array: a 5-level select tree.
-__device__ __forceinline__ uint32_t pick32(const uint32_t (&v)[32], uint32_t i) {
-  uint32_t a[16], b[8], c[4], d[2];
-#pragma unroll
-  for (int j = 0; j < 16; ++j) a[j] = (i & 1u) ? v[2 * j + 1] : v[2 * j];
-#pragma unroll
-  for (int j = 0; j < 8; ++j) b[j] = (i & 2u) ? a[2 * j + 1] : a[2 * j];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) c[j] = (i & 4u) ? b[2 * j + 1] : b[2 * j];
-#pragma unroll
-  for (int j = 0; j < 2; ++j) d[j] = (i & 8u) ? c[2 * j + 1] : c[2 * j];
-  return (i & 16u) ? d[1] : d[0];
 }
 
 struct TileRange {
@@ -619,22 +493,6 @@ rerank_kernel(const float* __restrict__ data, uint32_t dim, const uint64_t* __re
 }
 
 // ------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  }
-  return fn;
-}
-
 static int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint32_t kp) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) {

@@ -25,9 +25,10 @@ namespace {
 
 constexpr int kRtBM = 64;        // rows (queries or vectors) per CTA
 constexpr int kRtBN = 64;        // centroids per tile
-constexpr int kRtBK = 16;        // dimensions per shared-memory stage
+constexpr int kRtBK = 32;        // dimensions per shared-memory stage
 constexpr int kRtThreads = 256;  // 16 x 16 threads, 4 x 4 outputs each
 constexpr uint32_t kMaxProbes = 16;
+constexpr uint32_t kMaxSlices = 8;  // centroid slices of the routing launch (more CTAs for few queries)
 
 __device__ __forceinline__ uint64_t rt_mix64(uint64_t x) {  // splitmix64 finaliser
   x ^= x >> 30; x *= 0xbf58476d1ce4e5b9ull;
@@ -46,7 +47,10 @@ template <int METRIC>
 __global__ void __launch_bounds__(kRtThreads)
 nearest_centroids_kernel(const float* __restrict__ X, uint64_t m, uint32_t dim,
                          const float* __restrict__ cen, const float* __restrict__ cnorm, uint32_t C,
-                         uint32_t P, uint32_t* __restrict__ out) {
+                         uint32_t P, uint32_t* __restrict__ out_ids, uint64_t* __restrict__ out_keys) {
+  // blockIdx.x = row tile, blockIdx.y = slice of the centroids (gridDim.y slices of whole tiles).
+  // out_ids  [m, P]             : centroid ids, best first (gridDim.y must be 1)
+  // out_keys [m, gridDim.y, P]  : the slice's best (score, centroid) keys, merged by the consumer
   __shared__ __align__(16) float As[kRtBK][kRtBM + 4];
   __shared__ __align__(16) float Bs[kRtBK][kRtBN + 4];
   __shared__ float S[kRtBM][kRtBN + 1];
@@ -55,27 +59,53 @@ nearest_centroids_kernel(const float* __restrict__ X, uint64_t m, uint32_t dim,
   const uint32_t tid = threadIdx.x;
   const uint32_t tx = tid & 15u, ty = tid >> 4;
   const uint64_t row0 = static_cast<uint64_t>(blockIdx.x) * kRtBM;
-  const uint32_t lrow = tid >> 2, lk = (tid & 3u) * 4;  // this thread's float4 of a 64 x 16 stage
+  // this thread's two float4 of a 64 x 32 stage: rows lrow and lrow + 32, dimensions lk..lk+3
+  const uint32_t lrow = tid >> 3, lk = (tid & 7u) * 4;
+  const uint32_t tiles = (C + kRtBN - 1) / kRtBN;
+  const uint32_t tiles_per = (tiles + gridDim.y - 1) / gridDim.y;
+  const uint32_t c_begin = blockIdx.y * tiles_per * kRtBN;
+  const uint32_t c_end = (c_begin + tiles_per * kRtBN) < C ? (c_begin + tiles_per * kRtBN) : C;
 
   for (uint32_t j = tid; j < kMaxProbes * kRtBM; j += kRtThreads) (&top[0][0])[j] = kMaxKey;
 
-  for (uint32_t c0 = 0; c0 < C; c0 += kRtBN) {
+  const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  const bool r0 = row0 + lrow < m, r1 = row0 + lrow + 32 < m;
+  const float* xa = X + (row0 + lrow) * dim + lk;
+  const float* xb = xa + 32ull * dim;
+
+  for (uint32_t c0 = c_begin; c0 < c_end; c0 += kRtBN) {
     float acc[4][4];
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
       for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+    const bool b0 = c0 + lrow < C, b1 = c0 + lrow + 32 < C;
+    const float* ca = cen + static_cast<uint64_t>(c0 + lrow) * dim + lk;
+    const float* cb = ca + 32ull * dim;
 
+    // software pipeline: the loads of stage s+1 are in flight while stage s is multiplied
+    float4 a0 = zero4, a1 = zero4, q0 = zero4, q1 = zero4;
+    if (lk < dim) {
+      if (r0) a0 = ldg_f4(xa);
+      if (r1) a1 = ldg_f4(xb);
+      if (b0) q0 = ldg_f4(ca);
+      if (b1) q1 = ldg_f4(cb);
+    }
     for (uint32_t k0 = 0; k0 < dim; k0 += kRtBK) {
-      float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
-      if (k0 + lk < dim) {
-        if (row0 + lrow < m) a = ldg_f4(X + (row0 + lrow) * dim + k0 + lk);
-        if (c0 + lrow < C) b = ldg_f4(cen + static_cast<uint64_t>(c0 + lrow) * dim + k0 + lk);
-      }
       __syncthreads();  // the previous stage (and the previous tile's row scan) is done
-      As[lk + 0][lrow] = a.x; As[lk + 1][lrow] = a.y; As[lk + 2][lrow] = a.z; As[lk + 3][lrow] = a.w;
-      Bs[lk + 0][lrow] = b.x; Bs[lk + 1][lrow] = b.y; Bs[lk + 2][lrow] = b.z; Bs[lk + 3][lrow] = b.w;
+      As[lk + 0][lrow] = a0.x; As[lk + 1][lrow] = a0.y; As[lk + 2][lrow] = a0.z; As[lk + 3][lrow] = a0.w;
+      As[lk + 0][lrow + 32] = a1.x; As[lk + 1][lrow + 32] = a1.y; As[lk + 2][lrow + 32] = a1.z; As[lk + 3][lrow + 32] = a1.w;
+      Bs[lk + 0][lrow] = q0.x; Bs[lk + 1][lrow] = q0.y; Bs[lk + 2][lrow] = q0.z; Bs[lk + 3][lrow] = q0.w;
+      Bs[lk + 0][lrow + 32] = q1.x; Bs[lk + 1][lrow + 32] = q1.y; Bs[lk + 2][lrow + 32] = q1.z; Bs[lk + 3][lrow + 32] = q1.w;
       __syncthreads();
+      const uint32_t kn = k0 + kRtBK + lk;
+      a0 = a1 = q0 = q1 = zero4;
+      if (kn < dim) {
+        if (r0) a0 = ldg_f4(xa + k0 + kRtBK);
+        if (r1) a1 = ldg_f4(xb + k0 + kRtBK);
+        if (b0) q0 = ldg_f4(ca + k0 + kRtBK);
+        if (b1) q1 = ldg_f4(cb + k0 + kRtBK);
+      }
 #pragma unroll
       for (int kk = 0; kk < kRtBK; ++kk) {
         const float4 av = *reinterpret_cast<const float4*>(&As[kk][ty * 4]);
@@ -119,7 +149,8 @@ nearest_centroids_kernel(const float* __restrict__ X, uint64_t m, uint32_t dim,
     const uint32_t r = j / P, p = j % P;
     if (row0 + r < m) {
       const uint64_t key = top[p][r];
-      out[(row0 + r) * P + p] = key == kMaxKey ? kInvalid : key_id(key);
+      if (out_keys) out_keys[((row0 + r) * gridDim.y + blockIdx.y) * P + p] = key;
+      else out_ids[(row0 + r) * P + p] = key == kMaxKey ? kInvalid : key_id(key);
     }
   }
 }
@@ -282,7 +313,11 @@ centroid_update_kernel(const float* __restrict__ sample, uint32_t dim, const uin
 // pair are distinct, pairs are disjoint, so a query never gets the same seed twice.
 // ---------------------------------------------------------------------------------------
 struct RouteArgs {
-  const uint32_t* probes;  // [nq, p]
+  const uint64_t* keys;  // [nq, slices, T] (score, centroid) keys of every centroid slice, ascending
+  uint32_t slices, T;    // T = p (exact keys) or p + extra (tf32 keys, re-scored here)
+  int rescore;           // keys came from the tensor-core kernel
+  const int* status;     // non-zero: the tensor-core kernel gave up, write "no seed" everywhere
+  const float* queries; const float* cen; const float* cnorm; uint32_t dim; int metric;
   uint32_t p, S, C;
   uint64_t nq, n, seed;
   const uint32_t* offsets;
@@ -302,11 +337,68 @@ __device__ __forceinline__ uint32_t lower_bound_u32(const uint32_t* a, uint32_t 
 }
 
 __global__ void __launch_bounds__(256) route_seeds_kernel(RouteArgs a) {
+  __shared__ uint32_t s_probes[8][kMaxProbes];
   const uint64_t q = (static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const uint32_t lane = threadIdx.x & 31u;
-  if (q >= a.nq) return;
+  if (q >= a.nq) return;  // whole warps leave together
   const uint32_t n32 = static_cast<uint32_t>(a.n);
-
+  uint32_t* probes = s_probes[threadIdx.x >> 5];
+  if (a.status && *a.status != 0) {
+    for (uint32_t s = lane; s < a.S; s += 32) a.seeds[q * a.S + s] = kInvalid;
+    return;
+  }
+  {
+    // merge of the slices' lists: rounds of "smallest remaining key" (keys are distinct)
+    uint64_t mine[kMaxSlices * kMaxProbes / 32];
+    const uint32_t total = a.slices * a.T;
+#pragma unroll
+    for (uint32_t i = 0; i < kMaxSlices * kMaxProbes / 32; ++i)
+      mine[i] = lane + 32 * i < total ? a.keys[q * total + lane + 32 * i] : kMaxKey;
+    uint64_t cand_key = kMaxKey;  // lane j ends up with the j-th smallest key
+    for (uint32_t j = 0; j < a.T; ++j) {
+      uint64_t best = mine[0];
+#pragma unroll
+      for (uint32_t i = 1; i < kMaxSlices * kMaxProbes / 32; ++i) best = mine[i] < best ? mine[i] : best;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const uint64_t other = __shfl_xor_sync(0xFFFFFFFFu, best, o);
+        best = other < best ? other : best;
+      }
+#pragma unroll
+      for (uint32_t i = 0; i < kMaxSlices * kMaxProbes / 32; ++i)
+        if (mine[i] == best) mine[i] = kMaxKey;
+      if (lane == j) cand_key = best;
+    }
+    if (a.rescore) {
+      // exact score of candidate `lane`: the same fused-multiply-add chain as the exact scan
+      if (cand_key != kMaxKey) {
+        const uint32_t c = key_id(cand_key);
+        const float* qv = a.queries + q * a.dim;
+        const float* cv = a.cen + static_cast<uint64_t>(c) * a.dim;
+        float acc = 0.0f;
+        for (uint32_t k = 0; k < a.dim; k += 4) {
+          const float4 x = ldg_f4(qv + k), y = ldg_f4(cv + k);
+          acc = __fmaf_rn(x.x, y.x, acc);
+          acc = __fmaf_rn(x.y, y.y, acc);
+          acc = __fmaf_rn(x.z, y.z, acc);
+          acc = __fmaf_rn(x.w, y.w, acc);
+        }
+        const float sc = a.metric == GRAB_METRIC_L2 ? __fmaf_rn(-2.0f, acc, __ldg(a.cnorm + c)) : -acc;
+        cand_key = make_key(sc, c);
+      }
+    }
+    for (uint32_t j = 0; j < a.p; ++j) {  // the p best of the (re-scored) candidates, best first
+      uint64_t best = cand_key;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const uint64_t other = __shfl_xor_sync(0xFFFFFFFFu, best, o);
+        best = other < best ? other : best;
+      }
+      if (cand_key == best) cand_key = kMaxKey;
+      if (lane == 0) probes[j] = best == kMaxKey ? kInvalid : key_id(best);
+    }
+    __syncwarp();
+  }
   // the query's id windows
   uint32_t nwin = 1, wlo = 0, whi = n32, mask = 0;
   bool check = false;  // no id window: test the predicate on every pick
@@ -315,12 +407,8 @@ __global__ void __launch_bounds__(256) route_seeds_kernel(RouteArgs a) {
     tlo = a.lo ? a.lo[q] : a.lo1;
     thi = a.hi ? a.hi[q] : a.hi1;
     if (a.ts_sorted) {
-      uint32_t b = 0, e = n32;
-      while (b < e) { const uint32_t mid = (b + e) >> 1; if (a.ts[mid] < tlo) b = mid + 1; else e = mid; }
-      wlo = b;
-      e = n32;
-      while (b < e) { const uint32_t mid = (b + e) >> 1; if (a.ts[mid] < thi) b = mid + 1; else e = mid; }
-      whi = b;
+      wlo = warp_lower_bound_u64(a.ts, n32, tlo);
+      whi = warp_lower_bound_u64(a.ts, n32, thi);
       if (whi <= wlo) nwin = 0;
     } else {
       check = true;
@@ -339,7 +427,7 @@ __global__ void __launch_bounds__(256) route_seeds_kernel(RouteArgs a) {
     uint32_t id = kInvalid;
     if (nwin) {
       const uint32_t j = s % p, t = s / p, w = t % nwin, r = t / nwin;
-      const uint32_t c = a.probes[q * p + j];
+      const uint32_t c = probes[j];
       if (c < a.C) {
         uint32_t lo_id = wlo, hi_id = whi;
         if (a.filter_kind == GRAB_FILTER_LABELS && a.label_offsets) {
@@ -380,17 +468,29 @@ __global__ void __launch_bounds__(256) route_seeds_kernel(RouteArgs a) {
 
 template <int METRIC>
 cudaError_t launch_nearest(const float* X, uint64_t m, uint32_t dim, const float* cen, const float* cnorm,
-                           uint32_t C, uint32_t P, uint32_t* out, cudaStream_t st) {
+                           uint32_t C, uint32_t P, uint32_t* out_ids, uint64_t* out_keys, uint32_t slices,
+                           cudaStream_t st) {
   if (m == 0) return cudaSuccess;
-  nearest_centroids_kernel<METRIC><<<static_cast<unsigned>((m + kRtBM - 1) / kRtBM), kRtThreads, 0, st>>>(
-      X, m, dim, cen, cnorm, C, P, out);
+  const dim3 grid(static_cast<unsigned>((m + kRtBM - 1) / kRtBM), slices);
+  nearest_centroids_kernel<METRIC><<<grid, kRtThreads, 0, st>>>(X, m, dim, cen, cnorm, C, P, out_ids, out_keys);
   return cudaGetLastError();
 }
 
 cudaError_t nearest(int metric, const float* X, uint64_t m, uint32_t dim, const float* cen, const float* cnorm,
-                    uint32_t C, uint32_t P, uint32_t* out, cudaStream_t st) {
-  return metric == GRAB_METRIC_L2 ? launch_nearest<GRAB_METRIC_L2>(X, m, dim, cen, cnorm, C, P, out, st)
-                                  : launch_nearest<GRAB_METRIC_IP>(X, m, dim, cen, cnorm, C, P, out, st);
+                    uint32_t C, uint32_t P, uint32_t* out_ids, cudaStream_t st, uint64_t* out_keys = nullptr,
+                    uint32_t slices = 1) {
+  return metric == GRAB_METRIC_L2
+             ? launch_nearest<GRAB_METRIC_L2>(X, m, dim, cen, cnorm, C, P, out_ids, out_keys, slices, st)
+             : launch_nearest<GRAB_METRIC_IP>(X, m, dim, cen, cnorm, C, P, out_ids, out_keys, slices, st);
+}
+
+// Centroid slices for a routing launch of nq queries: enough CTAs to fill the GPU a few times.
+uint32_t route_slices(uint64_t nq, uint32_t C) {
+  const uint64_t row_tiles = (nq + kRtBM - 1) / kRtBM;
+  const uint32_t col_tiles = (C + kRtBN - 1) / kRtBN;
+  uint32_t s = 1;
+  while (s < kMaxSlices && s * 2 <= col_tiles && row_tiles * s < 4 * 148) s *= 2;
+  return s;
 }
 
 // assign[m] -> offsets[C+1], members[m]; counts is scratch of ceil(m/kChunk) * C words
@@ -463,6 +563,11 @@ int router_build_impl(const float* d_dataset, uint32_t dim, uint64_t n, int metr
   return GRAB_OK;
 }
 
+bool route_tc_usable(const float*, uint64_t, uint32_t, const float*, uint32_t, uint32_t);
+uint32_t route_tc_slices(uint64_t, uint32_t);
+int route_tc_launch(int, const float*, uint64_t, uint32_t, const float*, const float*, uint32_t, uint32_t, uint32_t,
+                    uint64_t*, int*, cudaStream_t);
+
 int route_seeds_impl(const grab_router* r, const float* d_queries, uint64_t nq, uint64_t n, const grab_filter* f,
                      uint32_t probes, uint32_t S, uint64_t seed, uint32_t* d_seeds, void* d_ws, size_t ws_bytes,
                      cudaStream_t st) {
@@ -511,10 +616,28 @@ int route_seeds_impl(const grab_router* r, const float* d_queries, uint64_t nq, 
     set_last_error("route_seeds: workspace %zu < %zu bytes", ws_bytes, need);
     return GRAB_ERR_WORKSPACE;
   }
-  uint32_t* d_probes = static_cast<uint32_t*>(ws);
-  GRAB_CUDA_TRY(nearest(r->metric, d_queries, nq, r->dim, r->d_centroids, r->d_centroid_norms, r->num_centroids,
-                        probes, d_probes, st));
-  a.probes = d_probes;
+  int* d_status = static_cast<int*>(ws);
+  uint64_t* d_keys = reinterpret_cast<uint64_t*>(static_cast<char*>(ws) + 256);
+  const uint32_t T_tc = probes + 4 <= 16 ? probes + 4 : 16;
+  a.queries = d_queries; a.cen = r->d_centroids; a.cnorm = r->d_centroid_norms; a.dim = r->dim; a.metric = r->metric;
+  if (!(r->flags & GRAB_ROUTER_EXACT_SCAN) && probes + 4 <= 16 &&
+      route_tc_usable(d_queries, nq, r->dim, r->d_centroids, r->num_centroids, T_tc)) {
+    // tensor cores: tf32 scores, probes + 4 candidates per query, re-scored exactly by the seed kernel
+    a.slices = route_tc_slices(nq, r->num_centroids);
+    a.T = T_tc;
+    a.rescore = 1;
+    a.status = d_status;
+    GRAB_CUDA_TRY(cudaMemsetAsync(d_status, 0, sizeof(int), st));
+    int rc = route_tc_launch(r->metric, d_queries, nq, r->dim, r->d_centroids, r->d_centroid_norms,
+                             r->num_centroids, a.T, a.slices, d_keys, d_status, st);
+    if (rc != GRAB_OK) return rc;
+  } else {
+    a.slices = route_slices(nq, r->num_centroids);
+    a.T = probes;
+    GRAB_CUDA_TRY(nearest(r->metric, d_queries, nq, r->dim, r->d_centroids, r->d_centroid_norms, r->num_centroids,
+                          probes, nullptr, st, d_keys, a.slices));
+  }
+  a.keys = d_keys;
   route_seeds_kernel<<<static_cast<unsigned>((nq * 32 + 255) / 256), 256, 0, st>>>(a);
   GRAB_CUDA_TRY(cudaGetLastError());
   if (own.ptr) GRAB_CUDA_TRY(cudaStreamSynchronize(st));
@@ -534,5 +657,6 @@ int nearest_centroids_impl(const grab_router* r, const float* d_rows, uint64_t m
 }  // namespace grab
 
 extern "C" size_t grab_route_seeds_workspace_bytes(uint64_t nq, uint32_t probes) {
-  return ((sizeof(uint32_t) * nq * (probes ? probes : 1) + 255) / 256) * 256;
+  // a status word, then (score, centroid) keys of up to 8 centroid slices per query, probes + 4 each
+  return 256 + ((sizeof(uint64_t) * nq * 8 * (probes + 4) + 255) / 256) * 256;
 }

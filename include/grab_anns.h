@@ -299,7 +299,12 @@ typedef struct grab_router {
   const float* d_centroid_norms;    /* [num_centroids] squared norms */
   const uint32_t* d_member_offsets; /* [num_centroids + 1] */
   const uint32_t* d_members;        /* [n] ids grouped by nearest centroid, ascending inside a group */
+  uint32_t flags;                   /* GRAB_ROUTER_* */
 } grab_router;
+/* grab_route_seeds ranks the centroids with the exact fp32 scan instead of the tensor cores
+ * (tf32 products, probes + 4 candidates re-scored exactly).  Both give the same seeds unless
+ * tf32 rounding moves a centroid more than four ranks. */
+#define GRAB_ROUTER_EXACT_SCAN 1u
 
 /* Trains `num_centroids` centroids (Lloyd, `iterations` rounds over a strided sample of
  * max_sample rows; 0 = 64 per centroid), assigns all n vectors and writes the four arrays a

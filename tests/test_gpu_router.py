@@ -129,3 +129,35 @@ def test_routed_seeds_reach_separated_clusters(grab, oracle):
     assert ((routed >= lo[:, None].astype(np.int64)) & (routed < hi[:, None].astype(np.int64)) | (routed < 0)).all()
     r_plain, r_routed = oracle.recall(plain.cpu().numpy(), gt), oracle.recall(routed, gt)
     assert r_routed > 0.95 and r_routed > r_plain + 0.1, (r_plain, r_routed)
+
+
+@pytest.mark.parametrize("dim,metric,nc,nq", [(128, 0, 256, 1000), (100, 0, 200, 300), (768, 1, 384, 513)])
+def test_tensor_core_routing_matches_exact_scan(grab, oracle, dim, metric, nc, nq):
+    """Centroid ranking on the tensor cores (tf32, probes + 4 candidates re-scored exactly) gives the
+    seeds of the exact fp32 scan, which are the oracle's: ragged row, column and K tiles included."""
+    rng = np.random.default_rng(dim + nc)
+    n = 30000 if dim < 768 else 12000
+    data = clustered(n, dim, 60, 0.7, dim + 7)
+    if metric == 1:
+        data /= np.linalg.norm(data, axis=1, keepdims=True)
+    q = data[rng.integers(0, n, nq)] + np.float32(0.02) * rng.standard_normal((nq, dim)).astype(np.float32)
+    d_data, d_q = _t(data), _t(q)
+    r = grab.router_build(d_data, nc, metric=metric, iterations=3, max_sample=8000)
+    cen, cnorm, offs, mem = (r.centroids.cpu().numpy(), r.norms.cpu().numpy(), _u32(r.offsets), _u32(r.members))
+    ts = np.arange(n, dtype=np.uint64)
+    lo = rng.integers(0, n // 2, nq).astype(np.uint64)
+    hi = lo + np.uint64(n // 3)
+    f = grab.make_filter(grab.FILTER_TS_RANGE, ts=_t(ts.view(np.int64)), lo=_t(lo.view(np.int64)),
+                         hi=_t(hi.view(np.int64)), ts_sorted=True)
+    for P, S in [(4, 32), (1, 8), (12, 48)]:
+        tc = _u32(grab.route_seeds(r.exact(False), d_q, n, f, probes=P, seeds_per_query=S))
+        ex = _u32(grab.route_seeds(r.exact(True), d_q, n, f, probes=P, seeds_per_query=S))
+        probes = oracle.nearest_centroids(q, cen, cnorm, metric, P)
+        want = oracle.route_seeds(probes, n, offs, mem, S, ts=ts, lo=lo, hi=hi)
+        assert np.array_equal(ex, want)
+        assert np.array_equal(tc, want)
+    r.exact(False)
+    # 13 probes and more: no room for 4 spare candidates, the exact scan runs
+    tc = _u32(grab.route_seeds(r, d_q, n, f, probes=14, seeds_per_query=56))
+    probes = oracle.nearest_centroids(q, cen, cnorm, metric, 14)
+    assert np.array_equal(tc, oracle.route_seeds(probes, n, offs, mem, 56, ts=ts, lo=lo, hi=hi))
