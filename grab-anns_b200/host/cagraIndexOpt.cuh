@@ -61,6 +61,17 @@ class CagraIndexOpt {
   void setKnnPrecision(int precision) { knn_precision_ = precision; }
   void setSeed(uint64_t seed) { seed_ = seed; }
   void setInsertBatch(size_t batch) { insert_batch_ = batch ? batch : 1024; }
+  // Entry-point router: searches that get no seeds from the caller start from members of the
+  // query's nearest k-means centroids that pass the filter, instead of uniformly drawn ids.
+  // centroids = 0 switches it off (the reference's behaviour), kRouterAuto picks about sqrt(n).
+  // The centroids are trained on the first query after build/load; inserts only re-assign.
+  static constexpr uint32_t kRouterAuto = 0xFFFFFFFFu;
+  void setRouter(uint32_t centroids, uint32_t probes = 4, uint32_t seeds_per_query = 32) {
+    router_centroids_ = centroids;
+    router_probes_ = probes ? probes : 4;
+    router_seeds_ = seeds_per_query ? seeds_per_query : 32;
+    router_.reset();
+  }
 
  private:
   uint64_t bucket_of(uint64_t ts) const { return ts / bucket_width_; }
@@ -83,6 +94,11 @@ class CagraIndexOpt {
   // the reference inserts 32 at a time (src/cagraIndexOpt.cu:590); the sparse mailboxes and the
   // exact kNN inside the batch make four-digit batches as good and far faster
   size_t insert_batch_ = 1024;
+  struct RouterState;
+  struct RouterDeleter { void operator()(RouterState*) const; };
+  const grab_router* ensure_router();  // nullptr when switched off or the index is too small
+  uint32_t router_centroids_ = kRouterAuto, router_probes_ = 4, router_seeds_ = 32;
+  std::unique_ptr<RouterState, RouterDeleter> router_;
 };
 
 }  // namespace cagra

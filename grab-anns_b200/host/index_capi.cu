@@ -46,6 +46,9 @@ int grab_index_opt_set_query_params(void* h, uint32_t itopk, uint32_t width, uin
                                     uint32_t hash_bitlen) {
   return guarded([&] { O(h)->setQueryParams(itopk, width, min_iter, max_iter, hash_bitlen); });
 }
+int grab_index_opt_set_router(void* h, uint32_t centroids, uint32_t probes, uint32_t seeds_per_query) {
+  return guarded([&] { O(h)->setRouter(centroids, probes, seeds_per_query); });
+}
 int grab_index_opt_add(void* h, size_t n, const float* v, const uint64_t* ts) { return guarded([&] { O(h)->add(n, v, ts); }); }
 int grab_index_opt_build(void* h) { return guarded([&] { O(h)->build(); }); }
 int grab_index_opt_insert(void* h, size_t n, const float* v, const uint64_t* ts) { return guarded([&] { O(h)->insert(n, v, ts); }); }

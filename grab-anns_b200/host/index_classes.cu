@@ -58,11 +58,19 @@ grab_search_args make_args(const float* d_data, uint64_t n, uint32_t dim, int me
 
 // queries up, one filtered search, results down
 void run_search(grab_search_args a, const float* host_q, size_t nq, uint32_t dim, int k, const uint32_t* host_seeds,
-                size_t seeds_per_query, bool broadcast_seeds, int64_t* host_ids, float* host_dists) {
+                size_t seeds_per_query, bool broadcast_seeds, int64_t* host_ids, float* host_dists,
+                const grab_router* router = nullptr, uint32_t probes = 0, uint32_t routed_seeds = 0) {
   Scratch dq(nq * dim * sizeof(float)), di(nq * k * sizeof(int64_t)), dd(nq * k * sizeof(float));
   cu(cudaMemcpy(dq.p, host_q, nq * dim * sizeof(float), cudaMemcpyHostToDevice), "H2D queries");
   std::unique_ptr<Scratch> ds;
-  if (host_seeds && seeds_per_query) {
+  if (router && !(host_seeds && seeds_per_query)) {
+    // seeds from the entry-point router: members of the nearest centroids that pass the filter
+    ds.reset(new Scratch(nq * routed_seeds * sizeof(uint32_t)));
+    ok(grab_route_seeds(router, dq.as<float>(), nq, a.n, &a.filter, probes, routed_seeds, a.seed, ds->as<uint32_t>(),
+                        nullptr, 0, nullptr), "seed routing");
+    a.d_seeds = ds->as<uint32_t>();
+    a.seeds_per_query = routed_seeds;
+  } else if (host_seeds && seeds_per_query) {
     ds.reset(new Scratch(nq * seeds_per_query * sizeof(uint32_t)));
     if (broadcast_seeds) {
       std::vector<uint32_t> all(nq * seeds_per_query);
@@ -311,6 +319,49 @@ std::vector<uint32_t> CagraIndexOpt::sample_seeds_by_time(uint64_t min_ts, uint6
   return sample_ids(cand, num, seed_);
 }
 
+struct CagraIndexOpt::RouterState {
+  grab_router r{};
+  std::unique_ptr<Scratch> cen, norms, offsets, members;
+  size_t assigned = 0;  // vectors covered by the member lists
+  size_t trained = 0;   // index size when the centroids were trained
+};
+void CagraIndexOpt::RouterDeleter::operator()(RouterState* s) const { delete s; }
+
+const grab_router* CagraIndexOpt::ensure_router() {
+  const size_t n = current_size_;
+  if (router_centroids_ == 0 || n < 4096) return nullptr;
+  if (router_ && router_->assigned == n) return &router_->r;
+  uint32_t c = router_centroids_;
+  if (c == kRouterAuto) {  // about sqrt(n), a power of two in [64, 4096]
+    c = 64;
+    while (c < 4096 && static_cast<size_t>(c) * c < n) c *= 2;
+  }
+  if (c > n / 8) c = static_cast<uint32_t>(n / 8);
+  const bool retrain = !router_ || router_->r.num_centroids != c || n > 2 * router_->trained;
+  if (retrain) {
+    router_.reset(new RouterState());
+    router_->cen.reset(new Scratch(static_cast<size_t>(c) * dim_ * sizeof(float)));
+    router_->norms.reset(new Scratch(c * sizeof(float)));
+    router_->offsets.reset(new Scratch((c + 1) * sizeof(uint32_t)));
+    router_->trained = n;
+  }
+  router_->members.reset(new Scratch(n * sizeof(uint32_t)));
+  ok(grab_router_build(static_cast<float*>(d_data_->data()), dim_, n, metric_, c, retrain ? 10 : 0, 0,
+                       router_->cen->as<float>(), router_->norms->as<float>(), router_->offsets->as<uint32_t>(),
+                       router_->members->as<uint32_t>(), nullptr),
+     "router build");
+  router_->r.num_centroids = c;
+  router_->r.dim = dim_;
+  router_->r.metric = metric_;
+  router_->r.d_centroids = router_->cen->as<float>();
+  router_->r.d_centroid_norms = router_->norms->as<float>();
+  router_->r.d_member_offsets = router_->offsets->as<uint32_t>();
+  router_->r.d_members = router_->members->as<uint32_t>();
+  router_->r.flags = 0;
+  router_->assigned = n;
+  return &router_->r;
+}
+
 void CagraIndexOpt::build() {
   const size_t n = h_data_.size() / dim_;
   if (n == 0) return;
@@ -350,7 +401,8 @@ void CagraIndexOpt::query(const float* host_queries, size_t num_queries, int k, 
                                  static_cast<uint32_t*>(d_graph_->data()), graph_degree_, nullptr, num_queries, k,
                                  search_params_, nullptr, nullptr, seed_);
   a.filter.kind = GRAB_FILTER_NONE;
-  run_search(a, host_queries, num_queries, dim_, k, seeds, num_seeds_per_query, false, host_indices, host_dists);
+  run_search(a, host_queries, num_queries, dim_, k, seeds, num_seeds_per_query, false, host_indices, host_dists,
+             ensure_router(), router_probes_, router_seeds_);
 }
 
 void CagraIndexOpt::query_local(const float* host_queries, size_t num_queries, int k, uint64_t target_timestamp,
@@ -395,7 +447,8 @@ void CagraIndexOpt::range_search(const float* host_queries, size_t nq, int k, co
   std::vector<uint32_t> seeds;
   size_t spq = 0;
   bool broadcast = true;
-  if (!ts_sorted_) {
+  const grab_router* router = ensure_router();
+  if (!ts_sorted_ && !router) {
     // host seed sampling as the reference does it: up to 500 ids per bucket, then a uniform
     // sample of max(32, itopk/4) (src/cagraIndexOpt.cu:441-474); per query when ranges differ
     spq = std::max(32u, search_params_.itopk_size / 4);
@@ -424,7 +477,8 @@ void CagraIndexOpt::range_search(const float* host_queries, size_t nq, int k, co
       seeds = sample_range(lo1, hi1, 0);
     }
   }
-  run_search(a, host_queries, nq, dim_, k, seeds.empty() ? nullptr : seeds.data(), spq, broadcast, ids, dists);
+  run_search(a, host_queries, nq, dim_, k, seeds.empty() ? nullptr : seeds.data(), spq, broadcast, ids, dists,
+             router, router_probes_, router_seeds_);
 }
 
 void CagraIndexOpt::query_range(const float* host_queries, size_t num_queries, int k, uint64_t start_bucket,

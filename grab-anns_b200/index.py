@@ -96,6 +96,10 @@ class CagraIndexOpt(_Base):
         self._call("query", _ptr(q), C.c_size_t(q.shape[0]), C.c_int(k), _ptr(ids), _ptr(d))
         return ids, d
 
+    def set_router(self, centroids=0xFFFFFFFF, probes=4, seeds_per_query=32):
+        """Entry-point router for searches without caller seeds: 0 = off, 0xFFFFFFFF = about sqrt(n)."""
+        self._call("set_router", C.c_uint32(centroids), C.c_uint32(probes), C.c_uint32(seeds_per_query))
+
     def query_local(self, queries, k, target_timestamp):
         q = _f32(queries)
         ids, d = self._out(q.shape[0], k)

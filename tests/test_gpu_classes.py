@@ -127,6 +127,41 @@ def test_opt_per_query_ranges_with_bucket_width(grab, oracle, index_mod):
     assert oracle.recall(ids, gt) > 0.95
 
 
+def test_opt_router_on_separated_clusters_and_after_insert(grab, oracle, index_mod):
+    """Well-separated clusters, short searches: with uniformly drawn seeds most queries never reach
+    their cluster; the class's entry-point router (default on) starts inside it.  Inserted vectors
+    join the member lists on the next query."""
+    import torch
+    n, extra, dim, k = 24000, 4000, 64, 10
+    data = clustered(n + extra, dim, 120, 0.15, 81)
+    ts = np.arange(n + extra, dtype=np.uint64)
+    rng = np.random.default_rng(82)
+
+    def recall_of(idx, upto):
+        q = data[rng.integers(0, upto, 200)] + np.float32(0.01)
+        lo = rng.integers(0, upto - upto // 4, 200).astype(np.uint64)
+        hi = lo + np.uint64(upto // 4)
+        ids, _ = idx.query_range_batch(q, k, lo, hi)
+        assert (((ids >= lo[:, None]) & (ids < hi[:, None])) | (ids < 0)).all()
+        f = grab.make_filter(grab.FILTER_TS_RANGE, ts=torch.from_numpy(ts[:upto].view(np.int64)).cuda(),
+                             lo=torch.from_numpy(lo.view(np.int64)).cuda(), hi=torch.from_numpy(hi.view(np.int64)).cuda())
+        gt = grab.exact_search(torch.from_numpy(data[:upto]).cuda(), torch.from_numpy(q).cuda(), k, flt=f)[0]
+        return oracle.recall(ids, gt.cpu().numpy())
+
+    idx = index_mod.CagraIndexOpt(dim, 32, 24, bucket_width=4000)
+    idx.add(data[:n], ts[:n])
+    idx.build()
+    idx.set_query_params(64, 2, 0, 8, 11)
+    idx.set_router(0)
+    r_off = recall_of(idx, n)
+    idx.set_router()                       # automatic size, the default
+    r_on = recall_of(idx, n)
+    assert r_on > 0.95 and r_on > r_off + 0.1, (r_off, r_on)
+    idx.insert(data[n:], ts[n:])
+    r_ins = recall_of(idx, n + extra)
+    assert r_ins > 0.9, r_ins
+
+
 def test_cagra_index_build_insert_range_save(grab, oracle, index_mod, tmp_path):
     # tests/test_cagra_insert.cu: build 50 %, insert 50 % in batches of 64, recall@10 > 90 % (:284)
     # tests/test_cagra_auto.cu: query_range at several ratios against the exact filtered ground truth
