@@ -435,6 +435,8 @@ def main():
         except Exception:
             pass
         peak = float(peaks.get("hbm_gbs", 6650.0))
+        if args.sharded:
+            alg_bytes //= world     # counters were summed over the ranks; the roofline is one GPU's launch
         achieved = alg_bytes / (ms_search / 1e3) / 1e9
         # dram__bytes_read.sum + dram__bytes_write.sum of one search launch at the default full-size
         # configuration (ncu capture summarised in profiles/graph_search_kernel_C2.md)

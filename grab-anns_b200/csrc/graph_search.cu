@@ -28,13 +28,17 @@ namespace grab {
 #define GRAB_SEARCH_THREADS 64
 #endif
 constexpr int kSearchThreads = GRAB_SEARCH_THREADS;
-constexpr int kSearchTeams = kSearchThreads / kTeam;  // 16
+constexpr int kSearchTeams = kSearchThreads / kTeam;  // 8 teams of 8 lanes
 // vectors in flight per team and resident CTAs per SM the register budget is capped for
 #ifndef GRAB_SEARCH_UNROLL
 #define GRAB_SEARCH_UNROLL 2
 #endif
 #ifndef GRAB_SEARCH_CTAS_PER_SM
-#define GRAB_SEARCH_CTAS_PER_SM 12
+#define GRAB_SEARCH_CTAS_PER_SM 14
+#endif
+#ifndef GRAB_SEARCH_QREG
+#define GRAB_SEARCH_QREG 0  // 1: the query's float4 chunks live in registers (fixed dims); 0: re-read from shared
+                            // memory, which frees the registers for 14 CTAs per SM (measured faster)
 #endif
 constexpr int kSearchUnroll = GRAB_SEARCH_UNROLL;
 constexpr int kSearchCtasPerSm = GRAB_SEARCH_CTAS_PER_SM;
@@ -194,12 +198,17 @@ graph_search_kernel(const SearchKernelArgs a) {
   };
   __syncthreads();
 
+#if GRAB_SEARCH_QREG
   float4 qreg[CPL > 0 ? CPL : 1];
   if (CPL > 0) {
 #pragma unroll
     for (int c = 0; c < CPL; ++c)
       qreg[c] = *reinterpret_cast<const float4*>(q_smem + 4 * (lane8 + kTeam * c));
   }
+#define GRAB_Q(c) qreg[c]
+#else
+#define GRAB_Q(c) (*reinterpret_cast<const float4*>(q_smem + 4 * (lane8 + kTeam * (c))))
+#endif
 
   // ---- seeds (compute_distance.cuh:204-269): provided ids, else pseudo-random ids ----
   {
@@ -246,7 +255,7 @@ graph_search_kernel(const SearchKernelArgs a) {
 
   uint32_t iter = 0;
   for (;;) {
-    // ---- distances of the compacted candidates: 16 teams, vectors gathered with 16-byte loads;
+    // ---- distances of the compacted candidates: 8 teams, vectors gathered with 16-byte loads;
     //      a key is kept only if it beats the current worst entry of the itopk list ----
     const uint32_t ncand = s_ncand;
     const uint64_t worst = queue[a.sort_cap - 1];
@@ -272,7 +281,7 @@ graph_search_kernel(const SearchKernelArgs a) {
         for (int u = 0; u < kSearchUnroll; ++u)
 #pragma unroll
           for (int c = 0; c < CPL; ++c)
-            if (ok[u]) acc[u] = accum4<METRIC>(acc[u], qreg[c], x[u][c]);
+            if (ok[u]) acc[u] = accum4<METRIC>(acc[u], GRAB_Q(c), x[u][c]);
       } else {
         for (uint32_t c = lane8; c < nchunk; c += kTeam) {
           const float4 qv = *reinterpret_cast<const float4*>(q_smem + 4 * c);

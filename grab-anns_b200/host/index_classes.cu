@@ -675,31 +675,18 @@ uint64_t TimeStampIndex::insert(const float* vectors, const uint64_t* timestamps
   return start;
 }
 
-// Lloyd's k-means: the assignment step is the exact nearest-centroid scan on the GPU.
+// Lloyd's k-means over all n points on the device (the router's deterministic trainer: tiled
+// nearest-centroid kernel, grouped member lists, ordered means); the reference calls
+// faiss::Clustering here (src/timeStampIndex.cu:169-179).
 static std::vector<float> kmeans(const float* h_data, size_t n, uint32_t dim, size_t kc, int iters) {
-  std::vector<float> cen(kc * dim);
-  for (size_t c = 0; c < kc; ++c) memcpy(&cen[c * dim], h_data + (c * n / kc) * dim, dim * sizeof(float));
-  Scratch dd(n * dim * sizeof(float)), dc(kc * dim * sizeof(float)), di(n * sizeof(int64_t)), ds(n * sizeof(float));
+  Scratch dd(n * dim * sizeof(float)), dc(kc * dim * sizeof(float)), dn(kc * sizeof(float)),
+      doff((kc + 1) * sizeof(uint32_t)), dmem(n * sizeof(uint32_t));
   cu(cudaMemcpy(dd.p, h_data, n * dim * sizeof(float), cudaMemcpyHostToDevice), "H2D kmeans data");
-  std::vector<int64_t> assign(n);
-  std::vector<double> sum(kc * dim);
-  std::vector<size_t> cnt(kc);
-  for (int it = 0; it < iters; ++it) {
-    cu(cudaMemcpy(dc.p, cen.data(), cen.size() * sizeof(float), cudaMemcpyHostToDevice), "H2D centroids");
-    ok(grab_exact_search(dc.as<float>(), kc, dim, GRAB_METRIC_L2, nullptr, dd.as<float>(), n, 1, di.as<int64_t>(),
-                         ds.as<float>(), nullptr, 0, nullptr), "kmeans assignment");
-    cu(cudaMemcpy(assign.data(), di.p, n * sizeof(int64_t), cudaMemcpyDeviceToHost), "D2H assignment");
-    std::fill(sum.begin(), sum.end(), 0.0);
-    std::fill(cnt.begin(), cnt.end(), 0);
-    for (size_t i = 0; i < n; ++i) {
-      const size_t c = static_cast<size_t>(assign[i]);
-      ++cnt[c];
-      for (uint32_t d = 0; d < dim; ++d) sum[c * dim + d] += h_data[i * dim + d];
-    }
-    for (size_t c = 0; c < kc; ++c)
-      if (cnt[c])
-        for (uint32_t d = 0; d < dim; ++d) cen[c * dim + d] = static_cast<float>(sum[c * dim + d] / cnt[c]);
-  }
+  ok(grab_router_build(dd.as<float>(), dim, n, GRAB_METRIC_L2, static_cast<uint32_t>(kc), static_cast<uint32_t>(iters), n,
+                       dc.as<float>(), dn.as<float>(), doff.as<uint32_t>(), dmem.as<uint32_t>(), nullptr),
+     "k-means");
+  std::vector<float> cen(kc * dim);
+  cu(cudaMemcpy(cen.data(), dc.p, cen.size() * sizeof(float), cudaMemcpyDeviceToHost), "D2H centroids");
   return cen;
 }
 
