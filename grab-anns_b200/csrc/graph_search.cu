@@ -283,15 +283,26 @@ graph_search_kernel(const SearchKernelArgs a) {
           for (int c = 0; c < CPL; ++c)
             if (ok[u]) acc[u] = accum4<METRIC>(acc[u], GRAB_Q(c), x[u][c]);
       } else {
-        for (uint32_t c = lane8; c < nchunk; c += kTeam) {
-          const float4 qv = *reinterpret_cast<const float4*>(q_smem + 4 * c);
-          float4 x[kSearchUnroll];
+        // any dimension: four chunks per vector in flight, accumulated in ascending chunk order
+        for (uint32_t c0 = lane8; c0 < nchunk; c0 += 4 * kTeam) {
+          float4 x[kSearchUnroll][4];
 #pragma unroll
           for (int u = 0; u < kSearchUnroll; ++u)
-            if (ok[u]) x[u] = ldg_f4(a.data + static_cast<size_t>(id[u]) * a.dim + 4 * c);
 #pragma unroll
-          for (int u = 0; u < kSearchUnroll; ++u)
-            if (ok[u]) acc[u] = accum4<METRIC>(acc[u], qv, x[u]);
+            for (int i = 0; i < 4; ++i) {
+              const uint32_t c = c0 + i * kTeam;
+              if (ok[u] && c < nchunk) x[u][i] = ldg_f4(a.data + static_cast<size_t>(id[u]) * a.dim + 4 * c);
+            }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t c = c0 + i * kTeam;
+            if (c < nchunk) {
+              const float4 qv = *reinterpret_cast<const float4*>(q_smem + 4 * c);
+#pragma unroll
+              for (int u = 0; u < kSearchUnroll; ++u)
+                if (ok[u]) acc[u] = accum4<METRIC>(acc[u], qv, x[u][i]);
+            }
+          }
         }
       }
 #pragma unroll
