@@ -41,15 +41,17 @@ def parse():
     ap.add_argument("--itopk", type=int, default=64)
     ap.add_argument("--width", type=int, default=3)
     ap.add_argument("--max-iter", type=int, default=0,
-                    help="0 = 6 with the entry-point router, 20 without")
+                    help="0 = 5 with the entry-point router, 20 without")
     ap.add_argument("--router-centroids", type=int, default=1024,
                     help="centroids of the entry-point router that draws the seeds (0 = seeds drawn "
                          "uniformly inside the filter by the search kernel)")
-    ap.add_argument("--probes", type=int, default=4, help="nearest centroids the seeds are taken from")
-    ap.add_argument("--seeds", type=int, default=32, help="routed seeds per query")
+    ap.add_argument("--probes", type=int, default=2, help="nearest centroids the seeds are taken from")
+    ap.add_argument("--seeds", type=int, default=64, help="routed seeds per query")
     ap.add_argument("--hash-bitlen", type=int, default=11)
     ap.add_argument("--knn-precision", type=int, default=1,
                     help="0 exact scan, 1 bf16 tensor cores (exact for integer-valued data), 2 split bf16")
+    ap.add_argument("--global-candidates", type=int, default=0,
+                    help="cross-bucket candidates of the build: 0 auto, 1 all-pairs, 2 routed graph search")
     ap.add_argument("--cpu-sample", type=int, default=0, help="queries in the CPU sample (0 = auto)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-overlap", action="store_true",
@@ -246,7 +248,7 @@ def workload_config(args, w):
 def main():
     args = parse()
     if args.max_iter == 0:
-        args.max_iter = 6 if args.router_centroids else 20
+        args.max_iter = 5 if args.router_centroids else 20
     if args.impl == "reference":
         return run_reference(args)
 
@@ -295,7 +297,8 @@ def main():
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     graph = grab.build_time_partitioned_graph(d_base, d_bucket, sizes, deg, args.local_degree, metric=w["metric"],
-                                              knn_precision=args.knn_precision)
+                                              knn_precision=args.knn_precision,
+                                              global_candidates=args.global_candidates)
     torch.cuda.synchronize()
     build_s = time.perf_counter() - t0
     router, router_s = None, 0.0
@@ -544,9 +547,10 @@ def main():
         # dram__bytes_read.sum + dram__bytes_write.sum of one search launch at the default full-size
         # configuration (ncu capture summarised in profiles/graph_search_kernel_C2.md)
         default_cfg = (args.workload == "C2" and args.scale == 1.0 and args.buckets == 20 and args.itopk == 64 and
-                       args.width == 3 and args.max_iter == 6 and args.hash_bitlen == 11 and
+                       args.width == 3 and args.max_iter == 5 and args.hash_bitlen == 11 and
                        args.selectivity == 0.10 and not args.sharded and args.router_centroids == 1024 and
-                       args.probes == 4 and args.seeds == 32 and args.local_degree == 48)
+                       args.probes == 2 and args.seeds == 64 and args.local_degree == 48 and
+                       args.global_candidates in (0, 1))
         traffic = 1488718336 + 1193216 if default_cfg else None
         line = {
             "metric": "filtered QPS at recall@10>=0.95",
@@ -556,6 +560,7 @@ def main():
             "dtype": "f32", "data": "synthetic", "config": workload_config(args, w),
             "recall_at_10": recall, "results_in_range": in_range,
             "build": {"seconds": build_s, "mvec_per_s": n / build_s / 1e6, "knn_precision": args.knn_precision,
+                      "global_candidates": args.global_candidates,
                       "router_seconds": router_s},
             "ms_search_kernel": ms_search, "ms_router": ms - ms_search if router is not None and not args.sharded else None,
             "e2e": {"value": (1 if args.sharded else world) * nq / (ms_e2e / 1e3), "unit": "queries/s",

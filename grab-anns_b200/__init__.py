@@ -19,6 +19,7 @@ METRIC_L2, METRIC_IP = 0, 1
 FILTER_NONE, FILTER_TS_RANGE, FILTER_LABELS, FILTER_PREFIX = 0, 1, 2, 3
 KNN_EXACT_SCAN, KNN_TC_BF16, KNN_TC_SPLIT = 0, 1, 2
 ROUTER_EXACT_SCAN = 1
+GLOBAL_AUTO, GLOBAL_ALL_PAIRS, GLOBAL_ROUTED_SEARCH = 0, 1, 2
 
 
 class GrabError(RuntimeError):
@@ -214,18 +215,26 @@ def knn_graph_blocks(dataset, block_offsets, k, mode=0, metric=METRIC_L2, want_d
     return (out, dists) if want_dists else out
 
 
+class TpBuildOptions(C.Structure):
+    _fields_ = [("knn_precision", C.c_int32), ("global_candidates", C.c_int32),
+                ("search_iterations", C.c_uint32), ("search_width", C.c_uint32)]
+
+
 def build_time_partitioned_graph(dataset, bucket, bucket_sizes, total_degree, local_degree,
-                                 metric=METRIC_L2, knn_precision=KNN_TC_SPLIT):
+                                 metric=METRIC_L2, knn_precision=KNN_TC_SPLIT, global_candidates=GLOBAL_AUTO,
+                                 search_iterations=0, search_width=0):
+    """grab_build_time_partitioned_graph_ex; global_candidates: GLOBAL_AUTO / _ALL_PAIRS / _ROUTED_SEARCH."""
     import numpy as np
     import torch
     n, dim = dataset.shape
     sizes = np.ascontiguousarray(np.asarray(bucket_sizes, dtype=np.uint64))
     graph = torch.full((n, total_degree), -1, dtype=torch.int32, device=dataset.device)
     torch.cuda.synchronize()
-    check(lib().grab_build_time_partitioned_graph(_p(dataset), C.c_uint64(n), C.c_uint32(dim),
-                                                  C.c_int(metric), _p(graph), _p(bucket), _p(sizes),
-                                                  C.c_uint32(len(sizes)), C.c_uint32(total_degree),
-                                                  C.c_uint32(local_degree), C.c_int(knn_precision)))
+    opt = TpBuildOptions(knn_precision, global_candidates, search_iterations, search_width)
+    check(lib().grab_build_time_partitioned_graph_ex(_p(dataset), C.c_uint64(n), C.c_uint32(dim),
+                                                     C.c_int(metric), _p(graph), _p(bucket), _p(sizes),
+                                                     C.c_uint32(len(sizes)), C.c_uint32(total_degree),
+                                                     C.c_uint32(local_degree), C.byref(opt)))
     return graph
 
 
@@ -278,7 +287,7 @@ def nearest_centroids(router: Router, rows, probes=1):
     return out
 
 
-def route_seeds(router: Router, queries, n, flt: Filter | None = None, probes=4, seeds_per_query=32,
+def route_seeds(router: Router, queries, n, flt: Filter | None = None, probes=2, seeds_per_query=64,
                 seed=0x1234ABCD, out=None, ws=None):
     """grab_route_seeds: int32 tensor [nq, seeds_per_query] (-1 = no seed found) for `seeds=`."""
     import torch

@@ -326,14 +326,84 @@ int grab_inject_reverse_remote_device(uint32_t* d_graph, uint64_t n, uint32_t to
   return inject_reverse_impl(d_graph, n, total_degree, local_degree, max_rev, static_cast<cudaStream_t>(stream));
 }
 
-int grab_build_time_partitioned_graph(const float* d_dataset, uint64_t total_num, uint32_t dim, int metric,
-                                      uint32_t* d_graph, const uint64_t* d_bucket,
-                                      const uint64_t* h_bucket_sizes, uint32_t num_buckets,
-                                      uint32_t total_degree, uint32_t local_degree, int knn_precision) {
+// int64 search results -> the uint32 candidate lists the remote-edge kernel consumes
+static __global__ void ids_to_cand_kernel(const int64_t* __restrict__ ids, uint64_t count, uint32_t* __restrict__ cand) {
+  const uint64_t i = blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x;
+  if (i < count) cand[i] = ids[i] < 0 ? kInvalid : static_cast<uint32_t>(ids[i]);
+}
+
+// Cross-bucket candidates by search instead of all-pairs (what the reference obtains from a
+// FAISS IVF-PQ index over the whole dataset, cagra_opt.cu:813-847): every vector is a query;
+// seeds are members of its nearest router centroids, spread evenly over all ids and hence over
+// all buckets; the search walks the local edges already in the graph (prefix filter), so each
+// seeded bucket contributes its neighbourhood of the query; the gk best overall are the
+// candidates (own-bucket hits and the vector itself are skipped by the remote-edge kernel).
+// Linear in N where the all-pairs stage is quadratic.
+static int global_candidates_by_search(const float* d_dataset, uint64_t n, uint32_t dim, int metric,
+                                       const uint32_t* d_graph, uint32_t total_degree, uint32_t local_degree,
+                                       uint32_t gk, uint32_t iterations, uint32_t width, uint32_t* d_cand) {
+  StageTimer tm("global candidates (routed search)");
+  uint32_t C = 256;
+  while (C < 8192 && static_cast<uint64_t>(C) * C < n) C *= 2;
+  ScopedDeviceBuffer cen, norms, offs, members;
+  GRAB_CUDA_TRY(cen.alloc(sizeof(float) * C * dim));
+  GRAB_CUDA_TRY(norms.alloc(sizeof(float) * C));
+  GRAB_CUDA_TRY(offs.alloc(sizeof(uint32_t) * (C + 1)));
+  GRAB_CUDA_TRY(members.alloc(sizeof(uint32_t) * n));
+  GRAB_TRY(router_build_impl(d_dataset, dim, n, metric, C, 10, 0, cen.as<float>(), norms.as<float>(),
+                             offs.as<uint32_t>(), members.as<uint32_t>(), nullptr));
+  grab_router r{};
+  r.num_centroids = C; r.dim = dim; r.metric = metric;
+  r.d_centroids = cen.as<float>(); r.d_centroid_norms = norms.as<float>();
+  r.d_member_offsets = offs.as<uint32_t>(); r.d_members = members.as<uint32_t>();
+  tm.mark("router");
+  const uint64_t chunk = 1ull << 18;
+  const uint32_t S = 64, probes = 4;
+  grab_search_params p{gk > 128 ? 256u : 128u, width ? width : 4, 0, iterations ? iterations : 10, 12};
+  ScopedDeviceBuffer seeds, ids, dists, rws, sws;
+  const size_t rws_bytes = grab_route_seeds_workspace_bytes(chunk, probes);
+  const size_t sws_bytes = grab_graph_search_workspace_bytes(chunk, p.hash_bitlen);
+  GRAB_CUDA_TRY(seeds.alloc(sizeof(uint32_t) * chunk * S));
+  GRAB_CUDA_TRY(ids.alloc(sizeof(int64_t) * chunk * gk));
+  GRAB_CUDA_TRY(dists.alloc(sizeof(float) * chunk * gk));
+  GRAB_CUDA_TRY(rws.alloc(rws_bytes));
+  GRAB_CUDA_TRY(sws.alloc(sws_bytes));
+  for (uint64_t q0 = 0; q0 < n; q0 += chunk) {
+    const uint64_t nq = n - q0 < chunk ? n - q0 : chunk;
+    const float* q = d_dataset + q0 * dim;
+    GRAB_TRY(route_seeds_impl(&r, q, nq, n, nullptr, probes, S, 0x5eed5eedull + q0, seeds.as<uint32_t>(), rws.ptr,
+                              rws_bytes, nullptr));
+    grab_search_args a;
+    memset(&a, 0, sizeof(a));
+    a.d_dataset = d_dataset; a.n = n; a.dim = dim; a.metric = metric;
+    a.d_graph = d_graph; a.graph_degree = total_degree;
+    a.d_queries = q; a.nq = nq; a.k = gk; a.params = p;
+    a.filter.kind = GRAB_FILTER_PREFIX; a.filter.active_degree = local_degree;
+    a.d_seeds = seeds.as<uint32_t>(); a.seeds_per_query = S; a.seed = 0x5eed5eedull + q0;
+    a.d_out_ids = ids.as<int64_t>(); a.d_out_dists = dists.as<float>();
+    a.id_scale = 1; a.d_ws = sws.ptr; a.ws_bytes = sws_bytes;
+    GRAB_TRY(graph_search_impl(&a));
+    ids_to_cand_kernel<<<static_cast<unsigned>((nq * gk + 255) / 256), 256>>>(ids.as<int64_t>(), nq * gk, d_cand + q0 * gk);
+    GRAB_CUDA_TRY(cudaGetLastError());
+  }
+  GRAB_CUDA_TRY(cudaDeviceSynchronize());
+  tm.mark("search");
+  return GRAB_OK;
+}
+
+int grab_build_time_partitioned_graph_ex(const float* d_dataset, uint64_t total_num, uint32_t dim, int metric,
+                                         uint32_t* d_graph, const uint64_t* d_bucket,
+                                         const uint64_t* h_bucket_sizes, uint32_t num_buckets,
+                                         uint32_t total_degree, uint32_t local_degree,
+                                         const grab_tp_build_options* options) {
   GRAB_REQUIRE(d_dataset && d_graph && d_bucket && h_bucket_sizes, "build_time_partitioned_graph: null pointer");
   GRAB_REQUIRE(num_buckets >= 1, "build_time_partitioned_graph: no buckets");
   GRAB_REQUIRE(total_degree >= 4 && total_degree <= 256 && local_degree >= 1 && local_degree <= total_degree,
                "build_time_partitioned_graph: bad degrees %u/%u", local_degree, total_degree);
+  const int knn_precision = options ? options->knn_precision : GRAB_KNN_TC_SPLIT;
+  int global_mode = options ? options->global_candidates : GRAB_GLOBAL_AUTO;
+  GRAB_REQUIRE(global_mode >= GRAB_GLOBAL_AUTO && global_mode <= GRAB_GLOBAL_ROUTED_SEARCH,
+               "build_time_partitioned_graph: unknown global_candidates mode %d", global_mode);
   std::vector<uint64_t> offs(num_buckets + 1, 0);
   for (uint32_t b = 0; b < num_buckets; ++b) offs[b + 1] = offs[b] + h_bucket_sizes[b];
   GRAB_REQUIRE(offs[num_buckets] == total_num, "build_time_partitioned_graph: bucket sizes sum to %llu, not %llu",
@@ -360,11 +430,22 @@ int grab_build_time_partitioned_graph(const float* d_dataset, uint64_t total_num
   gk = (gk + 32) - (gk % 32);
   if (gk < 64) gk = 64;
   if (gk > 256) gk = 256;
+  // all-pairs is exact but quadratic (0.5 s at 1M x 128, 75 s at 12.5M x 96): from 2^21 vectors on the
+  // routed search takes over (within 1 pp of the all-pairs graph in range-search recall)
+  if (global_mode == GRAB_GLOBAL_AUTO)
+    global_mode = total_num >= (1ull << 21) ? GRAB_GLOBAL_ROUTED_SEARCH : GRAB_GLOBAL_ALL_PAIRS;
+  if (total_num < 4096) global_mode = GRAB_GLOBAL_ALL_PAIRS;
   {
     ScopedDeviceBuffer cand;
     GRAB_CUDA_TRY(cand.alloc(sizeof(uint32_t) * total_num * gk));
-    GRAB_TRY(knn_dispatch(d_dataset, total_num, dim, metric, offs.data(), num_buckets, gk, 1,
-                          gk <= 204 ? knn_precision : GRAB_KNN_EXACT_SCAN, cand.as<uint32_t>(), nullptr, nullptr));
+    if (global_mode == GRAB_GLOBAL_ROUTED_SEARCH) {
+      GRAB_TRY(global_candidates_by_search(d_dataset, total_num, dim, metric, d_graph, total_degree, local_degree, gk,
+                                           options ? options->search_iterations : 0,
+                                           options ? options->search_width : 0, cand.as<uint32_t>()));
+    } else {
+      GRAB_TRY(knn_dispatch(d_dataset, total_num, dim, metric, offs.data(), num_buckets, gk, 1,
+                            gk <= 204 ? knn_precision : GRAB_KNN_EXACT_SCAN, cand.as<uint32_t>(), nullptr, nullptr));
+    }
     tm.mark("global candidates");
     GRAB_TRY(remote_edges_impl(d_graph, d_bucket, cand.as<uint32_t>(), total_num, total_degree, local_degree,
                                gk, nullptr));
@@ -373,6 +454,19 @@ int grab_build_time_partitioned_graph(const float* d_dataset, uint64_t total_num
   }
   GRAB_CUDA_TRY(cudaDeviceSynchronize());
   return GRAB_OK;
+}
+
+int grab_build_time_partitioned_graph(const float* d_dataset, uint64_t total_num, uint32_t dim, int metric,
+                                      uint32_t* d_graph, const uint64_t* d_bucket,
+                                      const uint64_t* h_bucket_sizes, uint32_t num_buckets,
+                                      uint32_t total_degree, uint32_t local_degree, int knn_precision) {
+  grab_tp_build_options o;
+  o.knn_precision = knn_precision;
+  o.global_candidates = GRAB_GLOBAL_AUTO;
+  o.search_iterations = 0;
+  o.search_width = 0;
+  return grab_build_time_partitioned_graph_ex(d_dataset, total_num, dim, metric, d_graph, d_bucket, h_bucket_sizes,
+                                              num_buckets, total_degree, local_degree, &o);
 }
 
 int grab_update_topology_v1(uint32_t* d_graph, const int64_t* d_search_indices, uint64_t num_existing,

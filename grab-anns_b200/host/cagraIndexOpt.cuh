@@ -66,10 +66,10 @@ class CagraIndexOpt {
   // centroids = 0 switches it off (the reference's behaviour), kRouterAuto picks about sqrt(n).
   // The centroids are trained on the first query after build/load; inserts only re-assign.
   static constexpr uint32_t kRouterAuto = 0xFFFFFFFFu;
-  void setRouter(uint32_t centroids, uint32_t probes = 4, uint32_t seeds_per_query = 32) {
+  void setRouter(uint32_t centroids, uint32_t probes = 2, uint32_t seeds_per_query = 64) {
     router_centroids_ = centroids;
-    router_probes_ = probes ? probes : 4;
-    router_seeds_ = seeds_per_query ? seeds_per_query : 32;
+    router_probes_ = probes ? probes : 2;
+    router_seeds_ = seeds_per_query ? seeds_per_query : 64;
     router_.reset();
   }
 
@@ -97,7 +97,7 @@ class CagraIndexOpt {
   struct RouterState;
   struct RouterDeleter { void operator()(RouterState*) const; };
   const grab_router* ensure_router();  // nullptr when switched off or the index is too small
-  uint32_t router_centroids_ = kRouterAuto, router_probes_ = 4, router_seeds_ = 32;
+  uint32_t router_centroids_ = kRouterAuto, router_probes_ = 2, router_seeds_ = 64;
   std::unique_ptr<RouterState, RouterDeleter> router_;
 };
 

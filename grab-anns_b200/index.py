@@ -96,7 +96,7 @@ class CagraIndexOpt(_Base):
         self._call("query", _ptr(q), C.c_size_t(q.shape[0]), C.c_int(k), _ptr(ids), _ptr(d))
         return ids, d
 
-    def set_router(self, centroids=0xFFFFFFFF, probes=4, seeds_per_query=32):
+    def set_router(self, centroids=0xFFFFFFFF, probes=2, seeds_per_query=64):
         """Entry-point router for searches without caller seeds: 0 = off, 0xFFFFFFFF = about sqrt(n)."""
         self._call("set_router", C.c_uint32(centroids), C.c_uint32(probes), C.c_uint32(seeds_per_query))
 

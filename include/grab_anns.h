@@ -241,6 +241,22 @@ int grab_build_time_partitioned_graph(const float* d_dataset, uint64_t total_num
                                       const uint64_t* h_bucket_sizes, uint32_t num_buckets,
                                       uint32_t total_degree, uint32_t local_degree,
                                       int knn_precision);
+/* The same build with its choices spelled out.  Cross-bucket candidates (the reference's
+ * IVF-PQ search over the whole dataset, cagra_opt.cu:813-847) come either from the all-pairs
+ * tensor-core kernel (exact top candidates, quadratic in N) or from a routed graph search over
+ * the local edges (approximate, linear in N); AUTO takes all-pairs below 2^21 vectors. */
+enum grab_global_candidates { GRAB_GLOBAL_AUTO = 0, GRAB_GLOBAL_ALL_PAIRS = 1, GRAB_GLOBAL_ROUTED_SEARCH = 2 };
+typedef struct grab_tp_build_options {
+  int knn_precision;      /* grab_knn_precision */
+  int global_candidates;  /* grab_global_candidates */
+  uint32_t search_iterations; /* routed search: iterations per vector (0 = 10) */
+  uint32_t search_width;      /* routed search: parents per iteration (0 = 4) */
+} grab_tp_build_options;
+int grab_build_time_partitioned_graph_ex(const float* d_dataset, uint64_t total_num, uint32_t dim,
+                                         int metric, uint32_t* d_graph, const uint64_t* d_bucket,
+                                         const uint64_t* h_bucket_sizes, uint32_t num_buckets,
+                                         uint32_t total_degree, uint32_t local_degree,
+                                         const grab_tp_build_options* options);
 
 /* ------------------------------------------------------------------------------------ */
 /* Insert: topology updates.  v1: src/index/insert.cuh:62-72 (insert.cu:225-440).        */

@@ -21,7 +21,7 @@ int grab_index_opt_configure(void* h, uint64_t bucket_width, int metric, int knn
 int grab_index_opt_set_query_params(void* h, uint32_t itopk, uint32_t width, uint32_t min_iter, uint32_t max_iter,
                                     uint32_t hash_bitlen);
 /* Entry-point router of the searches that get no seeds from the caller: centroids = 0 off,
- * 0xFFFFFFFF (default) about sqrt(n); probes / seeds_per_query = 0 keep 4 / 32. */
+ * 0xFFFFFFFF (default) about sqrt(n); probes / seeds_per_query = 0 keep 2 / 64. */
 int grab_index_opt_set_router(void* h, uint32_t centroids, uint32_t probes, uint32_t seeds_per_query);
 int grab_index_opt_add(void* h, size_t n, const float* vectors, const uint64_t* timestamps);
 int grab_index_opt_build(void* h);

@@ -516,3 +516,36 @@ def test_time_partitioned_build_tensor_core(grab, oracle):
     g_tc = _u32(grab.build_time_partitioned_graph(_t(data), _t(bucket.view(np.int64)), [n // nb] * nb, total, local,
                                                   knn_precision=grab.KNN_TC_SPLIT))
     assert (g_ex == g_tc).mean() > 0.98
+
+
+def test_time_partitioned_build_routed_search_candidates(grab, oracle):
+    """Cross-bucket candidates from the routed graph search over the local edges (the linear-time
+    stand-in for the all-pairs stage): remote columns leave the bucket, and range searches over several
+    buckets are as good as on the all-pairs graph."""
+    rng = np.random.default_rng(91)
+    n, dim, nb, total, local, nq, k = 40000, 64, 10, 32, 24, 300, 10
+    data = clustered(n, dim, 80, 0.6, 92)
+    ts = np.arange(n, dtype=np.uint64)
+    sizes = [n // nb] * nb
+    bucket = (ts // np.uint64(n // nb))
+    d_data, d_bucket = _t(data), _t(bucket.view(np.int64))
+    q = data[rng.integers(0, n, nq)] + np.float32(0.02)
+    lo = rng.integers(0, n - n // 3, nq).astype(np.uint64)
+    hi = lo + np.uint64(n // 3)
+    gt, _ = oracle.exact_search(data, q, k, ts=ts, lo=lo, hi=hi)
+    f = grab.make_filter(grab.FILTER_TS_RANGE, ts=_t(ts.view(np.int64)), lo=_t(lo.view(np.int64)),
+                         hi=_t(hi.view(np.int64)), ts_sorted=True)
+    rec = {}
+    for mode in (grab.GLOBAL_ALL_PAIRS, grab.GLOBAL_ROUTED_SEARCH):
+        graph = grab.build_time_partitioned_graph(d_data, d_bucket, sizes, total, local, global_candidates=mode)
+        g = _u32(graph)
+        rows = np.arange(n)[:, None]
+        loc, rem = g[:, :local], g[:, local:]
+        assert (bucket[np.where(loc == 0xFFFFFFFF, rows, loc)] == bucket[:, None]).all()
+        valid = rem != 0xFFFFFFFF
+        assert valid.mean() > 0.95
+        assert (bucket[np.where(valid, rem, 0)] != bucket[:, None])[valid].all()
+        gi, _ = grab.graph_search(d_data, graph, _t(q), k, grab.SearchParams(64, 4, 0, 32, 12), flt=f)
+        rec[mode] = oracle.recall(gi.cpu().numpy(), gt)
+    assert rec[grab.GLOBAL_ROUTED_SEARCH] > 0.9
+    assert rec[grab.GLOBAL_ROUTED_SEARCH] >= rec[grab.GLOBAL_ALL_PAIRS] - 0.02, rec
