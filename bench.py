@@ -551,7 +551,7 @@ def main():
                        args.selectivity == 0.10 and not args.sharded and args.router_centroids == 1024 and
                        args.probes == 2 and args.seeds == 64 and args.local_degree == 48 and
                        args.global_candidates in (0, 1))
-        traffic = 1488718336 + 1193216 if default_cfg else None
+        traffic = 1364566272 + 1159168 if default_cfg else None
         line = {
             "metric": "filtered QPS at recall@10>=0.95",
             "value": (1 if args.sharded else world) * nq / (ms / 1e3), "unit": "queries/s",

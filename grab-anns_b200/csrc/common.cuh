@@ -163,6 +163,24 @@ __device__ __forceinline__ void block_bitonic_sort(uint64_t* keys, uint32_t n) {
     }
   }
 }
+// The same search over a[b0, e0) of a non-decreasing uint32 array.
+__device__ __forceinline__ uint32_t warp_lower_bound_u32(const uint32_t* __restrict__ a, uint32_t b0, uint32_t e0,
+                                                         uint32_t x) {
+  const uint32_t lane = lane_id();
+  uint32_t b = b0, e = e0;
+  while (e - b > 32) {
+    const uint32_t span = e - b;
+    const uint32_t pos = b + static_cast<uint32_t>((static_cast<uint64_t>(lane + 1) * span) / 33);
+    const uint32_t below = __ballot_sync(0xFFFFFFFFu, __ldg(a + pos) < x);
+    const uint32_t k = __popc(below);
+    const uint32_t nb = k > 0 ? b + static_cast<uint32_t>((static_cast<uint64_t>(k) * span) / 33) + 1 : b;
+    const uint32_t ne = k < 32 ? b + static_cast<uint32_t>((static_cast<uint64_t>(k + 1) * span) / 33) : e;
+    b = nb;
+    e = ne;
+  }
+  const uint32_t below = __ballot_sync(0xFFFFFFFFu, b + lane < e && __ldg(a + b + lane) < x);
+  return b + __popc(below);
+}
 #endif  // __CUDACC__
 
 inline uint32_t next_pow2(uint32_t v) {

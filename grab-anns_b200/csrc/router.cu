@@ -28,6 +28,7 @@ constexpr int kRtBN = 64;        // centroids per tile
 constexpr int kRtBK = 32;        // dimensions per shared-memory stage
 constexpr int kRtThreads = 256;  // 16 x 16 threads, 4 x 4 outputs each
 constexpr uint32_t kMaxProbes = 16;
+constexpr uint32_t kMaxSharedPairs = 64;  // (probe, window) pairs whose sub-runs are shared through shared memory
 constexpr uint32_t kMaxSlices = 8;  // centroid slices of the routing launch (more CTAs for few queries)
 
 __device__ __forceinline__ uint64_t rt_mix64(uint64_t x) {  // splitmix64 finaliser
@@ -338,6 +339,7 @@ __device__ __forceinline__ uint32_t lower_bound_u32(const uint32_t* a, uint32_t 
 
 __global__ void __launch_bounds__(256) route_seeds_kernel(RouteArgs a) {
   __shared__ uint32_t s_probes[8][kMaxProbes];
+  __shared__ uint32_t s_pair_b[8][kMaxSharedPairs], s_pair_e[8][kMaxSharedPairs];
   const uint64_t q = (static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const uint32_t lane = threadIdx.x & 31u;
   if (q >= a.nq) return;  // whole warps leave together
@@ -423,23 +425,73 @@ __global__ void __launch_bounds__(256) route_seeds_kernel(RouteArgs a) {
   const uint32_t pairs = p * (nwin ? nwin : 1);
   const uint32_t per = (a.S + pairs - 1) / pairs;
 
+  // id window of label `w` of the mask (labels grouped by id), else the query's one window
+  auto window_of = [&](uint32_t w, uint32_t& lo_id, uint32_t& hi_id) {
+    lo_id = wlo;
+    hi_id = whi;
+    if (a.filter_kind == GRAB_FILTER_LABELS && a.label_offsets) {
+      uint32_t mm = mask;
+      for (uint32_t skip = w; skip > 0; --skip) mm &= mm - 1;
+      const uint32_t lab = __ffs(mm) - 1;
+      lo_id = a.label_offsets[lab];
+      hi_id = a.label_offsets[lab + 1];
+    }
+  };
+  // Sub-run [b, e) of every (probe j, window w) pair, pair index j + p*w: computed once per pair --
+  // by the whole warp (32-way search) when the pairs are few, else one pair per lane -- and shared
+  // through shared memory; the slots below only pick positions inside their pair's sub-run.
+  uint32_t* pb = s_pair_b[threadIdx.x >> 5];
+  uint32_t* pe = s_pair_e[threadIdx.x >> 5];
+  const bool shared_pairs = nwin != 0 && pairs <= kMaxSharedPairs;
+  if (shared_pairs) {
+    if (pairs <= 4) {
+      for (uint32_t pi = 0; pi < pairs; ++pi) {  // uniform across the warp
+        const uint32_t c = probes[pi % p];
+        uint32_t b = 0, e = 0;
+        if (c < a.C) {
+          uint32_t lo_id, hi_id;
+          window_of(pi / p, lo_id, hi_id);
+          const uint32_t rb = a.offsets[c], re = a.offsets[c + 1];
+          b = warp_lower_bound_u32(a.members, rb, re, lo_id);
+          e = warp_lower_bound_u32(a.members, b, re, hi_id);
+        }
+        if (lane == 0) { pb[pi] = b; pe[pi] = e; }
+      }
+    } else {
+      for (uint32_t pi = lane; pi < pairs; pi += 32) {
+        const uint32_t c = probes[pi % p];
+        uint32_t b = 0, e = 0;
+        if (c < a.C) {
+          uint32_t lo_id, hi_id;
+          window_of(pi / p, lo_id, hi_id);
+          const uint32_t rb = a.offsets[c], re = a.offsets[c + 1];
+          b = lower_bound_u32(a.members, rb, re, lo_id);
+          e = lower_bound_u32(a.members, b, re, hi_id);
+        }
+        pb[pi] = b;
+        pe[pi] = e;
+      }
+    }
+    __syncwarp();
+  }
+
   for (uint32_t s = lane; s < a.S; s += 32) {
     uint32_t id = kInvalid;
     if (nwin) {
       const uint32_t j = s % p, t = s / p, w = t % nwin, r = t / nwin;
       const uint32_t c = probes[j];
       if (c < a.C) {
-        uint32_t lo_id = wlo, hi_id = whi;
-        if (a.filter_kind == GRAB_FILTER_LABELS && a.label_offsets) {
-          uint32_t mm = mask;
-          for (uint32_t skip = w; skip > 0; --skip) mm &= mm - 1;
-          const uint32_t lab = __ffs(mm) - 1;
-          lo_id = a.label_offsets[lab];
-          hi_id = a.label_offsets[lab + 1];
+        uint32_t b, e;
+        if (shared_pairs) {
+          b = pb[j + p * w];
+          e = pe[j + p * w];
+        } else {
+          uint32_t lo_id, hi_id;
+          window_of(w, lo_id, hi_id);
+          const uint32_t rb = a.offsets[c], re = a.offsets[c + 1];
+          b = lower_bound_u32(a.members, rb, re, lo_id);
+          e = lower_bound_u32(a.members, b, re, hi_id);
         }
-        const uint32_t rb = a.offsets[c], re = a.offsets[c + 1];
-        const uint32_t b = lower_bound_u32(a.members, rb, re, lo_id);
-        const uint32_t e = lower_bound_u32(a.members, b, re, hi_id);
         const uint32_t L = e - b;
         if (r < L) {
           const uint32_t step = L / per > 1 ? L / per : 1;
