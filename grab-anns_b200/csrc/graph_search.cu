@@ -372,17 +372,26 @@ graph_search_kernel(const SearchKernelArgs a) {
     const uint32_t nparents = s_nparents;
     if (nparents == 0) break;
 
-    // ---- expand: neighbour id -> filter -> visited set -> compacted survivor list ----
+    // ---- expand: neighbour id -> filter -> visited set -> compacted survivor list.  A thread owns
+    //      graph columns; the ids of up to four parents' rows are loaded before any is processed, so
+    //      the row reads of an iteration overlap instead of queueing behind the hash probes ----
     uint32_t my_edges = 0;
-    const uint32_t tasks = nparents * a.active_deg;
-    for (uint32_t t = tid; t < tasks; t += kSearchThreads) {
-      const uint32_t p = parents[t / a.active_deg];
-      const uint32_t nb = __ldg(a.graph + static_cast<size_t>(p) * a.deg + (t % a.active_deg));
-      if (nb < a.n) {
-        ++my_edges;
-        if (passes(nb) && hash_insert(hash, a.hash_bitlen, nb)) {
-          const uint32_t pos = atomicAdd(&s_ncand, 1u);
-          cand[pos] = nb;
+    for (uint32_t col = tid; col < a.active_deg; col += kSearchThreads) {
+      for (uint32_t p0 = 0; p0 < nparents; p0 += 4) {
+        uint32_t nbv[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          nbv[u] = p0 + u < nparents ? __ldg(a.graph + static_cast<size_t>(parents[p0 + u]) * a.deg + col) : kInvalid;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const uint32_t nb = nbv[u];
+          if (nb < a.n) {
+            ++my_edges;
+            if (passes(nb) && hash_insert(hash, a.hash_bitlen, nb)) {
+              const uint32_t pos = atomicAdd(&s_ncand, 1u);
+              cand[pos] = nb;
+            }
+          }
         }
       }
     }
