@@ -498,19 +498,24 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item()) / steps
 
-    # the timed region lasts milliseconds, an nvidia-smi sample takes 100 ms: the same step loop keeps the GPU
-    # under load before and after the timed steps until the sampler has collected a few samples
+    # the timed region lasts milliseconds, an nvidia-smi sample takes 100 ms: the same kernels keep the GPU
+    # under load before and after the timed steps until the sampler has collected a few samples.  The loops
+    # run a rank-dependent number of times, so they must not contain a collective (the sharded step does).
+    def load_step():
+        route()
+        search_only()
+
     sampler = ClockSampler(local_rank)
     sampler.start()
     t_end = time.perf_counter() + 1.5
     while len(sampler.samples) < 1 and time.perf_counter() < t_end:
-        step()
+        load_step()
         torch.cuda.synchronize()
     ms = timed(step, args.steps, max(args.warmup, 3))
     t_end = time.perf_counter() + 1.0
     have = len(sampler.samples)
     while len(sampler.samples) < have + 3 and time.perf_counter() < t_end:
-        step()
+        load_step()
         torch.cuda.synchronize()
     clocks = sampler.stop()
     ms_e2e = timed(e2e_step, args.steps, max(args.warmup, 3))
