@@ -202,6 +202,9 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        # torchrun pins OMP_NUM_THREADS to 1 for its workers; the CPU arm uses every core this process may run on
+        os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)))
     import oracle
     w = workload(args)
     sample = args.cpu_sample or auto_cpu_sample(w, target_s=8.0)
