@@ -50,3 +50,150 @@ def sharded_search(search_fn, merge_fn, k: int, rank: int, world: int, dist_mod=
     """search_fn() -> (ids [nq,k] GLOBAL int64, dists [nq,k]) on this rank's shard."""
     ids, dists = search_fn()
     return gather_and_merge(dists, ids, k, merge_fn, dist_mod, group)
+
+
+def merge_topk_host(dists, ids, k: int):
+    """CPU merge of per-shard ascending lists [nq, G, k] by (dist, id); ids < 0 are empty.  Same
+    contract as grab_merge_topk (returns (ids, dists)); used when the results live in host memory."""
+    import torch
+    d = dists.detach().cpu().numpy() if hasattr(dists, "detach") else np.asarray(dists)
+    i = ids.detach().cpu().numpy() if hasattr(ids, "detach") else np.asarray(ids)
+    nq = d.shape[0]
+    d = d.reshape(nq, -1).astype(np.float32)
+    i = i.reshape(nq, -1).astype(np.int64)
+    empty = i < 0
+    dk = np.where(empty, np.float32(np.inf), d)
+    ik = np.where(empty, np.iinfo(np.int64).max, i)
+    order = np.lexsort((ik, dk), axis=1)[:, :k]           # primary dist, secondary id
+    out_i = np.take_along_axis(i, order, axis=1)
+    out_d = np.take_along_axis(d, order, axis=1)
+    gone = np.take_along_axis(empty, order, axis=1)
+    out_i[gone] = -1
+    out_d[gone] = np.float32(3.40282e38)
+    return torch.from_numpy(out_i), torch.from_numpy(out_d)
+
+
+# ---------------------------------------------------------------------------------------------
+# Sharded index on disk: one index file per rank in the reference's own format plus a manifest.
+# ---------------------------------------------------------------------------------------------
+MANIFEST_NAME = "manifest.json"
+MANIFEST_VERSION = 1
+
+
+def shard_file(directory: str, rank: int) -> str:
+    import os
+    return os.path.join(directory, f"shard_{rank:03d}.mcag")
+
+
+def write_manifest(directory: str, world: int, shard_sizes, dim: int, graph_degree: int, local_degree: int,
+                   metric: int = 0, bucket_width: int = 1, fmt: str = "MCAG"):
+    """Written by rank 0 after every rank saved its shard: the striping rule and what each file holds."""
+    import json
+    import os
+    shard_sizes = [int(s) for s in shard_sizes]
+    if len(shard_sizes) != world:
+        raise ValueError(f"{len(shard_sizes)} shard sizes for {world} ranks")
+    m = {"version": MANIFEST_VERSION, "format": fmt, "striping": "gid % world == rank, local id = gid // world",
+         "world": int(world), "total": int(sum(shard_sizes)), "shard_sizes": shard_sizes, "dim": int(dim),
+         "graph_degree": int(graph_degree), "local_degree": int(local_degree), "metric": int(metric),
+         "bucket_width": int(bucket_width),
+         "files": [os.path.basename(shard_file(directory, r)) for r in range(world)]}
+    tmp = os.path.join(directory, MANIFEST_NAME + ".tmp")
+    with open(tmp, "w") as fh:
+        json.dump(m, fh, indent=1)
+    os.replace(tmp, os.path.join(directory, MANIFEST_NAME))
+    return m
+
+
+def read_manifest(directory: str, world: int | None = None):
+    """Loads and checks a manifest; `world` = the number of ranks that want to load it."""
+    import json
+    import os
+    path = os.path.join(directory, MANIFEST_NAME)
+    with open(path) as fh:
+        m = json.load(fh)
+    if m.get("version") != MANIFEST_VERSION:
+        raise ValueError(f"{path}: manifest version {m.get('version')} is not {MANIFEST_VERSION}")
+    if world is not None and m["world"] != world:
+        raise ValueError(f"{path}: written by {m['world']} ranks, loaded by {world} (ids are striped by "
+                         "gid % world, so the rank count must match)")
+    if len(m["shard_sizes"]) != m["world"] or sum(m["shard_sizes"]) != m["total"]:
+        raise ValueError(f"{path}: shard sizes do not add up to the total")
+    sizes = m["shard_sizes"]
+    want = [len(range(r, m["total"], m["world"])) for r in range(m["world"])]
+    if sizes != want:
+        raise ValueError(f"{path}: shard sizes {sizes} are not a gid % world striping of {m['total']} vectors")
+    for f in m["files"]:
+        if not os.path.exists(os.path.join(directory, f)):
+            raise FileNotFoundError(os.path.join(directory, f))
+    return m
+
+
+class ShardedIndex:
+    """One time-partitioned index per rank over the stripe gid % world == rank.
+
+    `make_index()` returns the per-rank index (index.CagraIndexOpt in production; anything with
+    add / build / insert / query_range_batch / save / load / size in the tests).  Queries are the
+    same on every rank; results carry global ids and are identical on every rank.  `merge_fn` /
+    `to_tensor` default to the host merge on CPU tensors (gloo); with NCCL pass
+    merge_fn=grab.merge_topk and to_tensor=lambda a: torch.from_numpy(a).cuda()."""
+
+    def __init__(self, make_index, rank: int, world: int, dist_mod=None, group=None, merge_fn=None,
+                 to_tensor=None):
+        import torch
+        self.index = make_index()
+        self.rank, self.world = rank, world
+        self.dist_mod, self.group = dist_mod, group
+        self.merge_fn = merge_fn or merge_topk_host
+        self.to_tensor = to_tensor or (lambda a: torch.from_numpy(np.ascontiguousarray(a)))
+        self.total = 0
+
+    def add_and_build(self, vectors, timestamps):
+        """vectors / timestamps: the GLOBAL arrays (the same on every rank); this rank keeps its stripe."""
+        self.index.add(np.ascontiguousarray(stripe(vectors, self.rank, self.world)),
+                       np.ascontiguousarray(stripe(timestamps, self.rank, self.world)))
+        self.index.build()
+        self.total = int(vectors.shape[0])
+
+    def insert(self, vectors, timestamps):
+        """New vectors get the global ids total, total+1, ...; each rank inserts those of its residue."""
+        first = self.total
+        start = (self.rank - first) % self.world          # first new row owned by this rank
+        mine_v, mine_t = vectors[start::self.world], timestamps[start::self.world]
+        if mine_v.shape[0]:
+            self.index.insert(np.ascontiguousarray(mine_v), np.ascontiguousarray(mine_t))
+        self.total += int(vectors.shape[0])
+
+    def query_range_batch(self, queries, k: int, lo, hi):
+        ids, dists = self.index.query_range_batch(queries, k, lo, hi)
+        gids = local_to_global(ids, self.rank, self.world).astype(np.int64)
+        out_ids, out_d = gather_and_merge(self.to_tensor(dists.astype(np.float32)), self.to_tensor(gids), k,
+                                          self.merge_fn, self.dist_mod, self.group)
+        return out_ids.cpu().numpy(), out_d.cpu().numpy()
+
+    def save(self, directory: str, dim: int, graph_degree: int, local_degree: int, metric: int = 0,
+             bucket_width: int = 1):
+        import os
+        os.makedirs(directory, exist_ok=True)
+        self.index.save(shard_file(directory, self.rank))
+        self._barrier()
+        if self.rank == 0:
+            sizes = [len(range(r, self.total, self.world)) for r in range(self.world)]
+            write_manifest(directory, self.world, sizes, dim, graph_degree, local_degree, metric, bucket_width)
+        self._barrier()
+
+    def load(self, directory: str):
+        m = read_manifest(directory, self.world)
+        self.index.load(shard_file(directory, self.rank))
+        if int(self.index.size()) != m["shard_sizes"][self.rank]:
+            raise ValueError(f"shard {self.rank} holds {self.index.size()} vectors, the manifest says "
+                             f"{m['shard_sizes'][self.rank]}")
+        self.total = m["total"]
+        return m
+
+    def _barrier(self):
+        d = self.dist_mod
+        if d is None:
+            import torch.distributed as d
+        if d.is_initialized() and d.get_world_size(self.group) > 1:
+            d.barrier(group=self.group)
