@@ -74,3 +74,55 @@ def test_search_argument_checks(lib):
     a.filter.kind = grab.FILTER_NONE
     a.n = 1 << 31
     assert lib.grab_graph_search(C.byref(a)) == 1 and "2^31" in _err(lib)
+
+
+def test_router_argument_checks(lib):
+    grab = importlib.import_module("grab-anns_b200")
+    null = None
+    one = C.c_void_p(16)
+    build = lib.grab_router_build
+    assert build(null, 8, C.c_uint64(100), 0, 4, 2, C.c_uint64(0), one, one, one, one, null) == 1
+    assert "null pointer" in _err(lib)
+    assert build(one, 6, C.c_uint64(100), 0, 4, 2, C.c_uint64(0), one, one, one, one, null) == 1
+    assert "multiple of 4" in _err(lib)
+    assert build(one, 8, C.c_uint64(100), 0, 0, 2, C.c_uint64(0), one, one, one, one, null) == 1      # no centroids
+    assert build(one, 8, C.c_uint64(100), 0, 101, 2, C.c_uint64(0), one, one, one, one, null) == 1    # more than vectors
+    assert "num_centroids" in _err(lib)
+    assert build(one, 8, C.c_uint64(100), 5, 4, 2, C.c_uint64(0), one, one, one, one, null) == 1
+    assert "metric" in _err(lib)
+    assert build(one, 8, C.c_uint64(1 << 31), 0, 4, 2, C.c_uint64(0), one, one, one, one, null) == 1
+
+    r = grab.RouterStruct(16, 8, 0, 16, 16, 16, 16, 0)
+    route = lib.grab_route_seeds
+    args = lambda probes, seeds: (C.byref(r), one, C.c_uint64(4), C.c_uint64(100), null, probes, seeds,
+                                  C.c_uint64(1), one, null, C.c_size_t(0), null)
+    assert route(*args(0, 32)) == 1 and "probes" in _err(lib)
+    assert route(*args(17, 32)) == 1
+    assert route(*args(4, 0)) == 1 and "seeds_per_query" in _err(lib)
+    assert route(*args(4, 5000)) == 1
+    assert route(null, one, C.c_uint64(4), C.c_uint64(100), null, 4, 32, C.c_uint64(1), one, null, C.c_size_t(0),
+                 null) == 1
+    assert "router" in _err(lib)
+    empty = grab.RouterStruct(16, 8, 0, 16, 16, None, 16, 0)          # no member offsets
+    assert route(C.byref(empty), one, C.c_uint64(4), C.c_uint64(100), null, 4, 32, C.c_uint64(1), one, null,
+                 C.c_size_t(0), null) == 1
+    f = grab.Filter()
+    f.kind = grab.FILTER_TS_RANGE                                      # range filter without timestamps
+    assert route(C.byref(r), one, C.c_uint64(4), C.c_uint64(100), C.byref(f), 4, 32, C.c_uint64(1), one, null,
+                 C.c_size_t(0), null) == 1
+    assert "d_ts" in _err(lib)
+    f.kind = 9
+    assert route(C.byref(r), one, C.c_uint64(4), C.c_uint64(100), C.byref(f), 4, 32, C.c_uint64(1), one, null,
+                 C.c_size_t(0), null) == 1
+    # an empty batch is a success and touches nothing
+    assert route(C.byref(r), one, C.c_uint64(0), C.c_uint64(100), null, 4, 32, C.c_uint64(1), one, null,
+                 C.c_size_t(0), null) == 0
+    assert lib.grab_nearest_centroids(C.byref(r), one, C.c_uint64(4), 0, one, null) == 1
+    assert lib.grab_route_seeds_workspace_bytes(1000, 4) >= 256 + 8 * 1000 * 8 * 8
+
+    # build options: unknown cross-bucket candidate mode
+    offs = np.array([5, 5], dtype=np.uint64)
+    opt = grab.TpBuildOptions(1, 7, 0, 0)
+    assert lib.grab_build_time_partitioned_graph_ex(one, C.c_uint64(10), 8, 0, one, one, C.c_void_p(offs.ctypes.data),
+                                                    2, 4, 2, C.byref(opt)) == 1
+    assert "global_candidates" in _err(lib)
