@@ -83,7 +83,8 @@ def range_queries(nq, n, width, seed):
 
 
 def config(name, scale=1.0, isotropic=False):
-    """Workload of one benchmark config ('C1'..'C4'), optionally scaled down for tests."""
+    """Workload of one benchmark config ('C1'..'C5'), optionally scaled down for tests.  C5 at scale 1 is
+    100M vectors (38 GB on the host): a single process uses scale <= 0.125 (one 12.5M shard)."""
     if name == "C1":
         n, nq = int(100_000 * scale), max(8, int(1000 * scale))
         base, cen = gaussian_mixture(n, 128, 100, 0.2, 1001)
@@ -110,4 +111,12 @@ def config(name, scale=1.0, isotropic=False):
         q, _ = gaussian_mixture(nq, 96, 500, 0.2, 4002, centres=cen)
         return dict(base=base, queries=q, centres=cen, ts=np.arange(n, dtype=np.uint64), k=10,
                     degree=32, itopk=64, metric=0, dim=96)
+    if name == "C5":
+        n, nq = int(100_000_000 * scale), max(8, int(10_000 * min(1.0, scale * 8)))
+        n_centres = max(16, int(10_000 * min(1.0, scale * 8)))
+        base, cen = gaussian_mixture(n, 96, n_centres, 0.2, 5001)
+        q, _ = gaussian_mixture(nq, 96, n_centres, 0.2, 5002, centres=cen)
+        lo, hi = range_queries(nq, n, max(1, n // 10), 5003)
+        return dict(base=base, queries=q, ts=np.arange(n, dtype=np.uint64), lo=lo, hi=hi, k=100,
+                    degree=64, itopk=128, metric=0, dim=96)
     raise ValueError(name)
