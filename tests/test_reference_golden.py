@@ -44,3 +44,18 @@ def test_oracle_search_matches_reference_kernel_outputs(oracle):
         assert np.allclose(rd[same], od[same], rtol=1e-5, atol=1e-5)
         if mode == 2:
             assert ((ri >= gen.LO) & (ri < gen.HI) | (ri < 0)).all()
+
+
+def test_oracle_outputs_match_recorded_digests(oracle):
+    """Every restated function still produces the bytes recorded in tests/golden/oracle_digests.json."""
+    import json
+    gen_spec = importlib.util.spec_from_file_location("make_oracle_digests",
+                                                      os.path.join(HERE, "golden", "make_oracle_digests.py"))
+    gen = importlib.util.module_from_spec(gen_spec)
+    gen_spec.loader.exec_module(gen)
+    with open(os.path.join(HERE, "golden", "oracle_digests.json")) as fh:
+        want = json.load(fh)
+    got = gen.digests()
+    assert set(got) == set(want)
+    changed = sorted(k for k in want if got[k] != want[k])
+    assert not changed, f"oracle outputs changed for: {changed}"
