@@ -20,31 +20,73 @@ using SearchParams = grab_search_params;
 
 class CagraIndex {
  public:
-  CagraIndex(uint32_t dim, uint32_t graph_degree = 64, size_t vmm_max_bytes = 20ULL * 1024 * 1024 * 1024);
+  // dim must be a multiple of 4.  vmm_max_bytes bounds the virtual address range the growable
+  // device buffers reserve (70 % vectors, 20 % graph, 10 % timestamps, src/cagraIndex.cu:14-20);
+  // physical memory is mapped as the index grows.
+  CagraIndex(uint32_t dim,
+             uint32_t graph_degree = 64,
+             size_t vmm_max_bytes = 20ULL * 1024 * 1024 * 1024);
   ~CagraIndex();
 
-  void add(size_t num_vectors, const float* add_vectors, const uint64_t* add_timestamps = nullptr);
+  // Appends vectors to the host mirror; nothing is searchable before build().  Timestamps are
+  // optional, but query_range needs them for every vector.
+  void add(size_t num_vectors,
+           const float* add_vectors,
+           const uint64_t* add_timestamps = nullptr);
+
+  // kNN graph (tensor-core all-pairs + exact re-rank) -> prune -> reverse -> merge, all on the
+  // device (the reference: FAISS IVF-PQ candidates and host hops, src/cagraIndex.cu:80-124).
   void build();
-  void insert(size_t new_vectors, const float* insert_vectors, const uint64_t* insert_timestamps = nullptr);
-  void query(const float* host_queries, size_t num_queries, int k, int64_t* host_indices, float* host_dists,
-             uint32_t* seeds = nullptr, size_t num_seeds_per_query = 0);
-  void query_range(const float* host_queries, size_t num_queries, int k, float range_radius, uint64_t start_ts,
-                   uint64_t end_ts, int64_t* host_indices, float* host_dists, uint32_t* seeds = nullptr,
+
+  // Batched insert into a built index: search for neighbours among the existing nodes, write the
+  // new rows, repair reverse edges (src/cagraIndex.cu:126-212).  Batch size: setInsertBatch.
+  void insert(size_t new_vectors,
+              const float* insert_vectors,
+              const uint64_t* insert_timestamps = nullptr);
+
+  // Unfiltered search.  host_indices [num_queries, k] int64 (-1 = none), host_dists ascending.
+  // seeds: optional [num_queries, num_seeds_per_query] entry points.
+  void query(const float* host_queries,
+             size_t num_queries,
+             int k,
+             int64_t* host_indices,
+             float* host_dists,
+             uint32_t* seeds = nullptr,
+             size_t num_seeds_per_query = 0);
+
+  // Search among vectors with start_ts <= timestamp < end_ts.  range_radius >= 0.99 means "nearly
+  // everything": the unfiltered search runs instead, as in the reference (src/cagraIndex.cu:305-338).
+  void query_range(const float* host_queries,
+                   size_t num_queries,
+                   int k,
+                   float range_radius,
+                   uint64_t start_ts,
+                   uint64_t end_ts,
+                   int64_t* host_indices,
+                   float* host_dists,
+                   uint32_t* seeds = nullptr,
                    size_t num_seeds_per_query = 0);
 
   void setBuildParams(uint32_t inter_degree, uint32_t graph_degree) {
     build_params_.intermediate_degree = inter_degree;
     build_params_.graph_degree = graph_degree;
   }
-  void setQueryParams(uint32_t itopk_size, uint32_t search_width, uint32_t min_iterations, uint32_t max_iterations,
+  // Unlike the reference, insert() does not overwrite these (it has its own parameter set).
+  void setQueryParams(uint32_t itopk_size,
+                      uint32_t search_width,
+                      uint32_t min_iterations,
+                      uint32_t max_iterations,
                       uint32_t hash_bitlen) {
     search_params_ = {itopk_size, search_width, min_iterations, max_iterations, hash_bitlen};
   }
+
   void* get_data() { return h_data_.data(); }
-  const uint32_t* get_graph();
+  const uint32_t* get_graph();  // copies the device graph into the host mirror and returns it
+  size_t size() const { return h_data_.size() / dim_; }
+
+  // dim, degree, size, vectors, graph -- the reference's raw layout (src/cagraIndex.cu:352-395).
   void save(const std::string& filepath);
   void load(const std::string& filepath);
-  size_t size() const { return h_data_.size() / dim_; }
 
   // additions (not in the reference): metric, kNN precision of build(), reproducible seeds
   void setMetric(int metric) { metric_ = metric; }

@@ -2,7 +2,7 @@
 // (src/timeStampIndex.cuh:39-95): one CagraIndex per timestamp bucket plus a "virtual" index
 // over per-bucket centroids that routes a query to `probe_buckets` buckets.  The reference
 // builds the centroids with FAISS k-means (src/timeStampIndex.cu:169-179); here Lloyd's
-// iterations run on the GPU with the exact nearest-centroid scan as the assignment step.
+// iterations run on the device (grab_router_build: tiled nearest-centroid kernel, ordered means).
 // query_by_timestamp is declared but never defined in the reference
 // (src/timeStampIndex.cuh:59); it is defined here as a search inside one bucket.
 #pragma once
@@ -31,13 +31,41 @@ struct VectorLocation {
 
 class TimeStampIndex {
  public:
-  TimeStampIndex(uint32_t dim, uint32_t degree = 32, size_t cluster_ratio = 1000);
+  // One CagraIndex of the given degree per distinct timestamp.  cluster_ratio is kept for source
+  // compatibility; the number of centroids per bucket follows the reference's 16 * sqrt(n) rule
+  // (src/timeStampIndex.cu:169-179).
+  TimeStampIndex(uint32_t dim,
+                 uint32_t degree = 32,
+                 size_t cluster_ratio = 1000);
   ~TimeStampIndex();
-  uint64_t insert(const float* vectors, const uint64_t* timestamps, size_t num_vectors);
+
+  // Appends vectors to the buckets of their timestamps (CagraIndex::insert per bucket; a bucket is
+  // created on first use).  Returns the global id of the first vector; ids are consecutive.  Takes
+  // the writer lock.
+  uint64_t insert(const float* vectors,
+                  const uint64_t* timestamps,
+                  size_t num_vectors);
+
+  // k-means centroids of every bucket (on the device), up to five entry points per centroid, and a
+  // CagraIndex over all centroids -- the router (src/timeStampIndex.cu:141-238).  Writer lock.
   void build_virtual_index();
-  void query(const float* query, size_t topk, int64_t* out_indices, float* out_dists, int probe_buckets = 5);
-  void query_by_timestamp(const float* query, size_t topk, uint64_t timestamp, int64_t* out_indices,
+
+  // One query: nearest centroids vote for buckets, the probe_buckets best are searched from their entry
+  // points, the per-bucket results are merged by distance (src/timeStampIndex.cu:240-419).  Reader lock;
+  // may be called from several threads.
+  void query(const float* query,
+             size_t topk,
+             int64_t* out_indices,
+             float* out_dists,
+             int probe_buckets = 5);
+
+  // Search inside the bucket of one timestamp (declared but never defined in the reference).
+  void query_by_timestamp(const float* query,
+                          size_t topk,
+                          uint64_t timestamp,
+                          int64_t* out_indices,
                           float* out_dists);
+
   size_t size() const;
 
  private:
