@@ -1,0 +1,60 @@
+"""Model of the register sort/merge network of the search kernel (csrc/graph_search.cu,
+warp_sort_merge_regs): element e lives in register e/32 of lane e%32, strides below 32 are xor
+exchanges between lanes, strides of 32 and more pair registers of one lane, the level equal to the padded
+candidate count sorts ascending, candidates are folded into the list by top[M-1-i] = min(top[M-1-i], c[i])
+followed by one bitonic merge level.  The model repeats that index arithmetic in numpy and compares with a
+plain sort for every candidate count and both list lengths (64 and 128); the CUDA code itself is covered by
+the GPU parity tests."""
+import numpy as np
+MAXK = np.uint64(0xFFFFFFFFFFFFFFFF)
+def stage(v, R, size, stride):
+    # v[r][lane]
+    if stride >= 32:
+        rs = stride >> 5
+        for r in range(R):
+            if (r & rs) == 0:
+                up = ((r << 5) & size) == 0
+                a, b = v[r].copy(), v[r | rs].copy()
+                swap = (a > b) == up
+                v[r] = np.where(swap, b, a); v[r | rs] = np.where(swap, a, b)
+    else:
+        lanes = np.arange(32)
+        lower = (lanes & stride) == 0
+        for r in range(R):
+            e = lanes + (r << 5)
+            up = (e & size) == 0
+            other = v[r][lanes ^ stride]
+            keep_min = lower == up
+            mn, mx = np.minimum(v[r], other), np.maximum(v[r], other)
+            v[r] = np.where(keep_min, mn, mx)
+def level(v, R, LOG, size):
+    for S in range(LOG - 1, -1, -1): stage(v, R, size, 1 << S)
+def sort_merge(top, cand, nkeep, R):
+    M = 32 * R; LOGM = {2: 6, 4: 7}[R]
+    lanes = np.arange(32)
+    c = [np.where(lanes + 32 * r < nkeep, np.resize(np.concatenate([cand, np.full(M, MAXK)]), M)[lanes + 32 * r], MAXK) for r in range(R)]
+    t = [top[lanes + 32 * r].copy() for r in range(R)]
+    padded = 32
+    while padded < nkeep: padded <<= 1
+    for LOG in range(1, LOGM + 1):
+        SIZE = 1 << LOG
+        if SIZE <= padded: level(c, R, LOG, M if SIZE == padded else SIZE)
+    for r in range(R):
+        partner = c[R - 1 - r][31 - lanes]
+        t[r] = np.minimum(partner, t[r])
+    level(t, R, LOGM, M)
+    out = np.empty(M, np.uint64)
+    for r in range(R): out[lanes + 32 * r] = t[r]
+    return out
+def test_network_sorts_and_merges_like_a_plain_sort():
+    rng = np.random.default_rng(1)
+    for R in (2, 4):
+        M = 32 * R
+        for trial in range(400):
+            nq = rng.integers(0, M + 1)           # filled part of the list
+            top = np.full(M, MAXK); top[:nq] = np.sort(rng.integers(0, 1 << 40, nq).astype(np.uint64))
+            nkeep = int(rng.integers(1, M + 1))
+            cand = rng.integers(0, 1 << 40, nkeep).astype(np.uint64)
+            got = sort_merge(top, cand, nkeep, R)
+            want = np.sort(np.concatenate([top, cand]))[:M]
+            assert np.array_equal(got, want), (R, trial, nkeep)
