@@ -58,3 +58,35 @@ def test_network_sorts_and_merges_like_a_plain_sort():
             got = sort_merge(top, cand, nkeep, R)
             want = np.sort(np.concatenate([top, cand]))[:M]
             assert np.array_equal(got, want), (R, trial, nkeep)
+
+
+def _warp_lower_bound(a, x):
+    """Model of warp_lower_bound_u64 / _u32 (csrc/common.cuh): 32 probes per round at b + (l+1)*span/33."""
+    n = len(a)
+    b, e = 0, n
+    lanes = np.arange(32, dtype=np.int64)
+    rounds = 0
+    while e - b > 32:
+        span = e - b
+        pos = b + ((lanes + 1) * span) // 33
+        assert (pos > b).all() and (pos < e).all() and (np.diff(pos) >= 1).all()
+        k = int((a[pos] < x).sum())
+        assert ((a[pos] < x) == (lanes < k)).all()                     # a prefix of the lanes
+        nb = b + (k * span) // 33 + 1 if k > 0 else b
+        ne = b + ((k + 1) * span) // 33 if k < 32 else e
+        b, e = nb, ne
+        rounds += 1
+    idx = b + lanes
+    below = (idx < e) & (a[np.minimum(idx, n - 1)] < x) if n else np.zeros(32, bool)
+    return b + int(below.sum()), rounds
+
+
+def test_cooperative_lower_bound_model():
+    rng = np.random.default_rng(2)
+    for n in (0, 1, 5, 32, 33, 34, 1000, 4097, 1 << 20):
+        base = np.sort(rng.integers(0, max(2, n // 3), n).astype(np.uint64))     # many duplicates
+        probes = [0, 1, np.uint64(2 ** 63)] + list(rng.integers(0, max(2, n // 3) + 2, 40).astype(np.uint64))
+        for x in probes:
+            got, rounds = _warp_lower_bound(base, np.uint64(x))
+            assert got == int(np.searchsorted(base, np.uint64(x), side="left")), (n, x)
+            assert rounds <= 4                                                   # 2^20 entries: four rounds
