@@ -90,3 +90,33 @@ def test_cooperative_lower_bound_model():
             got, rounds = _warp_lower_bound(base, np.uint64(x))
             assert got == int(np.searchsorted(base, np.uint64(x), side="left")), (n, x)
             assert rounds <= 4                                                   # 2^20 entries: four rounds
+
+
+def test_chunked_grouping_model(oracle):
+    """Model of the router's grouping kernels (csrc/router.cu): per-chunk counts, a column scan over the
+    chunks, offsets, then one warp per chunk walking its ids 32 at a time and ranking equal keys by lane.
+    The result must be the stable grouping the oracle computes."""
+    rng = np.random.default_rng(3)
+    chunk = 2048
+    for n, nc in ((1, 1), (31, 3), (5000, 7), (12345, 64)):
+        assign = rng.integers(0, nc, n).astype(np.uint32)
+        nchunks = (n + chunk - 1) // chunk
+        counts = np.zeros((nchunks, nc), np.int64)
+        for i, c in enumerate(assign):
+            counts[i // chunk, c] += 1
+        totals = counts.sum(0)
+        base = np.cumsum(counts, axis=0) - counts                     # column scan, exclusive
+        offsets = np.concatenate([[0], np.cumsum(totals)])
+        members = np.full(n, -1, np.int64)
+        for w in range(nchunks):
+            row = base[w].copy()
+            for i0 in range(w * chunk, min(n, (w + 1) * chunk), 32):
+                ids = np.arange(i0, min(i0 + 32, n, (w + 1) * chunk))
+                keys = assign[ids]
+                for lane, (i, c) in enumerate(zip(ids, keys)):
+                    rank = int((keys[:lane] == c).sum())              # lanes with the same key and a lower index
+                    members[offsets[c] + row[c] + rank] = i
+                for c in np.unique(keys):
+                    row[c] += int((keys == c).sum())                  # the leader lane advances the counter
+        offs, mem = oracle.group_by_centroid(assign, nc)
+        assert np.array_equal(offsets.astype(np.uint32), offs) and np.array_equal(members.astype(np.uint32), mem)
