@@ -1,19 +1,29 @@
 #!/usr/bin/env python
 """Benchmark of the filtered-search hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload C1..C5]
 
-One step = one pass of the timestamp-range filtered graph search over the whole query batch of
-the workload (default: the 1M x 128 descriptor-like base, 10 000 queries, 10 % ranges, k 10,
-degree 64).  Prints ONE JSON line (rank 0).  `value` is device-resident throughput, `e2e` the
-same metric through the public call with host buffers, `roofline` the achieved algorithmic HBM
-bandwidth of the search kernel, `cpu_baseline` the CPU exact filtered scan on the same box.
-With N > 1 every rank holds a replica of the index and answers its own slice of queries
-(no data-path collective).
+One step = one pass of the filtered graph search (entry-point routing + search) over the whole query batch of
+the workload (default C2: 1M x 128 descriptor-like base, 10 000 queries, 10 % timestamp ranges, k 10, degree 64).
+Prints ONE JSON line (rank 0):
+  value         device-resident throughput (inputs already in HBM), CUDA events on the launching stream
+  e2e           the same steps with pinned HOST buffers in and out (double-buffered; the one-stream figure beside it)
+  e2e_class     CagraIndexOpt::query_range_batch through the C handles with pageable host arrays (what a user of
+                the reference calls)
+  roofline      achieved algorithmic HBM bandwidth of the search kernel against the measured copy peak
+  cpu_baseline  CPU exact filtered scan on the same box; `parity` = GPU exact ids against the CPU oracle's at the
+                workload's full shape
+With N > 1 every rank holds a replica of the index and answers its own slice of the query stream (`value`, no
+data-path collective), and the line also carries `sharded`: the id-striped index (gid % N == rank), the same
+queries on every rank, per-shard top-k exchanged by ONE NCCL all-gather inside the C library and merged on the
+device -- timed in the same run.  `--workload C4` times batched inserts, `--workload C5` the 12.5M-per-GPU shards.
+`--impl reference` times the reference's CPU paths (exact filtered scan, HNSW harness restated) and, when a GPU is
+present, the reference's own search kernel compiled for this GPU.
 """
 import argparse
 import importlib
 import json
+import math
 import os
 import subprocess
 import sys
@@ -26,6 +36,8 @@ sys.path.insert(0, os.path.join(ROOT, "oracle"))
 
 import numpy as np
 
+METRIC_NAME = "filtered QPS at recall@10>=0.95"
+
 
 def parse():
     ap = argparse.ArgumentParser()
@@ -33,50 +45,123 @@ def parse():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="C2")
+    ap.add_argument("--workload", default="C2", choices=["C1", "C2", "C3", "C4", "C5"])
     ap.add_argument("--scale", type=float, default=1.0, help="shrink the workload (tests / profiling)")
     ap.add_argument("--selectivity", type=float, default=0.10)
     ap.add_argument("--buckets", type=int, default=20)
-    ap.add_argument("--local-degree", type=int, default=48)
-    ap.add_argument("--itopk", type=int, default=64)
-    ap.add_argument("--width", type=int, default=3)
+    ap.add_argument("--local-degree", type=int, default=0, help="0 = three quarters of the graph degree")
+    ap.add_argument("--itopk", type=int, default=0, help="0 = the workload's (64; 128 for k = 100)")
+    ap.add_argument("--width", type=int, default=0, help="0 = 3 (4 for k = 100)")
     ap.add_argument("--max-iter", type=int, default=0,
-                    help="0 = 5 with the entry-point router, 20 without")
-    ap.add_argument("--router-centroids", type=int, default=1024,
-                    help="centroids of the entry-point router that draws the seeds (0 = seeds drawn "
-                         "uniformly inside the filter by the search kernel)")
-    ap.add_argument("--probes", type=int, default=2, help="nearest centroids the seeds are taken from")
+                    help="0 = 5 with the entry-point router (12 for k = 100), 20 without")
+    ap.add_argument("--router-centroids", type=int, default=-1,
+                    help="centroids of the entry-point router that draws the seeds (-1 = about n / 1000, 0 = seeds "
+                         "drawn uniformly inside the filter by the search kernel)")
+    ap.add_argument("--probes", type=int, default=0, help="nearest centroids the seeds are taken from (0 = 2; 4 for k = 100)")
     ap.add_argument("--seeds", type=int, default=64, help="routed seeds per query")
-    ap.add_argument("--hash-bitlen", type=int, default=11)
-    ap.add_argument("--knn-precision", type=int, default=1,
-                    help="0 exact scan, 1 bf16 tensor cores (exact for integer-valued data), 2 split bf16")
+    ap.add_argument("--hash-bitlen", type=int, default=0, help="0 = 11 (12 for k = 100)")
+    ap.add_argument("--knn-precision", type=int, default=-1,
+                    help="0 exact scan, 1 bf16 tensor cores (exact for integer-valued data), 2 split bf16; -1 = 1 for "
+                         "C2, 2 otherwise")
     ap.add_argument("--global-candidates", type=int, default=0,
                     help="cross-bucket candidates of the build: 0 auto, 1 all-pairs, 2 routed graph search")
     ap.add_argument("--cpu-sample", type=int, default=0, help="queries in the CPU sample (0 = auto)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the GPU-exact-vs-CPU-oracle check at config shape")
+    ap.add_argument("--no-class-e2e", action="store_true", help="skip the timing of the class call")
     ap.add_argument("--no-overlap", action="store_true",
-                    help="end-to-end steps on one stream (no overlap of the copies with the search)")
+                    help="end-to-end steps on one stream only (no overlap of the copies with the search)")
     ap.add_argument("--no-hnsw", action="store_true", help="reference arm: skip the CPU HNSW harness")
+    ap.add_argument("--hnsw-base", type=int, default=0, help="reference arm: HNSW over this many vectors (0 = all)")
+    ap.add_argument("--no-ref-kernel", action="store_true",
+                    help="reference arm: skip the timing of the reference's own search kernel on the GPU")
     ap.add_argument("--sharded", action="store_true",
-                    help="stripe the index by id across the ranks (all_gather + device merge of the per-shard "
-                         "top-k) instead of replicating it")
-    return ap.parse_args()
+                    help="time ONLY the id-sharded path (`value` = its QPS); without it N > 1 times replicas and adds "
+                         "the sharded path as a sub-record")
+    ap.add_argument("--no-sharded-record", action="store_true", help="N > 1: skip the sharded sub-record")
+    ap.add_argument("--emulate-shards", type=int, default=0,
+                    help="one GPU: build G id-striped shards one after the other, search each with the per-shard "
+                         "effort of a G-GPU run, merge, and report the merged recall and the per-shard step time")
+    ap.add_argument("--shard-iters", type=int, default=0, help="per-shard search iterations (0 = schedule by G)")
+    ap.add_argument("--shard-seeds", type=int, default=0, help="per-shard routed seeds (0 = schedule by G)")
+    ap.add_argument("--shard-run", type=int, default=0, help="per-shard result run length (0 = k/G + margin)")
+    ap.add_argument("--shard-centroids", type=int, default=0, help="per-shard router centroids (0 = centroids / G)")
+    ap.add_argument("--shard-probes", type=int, default=0, help="per-shard probes (0 = as the single index)")
+    ap.add_argument("--insert-batches", type=int, default=10, help="C4: number of insert batches")
+    ap.add_argument("--insert-batch-size", type=int, default=0, help="C4: vectors per class-internal batch (0 = default)")
+    a = ap.parse_args()
+    return a
 
 
+def resolve_defaults(args, w):
+    """Workload-dependent defaults (the swept operating points recorded in the design notes)."""
+    big_k = w["k"] >= 100
+    if args.itopk == 0:
+        args.itopk = max(64, w.get("itopk", 64))
+    if args.width == 0:
+        args.width = 4 if big_k else 3
+    if args.probes == 0:
+        args.probes = 4 if big_k else 2
+    if args.hash_bitlen == 0:
+        args.hash_bitlen = 12 if big_k else 11
+    if args.local_degree == 0:
+        args.local_degree = w["degree"] * 3 // 4
+    if args.router_centroids < 0:
+        n = w["n"]
+        args.router_centroids = 1024 if n <= 2_000_000 else 4096
+    if args.max_iter == 0:
+        args.max_iter = (12 if big_k else 5) if args.router_centroids else 20
+    if args.knn_precision < 0:
+        args.knn_precision = 1 if args.workload == "C2" else 2
+    return args
+
+
+# ------------------------------------------------------------------------------------------------------
+# workloads
+# ------------------------------------------------------------------------------------------------------
 def workload(args):
+    """Host arrays of the workload (C5 is generated on the device, see c5_shard)."""
     ds = importlib.import_module("grab-anns_b200.datasets")
     w = ds.config(args.workload, args.scale)
     n = w["base"].shape[0]
-    if "ts" in w:
+    w["n"] = n
+    if "lo" in w or args.workload in ("C1", "C2"):
         width = max(1, int(n * args.selectivity))
         w["lo"], w["hi"] = ds.range_queries(w["queries"].shape[0], n, width, 2003)
-    else:
+    elif "labels" in w:
         # label workloads: vectors grouped by label (ids are arbitrary), one bucket per label
         order = np.argsort(w["labels"], kind="stable")
         w["base"] = np.ascontiguousarray(w["base"][order])
         w["labels"] = np.ascontiguousarray(w["labels"][order])
         w["label_offsets"] = np.searchsorted(w["labels"], np.arange(33), side="left").astype(np.uint32)
     return w
+
+
+def c5_shard(rank, world, scale, device):
+    """The C5 stripe of one rank, generated on the device: 12.5M x 96 per rank (10 000-centre Gaussian mixture,
+    sigma 0.2), global id of local row i = i * world + rank, timestamp = global id.  Centres and queries are the
+    same on every rank (seeded host generator)."""
+    import torch
+    n_local = int(12_500_000 * scale)
+    dim, ncent, nq = 96, max(16, int(10_000 * min(1.0, scale * 4))), max(64, int(10_000 * min(1.0, scale * 4)))
+    hg = np.random.Generator(np.random.PCG64(5001))
+    cen_h = hg.standard_normal((ncent, dim), dtype=np.float32)
+    qg = np.random.Generator(np.random.PCG64(5002))
+    q_h = (cen_h[qg.integers(0, ncent, nq)] + np.float32(0.2) * qg.standard_normal((nq, dim), dtype=np.float32))
+    cen = torch.from_numpy(cen_h).to(device)
+    g = torch.Generator(device=device)
+    g.manual_seed(5100 + rank)
+    base = torch.empty((n_local, dim), device=device)
+    for s in range(0, n_local, 1 << 20):
+        e = min(n_local, s + (1 << 20))
+        idx = torch.randint(0, ncent, (e - s,), generator=g, device=device)
+        base[s:e] = cen[idx] + 0.2 * torch.randn((e - s, dim), generator=g, device=device)
+    n_total = n_local * world
+    ts = torch.arange(n_local, dtype=torch.int64, device=device) * world + rank
+    width = max(1, n_total // 10)
+    lo = qg.integers(0, n_total - width + 1, nq).astype(np.uint64)
+    return dict(base=base, ts=ts, queries=q_h.astype(np.float32), lo=lo, hi=lo + np.uint64(width), k=100, degree=64,
+                itopk=128, metric=0, dim=dim, n=n_local, n_total=n_total)
 
 
 class ClockSampler:
@@ -131,9 +216,12 @@ class ClockSampler:
                 "reasons": sorted(reasons)}
 
 
-def cpu_exact_qps(w, sample, threads_note=True):
-    """CPU arm: exact filtered brute force (tests/test_cagra_auto.cu:57-89 restated, OpenMP over
-    queries, sequential fp32 sum) on `sample` queries of the workload."""
+# ------------------------------------------------------------------------------------------------------
+# CPU legs (the only places that touch oracle/)
+# ------------------------------------------------------------------------------------------------------
+def cpu_exact_qps(w, sample):
+    """Exact filtered brute force (tests/test_cagra_auto.cu:57-89 restated, OpenMP over queries, sequential fp32
+    sum) on `sample` queries of the workload."""
     import oracle
     q = w["queries"][:sample]
     t0 = time.perf_counter()
@@ -154,48 +242,204 @@ def auto_cpu_sample(w, target_s=12.0):
     return int(max(probe, min(w["queries"].shape[0], qps * target_s)))
 
 
-def hnsw_harness(w, base_n=50_000, add_n=50_000, batches=10, batch=32):
-    """The reference's CPU baseline harness (tests/test_faiss_hnsw_insert.cpp:69-204) with its own sizes
-    and parameters on the first vectors of the workload: HNSW M 32, efConstruction 128, efSearch 64; build
-    on `base_n`, timed add of `add_n` -> vectors/s, `batches` x `batch` queries -> QPS and recall@10
-    against the exact scan.  Unfiltered like the harness, plus a post-filtered variant for the range
-    predicate (over-fetch k / selectivity).  HNSW restatement, not FAISS: parity unpinned."""
+def parity_at_config_shape(w, gpu_ids, gpu_dists, sample=1000):
+    """The GPU exact kernel's ids against the CPU oracle's canonical-order ids on `sample` queries over the FULL base
+    of the workload, the distance error against float64, and how tie-sensitive the comparison is: queries whose
+    k-th / (k+1)-th distance gap is below 1e-6 relative in float64, and ids that differ between the canonical
+    summation order and the reference's sequential one (tests/test_cagra_auto.cu:48-50)."""
     import oracle
-    n = min(base_n + add_n, w["base"].shape[0])
-    base_n = n // 2
+    sample = min(sample, w["queries"].shape[0])
+    q, k = w["queries"][:sample], w["k"]
+    kw = dict(ts=w["ts"], lo=w["lo"][:sample], hi=w["hi"][:sample]) if "ts" in w else \
+        dict(labels=w["labels"], masks=w["masks"][:sample])
+    t0 = time.perf_counter()
+    ci, cd = oracle.exact_search(w["base"], q, k + 1, metric=w["metric"], canonical=True, **kw)
+    si, _ = oracle.exact_search(w["base"], q, k, metric=w["metric"], canonical=False, **kw)
+    gi, gd = gpu_ids[:sample], gpu_dists[:sample]
+    match = bool(np.array_equal(gi, ci[:, :k]))
+    bits = bool(np.array_equal(gd.view(np.uint32)[gi >= 0], cd[:, :k].view(np.uint32)[gi >= 0]))
+    # float64 distances of the k+1 nearest
+    base, worst, ties = w["base"], 0.0, 0
+    for i in range(sample):
+        ids = ci[i][ci[i] >= 0]
+        x = base[ids].astype(np.float64)
+        qq = q[i].astype(np.float64)
+        d64 = ((x - qq) ** 2).sum(1) if w["metric"] == 0 else -(x @ qq)
+        got = cd[i][: ids.size].astype(np.float64)
+        denom = np.maximum(np.abs(d64), 1e-30)
+        worst = max(worst, float(np.max(np.abs(got - d64) / denom)) if ids.size else 0.0)
+        if ids.size == k + 1 and abs(d64[k] - d64[k - 1]) <= 1e-6 * max(abs(d64[k - 1]), 1e-30):
+            ties += 1
+    return {"queries": int(sample), "base_vectors": int(base.shape[0]), "exact_ids_match": match,
+            "exact_dist_bits_match": bits, "ids_differing": int((gi != ci[:, :k]).sum()),
+            "max_rel_dist_err_vs_fp64": worst, "tolerance": 1e-4,
+            "tie_sensitive_queries": int(ties),
+            "ids_differing_canonical_vs_sequential_order": int((si != ci[:, :k]).sum()),
+            "seconds": time.perf_counter() - t0}
+
+
+def hnsw_cpu(w, base_n=0, batch=32, target_recall=0.95):
+    """The reference's CPU baseline harness (tests/test_faiss_hnsw_insert.cpp:69-204) restated: HNSW M 32,
+    efConstruction 128; build on the first half, TIMED add of the second half -> vectors/s, then search in batches of
+    32 queries.  The harness has no filter: the range predicate is applied by post-filtering an over-fetched result
+    (fetch = 16 k at 10 % selectivity, ef = 2 fetch).  HNSW restatement, not FAISS: parity unpinned."""
+    import oracle
+    n = w["base"].shape[0] if base_n <= 0 else min(base_n, w["base"].shape[0])
     data = np.ascontiguousarray(w["base"][:n])
     h = oracle.HNSW(data, M=32, ef_construction=128)
-    t0 = time.perf_counter(); h.add(base_n); t1 = time.perf_counter()
-    h.add(n - base_n); t2 = time.perf_counter()
-    nq = min(batches * batch, w["queries"].shape[0])
-    q = w["queries"][:nq]
+    half = n // 2
+    t0 = time.perf_counter(); h.add(half); t1 = time.perf_counter()
+    h.add(n - half); t2 = time.perf_counter()
     k = w["k"]
+    nq = min(1024, w["queries"].shape[0])
+    q = w["queries"][:nq]
     t3 = time.perf_counter()
-    for b in range(0, nq, batch):
-        ids_b, _ = h.search(q[b:b + batch], k, ef=64)
-        ids = ids_b if b == 0 else np.concatenate([ids, ids_b])
+    ids = np.concatenate([h.search(q[b:b + batch], k, ef=64)[0] for b in range(0, nq, batch)])
     t4 = time.perf_counter()
-    gt, _ = oracle.exact_search(data, q, k, canonical=False)
+    gt, _ = oracle.exact_search(data, q, k, metric=w["metric"], canonical=False)
     out = {"kind": "HNSW restatement (not FAISS), parity unpinned", "vectors": int(n), "cores": oracle.num_threads(),
-           "build_s": t1 - t0, "insert_vectors_per_s": (n - base_n) / (t2 - t1),
-           "qps_unfiltered": nq / (t4 - t3), "recall_at_10_unfiltered": oracle.recall(ids, gt)}
-    if "ts" in w:  # range predicate by post-filtering an over-fetched result
-        width = max(1, n // 10)
-        rng = np.random.default_rng(7)
-        lo = rng.integers(0, n - width + 1, nq).astype(np.uint64)
-        hi = lo + np.uint64(width)
-        fetch = min(n, 16 * k)
-        t5 = time.perf_counter()
-        ids_f, _ = h.search(q, fetch, ef=max(64, 2 * fetch))
-        res = np.full((nq, k), -1, dtype=np.int64)
-        for i in range(nq):
-            keep = ids_f[i][(ids_f[i] >= lo[i]) & (ids_f[i] < hi[i])][:k]
-            res[i, :keep.size] = keep
-        t6 = time.perf_counter()
-        gtf, _ = oracle.exact_search(data, q, k, ts=np.arange(n, dtype=np.uint64), lo=lo, hi=hi, canonical=False)
-        out.update({"qps_range_10pct_postfilter": nq / (t6 - t5), "recall_at_10_range": oracle.recall(res, gtf),
-                    "overfetch": int(fetch)})
-    return out
+           "M": 32, "ef_construction": 128, "build_first_half_s": t1 - t0,
+           "insert_vectors_per_s": (n - half) / (t2 - t1),
+           "qps_unfiltered_ef64": nq / (t4 - t3), "recall_at_10_unfiltered": oracle.recall(ids, gt)}
+    if "ts" in w:
+        sel = float(np.mean((w["hi"][:nq] - w["lo"][:nq]).astype(np.float64))) / w["base"].shape[0]
+        lo = np.minimum(w["lo"][:nq], np.uint64(max(0, n - int(sel * n))))     # ranges clipped into the indexed prefix
+        hi = lo + np.uint64(max(1, int(sel * n)))
+        gtf, _ = oracle.exact_search(data, q, k, ts=np.arange(n, dtype=np.uint64), lo=lo, hi=hi, metric=w["metric"],
+                                     canonical=False)
+        best = None
+        for mult in (16, 24, 32, 48):
+            fetch = min(n, int(mult * k * 0.1 / max(sel, 1e-3)))
+            t5 = time.perf_counter()
+            res = np.full((nq, k), -1, dtype=np.int64)
+            for b in range(0, nq, batch):
+                idf, _ = h.search(q[b:b + batch], fetch, ef=max(64, 2 * fetch))
+                for i in range(idf.shape[0]):
+                    keep = idf[i][(idf[i] >= lo[b + i]) & (idf[i] < hi[b + i])][:k]
+                    res[b + i, :keep.size] = keep
+            t6 = time.perf_counter()
+            rec = oracle.recall(res, gtf)
+            best = {"qps_range_postfilter": nq / (t6 - t5), "recall_at_10_range": rec, "overfetch": int(fetch),
+                    "ef_search": int(max(64, 2 * fetch)), "queries": int(nq), "selectivity": sel}
+            if rec >= target_recall:
+                break
+        out.update(best)
+    return out, h
+
+
+def reference_kernel_bar(args, w):
+    """The same-box bar: the REFERENCE's own search_kernel_range (src/index/search.cu:589, launcher arithmetic
+    cagra_opt.cu:1330-1442 restated in oracle/ref_harness.cu) compiled for this GPU, timed with CUDA events on the
+    workload's graph, ONE range shared by all queries (the only form it has), 32 uniform in-range seeds per query;
+    and the new kernel on the very same inputs, then in its routed default.  The graph is built by this repository
+    (the reference's build needs FAISS/RAFT, which are not installed)."""
+    try:
+        import torch
+        import ref_kernels
+        if not torch.cuda.is_available():
+            return {"unavailable": "no CUDA device in the reference arm's process"}
+        if not ref_kernels.available():
+            return {"unavailable": "oracle/_ref/libgrab_ref.so was not built (the reference's sources are needed at build time)"}
+        if w["dim"] not in (96, 128, 256, 960, 1024, 2048) or w["metric"] != 0 or "ts" not in w:
+            return {"unavailable": "the reference has no distance routine for this dimension / metric / filter "
+                                   "(compute_distance.cuh:181-190)"}
+        grab = importlib.import_module("grab-anns_b200")
+        grab.lib()
+        torch.cuda.set_device(0)
+        n, dim, k, deg = w["n"], w["dim"], w["k"], w["degree"]
+        d_base = torch.from_numpy(w["base"]).cuda()
+        d_ts = torch.from_numpy(w["ts"].view(np.int64)).cuda()
+        bsize = (n + args.buckets - 1) // args.buckets
+        h_bucket = w["ts"] // np.uint64(bsize)
+        sizes = np.bincount(h_bucket.astype(np.int64)).tolist()
+        graph = grab.build_time_partitioned_graph(d_base, torch.from_numpy(h_bucket.view(np.int64)).cuda(), sizes, deg,
+                                                  args.local_degree, metric=0, knn_precision=args.knn_precision,
+                                                  global_candidates=args.global_candidates)
+        nq = w["queries"].shape[0]
+        d_q = torch.from_numpy(w["queries"]).cuda()
+        width = max(1, int(n * args.selectivity))
+        lo = (n - width) // 3
+        hi = lo + width
+        rng = np.random.default_rng(77)
+        seeds = torch.from_numpy(rng.integers(lo, hi, size=(nq, 32)).astype(np.uint32).view(np.int32)).cuda()
+        flt = grab.make_filter(grab.FILTER_TS_RANGE, ts=d_ts, lo=lo, hi=hi, ts_sorted=True)
+        gt, _ = grab.exact_search(d_base, d_q, k, flt=flt)
+        gt = gt.cpu().numpy()
+
+        def recall(ids):
+            r = ids.cpu().numpy()
+            hit = sum(np.intersect1d(a, b[b >= 0]).size for a, b in zip(r, gt))
+            return hit / max(1, int((gt >= 0).sum()))
+
+        def time_ref(itopk, width_, iters, bitlen):
+            ms = []
+            for i in range(6):
+                ids, _, t = ref_kernels.search(2, d_base, graph, d_q, k, itopk, width_, iters, bitlen, ts=d_ts, lo=lo,
+                                               hi=hi, seeds=seeds)
+                if i:
+                    ms.append(t)
+            return float(np.mean(ms)), recall(ids)
+
+        def time_ours(itopk, width_, iters, bitlen, sd, f, route=None):
+            p = grab.SearchParams(itopk, width_, 0, iters, bitlen)
+            ids = torch.empty((nq, k), dtype=torch.int64, device="cuda")
+            dd = torch.empty((nq, k), dtype=torch.float32, device="cuda")
+
+            def fn():
+                s = route() if route else sd
+                grab.graph_search(d_base, graph, d_q, k, p, flt=f, seeds=s, out=(ids, dd))
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(5):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b) / 5, recall(ids)
+
+        points, cheapest = [], None
+        for iters in (4, 6, 8, 12, 16, 24, 32, 48, 64):
+            ms, rec = time_ref(64, 3, iters, 11)
+            points.append({"itopk": 64, "width": 3, "iterations": iters, "ms": ms, "qps": nq / ms * 1e3, "recall": rec})
+            if rec >= 0.95:
+                cheapest = points[-1]
+                break
+        out = {"kernel": "search_kernel_range (src/index/search.cu:589), sm_100a build of the reference's source",
+               "graph": "built by this repository", "range": [int(lo), int(hi)], "seeds_per_query": 32,
+               "queries": int(nq), "reference_points": points, "reference_cheapest_at_recall_0.95": cheapest}
+        eq = cheapest or points[-1]
+        ms_o, rec_o = time_ours(64, 3, eq["iterations"], 11, seeds, flt)
+        out["new_kernel_same_inputs_equal_parameters"] = {"itopk": 64, "width": 3, "iterations": eq["iterations"],
+                                                           "ms": ms_o, "qps": nq / ms_o * 1e3, "recall": rec_o}
+        ours_cheapest = None
+        for iters in (3, 4, 5, 6, 8, 12, 16, 24, 32):
+            ms_o2, rec_o2 = time_ours(64, 3, iters, 11, seeds, flt)
+            if rec_o2 >= 0.95:
+                ours_cheapest = {"itopk": 64, "width": 3, "iterations": iters, "ms": ms_o2, "qps": nq / ms_o2 * 1e3,
+                                 "recall": rec_o2}
+                break
+        out["new_kernel_same_inputs_cheapest_at_recall_0.95"] = ours_cheapest
+        if args.router_centroids:
+            router = grab.router_build(d_base, min(args.router_centroids, n), metric=0)
+            sd = torch.empty((nq, args.seeds), dtype=torch.int32, device="cuda")
+            rws = torch.empty(grab.lib().grab_route_seeds_workspace_bytes(nq, args.probes), dtype=torch.uint8,
+                              device="cuda")
+            route = lambda: grab.route_seeds(router, d_q, n, flt, probes=args.probes, seeds_per_query=args.seeds,
+                                             out=sd, ws=rws)
+            ms_r, rec_r = time_ours(args.itopk, args.width, args.max_iter, args.hash_bitlen, None, flt, route)
+            out["new_kernel_routed_default"] = {"itopk": args.itopk, "width": args.width, "iterations": args.max_iter,
+                                                "ms_route_plus_search": ms_r, "qps": nq / ms_r * 1e3, "recall": rec_r}
+        if cheapest:
+            out["speedup_at_equal_parameters"] = cheapest["ms"] / ms_o
+            if ours_cheapest:
+                out["speedup_at_equal_recall_same_seeds"] = cheapest["ms"] / ours_cheapest["ms"]
+            if "new_kernel_routed_default" in out and out["new_kernel_routed_default"]["recall"] >= 0.95:
+                out["speedup_at_equal_recall_routed"] = cheapest["ms"] / out["new_kernel_routed_default"]["ms_route_plus_search"]
+        return out
+    except Exception as e:  # the CPU numbers of the reference arm must survive a failure of this extra leg
+        return {"unavailable": f"{type(e).__name__}: {e}"}
 
 
 def run_reference(args):
@@ -206,8 +450,11 @@ def run_reference(args):
         # torchrun pins OMP_NUM_THREADS to 1 for its workers; the CPU arm uses every core this process may run on
         os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)))
     import oracle
+    if args.workload in ("C4", "C5"):
+        args.workload = "C2"     # the reference arm times the search configuration
     w = workload(args)
-    sample = args.cpu_sample or auto_cpu_sample(w, target_s=8.0)
+    resolve_defaults(args, w)
+    sample = args.cpu_sample or auto_cpu_sample(w, target_s=3.0)
     for _ in range(min(args.warmup, 1)):
         cpu_exact_qps(w, min(sample, oracle.num_threads()))
     times = []
@@ -217,43 +464,503 @@ def run_reference(args):
     ms = 1e3 * float(np.mean(times))
     qps = sample / (ms / 1e3)
     desc = f"{sample} of {w['queries'].shape[0]} queries per step, full base of {w['base'].shape[0]} vectors"
+    cpu = {"value": qps, "unit": "queries/s", "cores": oracle.num_threads(), "kind": "port",
+           "sample": desc + "; exact filtered brute force, the reference's CPU ground-truth routine restated "
+                            "(tests/test_cagra_auto.cu:48-89), recall 1.0",
+           "exact_scan_qps": qps}
+    value, ms_step, recall, what = qps, ms, 1.0, "exact filtered brute force"
+    if not args.no_hnsw and w["metric"] == 0:
+        h, index = hnsw_cpu(w, args.hnsw_base)
+        cpu["hnsw"] = h
+        if h.get("recall_at_10_range", 0.0) >= 0.95 and h["vectors"] == w["base"].shape[0] and \
+                h["qps_range_postfilter"] > qps:
+            # the reference's CPU baseline proper (its FAISS-HNSW harness, restated): the faster CPU path that
+            # meets the metric's recall bar is the arm's value
+            value, recall, what = h["qps_range_postfilter"], h["recall_at_10_range"], "HNSW + range post-filter"
+            ms_step = 1e3 * h["queries"] / value
+            cpu["value"] = value
+            cpu["sample"] = (f"{h['queries']} of {w['queries'].shape[0]} queries, HNSW (M 32, efC 128, "
+                             f"ef {h['ef_search']}, over-fetch {h['overfetch']}) over the full base, range applied "
+                             f"by post-filtering; HNSW restatement, not FAISS (parity unpinned); beside it: " + desc)
+        del index
     line = {
-        "impl": "reference", "metric": "filtered QPS at recall@10>=0.95", "value": qps, "unit": "queries/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+        "impl": "reference", "metric": METRIC_NAME, "value": value, "unit": "queries/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(args, w),
-        "recall_at_10": 1.0,
-        "cpu_baseline": {"value": qps, "unit": "queries/s", "cores": oracle.num_threads(), "kind": "port",
-                         "sample": desc + "; exact filtered brute force, the reference's CPU ground-truth "
-                                          "routine restated (FAISS-HNSW is not installed on this box)"},
-        "e2e": {"value": qps, "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "config": workload_config(args, w), "recall_at_10": recall, "path": what,
+        "cpu_baseline": cpu,
+        "e2e": {"value": value, "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    if not args.no_hnsw:
-        line["hnsw_harness"] = hnsw_harness(w)
+    if not args.no_ref_kernel:
+        line["reference_kernel"] = reference_kernel_bar(args, w)
     print(json.dumps(line), flush=True)
 
 
-def workload_config(args, w):
-    filt = f"timestamp-range filter {args.selectivity:.0%}" if "ts" in w else "label filter (1-3 of 16 Zipf labels)"
-    return {"workload": f"{args.workload}: {w['base'].shape[0]}x{w['dim']} fp32, {w['queries'].shape[0]} queries, "
-                        f"{filt}, k {w['k']}, degree {w['degree']}",
-            "n": int(w["base"].shape[0]), "dim": int(w["dim"]), "queries": int(w["queries"].shape[0]),
+def workload_config(args, w, sharded=False):
+    if "ts" in w:
+        filt = f"timestamp-range filter {args.selectivity:.0%}"
+    else:
+        filt = "label filter (1-3 of 16 Zipf labels)"
+    nq = w["queries"].shape[0]
+    return {"workload": f"{args.workload}: {w['n']}x{w['dim']} fp32, {nq} queries, {filt}, k {w['k']}, "
+                        f"degree {w['degree']}",
+            "n": int(w["n"]), "dim": int(w["dim"]), "queries": int(nq),
             "k": int(w["k"]), "graph_degree": int(w["degree"]), "local_degree": args.local_degree,
             "buckets": args.buckets if "ts" in w else 16, "selectivity": args.selectivity, "itopk": args.itopk,
             "search_width": args.width, "max_iterations": args.max_iter, "hash_bitlen": args.hash_bitlen,
             "router_centroids": args.router_centroids, "probes": args.probes, "routed_seeds": args.seeds,
-            "l2": "inputs (dataset + graph, 768 MB at full size) exceed the 126 MB L2",
+            "l2": "inputs (dataset + graph, 768 MB at C2 size) exceed the 126 MB L2",
             "parallelism": ("one process per GPU, index striped by id across the ranks, queries broadcast, "
-                            "all_gather + device merge of per-shard top-k") if getattr(args, "sharded", False) else
+                            "one all-gather + device merge of per-shard top-k") if sharded else
                            "one process per GPU, index replica per rank, queries partitioned"}
+
+
+# ------------------------------------------------------------------------------------------------------
+# the GPU path
+# ------------------------------------------------------------------------------------------------------
+class Index:
+    """One index on the current device: vectors, filter column, graph, entry-point router."""
+
+    def __init__(self, grab, args, w, d_base, ts=None, labels=None, label_offsets=None, n_total=None, centroids=None,
+                 id_scale=1, id_offset=0):
+        import torch
+        self.grab, self.w = grab, w
+        self.d_base = d_base
+        self.n, self.dim = d_base.shape
+        self.metric, self.k, self.deg = w["metric"], w["k"], w["degree"]
+        self.id_scale, self.id_offset = id_scale, id_offset
+        self.by_labels = labels is not None
+        if self.by_labels:
+            self.d_labels = labels if hasattr(labels, "is_cuda") else torch.from_numpy(labels).cuda()
+            self.d_offs = torch.from_numpy(label_offsets.view(np.int32)).cuda()
+            d_bucket = self.d_labels.to(torch.int64)
+        else:
+            self.d_ts = ts if hasattr(ts, "is_cuda") else torch.from_numpy(ts.view(np.int64)).cuda()
+            n_total = n_total or self.n
+            bsize = (n_total + args.buckets - 1) // args.buckets   # bucket width in timestamps
+            d_bucket = self.d_ts // bsize
+        sizes = torch.bincount(d_bucket).cpu().tolist()            # sorted keys: buckets are id runs
+        sizes = [s for s in sizes if s > 0] if self.by_labels else sizes
+        if self.by_labels:                                          # bucket ids must be dense for the build
+            d_bucket = torch.unique_consecutive(d_bucket, return_inverse=True)[1]
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        self.graph = grab.build_time_partitioned_graph(d_base, d_bucket.contiguous(), sizes, self.deg,
+                                                       args.local_degree, metric=self.metric,
+                                                       knn_precision=args.knn_precision,
+                                                       global_candidates=args.global_candidates)
+        torch.cuda.synchronize()
+        self.build_s = time.perf_counter() - t0
+        self.router, self.router_s = None, 0.0
+        centroids = args.router_centroids if centroids is None else centroids
+        if centroids:
+            t0 = time.perf_counter()
+            self.router = grab.router_build(d_base, min(centroids, self.n), metric=self.metric)
+            torch.cuda.synchronize()
+            self.router_s = time.perf_counter() - t0
+        self.centroids = centroids
+
+    def filter(self, lo, hi=None):
+        g = self.grab
+        if self.by_labels:
+            return g.make_filter(g.FILTER_LABELS, labels=self.d_labels, masks=lo, label_offsets=self.d_offs)
+        return g.make_filter(g.FILTER_TS_RANGE, ts=self.d_ts, lo=lo, hi=hi, ts_sorted=True)
+
+
+class Searcher:
+    """Preallocated state of one query batch size on one Index: seeds, workspaces, outputs."""
+
+    def __init__(self, index, nq, k, itopk, width, max_iter, bitlen, probes, seeds, want_keys=False):
+        import torch
+        g = index.grab
+        self.ix, self.nq, self.k = index, nq, k
+        self.params = g.SearchParams(itopk, width, 0, max_iter, bitlen)
+        self.probes, self.nseeds = probes, seeds
+        self.ids = torch.empty((nq, k), dtype=torch.int64, device="cuda")
+        self.d = torch.empty((nq, k), dtype=torch.float32, device="cuda")
+        self.keys = torch.empty((nq, k), dtype=torch.int64, device="cuda") if want_keys else None
+        self.ws = torch.empty(g.lib().grab_graph_search_workspace_bytes(nq, bitlen), dtype=torch.uint8, device="cuda")
+        self.seeds = self.route_ws = None
+        if index.router is not None:
+            self.seeds = torch.empty((nq, seeds), dtype=torch.int32, device="cuda")
+            self.route_ws = torch.empty(g.lib().grab_route_seeds_workspace_bytes(nq, probes), dtype=torch.uint8,
+                                        device="cuda")
+
+    def route(self, d_q, flt):
+        if self.ix.router is not None:
+            self.ix.grab.route_seeds(self.ix.router, d_q, self.ix.n, flt, probes=self.probes,
+                                     seeds_per_query=self.nseeds, out=self.seeds, ws=self.route_ws)
+        return self.seeds
+
+    def search(self, d_q, flt, out=None, stats=False, keys_only=False):
+        ix = self.ix
+        o = (None, None) if keys_only else (out or (self.ids, self.d))
+        return ix.grab.graph_search(ix.d_base, ix.graph, d_q, self.k, self.params, metric=ix.metric, flt=flt,
+                                    stats=stats, seeds=self.seeds, out=o, ws=self.ws, id_scale=ix.id_scale,
+                                    id_offset=ix.id_offset, out_keys=self.keys)
+
+    def step(self, d_q, flt, keys_only=False):
+        self.route(d_q, flt)
+        self.search(d_q, flt, keys_only=keys_only)
+
+
+def recall_of(res, gt):
+    hit = denom = 0
+    for r, g in zip(res, gt):
+        g = g[g >= 0]
+        hit += np.intersect1d(r, g).size
+        denom += g.size
+    return hit / max(denom, 1)
+
+
+def shard_schedule(args, G, k, centroids, probes):
+    """Per-shard search effort of a G-way id-striped index.  A stripe holds 1/G of every neighbourhood, so of the
+    global top-k it owns Binomial(k, 1/G) -- its own nearest few, the first entries a graph search settles: the run
+    it sends is k/G + 4 sigma + 1 long, and routing / iterations shrink with G (swept so that the MERGED recall
+    stays at the single index's)."""
+    p = 1.0 / G
+    run = k if G == 1 else min(k, int(math.ceil(k * p + 4.0 * math.sqrt(k * p * (1 - p)) + 1)))
+    big_k = k >= 100
+    iters = {1: args.max_iter, 2: max(3, args.max_iter - 1), 4: max(3, args.max_iter - 2),
+             8: max(2, args.max_iter - 3)}.get(G, max(2, args.max_iter - 3))
+    if big_k:
+        iters = {1: args.max_iter, 2: max(6, args.max_iter * 3 // 4), 4: max(5, args.max_iter * 7 // 12),
+                 8: max(4, args.max_iter // 2)}.get(G, max(4, args.max_iter // 2))
+    seeds = {1: args.seeds, 2: max(16, args.seeds * 3 // 4), 4: max(16, args.seeds // 2),
+             8: max(16, args.seeds * 3 // 8)}.get(G, max(16, args.seeds // 2))
+    return {"run_length": args.shard_run or run, "iterations": args.shard_iters or iters,
+            "seeds": args.shard_seeds or seeds,
+            "centroids": args.shard_centroids or (max(64, centroids // G) if centroids else 0),
+            "probes": args.shard_probes or probes}
+
+
+def time_events(torch, fn, steps, warmup, dist=None):
+    """Mean milliseconds per call of fn over `steps` calls, CUDA events on the current stream, max over ranks."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    t = torch.tensor([a.elapsed_time(b)], device="cuda", dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item()) / steps
+
+
+def sharded_record(args, grab, torch, dist, w, rank, world, steps, warmup, d_base_full=None, shard=None):
+    """The id-sharded path on `world` ranks: build this rank's stripe, search every query on it with the per-shard
+    effort, ONE all-gather of the key runs (NCCL inside the C library) + G-way device merge, pipelined over two
+    buffer sets so that the exchange of step i overlaps the search of step i+1."""
+    k = w["k"]
+    if shard is None:
+        base = np.ascontiguousarray(w["base"][rank::world])
+        ts = np.ascontiguousarray(w["ts"][rank::world])
+        d_base = torch.from_numpy(base).cuda()
+        n_total = w["n"]
+    else:
+        d_base, ts, n_total = shard["base"], shard["ts"], shard["n_total"]
+    sch = shard_schedule(args, world, k, args.router_centroids, args.probes)
+    ix = Index(grab, args, w, d_base, ts=ts, n_total=n_total, centroids=sch["centroids"], id_scale=world,
+               id_offset=rank)
+    nq = w["queries"].shape[0]
+    kp = sch["run_length"]
+    d_q = torch.from_numpy(w["queries"]).cuda()
+    d_lo = torch.from_numpy(w["lo"].view(np.int64)).cuda()
+    d_hi = torch.from_numpy(w["hi"].view(np.int64)).cuda()
+    flt = ix.filter(d_lo, d_hi)
+    comm = None
+    if world > 1:
+        comm = grab.Comm(world, rank, grab.torch_broadcast_bytes)
+    # exact sharded ground truth: per-stripe exact top-k with global ids, gathered and merged the same way
+    gi, gd = grab.exact_search(d_base, d_q, k, metric=w["metric"], flt=flt)
+    gi = torch.where(gi >= 0, gi * world + rank, gi)
+    f2o = lambda t: torch.where(t.view(torch.int32) < 0, ~t.view(torch.int32), t.view(torch.int32) | (-2 ** 31))
+    gkeys = (f2o(gd.contiguous()).to(torch.int64) & 0xFFFFFFFF) << 32 | gi.clamp(min=0)
+    gkeys = torch.where(gi >= 0, gkeys, torch.full_like(gkeys, -1))
+    gt_ids = (comm.gather_merge(gkeys, k)[0] if comm else grab.merge_sorted_keys(gkeys.unsqueeze(0).contiguous(), k)[0])
+    gt = gt_ids.cpu().numpy()
+
+    sets = []
+    for _ in range(2):
+        s = Searcher(ix, nq, kp, args.itopk, args.width, sch["iterations"], args.hash_bitlen, sch["probes"],
+                     sch["seeds"], want_keys=True)
+        s.gather = torch.empty((world, nq, kp), dtype=torch.int64, device="cuda")
+        s.out = (torch.empty((nq, k), dtype=torch.int64, device="cuda"),
+                 torch.empty((nq, k), dtype=torch.float32, device="cuda"))
+        s.ev_search, s.ev_merged, s.used = torch.cuda.Event(), torch.cuda.Event(), False
+        sets.append(s)
+    s_comm = torch.cuda.Stream(priority=-1)
+
+    def exchange(s):
+        if comm:
+            comm.gather_merge(s.keys, k, gather=s.gather, out=s.out)
+        else:
+            grab.merge_sorted_keys(s.keys.unsqueeze(0), k, out=s.out)
+
+    # correctness + counters, unpipelined
+    s0 = sets[0]
+    s0.route(d_q, flt)
+    _, _, stats = s0.search(d_q, flt, stats=True, keys_only=True)
+    exchange(s0)
+    torch.cuda.synchronize()
+    res = s0.out[0].cpu().numpy()
+    recall = recall_of(res, gt)
+    lo_i, hi_i = w["lo"][:, None].astype(np.int64), w["hi"][:, None].astype(np.int64)
+    in_range = bool(np.all(((res >= lo_i) & (res < hi_i)) | (res < 0)))
+
+    count = [0]
+
+    def pipelined_step():
+        s = sets[count[0] % 2]
+        count[0] += 1
+        main = torch.cuda.current_stream()
+        if s.used:
+            main.wait_event(s.ev_merged)       # the exchange that read this set's keys has finished
+        s.step(d_q, flt, keys_only=True)
+        s.ev_search.record(main)
+        with torch.cuda.stream(s_comm):
+            s_comm.wait_event(s.ev_search)
+            exchange(s)
+            s.ev_merged.record(s_comm)
+        s.used = True
+
+    def drain():
+        main = torch.cuda.current_stream()
+        for s in sets:
+            if s.used:
+                main.wait_event(s.ev_merged)
+
+    def timed_pipeline():
+        for _ in range(warmup):
+            pipelined_step()
+        drain()
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            pipelined_step()
+        drain()
+        b.record()
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        t = torch.tensor([a.elapsed_time(b)], device="cuda", dtype=torch.float64)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) / steps
+
+    def serial_step():
+        s0.step(d_q, flt, keys_only=True)
+        exchange(s0)
+
+    ms_pipe = timed_pipeline()
+    ms_serial = time_events(torch, serial_step, steps, warmup, dist)
+    ms_route = time_events(torch, lambda: s0.route(d_q, flt), steps, warmup, dist)
+    ms_search = time_events(torch, lambda: s0.search(d_q, flt, keys_only=True), steps, warmup, dist)
+    ms_exchange = time_events(torch, lambda: exchange(s0), steps, warmup, dist)
+    ms_merge = time_events(torch, lambda: grab.merge_sorted_keys(s0.gather if comm else s0.keys.unsqueeze(0), k,
+                                                                 out=s0.out), steps, warmup, dist)
+    st = torch.tensor([stats.iterations, stats.parents, stats.edges, stats.distances, stats.seeds, stats.hash_resets],
+                      device="cuda", dtype=torch.int64)
+    alg = grab.search_bytes(stats, nq, ix.dim, ix.deg, kp, 0)
+    peak = measured_peak()[0]
+    rec = {"world": world, "striping": "gid % world == rank", "shard_vectors": int(ix.n), "queries": int(nq),
+           "value": nq / (ms_pipe / 1e3), "unit": "queries/s", "ms_per_step": ms_pipe,
+           "pipelining": "two buffer sets: the exchange of step i (high-priority stream) overlaps the search of step i+1",
+           "qps_unpipelined": nq / (ms_serial / 1e3), "ms_per_step_unpipelined": ms_serial,
+           "recall_at_k_merged": recall, "k": int(k), "results_in_range": in_range,
+           "ground_truth": "exact filtered kernel per stripe, gathered and merged (the exact sharded result)",
+           "per_shard_effort": sch, "ms_route": ms_route, "ms_search": ms_search,
+           "ms_all_gather": max(0.0, ms_exchange - ms_merge), "ms_merge": ms_merge,
+           "bytes_gathered_per_rank": int(8 * nq * kp * world), "collectives_per_step": 1 if world > 1 else 0,
+           "search_kernel_roofline_frac": alg / (ms_search / 1e3) / 1e9 / peak,
+           "distances_per_query": stats.distances / nq, "build_seconds": ix.build_s, "router_seconds": ix.router_s,
+           "build_mvec_per_s": ix.n / ix.build_s / 1e6}
+    if comm:
+        comm.close()
+    del st
+    return rec
+
+
+def emulate_shards(args, grab, torch, w, G, steps, warmup):
+    """One GPU standing in for G: the stripes are built and searched one after the other with the per-shard effort
+    of a G-GPU run, their key runs merged by the same device merge.  Gives the MERGED recall of that effort and the
+    per-shard step time (what every rank of a G-GPU run does per step), without G GPUs."""
+    k, nq = w["k"], w["queries"].shape[0]
+    sch = shard_schedule(args, G, k, args.router_centroids, args.probes)
+    kp = sch["run_length"]
+    d_q = torch.from_numpy(w["queries"]).cuda()
+    d_lo = torch.from_numpy(w["lo"].view(np.int64)).cuda()
+    d_hi = torch.from_numpy(w["hi"].view(np.int64)).cuda()
+    all_keys = torch.empty((G, nq, kp), dtype=torch.int64, device="cuda")
+    d_full = torch.from_numpy(w["base"]).cuda()
+    d_ts_full = torch.from_numpy(w["ts"].view(np.int64)).cuda()
+    gt, _ = grab.exact_search(d_full, d_q, k, metric=w["metric"],
+                              flt=grab.make_filter(grab.FILTER_TS_RANGE, ts=d_ts_full, lo=d_lo, hi=d_hi, ts_sorted=True))
+    gt = gt.cpu().numpy()
+    del d_full
+    ms_steps, ms_search, dists = [], [], []
+    for r in range(G):
+        d_base = torch.from_numpy(np.ascontiguousarray(w["base"][r::G])).cuda()
+        ix = Index(grab, args, w, d_base, ts=np.ascontiguousarray(w["ts"][r::G]), n_total=w["n"],
+                   centroids=sch["centroids"], id_scale=G, id_offset=r)
+        flt = ix.filter(d_lo, d_hi)
+        s = Searcher(ix, nq, kp, args.itopk, args.width, sch["iterations"], args.hash_bitlen, sch["probes"],
+                     sch["seeds"], want_keys=True)
+        s.route(d_q, flt)
+        _, _, stats = s.search(d_q, flt, stats=True, keys_only=True)
+        all_keys[r].copy_(s.keys)
+        ms_steps.append(time_events(torch, lambda: s.step(d_q, flt, keys_only=True), steps, warmup))
+        ms_search.append(time_events(torch, lambda: s.search(d_q, flt, keys_only=True), steps, warmup))
+        dists.append(stats.distances / nq)
+        del ix, s, d_base
+    out = (torch.empty((nq, k), dtype=torch.int64, device="cuda"), torch.empty((nq, k), dtype=torch.float32, device="cuda"))
+    grab.merge_sorted_keys(all_keys, k, out=out)
+    ms_merge = time_events(torch, lambda: grab.merge_sorted_keys(all_keys, k, out=out), steps, warmup)
+    rec = recall_of(out[0].cpu().numpy(), gt)
+    return {"emulated_shards": G, "per_shard_effort": sch, "recall_at_k_merged": rec,
+            "ms_step_per_shard_max": max(ms_steps), "ms_search_per_shard_max": max(ms_search), "ms_merge": ms_merge,
+            "projected_qps": nq / (max(max(ms_steps), ms_merge) / 1e3), "distances_per_query_per_shard": float(np.mean(dists))}
+
+
+def measured_peak():
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        return float(peaks["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+def class_e2e(args, w, steps, warmup):
+    """What a user of the reference calls: CagraIndexOpt (add, build, query_range_batch) through the C handles of
+    include/grab_index.h, pageable host arrays in and out, wall clock around the call."""
+    index = importlib.import_module("grab-anns_b200.index")
+    n, nq, k = w["n"], w["queries"].shape[0], w["k"]
+    bsize = (n + args.buckets - 1) // args.buckets
+    ix = index.CagraIndexOpt(w["dim"], graph_degree=w["degree"], local_degree=args.local_degree,
+                             vmm_max_bytes=max(4 << 30, 4 * w["base"].nbytes), bucket_width=bsize, metric=w["metric"],
+                             knn_precision=args.knn_precision)
+    ix.set_query_params(args.itopk, args.width, 0, args.max_iter, args.hash_bitlen)
+    ix.set_router(args.router_centroids, args.probes, args.seeds)
+    t0 = time.perf_counter()
+    ix.add(w["base"], w["ts"])
+    ix.build()
+    build_s = time.perf_counter() - t0
+    q, lo, hi = w["queries"], w["lo"], w["hi"]
+    for _ in range(max(warmup, 3)):
+        ids, _ = ix.query_range_batch(q, k, lo, hi)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        ids, _ = ix.query_range_batch(q, k, lo, hi)
+    dt = (time.perf_counter() - t0) / steps
+    return ids, {"value": nq / dt, "unit": "queries/s", "ms_per_call": dt * 1e3,
+                 "call": "CagraIndexOpt::query_range_batch via grab_index_opt_query_range_batch, pageable host arrays",
+                 "h2d_bytes_per_step": int(q.nbytes + lo.nbytes + hi.nbytes), "d2h_bytes_per_step": int(12 * nq * k),
+                 "add_plus_build_seconds": build_s}
+
+
+def run_c4(args):
+    """C4: build on 1M x 96, then 10 batches of 100k inserts through the class (CagraIndexOpt::insert), after each
+    batch 10 000 range queries over the newest 20 % of the timestamps: insert Mvec/s and recall drift
+    (reference flow: tests/test_cagra_opt_insert_auto.cu:199-204, thresholds tests/test_cagra_opt_insert.cu:359-360)."""
+    import torch
+    grab = importlib.import_module("grab-anns_b200")
+    grab.lib()
+    index = importlib.import_module("grab-anns_b200.index")
+    ds = importlib.import_module("grab-anns_b200.datasets")
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    w = ds.config("C4", args.scale)
+    w["n"] = w["base"].shape[0]
+    resolve_defaults(args, w)
+    n0, dim, k, deg = w["n"], w["dim"], w["k"], w["degree"]
+    batch_n = max(1000, int(100_000 * args.scale))
+    nb = args.insert_batches
+    bsize = max(1, n0 // args.buckets)
+    kw = dict(insert_batch=args.insert_batch_size) if args.insert_batch_size else {}
+    ix = index.CagraIndexOpt(dim, graph_degree=deg, local_degree=args.local_degree,
+                             vmm_max_bytes=int(8 * (n0 + nb * batch_n) * dim * 4), bucket_width=bsize, metric=0,
+                             knn_precision=2, **kw)
+    ix.set_query_params(args.itopk, args.width, 0, args.max_iter, args.hash_bitlen)
+    ix.set_router(args.router_centroids, args.probes, args.seeds)
+    t0 = time.perf_counter()
+    ix.add(w["base"], w["ts"])
+    ix.build()
+    build_s = time.perf_counter() - t0
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+    sampler.start()
+    all_vec = [w["base"]]
+    per_batch = []
+    nq = w["queries"].shape[0]
+    total = n0
+    for b in range(nb):
+        rng = np.random.Generator(np.random.PCG64(4100 + b))
+        vec = (w["centres"][rng.integers(0, w["centres"].shape[0], batch_n)] +
+               np.float32(0.2) * rng.standard_normal((batch_n, dim), dtype=np.float32)).astype(np.float32)
+        ts = np.arange(total, total + batch_n, dtype=np.uint64)
+        t0 = time.perf_counter()
+        ix.insert(vec, ts)
+        dt = time.perf_counter() - t0
+        total += batch_n
+        all_vec.append(vec)
+        # 10 000 range queries over the newest 20 % of the timestamps
+        qg = np.random.Generator(np.random.PCG64(4002 + b))
+        q = (w["centres"][qg.integers(0, w["centres"].shape[0], nq)] +
+             np.float32(0.2) * qg.standard_normal((nq, dim), dtype=np.float32)).astype(np.float32)
+        lo = np.full(nq, total - total // 5, dtype=np.uint64)
+        hi = np.full(nq, total, dtype=np.uint64)
+        t0 = time.perf_counter()
+        ids, _ = ix.query_range_batch(q, k, lo, hi)
+        qdt = time.perf_counter() - t0
+        d_all = torch.from_numpy(np.concatenate(all_vec)).cuda()
+        d_ts = torch.arange(total, dtype=torch.int64, device="cuda")
+        flt = grab.make_filter(grab.FILTER_TS_RANGE, ts=d_ts, lo=int(lo[0]), hi=int(hi[0]), ts_sorted=True)
+        gt, _ = grab.exact_search(d_all, torch.from_numpy(q).cuda(), k, flt=flt)
+        gt = gt.cpu().numpy()
+        del d_all
+        rec = recall_of(ids, gt)
+        bound_errors = int(((ids >= 0) & ((ids < int(lo[0])) | (ids >= int(hi[0])))).sum())
+        # global (unfiltered) recall, the reference's second threshold
+        per_batch.append({"batch": b + 1, "index_size": int(total), "insert_seconds": dt,
+                          "insert_mvec_per_s": batch_n / dt / 1e6, "recall_at_10_newest_20pct": rec,
+                          "bound_errors": bound_errors, "query_qps_class_call": nq / qdt})
+        print(json.dumps({"progress": per_batch[-1]}), file=sys.stderr, flush=True)
+    clocks = sampler.stop()
+    tot_ins = sum(p["insert_seconds"] for p in per_batch)
+    line = {"metric": "insert Mvec/s (C4: 10 x 100k inserts, recall@10 over the newest 20 % after each)",
+            "value": nb * batch_n / tot_ins / 1e6, "unit": "Mvec/s", "n_gpus": 1, "steps": nb, "warmup": 0,
+            "ms_per_step": 1e3 * tot_ins / nb, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"C4: {n0}x{dim} fp32 + {nb} x {batch_n} inserts, 10 000 range queries over the "
+                                   f"newest 20 % after each batch, k {k}, degree {deg}",
+                       "itopk": args.itopk, "search_width": args.width, "max_iterations": args.max_iter,
+                       "router_centroids": args.router_centroids, "probes": args.probes, "routed_seeds": args.seeds},
+            "build": {"seconds": build_s, "mvec_per_s": n0 / build_s / 1e6},
+            "batches": per_batch,
+            "recall_min": min(p["recall_at_10_newest_20pct"] for p in per_batch),
+            "recall_first": per_batch[0]["recall_at_10_newest_20pct"],
+            "recall_last": per_batch[-1]["recall_at_10_newest_20pct"],
+            "bound_errors": sum(p["bound_errors"] for p in per_batch), "clocks": clocks}
+    print(json.dumps(line), flush=True)
 
 
 def main():
     args = parse()
-    if args.max_iter == 0:
-        args.max_iter = 5 if args.router_centroids else 20
     if args.impl == "reference":
         return run_reference(args)
+    if args.workload == "C4":
+        return run_c4(args)
 
     import torch
     rank = int(os.environ.get("RANK", "0"))
@@ -266,128 +973,125 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     grab = importlib.import_module("grab-anns_b200")
     grab.lib()  # raises if the CUDA extension is missing: there is no fallback
+    steps, warmup = args.steps, max(args.warmup, 3)
+    peak, peak_source = measured_peak()
+
+    if args.workload == "C5":
+        # 12.5M x 96 per rank, generated on the device; only the sharded path exists at this size
+        shard = c5_shard(rank, world, args.scale, torch.device("cuda", local_rank))
+        w = {key: shard[key] for key in ("queries", "lo", "hi", "k", "degree", "itopk", "metric", "dim", "n")}
+        w["ts"] = None
+        resolve_defaults(args, w)
+        if args.global_candidates == 0:
+            args.global_candidates = 2
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        rec = sharded_record(args, grab, torch, dist, w, rank, world, steps, warmup, shard=shard)
+        clocks = sampler.stop()
+        if rank == 0:
+            cfg = workload_config(args, dict(w, ts=True), sharded=True)
+            cfg["workload"] = (f"C5: {shard['n_total']}x96 fp32 striped over {world} GPU(s) ({shard['n']} per GPU, "
+                               f"generated on the device), {w['queries'].shape[0]} queries, timestamp-range filter "
+                               f"10%, k 100, degree 64")
+            line = {"metric": "filtered QPS at recall@100>=0.95", "value": rec["value"], "unit": "queries/s",
+                    "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": rec["ms_per_step"],
+                    "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+                    "data": "synthetic", "config": cfg, "recall_at_100": rec["recall_at_k_merged"],
+                    "results_in_range": rec["results_in_range"], "sharded": rec,
+                    "gpu_launches": (5 if world > 1 else 5) * steps,
+                    "roofline": {"bound": "hbm", "achieved": rec["search_kernel_roofline_frac"] * peak, "peak": peak,
+                                 "unit": "GB/s", "frac": rec["search_kernel_roofline_frac"], "traffic": None,
+                                 "peak_source": peak_source},
+                    "cpu_baseline": None, "clocks": clocks}
+            print(json.dumps(line), flush=True)
+        if dist is not None:
+            dist.destroy_process_group()
+        return
 
     w = workload(args)
+    resolve_defaults(args, w)
     base, queries = w["base"], w["queries"]
     n, dim = base.shape
     k, deg = w["k"], w["degree"]
-    sharded = importlib.import_module("grab-anns_b200.sharded")
-    if args.sharded:
-        # id-striped shard of this rank; the same queries on every rank
-        base = np.ascontiguousarray(sharded.stripe(base, rank, world))
-        w["ts"] = np.ascontiguousarray(sharded.stripe(w["ts"], rank, world))
-        n = base.shape[0]
-    # each rank answers its own, different slice of the query stream (same size on every rank)
-    if world > 1 and not args.sharded:
-        ds = importlib.import_module("grab-anns_b200.datasets")
-        queries = np.roll(queries, rank * 997, axis=0)
-        w["lo"], w["hi"] = ds.range_queries(queries.shape[0], n, max(1, int(n * args.selectivity)), 2003 + rank)
+    by_labels = "ts" not in w
     nq = queries.shape[0]
 
-    d_base = torch.from_numpy(base).cuda()
-    by_labels = "ts" not in w
-    if by_labels:
-        if args.sharded:
-            raise SystemExit("--sharded is implemented for the timestamp workloads")
-        h_bucket = w["labels"].astype(np.uint64)               # one bucket per label
-    else:
-        d_ts = torch.from_numpy(w["ts"].view(np.int64)).cuda()
-        n_total = n * world if args.sharded else n
-        bsize = (n_total + args.buckets - 1) // args.buckets   # bucket width in timestamps
-        h_bucket = w["ts"] // np.uint64(bsize)
-    sizes = np.bincount(h_bucket.astype(np.int64)).tolist()    # sorted keys: buckets are id runs
-    d_bucket = torch.from_numpy(h_bucket.view(np.int64)).cuda()
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    graph = grab.build_time_partitioned_graph(d_base, d_bucket, sizes, deg, args.local_degree, metric=w["metric"],
-                                              knn_precision=args.knn_precision,
-                                              global_candidates=args.global_candidates)
-    torch.cuda.synchronize()
-    build_s = time.perf_counter() - t0
-    router, router_s = None, 0.0
-    if args.router_centroids:
-        t0 = time.perf_counter()
-        router = grab.router_build(d_base, min(args.router_centroids, n), metric=w["metric"])
-        torch.cuda.synchronize()
-        router_s = time.perf_counter() - t0
+    if args.emulate_shards:
+        rec = emulate_shards(args, grab, torch, w, args.emulate_shards, steps, warmup)
+        print(json.dumps(rec), flush=True)
+        return
 
+    if args.sharded:
+        if by_labels:
+            raise SystemExit("--sharded is implemented for the timestamp workloads")
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        rec = sharded_record(args, grab, torch, dist, w, rank, world, steps, warmup)
+        clocks = sampler.stop()
+        if rank == 0:
+            line = {"metric": METRIC_NAME, "value": rec["value"], "unit": "queries/s", "n_gpus": world, "steps": steps,
+                    "warmup": warmup, "ms_per_step": rec["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+                    "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                    "config": workload_config(args, w, sharded=True), "recall_at_10": rec["recall_at_k_merged"],
+                    "results_in_range": rec["results_in_range"], "sharded": rec,
+                    "gpu_launches": (5 if world > 1 else 4) * steps, "cpu_baseline": None, "clocks": clocks}
+            print(json.dumps(line), flush=True)
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    # ---- replicas: each rank answers its own, different slice of the query stream (same size on every rank) ----
+    if world > 1:
+        ds = importlib.import_module("grab-anns_b200.datasets")
+        queries = np.roll(queries, rank * 997, axis=0)
+        if not by_labels:
+            w_lo, w_hi = ds.range_queries(nq, n, max(1, int(n * args.selectivity)), 2003 + rank)
+        else:
+            w_lo = w_hi = np.roll(w["masks"], rank * 997)
+    else:
+        w_lo, w_hi = (w["lo"], w["hi"]) if not by_labels else (w["masks"], w["masks"])
+
+    d_base = torch.from_numpy(base).cuda()
+    if by_labels:
+        ix = Index(grab, args, w, d_base, labels=w["labels"], label_offsets=w["label_offsets"])
+    else:
+        ix = Index(grab, args, w, d_base, ts=w["ts"])
     h_q = torch.from_numpy(queries).pin_memory()
     d_q = h_q.cuda()
     if by_labels:
-        h_lo = torch.from_numpy(w["masks"].view(np.int32)).pin_memory()    # per-query label masks
+        h_lo = torch.from_numpy(w_lo.view(np.int32)).pin_memory()    # per-query label masks
         h_hi = h_lo
         d_lo = d_hi = h_lo.cuda()
-        d_labels = torch.from_numpy(w["labels"]).cuda()
-        d_offs = torch.from_numpy(w["label_offsets"].view(np.int32)).cuda()
-        flt = grab.make_filter(grab.FILTER_LABELS, labels=d_labels, masks=d_lo, label_offsets=d_offs)
     else:
-        h_lo = torch.from_numpy(w["lo"].view(np.int64)).pin_memory()
-        h_hi = torch.from_numpy(w["hi"].view(np.int64)).pin_memory()
+        h_lo = torch.from_numpy(w_lo.view(np.int64)).pin_memory()
+        h_hi = torch.from_numpy(w_hi.view(np.int64)).pin_memory()
         d_lo, d_hi = h_lo.cuda(), h_hi.cuda()
-        flt = grab.make_filter(grab.FILTER_TS_RANGE, ts=d_ts, lo=d_lo, hi=d_hi, ts_sorted=True)
-    params = grab.SearchParams(args.itopk, args.width, 0, args.max_iter, args.hash_bitlen)
-    out_ids = torch.empty((nq, k), dtype=torch.int64, device="cuda")
-    out_d = torch.empty((nq, k), dtype=torch.float32, device="cuda")
+    flt = ix.filter(d_lo, d_hi)
+    S = Searcher(ix, nq, k, args.itopk, args.width, args.max_iter, args.hash_bitlen, args.probes, args.seeds)
     h_ids = torch.empty((nq, k), dtype=torch.int64).pin_memory()
     h_d = torch.empty((nq, k), dtype=torch.float32).pin_memory()
-    ws = torch.empty(grab.lib().grab_graph_search_workspace_bytes(nq, args.hash_bitlen), dtype=torch.uint8,
-                     device="cuda")
 
-    seeds = route_ws = None
-    if router is not None:
-        seeds = torch.empty((nq, args.seeds), dtype=torch.int32, device="cuda")
-        route_ws = torch.empty(grab.lib().grab_route_seeds_workspace_bytes(nq, args.probes), dtype=torch.uint8,
-                               device="cuda")
-
-    def route():
-        if router is not None:
-            grab.route_seeds(router, d_q, n, flt, probes=args.probes, seeds_per_query=args.seeds, out=seeds,
-                             ws=route_ws)
-
-    id_scale, id_offset = (world, rank) if args.sharded else (1, 0)
-    merge = lambda d, i, kk: grab.merge_topk(d, i, kk)
-    # ground truth from the exact filtered kernel (bit-exact against the CPU oracle in tests/)
+    # ground truth from the exact filtered kernel (bit-exact against the CPU oracle: tests/, and `parity` below)
     gt_ids, gt_d = grab.exact_search(d_base, d_q, k, metric=w["metric"], flt=flt)
-    route()
-    ids, dd, stats = grab.graph_search(d_base, graph, d_q, k, params, metric=w["metric"], flt=flt, stats=True,
-                                       seeds=seeds, out=(out_ids, out_d), ws=ws, id_scale=id_scale,
-                                       id_offset=id_offset)
-    if args.sharded:
-        gt_ids = torch.where(gt_ids >= 0, gt_ids * world + rank, gt_ids)
-        gt_ids, _ = sharded.gather_and_merge(gt_d, gt_ids, k, merge)
-        ids, _ = sharded.gather_and_merge(dd, ids, k, merge)
-        st = torch.tensor([stats.iterations, stats.parents, stats.edges, stats.distances, stats.seeds,
-                           stats.hash_resets], device="cuda", dtype=torch.int64)
-        dist.all_reduce(st) if dist is not None else None
-        stats = grab.SearchStats(*st.cpu().tolist())
+    S.route(d_q, flt)
+    ids, dd, stats = S.search(d_q, flt, stats=True)
     gt = gt_ids.cpu().numpy()
     res = ids.cpu().numpy()
-    hit = 0
-    denom = 0
-    for r, g in zip(res, gt):
-        g = g[g >= 0]
-        hit += np.intersect1d(r, g).size
-        denom += g.size
-    recall = hit / max(denom, 1)
+    recall = recall_of(res, gt)
     if by_labels:
         lab = w["labels"][np.clip(res, 0, n - 1)]
-        in_range = bool(np.all((((w["masks"][:, None] >> lab) & 1) == 1) | (res < 0)))
-    else:  # timestamps equal global ids in this workload
-        in_range = bool(np.all(((res >= w["lo"][:, None].astype(np.int64)) &
-                                (res < w["hi"][:, None].astype(np.int64))) | (res < 0)))
-    # sorted timestamps: id-window predicate, no gather (f = 0); labels: one byte per examined edge;
-    # sharded: every rank reads every query
-    alg_bytes = grab.search_bytes(stats, nq * (world if args.sharded else 1), dim, deg, k, 1 if by_labels else 0)
-
-    def search_only():
-        grab.graph_search(d_base, graph, d_q, k, params, metric=w["metric"], flt=flt, seeds=seeds,
-                          out=(out_ids, out_d), ws=ws, id_scale=id_scale, id_offset=id_offset)
+        in_range = bool(np.all((((w_lo[:, None] >> lab) & 1) == 1) | (res < 0)))
+    else:  # timestamps equal ids in this workload
+        in_range = bool(np.all(((res >= w_lo[:, None].astype(np.int64)) &
+                                (res < w_hi[:, None].astype(np.int64))) | (res < 0)))
+    # sorted timestamps: id-window predicate, no gather (f = 0); labels: one byte per examined edge
+    alg_bytes = grab.search_bytes(stats, nq, dim, deg, k, 1 if by_labels else 0)
 
     def step():
-        route()
-        search_only()
-        if args.sharded:
-            sharded.gather_and_merge(out_d, out_ids, k, merge)
+        S.step(d_q, flt)
+
+    def search_only():
+        S.search(d_q, flt)
 
     def e2e_step():
         d_q.copy_(h_q, non_blocking=True)
@@ -395,8 +1099,8 @@ def main():
         if not by_labels:
             d_hi.copy_(h_hi, non_blocking=True)
         step()
-        h_ids.copy_(out_ids, non_blocking=True)
-        h_d.copy_(out_d, non_blocking=True)
+        h_ids.copy_(S.ids, non_blocking=True)
+        h_d.copy_(S.d, non_blocking=True)
 
     def make_pipeline():
         """End-to-end steps as a serving loop runs them: two sets of device/pinned buffers, the host->device
@@ -408,11 +1112,8 @@ def main():
             q_ = torch.empty_like(d_q)
             lo_ = torch.empty_like(d_lo)
             hi_ = lo_ if by_labels else torch.empty_like(d_hi)
-            if by_labels:
-                f_ = grab.make_filter(grab.FILTER_LABELS, labels=d_labels, masks=lo_, label_offsets=d_offs)
-            else:
-                f_ = grab.make_filter(grab.FILTER_TS_RANGE, ts=d_ts, lo=lo_, hi=hi_, ts_sorted=True)
-            sets.append(dict(q=q_, lo=lo_, hi=hi_, flt=f_, ids=torch.empty_like(out_ids), d=torch.empty_like(out_d),
+            sets.append(dict(q=q_, lo=lo_, hi=hi_, flt=ix.filter(lo_, hi_), ids=torch.empty_like(S.ids),
+                             d=torch.empty_like(S.d),
                              h_ids=torch.empty((nq, k), dtype=torch.int64).pin_memory(),
                              h_d=torch.empty((nq, k), dtype=torch.float32).pin_memory(),
                              ev_in=torch.cuda.Event(), ev_done=torch.cuda.Event(), ev_out=torch.cuda.Event(),
@@ -434,12 +1135,8 @@ def main():
             main.wait_event(b["ev_in"])
             if b["used"]:
                 main.wait_event(b["ev_out"])           # the previous results of this set have left
-            sd = None
-            if router is not None:
-                sd = grab.route_seeds(router, b["q"], n, b["flt"], probes=args.probes, seeds_per_query=args.seeds,
-                                      out=seeds, ws=route_ws)
-            grab.graph_search(d_base, graph, b["q"], k, params, metric=w["metric"], flt=b["flt"], seeds=sd,
-                              out=(b["ids"], b["d"]), ws=ws)
+            S.route(b["q"], b["flt"])
+            S.search(b["q"], b["flt"], out=(b["ids"], b["d"]))
             b["ev_done"].record(main)
             with torch.cuda.stream(s_out):
                 s_out.wait_event(b["ev_done"])
@@ -455,9 +1152,9 @@ def main():
                     main.wait_event(b["ev_out"])
         return fn, drain, sets
 
-    def timed_pipeline(steps, warmup):
+    def timed_pipeline(steps_, warmup_):
         fn, drain, sets = make_pipeline()
-        for _ in range(warmup):
+        for _ in range(warmup_):
             fn()
         drain()
         torch.cuda.synchronize()
@@ -466,7 +1163,7 @@ def main():
         torch.cuda.synchronize()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        for _ in range(steps):
+        for _ in range(steps_):
             fn()
         drain()
         b.record()
@@ -478,16 +1175,17 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ref_ids = ids.cpu()
         same = all(float((s_["h_ids"] == ref_ids).float().mean()) > 0.999 for s_ in sets if s_["used"])
-        return float(t.item()) / steps, same
+        return float(t.item()) / steps_, same
 
-    def timed(fn, steps, warmup):
-        for _ in range(warmup):
+    def timed(fn, steps_, warmup_):
+        """Sum of per-step event pairs (the contract's timing), max over ranks."""
+        for _ in range(warmup_):
             fn()
         torch.cuda.synchronize()
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
-        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps_)]
         for a, b in evs:
             a.record()
             fn()
@@ -499,97 +1197,102 @@ def main():
         t = torch.tensor([total_ms], device="cuda", dtype=torch.float64)
         if dist is not None:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item()) / steps
+        return float(t.item()) / steps_
 
     # the timed region lasts milliseconds, an nvidia-smi sample takes 100 ms: the same kernels keep the GPU
-    # under load before and after the timed steps until the sampler has collected a few samples.  The loops
-    # run a rank-dependent number of times, so they must not contain a collective (the sharded step does).
-    def load_step():
-        route()
-        search_only()
-
+    # under load before and after the timed steps until the sampler has collected a few samples.  These loops run a
+    # rank-dependent number of times, so they contain no collective.
     sampler = ClockSampler(local_rank)
     sampler.start()
     t_end = time.perf_counter() + 1.5
     while len(sampler.samples) < 1 and time.perf_counter() < t_end:
-        load_step()
+        step()
         torch.cuda.synchronize()
-    ms = timed(step, args.steps, max(args.warmup, 3))
+    ms = timed(step, steps, warmup)
     t_end = time.perf_counter() + 1.0
     have = len(sampler.samples)
     while len(sampler.samples) < have + 3 and time.perf_counter() < t_end:
-        load_step()
+        step()
         torch.cuda.synchronize()
     clocks = sampler.stop()
-    ms_e2e = timed(e2e_step, args.steps, max(args.warmup, 3))
-    e2e_mode = "one stream: copy in, search, copy out, per step"
-    if not args.sharded and not args.no_overlap:
-        ms_e2e_seq = ms_e2e
-        ms_e2e, same = timed_pipeline(args.steps, max(args.warmup, 3))
+    ms_e2e_seq = timed(e2e_step, steps, warmup)
+    ms_e2e, e2e_mode = ms_e2e_seq, "one stream: copy in, route, search, copy out, per step"
+    if not args.no_overlap:
+        ms_e2e, same = timed_pipeline(steps, warmup)
         if not same:
             raise SystemExit("pipelined end-to-end steps returned different ids")
-        e2e_mode = ("double-buffered: the copies of neighbouring steps overlap the search on separate streams "
-                    f"(one stream, no overlap: {nq / (ms_e2e_seq / 1e3) * world:.0f} queries/s)")
+        e2e_mode = "double-buffered: the copies of neighbouring steps overlap the search on separate streams"
     # the dominant kernel alone (the search launch with the routed seeds already written), for the roofline
-    ms_search = timed(search_only, args.steps, max(args.warmup, 3)) if router is not None or args.sharded else ms
+    ms_search = timed(search_only, steps, warmup) if ix.router is not None else ms
 
-    cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        import oracle
-        sample = args.cpu_sample or auto_cpu_sample(w)
-        cqps, cdt = cpu_exact_qps(w, sample)
-        cpu = {"value": cqps, "unit": "queries/s", "cores": oracle.num_threads(), "kind": "port",
-               "sample": f"{sample} of {nq} queries over the full {n}-vector base in {cdt:.1f} s; exact filtered "
-                         "brute force (recall 1.0), OpenMP over queries"}
+    sharded = None
+    if world > 1 and not by_labels and not args.no_sharded_record:
+        del S
+        torch.cuda.empty_cache()
+        sharded = sharded_record(args, grab, torch, dist, w, rank, world, steps, warmup)
+
+    cpu = parity = e2e_cls = None
+    if rank == 0 and world == 1:
+        if not args.no_cpu_baseline:
+            import oracle
+            sample = args.cpu_sample or auto_cpu_sample(w)
+            cqps, cdt = cpu_exact_qps(w, sample)
+            cpu = {"value": cqps, "unit": "queries/s", "cores": oracle.num_threads(), "kind": "port",
+                   "sample": f"{sample} of {nq} queries over the full {n}-vector base in {cdt:.1f} s; exact filtered "
+                             "brute force (recall 1.0), OpenMP over queries"}
+        if not args.no_parity:
+            parity = parity_at_config_shape(w, gt, gt_d.cpu().numpy())
+        if not args.no_class_e2e and not by_labels:
+            try:
+                cids, e2e_cls = class_e2e(args, w, steps, warmup)
+                e2e_cls["recall_at_10"] = recall_of(cids, gt)
+            except Exception as e:
+                e2e_cls = {"unavailable": f"{type(e).__name__}: {e}"}
 
     if rank == 0:
-        peaks = {}
-        try:
-            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-        except Exception:
-            pass
-        peak = float(peaks.get("hbm_gbs", 6650.0))
-        if args.sharded:
-            alg_bytes //= world     # counters were summed over the ranks; the roofline is one GPU's launch
         achieved = alg_bytes / (ms_search / 1e3) / 1e9
-        # dram__bytes_read.sum + dram__bytes_write.sum of one search launch at the default full-size
-        # configuration (ncu capture summarised in profiles/graph_search_kernel_C2.md)
-        default_cfg = (args.workload == "C2" and args.scale == 1.0 and args.buckets == 20 and args.itopk == 64 and
-                       args.width == 3 and args.max_iter == 5 and args.hash_bitlen == 11 and
-                       args.selectivity == 0.10 and not args.sharded and args.router_centroids == 1024 and
-                       args.probes == 2 and args.seeds == 64 and args.local_degree == 48 and
-                       args.global_candidates in (0, 1))
-        traffic = 1364566272 + 1159168 if default_cfg else None
         line = {
-            "metric": "filtered QPS at recall@10>=0.95",
-            "value": (1 if args.sharded else world) * nq / (ms / 1e3), "unit": "queries/s",
-            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
-            "higher_is_better": True, "scaling": "strong" if args.sharded else "weak", "vs_baseline": None,
+            "metric": METRIC_NAME if k == 10 else f"filtered QPS at recall@{k}>=0.95",
+            "value": world * nq / (ms / 1e3), "unit": "queries/s",
+            "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic", "config": workload_config(args, w),
             "recall_at_10": recall, "results_in_range": in_range,
-            "build": {"seconds": build_s, "mvec_per_s": n / build_s / 1e6, "knn_precision": args.knn_precision,
-                      "global_candidates": args.global_candidates,
-                      "router_seconds": router_s},
-            "ms_search_kernel": ms_search, "ms_router": ms - ms_search if router is not None and not args.sharded else None,
-            "e2e": {"value": (1 if args.sharded else world) * nq / (ms_e2e / 1e3), "unit": "queries/s",
+            "build": {"seconds": ix.build_s, "mvec_per_s": n / ix.build_s / 1e6, "knn_precision": args.knn_precision,
+                      "global_candidates": args.global_candidates, "router_seconds": ix.router_s},
+            "ms_search_kernel": ms_search, "ms_router": ms - ms_search if ix.router is not None else None,
+            "e2e": {"value": world * nq / (ms_e2e / 1e3), "unit": "queries/s",
                     "h2d_bytes_per_step": int(h_q.numel() * 4 + (4 if by_labels else 16) * nq),
-                    "d2h_bytes_per_step": int(12 * nq * k), "mode": e2e_mode},
-            # per step: nearest-centroids + seed picking (router), id windows (sorted timestamps), search,
-            # and the merge after the all_gather when sharded
-            "gpu_launches": ((2 if router is not None else 0) + (1 if by_labels else 2) +
-                             (2 if args.sharded and world > 1 else 0)) * args.steps,
+                    "d2h_bytes_per_step": int(12 * nq * k), "mode": e2e_mode,
+                    "one_stream_value": world * nq / (ms_e2e_seq / 1e3)},
+            "e2e_class": e2e_cls,
+            # per step: centroid ranking + seed kernel (router), id windows (sorted timestamps), search
+            "gpu_launches": ((2 if ix.router is not None else 0) + (1 if by_labels else 2)) * steps,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": traffic,
-                         "peak_source": "measured" if peaks else "fallback",
+                         "frac": achieved / peak, "traffic": roofline_traffic(args, w, alg_bytes),
+                         "peak_source": peak_source,
                          "algorithmic_bytes_per_launch": int(alg_bytes),
                          "counters": {"seeds": stats.seeds, "parents": stats.parents, "edges": stats.edges,
                                       "distances": stats.distances, "iterations": stats.iterations,
                                       "hash_resets": stats.hash_resets}},
-            "cpu_baseline": cpu, "clocks": clocks,
+            "cpu_baseline": cpu, "parity": parity, "clocks": clocks,
         }
+        if sharded is not None:
+            line["sharded"] = sharded
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one search launch, per algorithmic byte, from the ncu capture of
+# the default configuration summarised in profiles/graph_search_kernel_C2.md (traffic grows with the work done)
+DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = 0.7305
+
+
+def roofline_traffic(args, w, alg_bytes):
+    default_cfg = (args.workload == "C2" and args.scale == 1.0 and args.buckets == 20 and args.selectivity == 0.10 and
+                   args.router_centroids == 1024)
+    return int(alg_bytes * DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE) if default_cfg else None
 
 
 if __name__ == "__main__":

@@ -63,7 +63,7 @@ class SearchArgs(C.Structure):
                 ("seeds_per_query", C.c_uint32), ("seed", C.c_uint64), ("d_out_ids", C.c_void_p),
                 ("d_out_dists", C.c_void_p), ("id_scale", C.c_uint64), ("id_offset", C.c_uint64),
                 ("d_stats", C.c_void_p), ("d_ws", C.c_void_p), ("ws_bytes", C.c_size_t),
-                ("stream", C.c_void_p)]
+                ("stream", C.c_void_p), ("d_out_keys", C.c_void_p)]
 
 
 class RouterStruct(C.Structure):
@@ -163,8 +163,10 @@ def exact_search(dataset, queries, k, metric=METRIC_L2, flt: Filter | None = Non
 
 def graph_search(dataset, graph, queries, k, params: SearchParams, metric=METRIC_L2,
                  flt: Filter | None = None, seeds=None, seed=0x1234ABCD, id_scale=1, id_offset=0,
-                 stats=False, out=None, ws=None):
-    """Filtered graph search; returns (ids, dists[, SearchStats])."""
+                 stats=False, out=None, ws=None, out_keys=None):
+    """Filtered graph search; returns (ids, dists[, SearchStats]).  out_keys: optional int64 tensor [nq, k] that
+    receives the results as (ordered distance << 32 | result id) keys for the sharded exchange step; with
+    out=(None, None) only the keys are written."""
     import torch
     n, dim = dataset.shape
     nq = queries.shape[0]
@@ -184,6 +186,7 @@ def graph_search(dataset, graph, queries, k, params: SearchParams, metric=METRIC
         a.d_seeds, a.seeds_per_query = _p(seeds), seeds.shape[1]
     a.seed = seed
     a.d_out_ids, a.d_out_dists = _p(ids), _p(dists)
+    a.d_out_keys = _p(out_keys)
     a.id_scale, a.id_offset = id_scale, id_offset
     st = None
     if stats:
@@ -247,6 +250,64 @@ def merge_topk(dists, ids, k):
     check(lib().grab_merge_topk(_p(dists), _p(ids), C.c_uint64(nq), C.c_uint32(parts), C.c_uint32(k),
                                 _p(out_ids), _p(out_d), _stream()))
     return out_ids, out_d
+
+
+def merge_sorted_keys(keys, k, out=None):
+    """grab_merge_sorted_keys: keys int64 tensor [parts, nq, run_length] (uint64 bits, runs ascending) -> (ids, dists)."""
+    import torch
+    parts, nq, kp = keys.shape
+    if out is None:
+        out = (torch.empty((nq, k), dtype=torch.int64, device=keys.device),
+               torch.empty((nq, k), dtype=torch.float32, device=keys.device))
+    check(lib().grab_merge_sorted_keys(_p(keys), C.c_uint64(nq), C.c_uint32(parts), C.c_uint32(kp), C.c_uint32(k),
+                                       _p(out[0]), _p(out[1]), _stream()))
+    return out
+
+
+class Comm:
+    """grab_comm: the communicator of the id-sharded search (NCCL inside the C library).  `broadcast_bytes(buf)`
+    must hand rank 0's 128-byte buffer to every rank (torch.distributed, MPI, a file -- any side channel)."""
+
+    def __init__(self, world: int, rank: int, broadcast_bytes):
+        import numpy as np
+        self.world, self.rank = world, rank
+        uid = np.zeros(128, dtype=np.uint8)
+        if rank == 0:
+            check(lib().grab_comm_unique_id(_p(uid), C.c_size_t(128)))
+        uid = np.ascontiguousarray(broadcast_bytes(uid), dtype=np.uint8)
+        h = C.c_void_p()
+        check(lib().grab_comm_create(_p(uid), C.c_int(world), C.c_int(rank), C.byref(h)))
+        self.handle = h
+
+    def gather_merge(self, keys, k, gather=None, out=None):
+        """All-gather of this rank's keys [nq, run_length] + G-way merge, on the current stream -> (ids, dists)."""
+        import torch
+        nq, kp = keys.shape
+        if gather is None:
+            gather = torch.empty((self.world, nq, kp), dtype=torch.int64, device=keys.device)
+        if out is None:
+            out = (torch.empty((nq, k), dtype=torch.int64, device=keys.device),
+                   torch.empty((nq, k), dtype=torch.float32, device=keys.device))
+        check(lib().grab_sharded_gather_merge(self.handle, _p(keys), C.c_uint64(nq), C.c_uint32(kp), C.c_uint32(k),
+                                              _p(gather), C.c_size_t(gather.numel() * 8), _p(out[0]), _p(out[1]),
+                                              _stream()))
+        return out
+
+    def close(self):
+        if self.handle:
+            lib().grab_comm_destroy(self.handle)
+            self.handle = None
+
+
+def torch_broadcast_bytes(buf):
+    """Side channel for Comm over an initialised torch.distributed group (any backend)."""
+    import torch
+    import torch.distributed as dist
+    t = torch.from_numpy(buf.copy())
+    if dist.get_backend() == "nccl":
+        t = t.cuda()
+    dist.broadcast(t, src=0)
+    return t.cpu().numpy()
 
 
 class Router:

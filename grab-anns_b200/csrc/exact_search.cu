@@ -154,7 +154,11 @@ exact_scan_kernel(const float* __restrict__ data, uint32_t dim, ScanFilter f,
       }
     }
     __syncthreads();
-    if (s_count + kScanStep > buf_cap) {  // uniform: every thread reads the same value
+    // Every thread must take the same branch (the sort below contains barriers).  The count is copied out and a
+    // second barrier keeps the next step's appends from changing it while slower warps are still reading it.
+    const uint32_t appended = s_count;
+    __syncthreads();
+    if (appended + kScanStep > buf_cap) {
       block_bitonic_sort(keys, total);
       for (uint32_t i = k + tid; i < total; i += kScanThreads) keys[i] = kMaxKey;
       if (tid == 0) {

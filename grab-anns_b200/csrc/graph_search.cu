@@ -21,6 +21,7 @@
 //     (the reference: every 30 iterations, search.cu:692-697).
 // HBM/latency-bound by design: no tensor cores.
 #include "common.cuh"
+#include "search_blocks.cuh"
 
 namespace grab {
 
@@ -70,184 +71,12 @@ struct SearchKernelArgs {
   uint32_t* global_hash;    // [nq, 2^bitlen] when the table does not fit shared memory
   int64_t* out_ids;
   float* out_dists;
+  uint64_t* out_keys;  // [nq,k] (ordered dist << 32 | result id), or NULL
   uint64_t id_scale, id_offset;
   unsigned long long* stats;  // grab_search_stats as 6 x u64, or NULL
   uint32_t ckeys_cap;
   uint32_t cand_cap, sort_cap;  // survivor list capacity; sort_cap = itopk rounded up to a power of two
 };
-
-__device__ __forceinline__ bool hash_insert(uint32_t* table, uint32_t bitlen, uint32_t key) {
-  // Open addressing, linear probe, slot = (key ^ key>>bitlen) & mask: hashmap.cuh:43-91.
-  const uint32_t mask = (1u << bitlen) - 1;
-  uint32_t idx = (key ^ (key >> bitlen)) & mask;
-  for (uint32_t i = 0; i <= mask; ++i) {
-    const uint32_t old = atomicCAS(&table[idx], kInvalid, key);
-    if (old == kInvalid) return true;
-    if (old == key) return false;
-    idx = (idx + 1) & mask;
-  }
-  return false;  // full table reads as "visited", as in the reference (hashmap.cuh:89-90)
-}
-
-// Search-queue keys: [ordered dist : 32 | id : 31 | expanded flag : 1].  Raising the flag of an
-// entry cannot move it past another entry (ids are unique), so the list stays sorted.
-__device__ __forceinline__ uint64_t make_skey(float d, uint32_t id) {
-  return (static_cast<uint64_t>(float_to_ordered(d)) << 32) | (static_cast<uint64_t>(id) << 1);
-}
-__device__ __forceinline__ uint32_t skey_id(uint64_t key) { return static_cast<uint32_t>(key & 0xFFFFFFFFull) >> 1; }
-__device__ __forceinline__ bool skey_expanded(uint64_t key) { return (key & 1ull) != 0; }
-
-__device__ __forceinline__ uint64_t mix64(uint64_t x) {  // splitmix64 finaliser
-  x ^= x >> 30; x *= 0xbf58476d1ce4e5b9ull;
-  x ^= x >> 27; x *= 0x94d049bb133111ebull;
-  x ^= x >> 31;
-  return x;
-}
-
-// Ascending bitonic sort of n (power of two, >= 32) keys in shared memory by ONE warp.
-__device__ __forceinline__ void warp_bitonic_sort_smem(uint64_t* keys, uint32_t n, uint32_t lane) {
-  for (uint32_t size = 2; size <= n; size <<= 1) {
-    for (uint32_t stride = size >> 1; stride > 0; stride >>= 1) {
-      for (uint32_t t = lane; t < (n >> 1); t += 32) {
-        const uint32_t lo = ((t & ~(stride - 1)) << 1) | (t & (stride - 1));
-        const uint32_t hi = lo | stride;
-        const bool up = (lo & size) == 0;
-        const uint64_t a = keys[lo], b = keys[hi];
-        if ((a > b) == up) { keys[lo] = b; keys[hi] = a; }
-      }
-      __syncwarp();
-    }
-  }
-}
-
-// Fold `ncand` sorted candidate keys into the sorted list top[0..m) (m a power of two), keeping
-// the m smallest: top[m-1-i] = min(top[m-1-i], cand[i]) leaves a bitonic sequence, which one
-// pass of bitonic merge stages sorts again.  One warp.
-__device__ __forceinline__ void warp_merge_into_topk(uint64_t* top, uint32_t m, const uint64_t* cand,
-                                                     uint32_t ncand, uint32_t lane) {
-  const uint32_t lim = ncand < m ? ncand : m;
-  for (uint32_t i = lane; i < lim; i += 32) {
-    const uint64_t a = top[m - 1 - i], b = cand[i];
-    if (b < a) top[m - 1 - i] = b;
-  }
-  __syncwarp();
-  for (uint32_t stride = m >> 1; stride > 0; stride >>= 1) {
-    for (uint32_t t = lane; t < (m >> 1); t += 32) {
-      const uint32_t lo = ((t & ~(stride - 1)) << 1) | (t & (stride - 1));
-      const uint32_t hi = lo | stride;
-      const uint64_t a = top[lo], b = top[hi];
-      if (a > b) { top[lo] = b; top[hi] = a; }
-    }
-    __syncwarp();
-  }
-}
-
-// ---------------------------------------------------------------------------------------
-// Register versions of the two functions above for lists of 32*R keys (R = 2, 4): element e
-// lives in register e/32 of lane e%32.  Compare-exchanges at strides below 32 are xor-shuffles,
-// strides of 32 and more pair registers of the same lane; no shared-memory round trip and no
-// warp barrier per stage, which is what the shared-memory versions spend their time on.
-// ---------------------------------------------------------------------------------------
-__device__ __forceinline__ uint64_t shfl_xor_u64(uint64_t v, uint32_t mask) {
-  return __shfl_xor_sync(0xFFFFFFFFu, v, mask);
-}
-
-// One bitonic stage at STRIDE inside sorted blocks of `size` (a block is ascending when its
-// index has bit `size` clear).  STRIDE is a compile-time constant so that register indices are.
-template <int R, uint32_t STRIDE>
-__device__ __forceinline__ void reg_bitonic_stage(uint64_t (&v)[R], uint32_t size, uint32_t lane) {
-  if (STRIDE >= 32) {
-    constexpr uint32_t RS = STRIDE >> 5;
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-      if ((r & RS) == 0) {
-        const bool up = (((static_cast<uint32_t>(r) << 5) & size) == 0);
-        const uint64_t a = v[r], b = v[(r | RS) < R ? (r | RS) : r];
-        const bool swap = (a > b) == up;
-        v[r] = swap ? b : a;
-        v[(r | RS) < R ? (r | RS) : r] = swap ? a : b;
-      }
-    }
-  } else {
-    const bool lower = (lane & STRIDE) == 0;
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-      const uint32_t e = lane + (static_cast<uint32_t>(r) << 5);
-      const bool up = (e & size) == 0;
-      const uint64_t other = shfl_xor_u64(v[r], STRIDE);
-      const bool keep_min = lower == up;
-      const uint64_t mn = v[r] < other ? v[r] : other, mx = v[r] < other ? other : v[r];
-      v[r] = keep_min ? mn : mx;
-    }
-  }
-}
-
-// All stages of one level (block size 2^LOG): strides 2^(LOG-1) ... 1.
-template <int R, int LOG, int S = LOG - 1>
-struct RegBitonicLevel {
-  static __device__ __forceinline__ void run(uint64_t (&v)[R], uint32_t size, uint32_t lane) {
-    reg_bitonic_stage<R, (1u << S)>(v, size, lane);
-    RegBitonicLevel<R, LOG, S - 1>::run(v, size, lane);
-  }
-};
-template <int R, int LOG>
-struct RegBitonicLevel<R, LOG, -1> {
-  static __device__ __forceinline__ void run(uint64_t (&)[R], uint32_t, uint32_t) {}
-};
-
-// Levels 1 .. LOG of a bitonic sort; levels above `padded` are skipped, the level equal to
-// `padded` sorts ascending (direction bit taken from the full list length M).
-template <int R, int LOG>
-struct RegBitonicSort {
-  static __device__ __forceinline__ void run(uint64_t (&v)[R], uint32_t padded, uint32_t lane) {
-    RegBitonicSort<R, LOG - 1>::run(v, padded, lane);
-    constexpr uint32_t SIZE = 1u << LOG;
-    if (SIZE <= padded) RegBitonicLevel<R, LOG>::run(v, SIZE == padded ? 32u * R : SIZE, lane);  // uniform
-  }
-};
-template <int R>
-struct RegBitonicSort<R, 0> {
-  static __device__ __forceinline__ void run(uint64_t (&)[R], uint32_t, uint32_t) {}
-};
-
-template <int R> struct Log2Of32R;
-template <> struct Log2Of32R<2> { static constexpr int value = 6; };
-template <> struct Log2Of32R<4> { static constexpr int value = 7; };
-
-// Sorts the nkeep (<= 32*R) candidate keys and folds them into the sorted list top[0..32*R).
-template <int R>
-__device__ __forceinline__ void warp_sort_merge_regs(uint64_t* top, const uint64_t* cand, uint32_t nkeep,
-                                                     uint32_t lane) {
-  constexpr uint32_t M = 32u * R;
-  constexpr int LOGM = Log2Of32R<R>::value;
-  uint64_t c[R], t[R];
-#pragma unroll
-  for (int r = 0; r < R; ++r) {
-    const uint32_t e = lane + 32u * r;
-    c[r] = e < nkeep ? cand[e] : kMaxKey;
-    t[r] = top[e];
-  }
-  // only as many sort levels as the candidates need (padded to a power of two >= 32)
-  uint32_t padded = 32;
-  while (padded < nkeep) padded <<= 1;
-  RegBitonicSort<R, LOGM>::run(c, padded, lane);
-  // sorted candidates occupy elements [0, padded); top[M-1-i] = min(top[M-1-i], cand[i])
-#pragma unroll
-  for (int r = 0; r < R; ++r) {
-    const uint64_t partner = __shfl_sync(0xFFFFFFFFu, c[R - 1 - r], 31u - lane);  // element M-1-e
-    t[r] = partner < t[r] ? partner : t[r];
-  }
-  RegBitonicLevel<R, LOGM>::run(t, M, lane);
-#pragma unroll
-  for (int r = 0; r < R; ++r) top[lane + 32u * r] = t[r];
-}
-
-// the 128-entry variant is kept out of line so that its registers do not count against the
-// common 64-entry path
-__device__ __noinline__ void warp_sort_merge_regs_128(uint64_t* top, const uint64_t* cand, uint32_t nkeep,
-                                                      uint32_t lane) {
-  warp_sort_merge_regs<4>(top, cand, nkeep, lane);
-}
 
 template <int METRIC, int CPL>
 __global__ void __launch_bounds__(kSearchThreads, kSearchCtasPerSm)
@@ -529,9 +358,10 @@ graph_search_kernel(const SearchKernelArgs a) {
   for (uint32_t i = tid; i < a.k; i += kSearchThreads) {
     const uint64_t key = queue[i];
     const bool empty = key == kMaxKey;
-    a.out_ids[qi * a.k + i] =
-        empty ? -1 : static_cast<int64_t>(static_cast<uint64_t>(skey_id(key)) * a.id_scale + a.id_offset);
-    a.out_dists[qi * a.k + i] = empty ? kFltMax : key_dist(key);
+    const uint64_t gid = static_cast<uint64_t>(skey_id(key)) * a.id_scale + a.id_offset;
+    if (a.out_ids) a.out_ids[qi * a.k + i] = empty ? -1 : static_cast<int64_t>(gid);
+    if (a.out_dists) a.out_dists[qi * a.k + i] = empty ? kFltMax : key_dist(key);
+    if (a.out_keys) a.out_keys[qi * a.k + i] = empty ? kMaxKey : ((key & 0xFFFFFFFF00000000ull) | gid);
   }
   if (a.stats && tid < 6) atomicAdd(&a.stats[tid], s_stats[tid]);
 }
@@ -571,7 +401,7 @@ __global__ void ts_window4_kernel(const uint64_t* __restrict__ ts, uint64_t n,
 // max(32, itopk/4) of its own (the class layer's rule, cagraIndexOpt.cu:441).
 int graph_search_impl(const grab_search_args* g) {
   GRAB_REQUIRE(g, "graph_search: null args");
-  GRAB_REQUIRE(g->d_dataset && g->d_graph && g->d_queries && g->d_out_ids && g->d_out_dists,
+  GRAB_REQUIRE(g->d_dataset && g->d_graph && g->d_queries && ((g->d_out_ids && g->d_out_dists) || g->d_out_keys),
                "graph_search: null pointer (the reference throws \"Graph is null!\", cagra_opt.cu:1123)");
   GRAB_REQUIRE(g->dim >= 4 && g->dim % 4 == 0, "graph_search: dim %u must be a multiple of 4", g->dim);
   GRAB_REQUIRE(g->n >= 1 && g->n < (1ull << 31), "graph_search: n must be in [1, 2^31)");
@@ -595,8 +425,10 @@ int graph_search_impl(const grab_search_args* g) {
   a.hash_bitlen = g->params.hash_bitlen;
   a.seeds = g->d_seeds; a.seeds_per_query = g->d_seeds ? g->seeds_per_query : 0;
   a.seed = g->seed; a.filter_kind = f.kind;
-  a.out_ids = g->d_out_ids; a.out_dists = g->d_out_dists;
+  a.out_ids = g->d_out_ids; a.out_dists = g->d_out_dists; a.out_keys = g->d_out_keys;
   a.id_scale = g->id_scale ? g->id_scale : 1; a.id_offset = g->id_offset;
+  GRAB_REQUIRE(!a.out_keys || (g->n - 1) * a.id_scale + a.id_offset < (1ull << 32),
+               "graph_search: d_out_keys holds 32-bit result ids, (n-1)*id_scale+id_offset does not fit");
   a.stats = reinterpret_cast<unsigned long long*>(g->d_stats);
 
   uint32_t itopk = g->k > g->params.itopk_size ? g->k : g->params.itopk_size;

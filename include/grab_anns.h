@@ -24,7 +24,7 @@
 extern "C" {
 #endif
 
-#define GRAB_ABI_VERSION 1
+#define GRAB_ABI_VERSION 2
 
 enum grab_status {
   GRAB_OK = 0,
@@ -129,7 +129,10 @@ int grab_exact_search_noalloc(const float* d_dataset, uint64_t n, uint32_t dim, 
 /* :375, :589).  itopk floor, seed-count and queue rules follow cagra_opt.cu:1108-1442.  */
 /* d_seeds [nq, seeds_per_query] uint32 or NULL (pseudo-random seeds inside the filter   */
 /* when the filter allows it).  id_scale/id_offset: result id = local*id_scale+id_offset */
-/* (striped shards; 1/0 for a single index).  d_stats may be NULL.                       */
+/* (striped shards; 1/0 for a single index).  d_stats may be NULL.  d_out_keys (optional, */
+/* [nq,k] uint64): the results once more as ascending keys [ordered fp32 distance : 32 |  */
+/* result id : 32] (all ones = empty) -- the form the sharded exchange step gathers; needs */
+/* result ids < 2^32.  With d_out_keys given, d_out_ids / d_out_dists may be NULL.         */
 /* ------------------------------------------------------------------------------------ */
 typedef struct grab_search_args {
   const float* d_dataset;
@@ -153,6 +156,7 @@ typedef struct grab_search_args {
   void* d_ws;
   size_t ws_bytes;
   void* stream;
+  uint64_t* d_out_keys;
 } grab_search_args;
 
 size_t grab_graph_search_workspace_bytes(uint64_t nq, uint32_t hash_bitlen);
@@ -300,6 +304,34 @@ int grab_merge_topk(const float* d_dists, const int64_t* d_ids, uint64_t nq, uin
                     uint32_t k, int64_t* d_out_ids, float* d_out_dists, void* stream);
 
 /* ------------------------------------------------------------------------------------ */
+/* Id-sharded multi-GPU search: one process per GPU, ids striped gid % G == rank, the same */
+/* queries on every rank, per-shard results exchanged with ONE all-gather and merged on the */
+/* device.  No reference counterpart (its device is fixed at compile time,                 */
+/* src/index/common.cuh:5-7).                                                             */
+/* grab_merge_sorted_keys: d_keys [parts, nq, run_length] ascending keys as written to       */
+/* grab_search_args.d_out_keys -> global top-k by (dist, id); a G-way merge by rank           */
+/* computation (no sort).  Missing results: id -1, dist 3.40282e38.                          */
+/* grab_comm_*: a communicator over NCCL (loaded at run time; GRAB_ERR_NCCL when it is        */
+/* missing or a call fails).  Rank 0 makes the unique id, the host passes it to every rank    */
+/* (any side channel), every rank calls grab_comm_create with its device current.             */
+/* grab_sharded_gather_merge: all-gather of this rank's [nq, run_length] keys into d_gather   */
+/* [world, nq, run_length] + the merge, both enqueued on `stream`; comm == NULL means one     */
+/* shard.  Every rank must call it with the same nq / run_length / k.                         */
+/* ------------------------------------------------------------------------------------ */
+int grab_merge_sorted_keys(const uint64_t* d_keys, uint64_t nq, uint32_t parts, uint32_t run_length,
+                           uint32_t k, int64_t* d_out_ids, float* d_out_dists, void* stream);
+#define GRAB_COMM_UNIQUE_ID_BYTES 128
+typedef struct grab_comm grab_comm;
+int grab_comm_unique_id(void* out, size_t bytes);
+int grab_comm_create(const void* unique_id, int world, int rank, grab_comm** out);
+int grab_comm_destroy(grab_comm* comm);
+int grab_comm_world(const grab_comm* comm);
+int grab_comm_rank(const grab_comm* comm);
+int grab_sharded_gather_merge(grab_comm* comm, const uint64_t* d_keys, uint64_t nq, uint32_t run_length,
+                              uint32_t k, uint64_t* d_gather, size_t gather_bytes, int64_t* d_out_ids,
+                              float* d_out_dists, void* stream);
+
+/* ------------------------------------------------------------------------------------ */
 /* Entry-point router: search seeds that pass the filter AND lie close to the query.     */
 /* Device version of the reference's host seed sampling (cagraIndexOpt.cu:441-511 for    */
 /* query_range, :313-336 for query_local; cagraIndex.cu:267-296) combined with the       */
@@ -341,6 +373,26 @@ size_t grab_route_seeds_workspace_bytes(uint64_t nq, uint32_t probes);
 int grab_route_seeds(const grab_router* router, const float* d_queries, uint64_t nq, uint64_t n,
                      const grab_filter* filter, uint32_t probes, uint32_t seeds_per_query, uint64_t seed,
                      uint32_t* d_seeds, void* d_ws, size_t ws_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------ */
+/* Device-level unit-test entry points for the search building blocks (not on the search */
+/* path).  They run the code of csrc/search_blocks.cuh as graph_search_kernel instantiates */
+/* it, so that the reference's own known-answer tests apply to it:                        */
+/* tests/test_bitonic.cu:73-156 and tests/test_sort_impl.cu:111-121 (warp sort == sorted   */
+/* input) and tests/test_hashmap.cu:144-187 (successful inserts == unique keys).          */
+/* ------------------------------------------------------------------------------------ */
+/* Per list (one warp each): the m sorted keys d_top[list] and ncand unsorted keys            */
+/* d_cand[list, 0..ncand) -> the m smallest of their union, ascending, in d_out[list].        */
+/* m: power of two in [64,1024].  variant 0 = the routine the search kernel picks for this m  */
+/* (registers for 64 and 128, shared memory above), 1 = the shared-memory routine.            */
+int grab_selftest_sort_merge(const uint64_t* d_top, const uint64_t* d_cand, uint64_t lists, uint32_t m,
+                             uint32_t ncand, uint32_t cand_stride, int variant, uint64_t* d_out,
+                             void* stream);
+/* One CTA of `threads` threads inserts d_keys[0..nkeys) concurrently into an empty visited     */
+/* table of 2^hash_bitlen slots (shared memory up to 2^13, as in the kernel); d_success[i] = 1  */
+/* when key i was new; d_table [2^hash_bitlen] receives the final table.                        */
+int grab_selftest_hash_insert(uint32_t* d_table, uint32_t hash_bitlen, const uint32_t* d_keys,
+                              uint32_t nkeys, uint32_t threads, uint32_t* d_success, void* stream);
 
 #ifdef __cplusplus
 }

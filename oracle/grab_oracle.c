@@ -732,9 +732,10 @@ void orc_insert_v1(uint32_t* graph, const int64_t* found, uint64_t num_existing,
 /* wang_hash slot choice (10% strong / 90% weak half for local; nearby third  */
 /* vs far part for remote by |bucket delta| <= 20).                           */
 /* ------------------------------------------------------------------------- */
-void orc_insert_opt(uint32_t* graph, const uint64_t* bucket, int64_t* local_knn, int64_t* global_knn,
-                    uint64_t num_existing, uint64_t num_new, uint64_t target_bucket,
-                    uint32_t total_deg, uint32_t local_deg, uint32_t k_local, uint32_t k_global) {
+/* Stage 1 (insert.cu:448-577): rows of the new nodes; used candidates are overwritten with -1. */
+void orc_insert_opt_fill(uint32_t* graph, const uint64_t* bucket, int64_t* local_knn, int64_t* global_knn,
+                         uint64_t num_existing, uint64_t num_new, uint32_t total_deg, uint32_t local_deg,
+                         uint32_t k_local, uint32_t k_global) {
   int max_remote = (int)(total_deg - local_deg);
   for (uint64_t t = 0; t < num_new; ++t) {
     uint64_t me = num_existing + t;
@@ -772,12 +773,18 @@ void orc_insert_opt(uint32_t* graph, const uint64_t* bucket, int64_t* local_knn,
       gc[i] = -1;
     }
   }
+}
+
+/* Stage 2 (insert.cu:579-640): mailboxes.  lcnt/rcnt [num_existing+num_new] hold the TRUE request
+ * counts; llist/rlist [.., local_deg/2] / [.., (total-local)/2] the first `max` senders in ascending
+ * (new id, column) order. */
+void orc_insert_opt_mailboxes(const uint32_t* graph, const uint64_t* bucket, uint64_t num_existing,
+                              uint64_t num_new, uint64_t target_bucket, uint32_t total_deg,
+                              uint32_t local_deg, uint32_t* lcnt, uint32_t* llist, uint32_t* rcnt,
+                              uint32_t* rlist) {
   uint32_t lmax = local_deg / 2, rmax = (total_deg - local_deg) / 2;
-  uint64_t ntot = num_existing + num_new;
-  uint32_t* lcnt = (uint32_t*)calloc(ntot, sizeof(uint32_t));
-  uint32_t* rcnt = (uint32_t*)calloc(ntot, sizeof(uint32_t));
-  uint32_t* llist = (uint32_t*)malloc(sizeof(uint32_t) * ntot * (lmax ? lmax : 1));
-  uint32_t* rlist = (uint32_t*)malloc(sizeof(uint32_t) * ntot * (rmax ? rmax : 1));
+  memset(lcnt, 0, sizeof(uint32_t) * (num_existing + num_new));
+  memset(rcnt, 0, sizeof(uint32_t) * (num_existing + num_new));
   for (uint64_t t = 0; t < num_new; ++t) {
     uint32_t src = (uint32_t)(num_existing + t);
     const uint32_t* nb = graph + (size_t)src * total_deg;
@@ -794,6 +801,13 @@ void orc_insert_opt(uint32_t* graph, const uint64_t* bucket, int64_t* local_knn,
       }
     }
   }
+}
+
+/* Stage 3 (insert.cu:653-765): every old node drains its local, then its remote mail. */
+void orc_insert_opt_apply(uint32_t* graph, const uint64_t* bucket, uint64_t num_existing,
+                          uint32_t total_deg, uint32_t local_deg, const uint32_t* lcnt,
+                          const uint32_t* llist, const uint32_t* rcnt, const uint32_t* rlist) {
+  uint32_t lmax = local_deg / 2, rmax = (total_deg - local_deg) / 2;
   for (uint64_t t = 0; t < num_existing; ++t) {
     uint32_t* row = graph + t * total_deg;
     uint32_t rng = wang_hash((uint32_t)t);
@@ -830,6 +844,22 @@ void orc_insert_opt(uint32_t* graph, const uint64_t* bucket, int64_t* local_knn,
       }
     }
   }
+}
+
+void orc_insert_opt(uint32_t* graph, const uint64_t* bucket, int64_t* local_knn, int64_t* global_knn,
+                    uint64_t num_existing, uint64_t num_new, uint64_t target_bucket,
+                    uint32_t total_deg, uint32_t local_deg, uint32_t k_local, uint32_t k_global) {
+  orc_insert_opt_fill(graph, bucket, local_knn, global_knn, num_existing, num_new, total_deg, local_deg,
+                      k_local, k_global);
+  uint32_t lmax = local_deg / 2, rmax = (total_deg - local_deg) / 2;
+  uint64_t ntot = num_existing + num_new;
+  uint32_t* lcnt = (uint32_t*)malloc(sizeof(uint32_t) * ntot);
+  uint32_t* rcnt = (uint32_t*)malloc(sizeof(uint32_t) * ntot);
+  uint32_t* llist = (uint32_t*)malloc(sizeof(uint32_t) * ntot * (lmax ? lmax : 1));
+  uint32_t* rlist = (uint32_t*)malloc(sizeof(uint32_t) * ntot * (rmax ? rmax : 1));
+  orc_insert_opt_mailboxes(graph, bucket, num_existing, num_new, target_bucket, total_deg, local_deg,
+                           lcnt, llist, rcnt, rlist);
+  orc_insert_opt_apply(graph, bucket, num_existing, total_deg, local_deg, lcnt, llist, rcnt, rlist);
   free(lcnt);
   free(rcnt);
   free(llist);

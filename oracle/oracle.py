@@ -181,6 +181,50 @@ def insert_opt(graph, bucket, local_knn, global_knn, num_existing, target_bucket
     return graph
 
 
+def insert_opt_fill(graph, bucket, local_knn, global_knn, num_existing, local_deg):
+    """Stage 1 of insert_opt alone: (graph with the new rows written, consumed local_knn, consumed global_knn)."""
+    graph = np.ascontiguousarray(graph, dtype=np.uint32).copy()
+    bucket = np.ascontiguousarray(bucket, dtype=np.uint64)
+    local_knn = np.ascontiguousarray(local_knn, dtype=np.int64).copy()
+    global_knn = np.ascontiguousarray(global_knn, dtype=np.int64).copy()
+    lib().orc_insert_opt_fill(_p(graph), _p(bucket), _p(local_knn), _p(global_knn), C.c_uint64(num_existing),
+                              C.c_uint64(local_knn.shape[0]), C.c_uint32(graph.shape[1]), C.c_uint32(local_deg),
+                              C.c_uint32(local_knn.shape[1]), C.c_uint32(global_knn.shape[1]))
+    return graph, local_knn, global_knn
+
+
+def insert_opt_mailboxes(graph, bucket, num_existing, target_bucket, local_deg):
+    """Stage 2: (local counts, local lists [n, local/2], remote counts, remote lists [n, remote/2]); counts are
+    the true request counts, lists keep the first `max` senders in ascending (new id, column) order; unused list
+    entries are 0xFFFFFFFF."""
+    graph = np.ascontiguousarray(graph, dtype=np.uint32)
+    bucket = np.ascontiguousarray(bucket, dtype=np.uint64)
+    n, total = graph.shape
+    lmax, rmax = local_deg // 2, (total - local_deg) // 2
+    lcnt, rcnt = np.zeros(n, dtype=np.uint32), np.zeros(n, dtype=np.uint32)
+    llist = np.full((n, max(lmax, 1)), 0xFFFFFFFF, dtype=np.uint32)
+    rlist = np.full((n, max(rmax, 1)), 0xFFFFFFFF, dtype=np.uint32)
+    lib().orc_insert_opt_mailboxes(_p(graph), _p(bucket), C.c_uint64(num_existing), C.c_uint64(n - num_existing),
+                                   C.c_uint64(target_bucket), C.c_uint32(total), C.c_uint32(local_deg), _p(lcnt),
+                                   _p(llist), _p(rcnt), _p(rlist))
+    return lcnt, llist[:, :lmax], rcnt, rlist[:, :rmax]
+
+
+def insert_opt_apply(graph, bucket, num_existing, local_deg, lcnt, llist, rcnt, rlist):
+    """Stage 3 on given mailboxes (lists [n, local/2] and [n, remote/2])."""
+    graph = np.ascontiguousarray(graph, dtype=np.uint32).copy()
+    bucket = np.ascontiguousarray(bucket, dtype=np.uint64)
+    lcnt, rcnt = np.ascontiguousarray(lcnt, dtype=np.uint32), np.ascontiguousarray(rcnt, dtype=np.uint32)
+    llist, rlist = np.ascontiguousarray(llist, dtype=np.uint32), np.ascontiguousarray(rlist, dtype=np.uint32)
+    if llist.size == 0:
+        llist = np.zeros(1, dtype=np.uint32)
+    if rlist.size == 0:
+        rlist = np.zeros(1, dtype=np.uint32)
+    lib().orc_insert_opt_apply(_p(graph), _p(bucket), C.c_uint64(num_existing), C.c_uint32(graph.shape[1]),
+                               C.c_uint32(local_deg), _p(lcnt), _p(llist), _p(rcnt), _p(rlist))
+    return graph
+
+
 def merge_topk(dists, ids, k):
     dists = _f32(dists)
     ids = np.ascontiguousarray(ids, dtype=np.int64)

@@ -1,5 +1,5 @@
-"""ctypes wrapper of oracle/_ref/libgrab_ref.so: the REFERENCE's own search kernels compiled for
-sm_100a from its sources (see oracle/Makefile, target `ref`).  Test infrastructure only."""
+"""ctypes wrapper of oracle/_ref/libgrab_ref.so: the REFERENCE's own search and insert kernels compiled
+for sm_100a from its sources (see oracle/Makefile, target `ref`).  Test infrastructure only."""
 from __future__ import annotations
 
 import ctypes as C
@@ -43,3 +43,94 @@ def search(mode, dataset, graph, queries, k, itopk, width, max_iter, hash_bitlen
     if rc != 0:
         raise RuntimeError(f"reference kernel harness returned {rc}")
     return ids.to(torch.int64), dists, ms.value
+
+
+def _check(rc, what):
+    if rc != 0:
+        raise RuntimeError(f"reference {what} returned {rc}")
+
+
+def _ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def update_topology_v1(graph, found, num_existing, search_k):
+    """update_topology_gpu_v1 (src/index/insert.cu:372-440) in place on `graph` (int32 CUDA tensor [n, deg] holding
+    uint32 bits); found int64 [num_new, search_k]."""
+    import torch
+    torch.cuda.synchronize()
+    _check(lib().ref_update_topology_v1(_ptr(graph), _ptr(found), C.c_uint64(num_existing),
+                                        C.c_uint64(found.shape[0]), C.c_uint32(graph.shape[1]),
+                                        C.c_uint32(search_k)), "update_topology_gpu_v1")
+
+
+def insert_opt_fill(graph, ts, local_knn, global_knn, num_existing, local_deg):
+    """fill_new_nodes_kernel_opt (insert.cu:448-577) in place; local candidates must be valid ids (the kernel
+    reads d_ts[candidate] before it tests the candidate's sign)."""
+    import torch
+    torch.cuda.synchronize()
+    _check(lib().ref_insert_opt_fill(_ptr(graph), _ptr(ts), _ptr(local_knn), _ptr(global_knn),
+                                     C.c_uint64(num_existing), C.c_uint64(local_knn.shape[0]),
+                                     C.c_uint32(graph.shape[1]), C.c_uint32(local_deg),
+                                     C.c_uint32(local_knn.shape[1]), C.c_uint32(global_knn.shape[1])), "fill kernel")
+
+
+def insert_opt_generate(graph, ts, num_existing, target_ts, local_deg):
+    """generate_update_requests_kernel_opt (insert.cu:579-640): returns (lcount, llist, rcount, rlist) CUDA tensors;
+    the order inside a list and, past the capacity, which senders were kept are an atomics race."""
+    import torch
+    n, total = graph.shape
+    lmax, rmax = local_deg // 2, (total - local_deg) // 2
+    dev = graph.device
+    lc = torch.zeros(n, dtype=torch.int32, device=dev)
+    rc = torch.zeros(n, dtype=torch.int32, device=dev)
+    ll = torch.full((n, max(lmax, 1)), -1, dtype=torch.int32, device=dev)
+    rl = torch.full((n, max(rmax, 1)), -1, dtype=torch.int32, device=dev)
+    torch.cuda.synchronize()
+    _check(lib().ref_insert_opt_generate(_ptr(graph), _ptr(lc), _ptr(ll), _ptr(rc), _ptr(rl),
+                                         C.c_uint64(num_existing), C.c_uint64(n - num_existing),
+                                         C.c_uint64(target_ts), _ptr(ts), C.c_uint32(total), C.c_uint32(local_deg)),
+           "generate kernel")
+    return lc, ll[:, :lmax], rc, rl[:, :rmax]
+
+
+def insert_opt_apply(graph, ts, num_existing, local_deg, lcount, llist, rcount, rlist):
+    """apply_topology_updates_kernel_opt (insert.cu:653-765) in place on `graph` with the given mailboxes
+    (lists contiguous [n, local/2] and [n, remote/2])."""
+    import torch
+    ll = llist.contiguous() if llist.numel() else torch.zeros(1, dtype=torch.int32, device=graph.device)
+    rl = rlist.contiguous() if rlist.numel() else torch.zeros(1, dtype=torch.int32, device=graph.device)
+    torch.cuda.synchronize()
+    _check(lib().ref_insert_opt_apply(_ptr(graph), _ptr(lcount), _ptr(ll), _ptr(rcount), _ptr(rl), _ptr(ts),
+                                      C.c_uint64(num_existing), C.c_uint32(graph.shape[1]), C.c_uint32(local_deg)),
+           "apply kernel")
+
+
+def update_topology_opt(graph, data, ts, local_knn, global_knn, num_existing, target_ts, local_deg):
+    """update_topology_gpu_opt (insert.cu:1398-1573) as the reference's insert calls it, in place."""
+    import torch
+    nn_, kl = local_knn.shape
+    kg = global_knn.shape[1]
+    ld = torch.zeros((nn_, kl), dtype=torch.float32, device=graph.device)
+    gd = torch.zeros((nn_, kg), dtype=torch.float32, device=graph.device)
+    torch.cuda.synchronize()
+    _check(lib().ref_update_topology_opt(_ptr(graph), _ptr(data), C.c_uint64(data.shape[1]), C.c_uint64(target_ts),
+                                         _ptr(ts), _ptr(local_knn), _ptr(ld), _ptr(global_knn), _ptr(gd),
+                                         C.c_uint64(num_existing), C.c_uint64(nn_), C.c_uint32(graph.shape[1]),
+                                         C.c_uint32(local_deg), C.c_uint32(kl), C.c_uint32(kg)),
+           "update_topology_gpu_opt")
+
+
+def find_near_nodes(data, num_existing, new, graph, search_k, itopk, width, max_iter, hash_bitlen):
+    """find_near_nodes (insert.cu:140-219): (ids int64 [num_new, search_k], exact dists ascending)."""
+    import torch
+    nn_ = new.shape[0]
+    ids = torch.empty((nn_, search_k), dtype=torch.int64, device=data.device)
+    dists = torch.empty((nn_, search_k), dtype=torch.float32, device=data.device)
+    torch.cuda.synchronize()
+    _check(lib().ref_find_near_nodes(_ptr(data), C.c_uint32(data.shape[1]), C.c_uint64(num_existing),
+                                     C.c_uint64(nn_), _ptr(new), _ptr(graph), C.c_uint32(graph.shape[1]),
+                                     C.c_uint32(search_k), C.c_uint32(itopk), C.c_uint32(width),
+                                     C.c_uint32(max_iter), C.c_uint32(hash_bitlen), _ptr(ids), _ptr(dists)),
+           "find_near_nodes")
+    return ids, dists

@@ -257,6 +257,32 @@ def test_merge_topk_bit_exact(grab, oracle):
     assert np.array_equal(gd.cpu().numpy(), od)
 
 
+def test_merge_sorted_keys_bit_exact(grab, oracle):
+    """grab_merge_sorted_keys (the G-way rank merge of the sharded exchange step) against the CPU merge: runs of
+    different fill, equal distances across shards (id tie-break), 1..8 shards, k below / equal / above the run
+    length, one query with no result at all."""
+    import torch
+    rng = np.random.default_rng(12)
+    for parts, kp, k, nq in [(8, 10, 10, 333), (2, 16, 10, 50), (4, 100, 100, 37), (1, 10, 10, 9), (8, 5, 10, 64),
+                             (3, 7, 20, 40)]:
+        d = np.sort(np.round(rng.random((parts, nq, kp)) * 40).astype(np.float32) / 8, axis=2)   # many ties
+        ids = rng.permutation(parts * nq * kp * 3)[: parts * nq * kp].reshape(parts, nq, kp).astype(np.int64)
+        fill = rng.integers(0, kp + 1, size=(parts, nq))
+        fill[:, 0] = 0                                            # query 0: every shard came back empty
+        empty = np.arange(kp)[None, None, :] >= fill[:, :, None]
+        f2o = lambda x: np.where(x.view(np.uint32) & 0x80000000, ~x.view(np.uint32), x.view(np.uint32) | 0x80000000)
+        keys = (f2o(d).astype(np.uint64) << np.uint64(32)) | ids.astype(np.uint64)
+        keys[empty] = np.uint64(0xFFFFFFFFFFFFFFFF)
+        keys = np.sort(keys, axis=2)                              # runs ascending by (dist, id)
+        dd = np.where(empty, np.float32(3.40282e38), d)
+        ii = np.where(empty, -1, ids)
+        oi, od = oracle.merge_topk(np.ascontiguousarray(dd.transpose(1, 0, 2)),
+                                   np.ascontiguousarray(ii.transpose(1, 0, 2)), k)
+        gi, gd = grab.merge_sorted_keys(_t(keys.view(np.int64)), k)
+        assert np.array_equal(gi.cpu().numpy(), oi), (parts, kp, k)
+        assert np.array_equal(gd.cpu().numpy(), od), (parts, kp, k)
+
+
 # ------------------------------------------------------------------ filtered graph search
 def _graph_fixture(oracle, n=20000, dim=64, deg=32, seed=31):
     data = clustered(n, dim, 40, 1.0, seed)
