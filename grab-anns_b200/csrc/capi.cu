@@ -88,6 +88,7 @@ int nearest_centroids_impl(const grab_router*, const float*, uint64_t, uint32_t,
 int merge_topk_impl(const float*, const int64_t*, uint64_t, uint32_t, uint32_t, int64_t*, float*,
                     cudaStream_t);
 int graph_search_impl(const grab_search_args*);
+int route_status_impl(const void*, cudaStream_t);
 int prune_device_impl(const uint32_t*, uint32_t*, uint64_t, uint32_t, uint32_t, uint8_t*, cudaStream_t);
 int reverse_device_impl(const uint32_t*, uint32_t*, uint32_t*, uint64_t, uint32_t, cudaStream_t);
 int merge_device_impl(uint32_t*, const uint32_t*, const uint32_t*, uint64_t, uint32_t, cudaStream_t);
@@ -505,6 +506,10 @@ int grab_route_seeds(const grab_router* router, const float* d_queries, uint64_t
                      uint32_t* d_seeds, void* d_ws, size_t ws_bytes, void* stream) {
   return route_seeds_impl(router, d_queries, nq, n, filter, probes, seeds_per_query, seed, d_seeds, d_ws, ws_bytes,
                           static_cast<cudaStream_t>(stream));
+}
+
+int grab_route_status(const void* d_ws, void* stream) {
+  return route_status_impl(d_ws, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

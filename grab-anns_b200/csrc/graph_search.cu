@@ -20,6 +20,9 @@
 //   * the visited table is cleared when half full and re-seeded from the current itopk
 //     (the reference: every 30 iterations, search.cu:692-697).
 // HBM/latency-bound by design: no tensor cores.
+#include <cstdlib>
+#include <cstring>
+
 #include "common.cuh"
 #include "search_blocks.cuh"
 
@@ -76,6 +79,7 @@ struct SearchKernelArgs {
   unsigned long long* stats;  // grab_search_stats as 6 x u64, or NULL
   uint32_t ckeys_cap;
   uint32_t cand_cap, sort_cap;  // survivor list capacity; sort_cap = itopk rounded up to a power of two
+  uint32_t inv_active_deg;      // ceil(2^32 / active_deg) (0 when active_deg == 1): e / active_deg = umulhi(e, inv)
 };
 
 template <int METRIC, int CPL>
@@ -366,6 +370,338 @@ graph_search_kernel(const SearchKernelArgs a) {
   if (a.stats && tid < 6) atomicAdd(&a.stats[tid], s_stats[tid]);
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Warp-split variant of the same search loop (lists of 64 or 128 entries, at most 128 candidates per warp and
+// iteration).  The two warps of a CTA no longer share a survivor list: each expands its own half of the
+// parents' edges, compacts its survivors by ballot (no shared counters), gathers THEIR vectors, keeps the keys
+// that beat the list's worst entry and sorts them in registers; then warp 0 folds both sorted runs into the
+// list and picks the next parents while the list is still in its registers.  Two block barriers per iteration
+// instead of five, no shared-memory atomics outside the visited set, and the merge work is split over both
+// warps.  Results are the same set the shared-list kernel finds whenever no candidate is dropped for capacity.
+// ---------------------------------------------------------------------------------------------------------
+#ifndef GRAB_SEARCH2_CTAS_PER_SM
+#define GRAB_SEARCH2_CTAS_PER_SM 14
+#endif
+
+template <int METRIC, int CPL, int R>
+__global__ void __launch_bounds__(kSearchThreads, GRAB_SEARCH2_CTAS_PER_SM)
+graph_search_split_kernel(const SearchKernelArgs a) {
+  static_assert(kSearchThreads == 64, "two warps per query");
+  constexpr uint32_t M = 32u * R;  // list length
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  uint64_t* queue = reinterpret_cast<uint64_t*>(smem_raw);                 // [M] sorted itopk list
+  uint64_t* wkeys = queue + M;                                             // [2][wcap] kept keys per warp
+  float* q_smem = reinterpret_cast<float*>(wkeys + 2 * a.ckeys_cap);       // [dim]
+  uint32_t* wcand = reinterpret_cast<uint32_t*>(q_smem + a.dim);           // [2][wcap] survivor ids per warp
+  uint32_t* parents = wcand + 2 * a.ckeys_cap;                             // [width]
+  uint32_t* hash = parents + ((a.width + 3) & ~3u);                        // [2^bitlen] (if local)
+  __shared__ uint32_t s_nparents, s_kept[2], s_inserted[2];
+
+  const uint64_t qi = blockIdx.x;
+  if (qi >= a.nq) return;
+  const uint32_t tid = threadIdx.x;
+  const uint32_t warp = tid >> 5, lane = tid & 31u;
+  const int lane8 = tid & (kTeam - 1);
+  const uint32_t wteam = lane / kTeam;  // team inside the warp, 0..3
+  const uint32_t wcap = a.ckeys_cap;
+  const uint32_t hsize = 1u << a.hash_bitlen;
+  if (a.global_hash) hash = a.global_hash + qi * hsize;
+  uint64_t* my_keys = wkeys + warp * wcap;
+  uint32_t* my_cand = wcand + warp * wcap;
+
+  for (uint32_t i = tid; i < a.dim / 4; i += kSearchThreads)
+    reinterpret_cast<float4*>(q_smem)[i] = __ldg(reinterpret_cast<const float4*>(a.queries + qi * a.dim) + i);
+  for (uint32_t i = tid; i < M; i += kSearchThreads) queue[i] = kMaxKey;
+  for (uint32_t i = tid; i < hsize / 4; i += kSearchThreads)
+    reinterpret_cast<uint4*>(hash)[i] = make_uint4(kInvalid, kInvalid, kInvalid, kInvalid);
+  if (tid == 0) s_nparents = 0;
+
+  uint64_t lo = 0, hi = 0;
+  uint32_t mask = 0;
+  if (a.filter_kind == GRAB_FILTER_TS_RANGE) {
+    lo = a.lo ? a.lo[qi] : a.lo1;
+    hi = a.hi ? a.hi[qi] : a.hi1;
+  } else if (a.filter_kind == GRAB_FILTER_LABELS) {
+    mask = a.masks ? a.masks[qi] : a.mask1;
+  }
+  uint32_t wbeg = 0, wend = 0;
+  const bool by_window = a.windows != nullptr && a.filter_kind == GRAB_FILTER_TS_RANGE;
+  if (a.windows) {
+    wbeg = a.windows[qi * 4];
+    wend = a.windows[qi * 4 + 1];
+    if (wend < wbeg) wend = wbeg;
+  }
+  auto passes = [&](uint32_t id) -> bool {
+    if (by_window) return id >= wbeg && id < wend;
+    if (a.filter_kind == GRAB_FILTER_TS_RANGE) {
+      const uint64_t t = __ldg(a.ts + id);
+      return t >= lo && t < hi;
+    }
+    if (a.filter_kind == GRAB_FILTER_LABELS) return (mask >> __ldg(a.labels + id)) & 1u;
+    return true;
+  };
+  const uint32_t lt_mask = (1u << lane) - 1u;
+  __syncthreads();
+
+  // ---- seeds (compute_distance.cuh:204-269): provided ids, else pseudo-random ids; every warp keeps its own ----
+  uint32_t ncand = 0;                     // warp-uniform: survivors in my_cand
+  uint32_t inserted_total = 0;            // warp-uniform: ids this warp put into the visited set since the last clear
+  unsigned long long st_edges = 0, st_dists = 0, st_seeds = 0;
+  {
+    const uint32_t wlen = wend - wbeg;
+    const bool generated_only = (a.seeds == nullptr);
+    const bool by_label_range = a.filter_kind == GRAB_FILTER_LABELS && a.label_offsets != nullptr && mask != 0;
+    const uint32_t nlab = __popc(mask);
+    const uint32_t attempts = (generated_only && !a.windows && !by_label_range && a.filter_kind != GRAB_FILTER_NONE &&
+                               a.filter_kind != GRAB_FILTER_PREFIX) ? 4 * a.num_seeds : a.num_seeds;
+    // every provided / window-drawn attempt may be taken; blind draws (4 attempts per seed) stop at the quota
+    const uint32_t my_quota = attempts == a.num_seeds ? wcap : (a.num_seeds + 1 - warp) / 2;
+    for (uint32_t i0 = 0; i0 < attempts; i0 += kSearchThreads) {
+      const uint32_t i = i0 + tid;
+      uint32_t id = kInvalid;
+      if (i < attempts) {
+        if (a.seeds && i < a.seeds_per_query) id = a.seeds[qi * a.seeds_per_query + i];
+        if (id >= a.n) {
+          if (a.windows) {
+            id = wlen ? wbeg + static_cast<uint32_t>(mix64(a.seed ^ (qi * 0x9e3779b97f4a7c15ull + i)) % wlen) : kInvalid;
+          } else if (by_label_range) {
+            uint32_t m = mask;
+            for (uint32_t skip = i % nlab; skip > 0; --skip) m &= m - 1;
+            const uint32_t lab = __ffs(m) - 1;
+            const uint32_t lb = a.label_offsets[lab], le = a.label_offsets[lab + 1];
+            id = le > lb ? lb + static_cast<uint32_t>(mix64(a.seed ^ (qi * 0x9e3779b97f4a7c15ull + i)) % (le - lb))
+                         : kInvalid;
+          } else {
+            id = static_cast<uint32_t>(((a.seed | 1ull) * static_cast<uint64_t>(i + 1)) % a.n);
+          }
+        }
+      }
+      const bool take = id < a.n && passes(id) && hash_insert(hash, a.hash_bitlen, id);
+      const uint32_t vote = __ballot_sync(0xFFFFFFFFu, take);
+      const uint32_t pos = ncand + __popc(vote & lt_mask);
+      if (take && pos < my_quota) my_cand[pos] = id;
+      ncand += __popc(vote);
+    }
+    inserted_total = ncand;
+    if (ncand > my_quota) ncand = my_quota;
+    st_seeds = ncand;
+  }
+  __syncwarp();
+
+  uint32_t iter = 0;
+  unsigned long long st_iters = 0, st_parents = 0, st_resets = 0;
+  for (;;) {
+    // ---- this warp's survivors: 4 teams, vectors gathered with 16-byte loads; a key is kept only if it beats
+    //      the current worst entry of the list ----
+    const uint64_t worst = queue[M - 1];
+    uint32_t nkeep = 0;  // warp-uniform
+    for (uint32_t j0 = 0; j0 < ncand; j0 += 4 * kSearchUnroll) {
+      uint32_t id[kSearchUnroll];
+      bool ok[kSearchUnroll];
+      float acc[kSearchUnroll];
+#pragma unroll
+      for (int u = 0; u < kSearchUnroll; ++u) {
+        const uint32_t j = j0 + u * 4 + wteam;
+        ok[u] = j < ncand;
+        id[u] = ok[u] ? my_cand[j] : 0;
+        acc[u] = 0.0f;
+      }
+      if (CPL > 0) {
+        float4 x[kSearchUnroll][CPL > 0 ? CPL : 1];
+#pragma unroll
+        for (int u = 0; u < kSearchUnroll; ++u)
+#pragma unroll
+          for (int c = 0; c < CPL; ++c)
+            if (ok[u]) x[u][c] = ldg_f4(a.data + static_cast<size_t>(id[u]) * a.dim + 4 * (lane8 + kTeam * c));
+#pragma unroll
+        for (int u = 0; u < kSearchUnroll; ++u)
+#pragma unroll
+          for (int c = 0; c < CPL; ++c)
+            if (ok[u])
+              acc[u] = accum4<METRIC>(acc[u], *reinterpret_cast<const float4*>(q_smem + 4 * (lane8 + kTeam * c)), x[u][c]);
+      } else {
+        const uint32_t nchunk = a.dim / 4;
+        for (uint32_t c0 = lane8; c0 < nchunk; c0 += 4 * kTeam) {
+          float4 x[kSearchUnroll][4];
+#pragma unroll
+          for (int u = 0; u < kSearchUnroll; ++u)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint32_t c = c0 + i * kTeam;
+              if (ok[u] && c < nchunk) x[u][i] = ldg_f4(a.data + static_cast<size_t>(id[u]) * a.dim + 4 * c);
+            }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t c = c0 + i * kTeam;
+            if (c < nchunk) {
+              const float4 qv = *reinterpret_cast<const float4*>(q_smem + 4 * c);
+#pragma unroll
+              for (int u = 0; u < kSearchUnroll; ++u)
+                if (ok[u]) acc[u] = accum4<METRIC>(acc[u], qv, x[u][i]);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kSearchUnroll; ++u) {
+        const float d = team_reduce<METRIC>(acc[u]);
+        const uint64_t key = make_skey(d, id[u]);
+        const bool keep = lane8 == 0 && ok[u] && key < worst;
+        const uint32_t vote = __ballot_sync(0xFFFFFFFFu, keep);
+        if (keep) my_keys[nkeep + __popc(vote & lt_mask)] = key;
+        nkeep += __popc(vote);
+      }
+    }
+    __syncwarp();
+    // ---- sort this warp's kept keys in registers ----
+    if (nkeep > 1) {
+      if (nkeep <= 32) warp_sort_regs<1>(my_keys, nkeep, lane);
+      else if (nkeep <= 64) warp_sort_regs<2>(my_keys, nkeep, lane);
+      else warp_sort_regs_128(my_keys, nkeep, lane);
+    }
+    if (lane == 0) {
+      s_kept[warp] = nkeep < M ? nkeep : M;
+      s_inserted[warp] = inserted_total;
+    }
+    __syncthreads();
+
+    // ---- warp 0: fold both runs into the list, pick up to `width` unexpanded parents, best first
+    //      (search.cu:38-107), while the list is in registers ----
+    const bool last = iter >= a.max_iter;
+    if (warp == 0) {
+      const uint32_t n0 = s_kept[0], n1 = s_kept[1];
+      uint64_t t[R];
+      if (n0 + n1 > 0) {
+        warp_merge_runs_regs<R>(queue, wkeys, n0, wkeys + wcap, n1, lane, t);
+      } else {
+#pragma unroll
+        for (int r = 0; r < R; ++r) t[r] = queue[lane + 32u * r];
+      }
+      uint32_t found = 0;
+      if (!last) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          const bool fresh = t[r] != kMaxKey && !skey_expanded(t[r]);
+          const uint32_t vote = __ballot_sync(0xFFFFFFFFu, fresh);
+          if (fresh && found < a.width) {
+            const uint32_t rank = found + __popc(vote & lt_mask);
+            if (rank < a.width) {
+              parents[rank] = skey_id(t[r]);
+              t[r] |= 1ull;
+            }
+          }
+          found += __popc(vote);
+        }
+        if (found > a.width) found = a.width;
+      }
+#pragma unroll
+      for (int r = 0; r < R; ++r) queue[lane + 32u * r] = t[r];
+      if (lane == 0) s_nparents = found;
+    }
+    __syncthreads();
+
+    // ---- visited table half full: clear and re-seed from the current list ----
+    if (s_inserted[0] + s_inserted[1] > hsize / 2) {  // uniform
+      for (uint32_t i = tid; i < hsize; i += kSearchThreads) hash[i] = kInvalid;
+      __syncthreads();
+      uint32_t kept = 0;
+      for (uint32_t i = tid; i < M; i += kSearchThreads) {
+        const uint64_t key = queue[i];
+        if (key != kMaxKey) { hash_insert(hash, a.hash_bitlen, skey_id(key)); ++kept; }
+      }
+      inserted_total = __reduce_add_sync(0xFFFFFFFFu, kept);
+      st_resets += (tid == 0);
+      __syncthreads();
+    }
+    const uint32_t nparents = s_nparents;
+    if (last || nparents == 0) break;
+
+    // ---- expand: flattened (parent, column) edges, thread t takes edges t, t+64, ...: neighbour id -> filter
+    //      -> visited set -> this warp's survivor list ----
+    ncand = 0;
+    const uint32_t total_edges = nparents * a.active_deg;
+    uint32_t my_edges = 0;
+    for (uint32_t e0 = 0; e0 < total_edges; e0 += 4 * kSearchThreads) {
+      uint32_t nbv[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const uint32_t e = e0 + u * kSearchThreads + tid;
+        nbv[u] = kInvalid;
+        if (e < total_edges) {
+          const uint32_t p = a.inv_active_deg ? __umulhi(e, a.inv_active_deg) : e;  // e / active_deg
+          const uint32_t col = e - p * a.active_deg;
+          nbv[u] = __ldg(a.graph + static_cast<size_t>(parents[p]) * a.deg + col);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const uint32_t nb = nbv[u];
+        const bool valid = nb < a.n;
+        my_edges += valid;
+        const bool take = valid && passes(nb) && hash_insert(hash, a.hash_bitlen, nb);
+        const uint32_t vote = __ballot_sync(0xFFFFFFFFu, take);
+        if (take) my_cand[ncand + __popc(vote & lt_mask)] = nb;
+        ncand += __popc(vote);
+      }
+    }
+    inserted_total += ncand;
+    st_dists += ncand;
+    st_edges += my_edges;
+    if (tid == 0) { st_iters += 1; st_parents += nparents; }
+    ++iter;
+    __syncwarp();
+  }
+
+  // ---- results: ascending (dist,id); id = local*scale + offset; empty slots are -1 ----
+  for (uint32_t i = tid; i < a.k; i += kSearchThreads) {
+    const uint64_t key = queue[i];
+    const bool empty = key == kMaxKey;
+    const uint64_t gid = static_cast<uint64_t>(skey_id(key)) * a.id_scale + a.id_offset;
+    if (a.out_ids) a.out_ids[qi * a.k + i] = empty ? -1 : static_cast<int64_t>(gid);
+    if (a.out_dists) a.out_dists[qi * a.k + i] = empty ? kFltMax : key_dist(key);
+    if (a.out_keys) a.out_keys[qi * a.k + i] = empty ? kMaxKey : ((key & 0xFFFFFFFF00000000ull) | gid);
+  }
+  if (a.stats) {
+    st_edges = __reduce_add_sync(0xFFFFFFFFu, static_cast<uint32_t>(st_edges));
+    if (lane == 0) {
+      atomicAdd(&a.stats[2], st_edges);
+      atomicAdd(&a.stats[3], st_dists);
+      atomicAdd(&a.stats[4], st_seeds);
+    }
+    if (tid == 0) {
+      atomicAdd(&a.stats[0], st_iters);
+      atomicAdd(&a.stats[1], st_parents);
+      atomicAdd(&a.stats[5], st_resets);
+    }
+  }
+}
+
+template <int METRIC, int R>
+static cudaError_t launch_search_split(const SearchKernelArgs& a, size_t smem, cudaStream_t st) {
+#define GRAB_SPLIT_LAUNCH(CPL)                                                                        \
+  do {                                                                                                \
+    cudaError_t e = cudaFuncSetAttribute(graph_search_split_kernel<METRIC, CPL, R>,                   \
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
+    if (e != cudaSuccess) return e;                                                                   \
+    graph_search_split_kernel<METRIC, CPL, R><<<(unsigned)a.nq, kSearchThreads, smem, st>>>(a);       \
+  } while (0)
+  if (a.dim == 96) GRAB_SPLIT_LAUNCH(3);
+  else if (a.dim == 128) GRAB_SPLIT_LAUNCH(4);
+  else GRAB_SPLIT_LAUNCH(0);
+#undef GRAB_SPLIT_LAUNCH
+  return cudaGetLastError();
+}
+
+// 0 = the shared-list kernel, 1 = the warp-split kernel where it applies (default).  GRAB_SEARCH_KERNEL=shared in
+// the environment selects the former for comparisons.
+static int search_kernel_choice() {
+  static const int choice = [] {
+    const char* v = getenv("GRAB_SEARCH_KERNEL");
+    return (v && strcmp(v, "shared") == 0) ? 0 : 1;
+  }();
+  return choice;
+}
+
 template <int METRIC>
 static cudaError_t launch_search(const SearchKernelArgs& a, size_t smem, cudaStream_t st) {
 #define GRAB_SEARCH_LAUNCH(CPL)                                                                   \
@@ -475,8 +811,22 @@ int graph_search_impl(const grab_search_args* g) {
 
   const bool local_hash = a.hash_bitlen <= 13;
   const size_t hash_bytes = sizeof(uint32_t) * (size_t(1) << a.hash_bitlen);
+  // warp-split kernel: lists of 64 / 128 entries, at most 128 candidates per warp and iteration
+  const uint32_t blind = (!g->d_seeds && !need_window && !(f.kind == GRAB_FILTER_LABELS && f.d_label_offsets) &&
+                          f.kind != GRAB_FILTER_NONE && f.kind != GRAB_FILTER_PREFIX) ? 1u : 0u;
+  const uint32_t warp_edges = (a.width * a.active_deg + kSearchThreads - 1) / kSearchThreads * 32;
+  const uint32_t warp_seeds = blind ? (nseeds + 1) / 2 : (nseeds + kSearchThreads - 1) / kSearchThreads * 32;
+  uint32_t wcap = next_pow2(warp_edges > warp_seeds ? warp_edges : warp_seeds);
+  if (wcap < 32) wcap = 32;
+  const bool split = search_kernel_choice() == 1 && (a.sort_cap == 64 || a.sort_cap == 128) && wcap <= 128;
+  a.inv_active_deg = a.active_deg > 1 ? static_cast<uint32_t>(((1ull << 32) + a.active_deg - 1) / a.active_deg) : 0;
   size_t smem = sizeof(uint64_t) * (a.sort_cap + a.ckeys_cap) + sizeof(float) * a.dim + sizeof(uint32_t) * a.cand_cap +
                 sizeof(uint32_t) * ((a.width + 3) & ~3u) + (local_hash ? hash_bytes : 0);
+  if (split) {
+    a.ckeys_cap = wcap;  // per-warp capacity of the kept-key and survivor lists
+    smem = sizeof(uint64_t) * (a.sort_cap + 2 * wcap) + sizeof(float) * a.dim + sizeof(uint32_t) * 2 * wcap +
+           sizeof(uint32_t) * ((a.width + 3) & ~3u) + (local_hash ? hash_bytes : 0);
+  }
   if (smem > 200 * 1024) {
     set_last_error("graph_search: itopk %u, width %u, degree %u, dim %u need %zu bytes of shared memory",
                    itopk, a.width, a.deg, a.dim, smem);
@@ -502,8 +852,16 @@ int graph_search_impl(const grab_search_args* g) {
   if (!local_hash)
     a.global_hash = reinterpret_cast<uint32_t*>(static_cast<char*>(ws) +
                                                 ((sizeof(uint32_t) * 4 * g->nq + 255) / 256) * 256);
-  cudaError_t e = g->metric == GRAB_METRIC_L2 ? launch_search<GRAB_METRIC_L2>(a, smem, st)
-                                              : launch_search<GRAB_METRIC_IP>(a, smem, st);
+  cudaError_t e;
+  if (split && a.sort_cap == 64)
+    e = g->metric == GRAB_METRIC_L2 ? launch_search_split<GRAB_METRIC_L2, 2>(a, smem, st)
+                                    : launch_search_split<GRAB_METRIC_IP, 2>(a, smem, st);
+  else if (split)
+    e = g->metric == GRAB_METRIC_L2 ? launch_search_split<GRAB_METRIC_L2, 4>(a, smem, st)
+                                    : launch_search_split<GRAB_METRIC_IP, 4>(a, smem, st);
+  else
+    e = g->metric == GRAB_METRIC_L2 ? launch_search<GRAB_METRIC_L2>(a, smem, st)
+                                    : launch_search<GRAB_METRIC_IP>(a, smem, st);
   GRAB_CUDA_TRY(e);
   if (own.ptr) GRAB_CUDA_TRY(cudaStreamSynchronize(st));
   return GRAB_OK;

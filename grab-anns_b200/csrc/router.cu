@@ -668,7 +668,8 @@ int route_seeds_impl(const grab_router* r, const float* d_queries, uint64_t nq, 
     set_last_error("route_seeds: workspace %zu < %zu bytes", ws_bytes, need);
     return GRAB_ERR_WORKSPACE;
   }
-  int* d_status = static_cast<int*>(ws);
+  int* d_status = static_cast<int*>(ws);   // word 0 of the workspace: GRAB_OK, or GRAB_ERR_TIMEOUT from a stalled pipeline
+  GRAB_CUDA_TRY(cudaMemsetAsync(d_status, 0, sizeof(int), st));
   uint64_t* d_keys = reinterpret_cast<uint64_t*>(static_cast<char*>(ws) + 256);
   const uint32_t T_tc = probes + 4 <= 16 ? probes + 4 : 16;
   a.queries = d_queries; a.cen = r->d_centroids; a.cnorm = r->d_centroid_norms; a.dim = r->dim; a.metric = r->metric;
@@ -679,7 +680,6 @@ int route_seeds_impl(const grab_router* r, const float* d_queries, uint64_t nq, 
     a.T = T_tc;
     a.rescore = 1;
     a.status = d_status;
-    GRAB_CUDA_TRY(cudaMemsetAsync(d_status, 0, sizeof(int), st));
     int rc = route_tc_launch(r->metric, d_queries, nq, r->dim, r->d_centroids, r->d_centroid_norms,
                              r->num_centroids, a.T, a.slices, d_keys, d_status, st);
     if (rc != GRAB_OK) return rc;
@@ -692,8 +692,27 @@ int route_seeds_impl(const grab_router* r, const float* d_queries, uint64_t nq, 
   a.keys = d_keys;
   route_seeds_kernel<<<static_cast<unsigned>((nq * 32 + 255) / 256), 256, 0, st>>>(a);
   GRAB_CUDA_TRY(cudaGetLastError());
-  if (own.ptr) GRAB_CUDA_TRY(cudaStreamSynchronize(st));
+  if (own.ptr) {
+    // the call owns its workspace and has to wait for it anyway: report a stalled tensor-core pipeline
+    // (all seeds of the batch were then written as "none") instead of returning degraded seeds silently
+    int status = 0;
+    GRAB_CUDA_TRY(cudaMemcpyAsync(&status, d_status, sizeof(int), cudaMemcpyDeviceToHost, st));
+    GRAB_CUDA_TRY(cudaStreamSynchronize(st));
+    if (status != GRAB_OK) {
+      set_last_error("route_seeds: the tensor-core centroid ranking gave up on a bounded wait");
+      return status == GRAB_ERR_TIMEOUT ? GRAB_ERR_TIMEOUT : GRAB_ERR_CUDA;
+    }
+  }
   return GRAB_OK;
+}
+
+int route_status_impl(const void* d_ws, cudaStream_t st) {
+  GRAB_REQUIRE(d_ws, "route_status: null workspace");
+  int status = 0;
+  GRAB_CUDA_TRY(cudaMemcpyAsync(&status, d_ws, sizeof(int), cudaMemcpyDeviceToHost, st));
+  GRAB_CUDA_TRY(cudaStreamSynchronize(st));
+  if (status != GRAB_OK) set_last_error("route_seeds: the tensor-core centroid ranking gave up on a bounded wait");
+  return status == GRAB_OK ? GRAB_OK : (status == GRAB_ERR_TIMEOUT ? GRAB_ERR_TIMEOUT : GRAB_ERR_CUDA);
 }
 
 int nearest_centroids_impl(const grab_router* r, const float* d_rows, uint64_t m, uint32_t probes, uint32_t* d_out,

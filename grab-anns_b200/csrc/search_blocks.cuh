@@ -142,6 +142,7 @@ struct RegBitonicSort<R, 0> {
 };
 
 template <int R> struct Log2Of32R;
+template <> struct Log2Of32R<1> { static constexpr int value = 5; };
 template <> struct Log2Of32R<2> { static constexpr int value = 6; };
 template <> struct Log2Of32R<4> { static constexpr int value = 7; };
 
@@ -178,6 +179,60 @@ __device__ __forceinline__ void warp_sort_merge_regs(uint64_t* top, const uint64
 static __device__ __noinline__ void warp_sort_merge_regs_128(uint64_t* top, const uint64_t* cand, uint32_t nkeep,
                                                       uint32_t lane) {
   warp_sort_merge_regs<4>(top, cand, nkeep, lane);
+}
+
+// ---------------------------------------------------------------------------------------
+// Two-stage variant used when every warp of the CTA collects its own candidates: each warp
+// sorts ITS kept keys in registers (warp_sort_regs), then one warp folds both sorted runs
+// into the sorted list (warp_merge_runs_regs).  Of two ascending runs a and b only the M
+// smallest of their union can enter a list of M entries; min(a[e], b[M-1-e]) for e < M is a
+// bitonic sequence that holds exactly those, so one merge level sorts it, and a second one
+// folds it into the list as above.
+// ---------------------------------------------------------------------------------------
+// Ascending in-place sort of keys[0, count), count <= 32*R, by one warp.
+template <int R>
+__device__ __forceinline__ void warp_sort_regs(uint64_t* keys, uint32_t count, uint32_t lane) {
+  uint64_t c[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const uint32_t e = lane + 32u * r;
+    c[r] = e < count ? keys[e] : kMaxKey;
+  }
+  RegBitonicSort<R, Log2Of32R<R>::value>::run(c, 32u * R, lane);
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const uint32_t e = lane + 32u * r;
+    if (e < count) keys[e] = c[r];
+  }
+}
+static __device__ __noinline__ void warp_sort_regs_128(uint64_t* keys, uint32_t count, uint32_t lane) {
+  warp_sort_regs<4>(keys, count, lane);
+}
+
+// top[0, 32*R) sorted; run0[0, n0) and run1[0, n1) ascending.  Leaves the 32*R smallest of the union,
+// sorted, in t (element e in register e/32 of lane e%32); the caller stores it.
+template <int R>
+__device__ __forceinline__ void warp_merge_runs_regs(const uint64_t* top, const uint64_t* run0, uint32_t n0,
+                                                     const uint64_t* run1, uint32_t n1, uint32_t lane,
+                                                     uint64_t (&t)[R]) {
+  constexpr uint32_t M = 32u * R;
+  constexpr int LOGM = Log2Of32R<R>::value;
+  uint64_t c[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const uint32_t e = lane + 32u * r;
+    const uint64_t a = e < n0 ? run0[e] : kMaxKey;
+    const uint64_t b = (M - 1 - e) < n1 ? run1[M - 1 - e] : kMaxKey;
+    c[r] = a < b ? a : b;
+    t[r] = top[e];
+  }
+  RegBitonicLevel<R, LOGM>::run(c, M, lane);
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const uint64_t partner = __shfl_sync(0xFFFFFFFFu, c[R - 1 - r], 31u - lane);  // element M-1-e
+    t[r] = partner < t[r] ? partner : t[r];
+  }
+  RegBitonicLevel<R, LOGM>::run(t, M, lane);
 }
 
 }  // namespace grab

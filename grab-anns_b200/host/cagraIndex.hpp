@@ -108,6 +108,7 @@ class CagraIndex {
   SearchParams search_params_, insert_params_;
   int metric_ = GRAB_METRIC_L2, knn_precision_ = GRAB_KNN_TC_SPLIT;
   uint64_t seed_ = 0x9E3779B97F4A7C15ull;
+  std::unique_ptr<grab::QueryArena, grab::QueryArenaDeleter> arena_;
   size_t insert_batch_ = 64;  // the reference's batch (src/cagraIndex.cu:165)
 };
 

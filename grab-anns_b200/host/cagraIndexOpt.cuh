@@ -91,6 +91,7 @@ class CagraIndexOpt {
   uint64_t bucket_width_ = 1;
   int metric_ = GRAB_METRIC_L2, knn_precision_ = GRAB_KNN_TC_SPLIT;
   uint64_t seed_ = 0x9E3779B97F4A7C15ull;
+  std::unique_ptr<grab::QueryArena, grab::QueryArenaDeleter> arena_;
   // the reference inserts 32 at a time (src/cagraIndexOpt.cu:590); the sparse mailboxes and the
   // exact kNN inside the batch make four-digit batches as good and far faster
   size_t insert_batch_ = 1024;

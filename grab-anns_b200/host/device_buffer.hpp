@@ -41,4 +41,8 @@ class DeviceBuffer {
   std::vector<std::pair<CUmemGenericAllocationHandle, size_t>> chunks_;
 };
 
+// Query scratch an index keeps across calls (defined with the classes, index_classes.cu).
+struct QueryArena;
+struct QueryArenaDeleter { void operator()(QueryArena*) const; };
+
 }  // namespace grab

@@ -56,38 +56,123 @@ grab_search_args make_args(const float* d_data, uint64_t n, uint32_t dim, int me
   return a;
 }
 
-// queries up, one filtered search, results down
-void run_search(grab_search_args a, const float* host_q, size_t nq, uint32_t dim, int k, const uint32_t* host_seeds,
-                size_t seeds_per_query, bool broadcast_seeds, int64_t* host_ids, float* host_dists,
-                const grab_router* router = nullptr, uint32_t probes = 0, uint32_t routed_seeds = 0) {
-  Scratch dq(nq * dim * sizeof(float)), di(nq * k * sizeof(int64_t)), dd(nq * k * sizeof(float));
-  cu(cudaMemcpy(dq.p, host_q, nq * dim * sizeof(float), cudaMemcpyHostToDevice), "H2D queries");
-  std::unique_ptr<Scratch> ds;
-  if (router && !(host_seeds && seeds_per_query)) {
-    // seeds from the entry-point router: members of the nearest centroids that pass the filter
-    ds.reset(new Scratch(nq * routed_seeds * sizeof(uint32_t)));
-    ok(grab_route_seeds(router, dq.as<float>(), nq, a.n, &a.filter, probes, routed_seeds, a.seed, ds->as<uint32_t>(),
-                        nullptr, 0, nullptr), "seed routing");
-    a.d_seeds = ds->as<uint32_t>();
-    a.seeds_per_query = routed_seeds;
-  } else if (host_seeds && seeds_per_query) {
-    ds.reset(new Scratch(nq * seeds_per_query * sizeof(uint32_t)));
-    if (broadcast_seeds) {
-      std::vector<uint32_t> all(nq * seeds_per_query);
-      for (size_t i = 0; i < nq; ++i) memcpy(all.data() + i * seeds_per_query, host_seeds, seeds_per_query * 4);
-      cu(cudaMemcpy(ds->p, all.data(), all.size() * 4, cudaMemcpyHostToDevice), "H2D seeds");
-    } else {
-      cu(cudaMemcpy(ds->p, host_seeds, nq * seeds_per_query * 4, cudaMemcpyHostToDevice), "H2D seeds");
+}  // namespace
+
+// Per-index query scratch that survives across calls (grow-only): device copies of the queries, per-query
+// ranges, seeds and results, the routing and search workspaces, and two streams.  The reference allocates and
+// frees all of this inside every query call (src/index/cagra_opt.cu:1136-1206: cudaMalloc / cudaFree plus two
+// device-wide synchronisations per call); here a query performs no allocation once the largest batch has been
+// seen.  Batches of 4096 queries and more are cut in two halves on two streams, so that the host-to-device copy
+// of the second half overlaps the search of the first and the result copy of the first the search of the
+// second.  One caller at a time per index (the mutex serialises others), as in the reference.
+namespace grab {
+struct QueryArena {
+  struct Buf {
+    void* p = nullptr;
+    size_t cap = 0;
+    void need(size_t bytes) {
+      if (bytes <= cap) return;
+      if (p) cudaFree(p);
+      p = nullptr;
+      cap = 0;
+      const size_t want = bytes + bytes / 4 + 256;
+      cu(cudaMalloc(&p, want), "cudaMalloc (query scratch)");
+      cap = want;
     }
-    a.d_seeds = ds->as<uint32_t>();
-    a.seeds_per_query = static_cast<uint32_t>(seeds_per_query);
+    ~Buf() { if (p) cudaFree(p); }
+    template <class T> T* as() { return static_cast<T*>(p); }
+  };
+  struct Slot {
+    cudaStream_t st = nullptr;
+    Buf q, lo, hi, ids, dists, seeds, search_ws, route_ws;
+    ~Slot() { if (st) cudaStreamDestroy(st); }
+  };
+  Slot slot[2];
+  std::mutex mu;
+};
+void QueryArenaDeleter::operator()(QueryArena* a) const { delete a; }
+}  // namespace grab
+
+namespace {
+
+grab::QueryArena& arena_of(std::unique_ptr<grab::QueryArena, grab::QueryArenaDeleter>& holder) {
+  if (!holder) holder.reset(new grab::QueryArena());
+  return *holder;
+}
+
+// queries up, one filtered search (routed seeds, caller's seeds, or the kernel's own draws), results down.
+// host_lo / host_hi: per-query ranges (NULL = the one range already in a.filter).
+void run_search(grab::QueryArena& A, grab_search_args a, const float* host_q, size_t nq, uint32_t dim, int k,
+                const uint32_t* host_seeds, size_t seeds_per_query, bool broadcast_seeds, const uint64_t* host_lo,
+                const uint64_t* host_hi, int64_t* host_ids, float* host_dists, const grab_router* router = nullptr,
+                uint32_t probes = 0, uint32_t routed_seeds = 0) {
+  std::lock_guard<std::mutex> lock(A.mu);
+  const bool own_seeds = host_seeds && seeds_per_query;
+  std::vector<uint32_t> expanded;
+  if (own_seeds && broadcast_seeds) {
+    expanded.resize(nq * seeds_per_query);
+    for (size_t i = 0; i < nq; ++i) memcpy(expanded.data() + i * seeds_per_query, host_seeds, seeds_per_query * 4);
+    host_seeds = expanded.data();
   }
-  a.d_queries = dq.as<float>();
-  a.d_out_ids = di.as<int64_t>();
-  a.d_out_dists = dd.as<float>();
-  ok(grab_graph_search(&a), "graph search");
-  cu(cudaMemcpy(host_ids, di.p, nq * k * sizeof(int64_t), cudaMemcpyDeviceToHost), "D2H ids");
-  cu(cudaMemcpy(host_dists, dd.p, nq * k * sizeof(float), cudaMemcpyDeviceToHost), "D2H dists");
+  const size_t chunks = nq >= 4096 ? 2 : 1;
+  const size_t per = (nq + chunks - 1) / chunks;
+  size_t count[2] = {0, 0};
+  for (size_t c = 0; c < chunks; ++c) {
+    grab::QueryArena::Slot& s = A.slot[c];
+    const size_t q0 = c * per, m = std::min(per, nq - q0);
+    count[c] = m;
+    if (!s.st) cu(cudaStreamCreateWithFlags(&s.st, cudaStreamNonBlocking), "cudaStreamCreate");
+    s.q.need(m * dim * sizeof(float));
+    s.ids.need(m * k * sizeof(int64_t));
+    s.dists.need(m * k * sizeof(float));
+    const size_t sws = grab_graph_search_workspace_bytes(m, a.params.hash_bitlen);
+    s.search_ws.need(sws);
+    cu(cudaMemcpyAsync(s.q.p, host_q + q0 * dim, m * dim * sizeof(float), cudaMemcpyHostToDevice, s.st), "H2D queries");
+    grab_search_args ac = a;
+    if (host_lo) {
+      s.lo.need(m * sizeof(uint64_t));
+      s.hi.need(m * sizeof(uint64_t));
+      cu(cudaMemcpyAsync(s.lo.p, host_lo + q0, m * sizeof(uint64_t), cudaMemcpyHostToDevice, s.st), "H2D range");
+      cu(cudaMemcpyAsync(s.hi.p, host_hi + q0, m * sizeof(uint64_t), cudaMemcpyHostToDevice, s.st), "H2D range");
+      ac.filter.d_lo = s.lo.as<uint64_t>();
+      ac.filter.d_hi = s.hi.as<uint64_t>();
+    }
+    ac.d_queries = s.q.as<float>();
+    ac.nq = m;
+    ac.d_out_ids = s.ids.as<int64_t>();
+    ac.d_out_dists = s.dists.as<float>();
+    ac.d_ws = s.search_ws.p;
+    ac.ws_bytes = sws;
+    ac.stream = s.st;
+    if (router && !own_seeds) {
+      // seeds from the entry-point router: members of the nearest centroids that pass the filter
+      const size_t rws = grab_route_seeds_workspace_bytes(m, probes);
+      s.route_ws.need(rws);
+      s.seeds.need(m * routed_seeds * sizeof(uint32_t));
+      ok(grab_route_seeds(router, s.q.as<float>(), m, a.n, &ac.filter, probes, routed_seeds, a.seed,
+                          s.seeds.as<uint32_t>(), s.route_ws.p, rws, s.st), "seed routing");
+      ac.d_seeds = s.seeds.as<uint32_t>();
+      ac.seeds_per_query = routed_seeds;
+    } else if (own_seeds) {
+      s.seeds.need(m * seeds_per_query * sizeof(uint32_t));
+      cu(cudaMemcpyAsync(s.seeds.p, host_seeds + q0 * seeds_per_query, m * seeds_per_query * 4, cudaMemcpyHostToDevice,
+                         s.st), "H2D seeds");
+      ac.d_seeds = s.seeds.as<uint32_t>();
+      ac.seeds_per_query = static_cast<uint32_t>(seeds_per_query);
+    }
+    ok(grab_graph_search(&ac), "graph search");
+  }
+  for (size_t c = 0; c < chunks; ++c) {
+    grab::QueryArena::Slot& s = A.slot[c];
+    const size_t q0 = c * per, m = count[c];
+    cu(cudaMemcpyAsync(host_ids + q0 * k, s.ids.p, m * k * sizeof(int64_t), cudaMemcpyDeviceToHost, s.st), "D2H ids");
+    cu(cudaMemcpyAsync(host_dists + q0 * k, s.dists.p, m * k * sizeof(float), cudaMemcpyDeviceToHost, s.st),
+       "D2H dists");
+  }
+  for (size_t c = 0; c < chunks; ++c) {
+    cu(cudaStreamSynchronize(A.slot[c].st), "query stream");
+    if (router && !own_seeds) ok(grab_route_status(A.slot[c].route_ws.p, A.slot[c].st), "seed routing");
+  }
 }
 
 void fill_no_data(int64_t* ids, float* dists, size_t count) {  // src/cagraIndexOpt.cu:341-347, 479-485
@@ -197,7 +282,8 @@ void CagraIndex::query(const float* host_queries, size_t num_queries, int k, int
                                  static_cast<uint32_t*>(d_graph_->data()), graph_degree_, nullptr, num_queries, k,
                                  search_params_, nullptr, nullptr, seed_);
   a.filter.kind = GRAB_FILTER_NONE;
-  run_search(a, host_queries, num_queries, dim_, k, seeds, num_seeds_per_query, false, host_indices, host_dists);
+  run_search(arena_of(arena_), a, host_queries, num_queries, dim_, k, seeds, num_seeds_per_query, false, nullptr,
+             nullptr, host_indices, host_dists);
 }
 
 void CagraIndex::query_range(const float* host_queries, size_t num_queries, int k, float range_radius, uint64_t start_ts,
@@ -226,8 +312,8 @@ void CagraIndex::query_range(const float* host_queries, size_t num_queries, int 
     sampled = sample_ids(in_range, search_params_.itopk_size, seed_);
     if (sampled.empty()) { fill_no_data(host_indices, host_dists, num_queries * k); return; }
   }
-  run_search(a, host_queries, num_queries, dim_, k, sampled.empty() ? nullptr : sampled.data(), sampled.size(), true,
-             host_indices, host_dists);
+  run_search(arena_of(arena_), a, host_queries, num_queries, dim_, k, sampled.empty() ? nullptr : sampled.data(),
+             sampled.size(), true, nullptr, nullptr, host_indices, host_dists);
 }
 
 void CagraIndex::save(const std::string& filepath) {  // src/cagraIndex.cu:352-368: dim, degree, size, data, graph
@@ -401,8 +487,8 @@ void CagraIndexOpt::query(const float* host_queries, size_t num_queries, int k, 
                                  static_cast<uint32_t*>(d_graph_->data()), graph_degree_, nullptr, num_queries, k,
                                  search_params_, nullptr, nullptr, seed_);
   a.filter.kind = GRAB_FILTER_NONE;
-  run_search(a, host_queries, num_queries, dim_, k, seeds, num_seeds_per_query, false, host_indices, host_dists,
-             ensure_router(), router_probes_, router_seeds_);
+  run_search(arena_of(arena_), a, host_queries, num_queries, dim_, k, seeds, num_seeds_per_query, false, nullptr,
+             nullptr, host_indices, host_dists, ensure_router(), router_probes_, router_seeds_);
 }
 
 void CagraIndexOpt::query_local(const float* host_queries, size_t num_queries, int k, uint64_t target_timestamp,
@@ -421,7 +507,8 @@ void CagraIndexOpt::query_local(const float* host_queries, size_t num_queries, i
                                  search_params_, nullptr, nullptr, seed_);
   a.filter.kind = GRAB_FILTER_PREFIX;
   a.filter.active_degree = static_cast<uint32_t>(local_degree_);
-  run_search(a, host_queries, num_queries, dim_, k, seeds.data(), seeds.size(), true, host_indices, host_dists);
+  run_search(arena_of(arena_), a, host_queries, num_queries, dim_, k, seeds.data(), seeds.size(), true, nullptr,
+             nullptr, host_indices, host_dists);
 }
 
 void CagraIndexOpt::range_search(const float* host_queries, size_t nq, int k, const uint64_t* lo, const uint64_t* hi,
@@ -432,15 +519,7 @@ void CagraIndexOpt::range_search(const float* host_queries, size_t nq, int k, co
   a.filter.kind = GRAB_FILTER_TS_RANGE;
   a.filter.d_ts = static_cast<uint64_t*>(d_ts_->data());
   a.filter.ts_sorted = ts_sorted_;
-  std::unique_ptr<Scratch> dlo, dhi;
-  if (lo) {
-    dlo.reset(new Scratch(nq * sizeof(uint64_t)));
-    dhi.reset(new Scratch(nq * sizeof(uint64_t)));
-    cu(cudaMemcpy(dlo->p, lo, nq * sizeof(uint64_t), cudaMemcpyHostToDevice), "H2D range");
-    cu(cudaMemcpy(dhi->p, hi, nq * sizeof(uint64_t), cudaMemcpyHostToDevice), "H2D range");
-    a.filter.d_lo = dlo->as<uint64_t>();
-    a.filter.d_hi = dhi->as<uint64_t>();
-  } else {
+  if (!lo) {
     a.filter.lo = lo1;
     a.filter.hi = hi1;
   }
@@ -477,8 +556,8 @@ void CagraIndexOpt::range_search(const float* host_queries, size_t nq, int k, co
       seeds = sample_range(lo1, hi1, 0);
     }
   }
-  run_search(a, host_queries, nq, dim_, k, seeds.empty() ? nullptr : seeds.data(), spq, broadcast, ids, dists,
-             router, router_probes_, router_seeds_);
+  run_search(arena_of(arena_), a, host_queries, nq, dim_, k, seeds.empty() ? nullptr : seeds.data(), spq, broadcast,
+             lo, hi, ids, dists, router, router_probes_, router_seeds_);
 }
 
 void CagraIndexOpt::query_range(const float* host_queries, size_t num_queries, int k, uint64_t start_bucket,

@@ -373,6 +373,12 @@ size_t grab_route_seeds_workspace_bytes(uint64_t nq, uint32_t probes);
 int grab_route_seeds(const grab_router* router, const float* d_queries, uint64_t nq, uint64_t n,
                      const grab_filter* filter, uint32_t probes, uint32_t seeds_per_query, uint64_t seed,
                      uint32_t* d_seeds, void* d_ws, size_t ws_bytes, void* stream);
+/* Outcome of the last grab_route_seeds that used the caller's workspace d_ws (the call itself only
+ * enqueues work): waits for `stream`, reads the status word at offset 0 of the workspace and returns
+ * GRAB_OK, or GRAB_ERR_TIMEOUT when the tensor-core centroid ranking gave up on a bounded wait (every
+ * seed of that batch was then written as 0xFFFFFFFF and the search fell back to its own draws).  A call
+ * without a workspace reports the same through its own return value. */
+int grab_route_status(const void* d_ws, void* stream);
 
 /* ------------------------------------------------------------------------------------ */
 /* Device-level unit-test entry points for the search building blocks (not on the search */
