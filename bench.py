@@ -89,6 +89,10 @@ def parse():
     ap.add_argument("--shard-probes", type=int, default=0, help="per-shard probes (0 = as the single index)")
     ap.add_argument("--insert-batches", type=int, default=10, help="C4: number of insert batches")
     ap.add_argument("--insert-batch-size", type=int, default=0, help="C4: vectors per class-internal batch (0 = default)")
+    ap.add_argument("--insert-reference-rules", action="store_true",
+                    help="C4: the reference's insert rules (random seeds, pseudo-random reverse-edge slots) instead of "
+                         "routed inserts with the distance-aware repair")
+    ap.add_argument("--insert-iters", type=int, default=0, help="C4: iterations of the routed insert searches (0 = 16)")
     a = ap.parse_args()
     return a
 
@@ -717,49 +721,47 @@ def sharded_record(args, grab, torch, dist, w, rank, world, steps, warmup, d_bas
     lo_i, hi_i = w["lo"][:, None].astype(np.int64), w["hi"][:, None].astype(np.int64)
     in_range = bool(np.all(((res >= lo_i) & (res < hi_i)) | (res < 0)))
 
-    count = [0]
+    class CudaSync:
+        """Stream / event operations of sharded.run_pipelined on this device."""
 
-    def pipelined_step():
-        s = sets[count[0] % 2]
-        count[0] += 1
-        main = torch.cuda.current_stream()
-        if s.used:
-            main.wait_event(s.ev_merged)       # the exchange that read this set's keys has finished
-        s.step(d_q, flt, keys_only=True)
-        s.ev_search.record(main)
-        with torch.cuda.stream(s_comm):
-            s_comm.wait_event(s.ev_search)
-            exchange(s)
-            s.ev_merged.record(s_comm)
-        s.used = True
+        def searched(self, i):
+            sets[i].ev_search.record(torch.cuda.current_stream())
 
-    def drain():
-        main = torch.cuda.current_stream()
-        for s in sets:
-            if s.used:
-                main.wait_event(s.ev_merged)
+        def wait_exchanged(self, i):
+            torch.cuda.current_stream().wait_event(sets[i].ev_merged)   # the exchange that read this set has finished
+
+        def on_exchange_stream(self, fn, i):
+            with torch.cuda.stream(s_comm):
+                s_comm.wait_event(sets[i].ev_search)
+                fn(i)
+                sets[i].ev_merged.record(s_comm)
+            sets[i].used = True
+
+        def drain(self):
+            main = torch.cuda.current_stream()
+            for s in sets:
+                if s.used:
+                    main.wait_event(s.ev_merged)
+
+        def begin(self):
+            torch.cuda.synchronize()
+            self.a, self.b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            self.a.record()
+
+        def end(self):
+            self.b.record()
+            torch.cuda.synchronize()
+            return self.a.elapsed_time(self.b)
 
     def timed_pipeline():
-        for _ in range(warmup):
-            pipelined_step()
-        drain()
-        torch.cuda.synchronize()
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(steps):
-            pipelined_step()
-        drain()
-        b.record()
-        torch.cuda.synchronize()
-        if dist is not None:
-            dist.barrier()
-        t = torch.tensor([a.elapsed_time(b)], device="cuda", dtype=torch.float64)
+        sharded_mod = importlib.import_module("grab-anns_b200.sharded")
+        ms = sharded_mod.run_pipelined(2, steps, warmup, lambda i: sets[i].step(d_q, flt, keys_only=True),
+                                       lambda i: exchange(sets[i]), CudaSync(),
+                                       barrier=(dist.barrier if dist is not None else None))
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
         if dist is not None:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item()) / steps
+        return float(t.item())
 
     def serial_step():
         s0.step(d_q, flt, keys_only=True)
@@ -894,6 +896,10 @@ def run_c4(args):
                              knn_precision=2, **kw)
     ix.set_query_params(args.itopk, args.width, 0, args.max_iter, args.hash_bitlen)
     ix.set_router(args.router_centroids, args.probes, args.seeds)
+    if args.insert_reference_rules:
+        ix.set_insert_mode(routed=False, repair_by_distance=False)
+    if args.insert_iters:
+        ix.set_insert_search_params(128, 4, args.insert_iters, 12)
     t0 = time.perf_counter()
     ix.add(w["base"], w["ts"])
     ix.build()
@@ -945,7 +951,11 @@ def run_c4(args):
             "config": {"workload": f"C4: {n0}x{dim} fp32 + {nb} x {batch_n} inserts, 10 000 range queries over the "
                                    f"newest 20 % after each batch, k {k}, degree {deg}",
                        "itopk": args.itopk, "search_width": args.width, "max_iterations": args.max_iter,
-                       "router_centroids": args.router_centroids, "probes": args.probes, "routed_seeds": args.seeds},
+                       "router_centroids": args.router_centroids, "probes": args.probes, "routed_seeds": args.seeds,
+                       "insert_rules": "reference (random seeds, pseudo-random reverse-edge slots)"
+                                       if args.insert_reference_rules else
+                                       "routed insert searches, distance-aware reverse-edge repair",
+                       "insert_batch": args.insert_batch_size or 4096},
             "build": {"seconds": build_s, "mvec_per_s": n0 / build_s / 1e6},
             "batches": per_batch,
             "recall_min": min(p["recall_at_10_newest_20pct"] for p in per_batch),

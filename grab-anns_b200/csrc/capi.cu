@@ -73,6 +73,16 @@ void* pool_get(int slot, size_t bytes, bool zeroed) {
   return e.ptr;
 }
 
+void pool_drop(int slot) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return;
+  std::lock_guard<std::mutex> lock(g_pool_mutex);
+  PoolEntry& e = g_pool[dev][slot];
+  if (e.ptr) cudaFree(e.ptr);
+  e.ptr = nullptr;
+  e.bytes = 0;
+}
+
 // implemented in the kernel translation units
 int exact_search_impl(const float*, uint64_t, uint32_t, int, const grab_filter*, const float*, uint64_t,
                       uint32_t, int64_t*, float*, void*, size_t, cudaStream_t);
@@ -97,7 +107,8 @@ int remote_edges_impl(uint32_t*, const uint64_t*, uint32_t*, uint64_t, uint32_t,
 int inject_reverse_impl(uint32_t*, uint64_t, uint32_t, uint32_t, uint32_t, cudaStream_t);
 int update_topology_v1_impl(uint32_t*, const int64_t*, uint64_t, uint64_t, uint32_t, uint32_t, cudaStream_t);
 int update_topology_opt_impl(uint32_t*, const uint64_t*, int64_t*, int64_t*, uint64_t, uint64_t, uint64_t,
-                             uint32_t, uint32_t, uint32_t, uint32_t, cudaStream_t);
+                             uint32_t, uint32_t, uint32_t, uint32_t, cudaStream_t, const float* = nullptr, uint32_t = 0,
+                             int = 0, bool = true);
 
 #define GRAB_TRY(expr)            \
   do {                            \

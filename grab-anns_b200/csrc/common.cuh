@@ -209,9 +209,24 @@ struct StageTimer {
 enum PoolSlot {
   kPoolMailCountsL = 0, kPoolMailCountsR, kPoolMailCursor, kPoolMailOffsets, kPoolMailTouched, kPoolMailCsr,
   kPoolMailMeta, kPoolInsIdsG, kPoolInsDistG, kPoolInsIdsL, kPoolInsDistL, kPoolInsBatchIds, kPoolInsBatchDist,
-  kPoolSearchWs, kPoolSlots
+  kPoolSearchWs, kPoolSearchWs2, kPoolRouteWs, kPoolRouteWs2, kPoolInsSeedsG, kPoolInsSeedsL, kPoolSlots
 };
 void* pool_get(int slot, size_t bytes, bool zeroed);
+// Frees a slot so that its next pool_get allocates (and, for zeroed slots, clears) it afresh: for error paths
+// that may leave a "zero between batches" slot dirty.
+void pool_drop(int slot);
+
+// What the time-partitioned insert may be told beyond the reference's arguments (NULL = the reference's behaviour:
+// self-drawn seeds for the global search, the caller's seed list for the bucket search, the reference's slot rule
+// for the reverse edges, device synchronisation before returning).
+struct InsertOptions {
+  const grab_router* router = nullptr;  // seeds of both searches from the entry-point router (old nodes only)
+  uint32_t probes = 2, routed_seeds = 32;
+  bool bucket_has_old_members = false;  // with a router: whether the bucket search can be seeded at all
+  bool repair_by_distance = false;      // reverse edges replace the farthest neighbour instead of a random slot
+  bool sync = true;                     // false: only enqueue on `stream`
+  cudaStream_t stream = nullptr;
+};
 
 // Scratch allocation used by the stateless entry points when the caller passes no
 // workspace: plain cudaMalloc, released on scope exit.

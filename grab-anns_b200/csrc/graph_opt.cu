@@ -835,16 +835,129 @@ mail_apply_kernel(uint32_t* __restrict__ graph, const uint64_t* __restrict__ buc
   }
 }
 
+// Distance-aware reverse-edge repair (an alternative to the reference's rule above, which overwrites a
+// pseudo-random slot -- 10 % strong half / 90 % weak half, insert.cu:693-712 -- whether or not the new node is any
+// closer than the neighbour it evicts; over many batches that erodes the rows of old nodes and recall drifts).
+// One warp per touched node t and column region [c0, c1): distances from t to the region's current neighbours and
+// to every new node that asked to be linked (up to 256 requests), then the requests are taken nearest first and
+// each replaces the FARTHEST current neighbour as long as it is closer than that one.  Empty slots count as
+// infinitely far, a request already present is skipped.  Ties go to the lower id / lower slot, so the result does
+// not depend on the order in which the requests were posted.
+constexpr int kRepairMaxRegion = 256;
+constexpr int kRepairMaxReq = 256;
+
+template <int METRIC, int REMOTE>
+__global__ void __launch_bounds__(kSelWarps * 32)
+mail_apply_dist_kernel(uint32_t* __restrict__ graph, const float* __restrict__ data, uint32_t dim,
+                       const uint32_t* __restrict__ touched, const MailMeta* __restrict__ meta,
+                       uint32_t* __restrict__ counts, const uint32_t* __restrict__ offsets,
+                       uint32_t* __restrict__ cursor, const uint64_t* __restrict__ csr, uint32_t c0, uint32_t c1,
+                       uint32_t total_deg) {
+  __shared__ float s_rowd[kSelWarps][kRepairMaxRegion];
+  __shared__ float s_reqd[kSelWarps][kRepairMaxReq];
+  __shared__ uint32_t s_req[kSelWarps][kRepairMaxReq];
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t i = blockIdx.x * kSelWarps + warp;
+  if (i >= meta->n_touched) return;
+  const uint32_t t = touched[i];
+  const uint32_t len = counts[t];
+  const uint64_t* seg = csr + offsets[t];
+  uint32_t* row = graph + static_cast<size_t>(t) * total_deg + c0;
+  const uint32_t rlen = c1 - c0;
+  const uint32_t nreq = len < kRepairMaxReq ? len : kRepairMaxReq;
+  float* rowd = s_rowd[warp];
+  float* reqd = s_reqd[warp];
+  uint32_t* req = s_req[warp];
+  for (uint32_t j = lane; j < nreq; j += 32) req[j] = static_cast<uint32_t>(seg[j] >> 32);
+  __syncwarp();
+  // distances: items [0, rlen) are the row's slots, [rlen, rlen + nreq) the requests; four teams of 8 lanes
+  const int lane8 = lane & (kTeam - 1);
+  const uint32_t team = lane / kTeam;
+  const uint32_t nchunk = dim / 4;
+  const float* vt = data + static_cast<size_t>(t) * dim;
+  for (uint32_t it0 = 0; it0 < rlen + nreq; it0 += 4) {
+    const uint32_t it = it0 + team;
+    uint32_t id = kInvalid;
+    if (it < rlen) id = row[it];
+    else if (it < rlen + nreq) id = req[it - rlen];
+    const bool valid = id != kInvalid;
+    float acc = 0.0f;
+    if (valid) {
+      const float* vx = data + static_cast<size_t>(id) * dim;
+      for (uint32_t c = lane8; c < nchunk; c += kTeam) acc = accum4<METRIC>(acc, ldg_f4(vt + 4 * c), ldg_f4(vx + 4 * c));
+    }
+    const float d = team_reduce<METRIC>(acc);
+    if (lane8 == 0) {
+      if (it < rlen) rowd[it] = valid ? d : kFltMax;
+      else if (it < rlen + nreq) reqd[it - rlen] = d;
+    }
+  }
+  __syncwarp();
+  // a request that is already a neighbour in this region, or a second copy of a request, is dropped
+  for (uint32_t j = lane; j < nreq; j += 32) {
+    const uint32_t src = req[j];
+    bool dup = false;
+    for (uint32_t x = 0; x < rlen; ++x) dup |= (row[x] == src);
+    for (uint32_t x = 0; x < j; ++x) dup |= (req[x] == src);
+    if (dup) reqd[j] = kFltMax;
+  }
+  __syncwarp();
+  for (uint32_t round = 0; round < nreq; ++round) {
+    // nearest remaining request, by (distance, id)
+    uint64_t best = kMaxKey;
+    uint32_t best_j = 0;
+    for (uint32_t j = lane; j < nreq; j += 32) {
+      const float d = reqd[j];
+      if (d < kFltMax) {
+        const uint64_t key = make_key(d, req[j]);
+        if (key < best) { best = key; best_j = j; }
+      }
+    }
+    for (int off = 16; off > 0; off >>= 1) {
+      const uint64_t ok = __shfl_xor_sync(0xFFFFFFFFu, best, off);
+      const uint32_t oj = __shfl_xor_sync(0xFFFFFFFFu, best_j, off);
+      if (ok < best) { best = ok; best_j = oj; }
+    }
+    if (best == kMaxKey) break;
+    // farthest current neighbour of the region, by (distance, slot) descending
+    uint64_t worst = 0;
+    for (uint32_t x = lane; x < rlen; x += 32) {
+      const uint64_t key = (static_cast<uint64_t>(float_to_ordered(rowd[x])) << 32) | (rlen - 1 - x);
+      if (key >= worst) worst = key;
+    }
+    for (int off = 16; off > 0; off >>= 1) {
+      const uint64_t ow = __shfl_xor_sync(0xFFFFFFFFu, worst, off);
+      if (ow > worst) worst = ow;
+    }
+    const uint32_t slot = rlen - 1 - static_cast<uint32_t>(worst & 0xFFFFFFFFull);
+    const float dnew = key_dist(best);
+    if (!(float_to_ordered(dnew) < static_cast<uint32_t>(worst >> 32))) break;  // every remaining request is farther still
+    if (lane == 0) {
+      row[slot] = key_id(best);
+      rowd[slot] = dnew;
+      reqd[best_j] = kFltMax;
+    }
+    __syncwarp();
+  }
+  if (lane == 0) {
+    cursor[t] = 0;
+    if (REMOTE) counts[t] = 0;
+  }
+}
+
 __global__ void mail_clear_kernel(const uint32_t* __restrict__ touched, const MailMeta* __restrict__ meta,
                                   uint32_t* __restrict__ counts) {
   const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < meta->n_touched) counts[touched[i]] = 0;
 }
 
+// d_dataset == NULL: the reference's slot rule.  Otherwise the distance-aware repair (regions of up to 256 columns).
+// sync: wait for the stream before returning (the stateless entry points do, the batched class insert does not).
 int update_topology_opt_impl(uint32_t* d_graph, const uint64_t* d_bucket, int64_t* d_local_knn,
                              int64_t* d_global_knn, uint64_t num_existing, uint64_t num_new,
                              uint64_t target_bucket, uint32_t total_deg, uint32_t local_deg,
-                             uint32_t k_local, uint32_t k_global, cudaStream_t st) {
+                             uint32_t k_local, uint32_t k_global, cudaStream_t st, const float* d_dataset,
+                             uint32_t dim, int metric, bool sync) {
   GRAB_REQUIRE(d_graph && d_bucket && d_local_knn && d_global_knn, "update_topology_opt: null pointer");
   GRAB_REQUIRE(local_deg >= 2 && local_deg < total_deg && total_deg - local_deg >= 2 && total_deg <= 512,
                "update_topology_opt: bad degrees %u/%u", local_deg, total_deg);
@@ -869,6 +982,14 @@ int update_topology_opt_impl(uint32_t* d_graph, const uint64_t* d_bucket, int64_
     set_last_error("update_topology_opt: out of device memory for the mailbox scratch");
     return GRAB_ERR_CUDA;
   }
+  // the counts and the cursor must be all-zero again when this call ends; if it ends early they are dropped and
+  // allocated (zeroed) afresh by the next batch
+  struct ZeroGuard {
+    bool done = false;
+    ~ZeroGuard() {
+      if (!done) { pool_drop(kPoolMailCountsL); pool_drop(kPoolMailCountsR); pool_drop(kPoolMailCursor); }
+    }
+  } zero_guard;
   GRAB_CUDA_TRY(cudaMemsetAsync(meta, 0, sizeof(MailMeta) * 2, st));
   uint32_t* touched_l = touched;
   uint32_t* touched_r = touched + max_edges;
@@ -887,7 +1008,14 @@ int update_topology_opt_impl(uint32_t* d_graph, const uint64_t* d_bucket, int64_
     mail_offsets_kernel<<<eg, 256, 0, st>>>(tl, meta + pass, counts, offsets);
     group_fill_kernel<<<eg, 256, 0, st>>>(e, total, offsets, cursor, csr);
     const unsigned ag = (unsigned)((total + kSelWarps - 1) / kSelWarps);  // upper bound on touched nodes
-    if (pass == 0)
+    if (d_dataset && e.c1 - e.c0 <= kRepairMaxRegion) {
+#define GRAB_REPAIR(M, R)                                                                                        \
+  mail_apply_dist_kernel<M, R><<<ag, kSelWarps * 32, 0, st>>>(d_graph, d_dataset, dim, tl, meta + pass, counts, \
+                                                             offsets, cursor, csr, e.c0, e.c1, total_deg)
+      if (metric == GRAB_METRIC_L2) { if (pass == 0) GRAB_REPAIR(GRAB_METRIC_L2, 0); else GRAB_REPAIR(GRAB_METRIC_L2, 1); }
+      else { if (pass == 0) GRAB_REPAIR(GRAB_METRIC_IP, 0); else GRAB_REPAIR(GRAB_METRIC_IP, 1); }
+#undef GRAB_REPAIR
+    } else if (pass == 0)
       mail_apply_kernel<0><<<ag, kSelWarps * 32, 0, st>>>(d_graph, d_bucket, tl, meta + pass, counts, counts_l, offsets,
                                                           cursor, csr, lmax, lmax, total_deg, local_deg);
     else
@@ -897,7 +1025,8 @@ int update_topology_opt_impl(uint32_t* d_graph, const uint64_t* d_bucket, int64_
   }
   mail_clear_kernel<<<(unsigned)((num_new * local_deg + 255) / 256), 256, 0, st>>>(touched_l, meta, counts_l);
   GRAB_CUDA_TRY(cudaGetLastError());
-  GRAB_CUDA_TRY(cudaStreamSynchronize(st));
+  if (sync) GRAB_CUDA_TRY(cudaStreamSynchronize(st));
+  zero_guard.done = true;
   return GRAB_OK;
 }
 

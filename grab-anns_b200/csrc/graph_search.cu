@@ -382,6 +382,10 @@ graph_search_kernel(const SearchKernelArgs a) {
 #ifndef GRAB_SEARCH2_CTAS_PER_SM
 #define GRAB_SEARCH2_CTAS_PER_SM 14
 #endif
+#ifndef GRAB_RANK_MERGE_HALF
+#define GRAB_RANK_MERGE_HALF 16
+#endif
+constexpr uint32_t kRankMergeHalf = GRAB_RANK_MERGE_HALF;  // per-warp kept keys up to which the merge is by rank (<= 16)
 
 template <int METRIC, int CPL, int R>
 __global__ void __launch_bounds__(kSearchThreads, GRAB_SEARCH2_CTAS_PER_SM)
@@ -396,6 +400,7 @@ graph_search_split_kernel(const SearchKernelArgs a) {
   uint32_t* parents = wcand + 2 * a.ckeys_cap;                             // [width]
   uint32_t* hash = parents + ((a.width + 3) & ~3u);                        // [2^bitlen] (if local)
   __shared__ uint32_t s_nparents, s_kept[2], s_inserted[2];
+  __shared__ uint32_t s_stat[6];  // iterations, parents, edges, distances, seeds, resets (this query)
 
   const uint64_t qi = blockIdx.x;
   if (qi >= a.nq) return;
@@ -415,6 +420,7 @@ graph_search_split_kernel(const SearchKernelArgs a) {
   for (uint32_t i = tid; i < hsize / 4; i += kSearchThreads)
     reinterpret_cast<uint4*>(hash)[i] = make_uint4(kInvalid, kInvalid, kInvalid, kInvalid);
   if (tid == 0) s_nparents = 0;
+  if (tid < 6) s_stat[tid] = 0;
 
   uint64_t lo = 0, hi = 0;
   uint32_t mask = 0;
@@ -446,7 +452,6 @@ graph_search_split_kernel(const SearchKernelArgs a) {
   // ---- seeds (compute_distance.cuh:204-269): provided ids, else pseudo-random ids; every warp keeps its own ----
   uint32_t ncand = 0;                     // warp-uniform: survivors in my_cand
   uint32_t inserted_total = 0;            // warp-uniform: ids this warp put into the visited set since the last clear
-  unsigned long long st_edges = 0, st_dists = 0, st_seeds = 0;
   {
     const uint32_t wlen = wend - wbeg;
     const bool generated_only = (a.seeds == nullptr);
@@ -484,12 +489,11 @@ graph_search_split_kernel(const SearchKernelArgs a) {
     }
     inserted_total = ncand;
     if (ncand > my_quota) ncand = my_quota;
-    st_seeds = ncand;
+    if (a.stats && lane == 0) atomicAdd(&s_stat[4], ncand);
   }
   __syncwarp();
 
   uint32_t iter = 0;
-  unsigned long long st_iters = 0, st_parents = 0, st_resets = 0;
   for (;;) {
     // ---- this warp's survivors: 4 teams, vectors gathered with 16-byte loads; a key is kept only if it beats
     //      the current worst entry of the list ----
@@ -553,8 +557,9 @@ graph_search_split_kernel(const SearchKernelArgs a) {
       }
     }
     __syncwarp();
-    // ---- sort this warp's kept keys in registers ----
-    if (nkeep > 1) {
+    // ---- a handful of kept keys (the usual case after the first iterations) is merged by rank and needs no
+    //      sort; more are sorted here, by this warp, in registers ----
+    if (nkeep > kRankMergeHalf) {
       if (nkeep <= 32) warp_sort_regs<1>(my_keys, nkeep, lane);
       else if (nkeep <= 64) warp_sort_regs<2>(my_keys, nkeep, lane);
       else warp_sort_regs_128(my_keys, nkeep, lane);
@@ -571,7 +576,17 @@ graph_search_split_kernel(const SearchKernelArgs a) {
     if (warp == 0) {
       const uint32_t n0 = s_kept[0], n1 = s_kept[1];
       uint64_t t[R];
-      if (n0 + n1 > 0) {
+      if (n0 + n1 > 0 && n0 <= kRankMergeHalf && n1 <= kRankMergeHalf) {
+        // neither warp sorted: lane j holds candidate j of the concatenation
+        uint64_t cand = kMaxKey;
+        if (lane < n0) cand = wkeys[lane];
+        else if (lane < n0 + n1) cand = wkeys[wcap + lane - n0];
+        warp_merge_by_rank<R>(queue, cand, n0 + n1, lane, t);
+      } else if (n0 + n1 > 0) {
+        // one run is sorted already; a short one that was left unsorted is sorted now
+        if (n0 > 1 && n0 <= kRankMergeHalf) warp_sort_regs<1>(wkeys, n0, lane);
+        if (n1 > 1 && n1 <= kRankMergeHalf) warp_sort_regs<1>(wkeys + wcap, n1, lane);
+        __syncwarp();
         warp_merge_runs_regs<R>(queue, wkeys, n0, wkeys + wcap, n1, lane, t);
       } else {
 #pragma unroll
@@ -610,7 +625,7 @@ graph_search_split_kernel(const SearchKernelArgs a) {
         if (key != kMaxKey) { hash_insert(hash, a.hash_bitlen, skey_id(key)); ++kept; }
       }
       inserted_total = __reduce_add_sync(0xFFFFFFFFu, kept);
-      st_resets += (tid == 0);
+      if (tid == 0) s_stat[5] += 1;
       __syncthreads();
     }
     const uint32_t nparents = s_nparents;
@@ -625,7 +640,9 @@ graph_search_split_kernel(const SearchKernelArgs a) {
       uint32_t nbv[4];
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        const uint32_t e = e0 + u * kSearchThreads + tid;
+        // inside every group of 64 consecutive edges warp 0 takes the even and warp 1 the odd ones, so that both
+        // warps see the same mix of local and cross-bucket columns (their survivor counts stay balanced)
+        const uint32_t e = e0 + u * kSearchThreads + 2 * lane + warp;
         nbv[u] = kInvalid;
         if (e < total_edges) {
           const uint32_t p = a.inv_active_deg ? __umulhi(e, a.inv_active_deg) : e;  // e / active_deg
@@ -645,9 +662,11 @@ graph_search_split_kernel(const SearchKernelArgs a) {
       }
     }
     inserted_total += ncand;
-    st_dists += ncand;
-    st_edges += my_edges;
-    if (tid == 0) { st_iters += 1; st_parents += nparents; }
+    if (a.stats) {
+      my_edges = __reduce_add_sync(0xFFFFFFFFu, my_edges);
+      if (lane == 0) { atomicAdd(&s_stat[2], my_edges); atomicAdd(&s_stat[3], ncand); }
+      if (tid == 0) { s_stat[0] += 1; s_stat[1] += nparents; }
+    }
     ++iter;
     __syncwarp();
   }
@@ -662,17 +681,8 @@ graph_search_split_kernel(const SearchKernelArgs a) {
     if (a.out_keys) a.out_keys[qi * a.k + i] = empty ? kMaxKey : ((key & 0xFFFFFFFF00000000ull) | gid);
   }
   if (a.stats) {
-    st_edges = __reduce_add_sync(0xFFFFFFFFu, static_cast<uint32_t>(st_edges));
-    if (lane == 0) {
-      atomicAdd(&a.stats[2], st_edges);
-      atomicAdd(&a.stats[3], st_dists);
-      atomicAdd(&a.stats[4], st_seeds);
-    }
-    if (tid == 0) {
-      atomicAdd(&a.stats[0], st_iters);
-      atomicAdd(&a.stats[1], st_parents);
-      atomicAdd(&a.stats[5], st_resets);
-    }
+    __syncthreads();
+    if (tid < 6) atomicAdd(&a.stats[tid], static_cast<unsigned long long>(s_stat[tid]));
   }
 }
 

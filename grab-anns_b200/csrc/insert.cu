@@ -18,7 +18,8 @@ int knn_blocks_impl(const float*, uint64_t, uint32_t, int, const uint64_t*, uint
                     float*, cudaStream_t);
 int update_topology_v1_impl(uint32_t*, const int64_t*, uint64_t, uint64_t, uint32_t, uint32_t, cudaStream_t);
 int update_topology_opt_impl(uint32_t*, const uint64_t*, int64_t*, int64_t*, uint64_t, uint64_t, uint64_t,
-                             uint32_t, uint32_t, uint32_t, uint32_t, cudaStream_t);
+                             uint32_t, uint32_t, uint32_t, uint32_t, cudaStream_t, const float* = nullptr, uint32_t = 0,
+                             int = 0, bool = true);
 
 #define GRAB_TRY(expr)              \
   do {                              \
@@ -98,15 +99,41 @@ int insert_v1_impl(const float* d_dataset, uint64_t num_existing, uint64_t num_n
   return GRAB_OK;
 }
 
+// A second stream and two events per device, so that the global and the bucket search of a batch overlap.
+struct SideStream {
+  cudaStream_t st = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr;
+};
+static SideStream* side_stream() {
+  static SideStream per_device[16];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return nullptr;
+  SideStream& s = per_device[dev];
+  if (!s.st) {
+    if (cudaStreamCreateWithFlags(&s.st, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+    if (cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+  }
+  return &s;
+}
+
+int route_seeds_impl(const grab_router*, const float*, uint64_t, uint64_t, const grab_filter*, uint32_t, uint32_t,
+                     uint64_t, uint32_t*, void*, size_t, cudaStream_t);
+
 int insert_opt_impl(const float* d_dataset, uint32_t* d_graph, const uint64_t* d_bucket, const uint32_t* d_seeds,
                     uint64_t num_existing, uint64_t num_new, uint64_t target_bucket, const float* d_queries,
                     uint32_t dim, uint32_t total_degree, uint32_t local_degree, grab_search_params params,
-                    uint32_t num_seeds_per_query, int metric) {
+                    uint32_t num_seeds_per_query, int metric, const InsertOptions* opt) {
   GRAB_REQUIRE(d_dataset && d_graph && d_bucket && d_queries, "insert: null pointer");
   if (num_new == 0) return GRAB_OK;
   GRAB_REQUIRE(num_existing >= 1, "insert: the index is empty (build it first)");
   const uint32_t search_k = params.itopk_size;  // cagra_opt.cu:1691
   GRAB_REQUIRE(search_k >= 2 && search_k <= 512, "insert: itopk_size %u outside [2,512]", search_k);
+  const InsertOptions defaults;
+  const InsertOptions& o = opt ? *opt : defaults;
+  cudaStream_t st = o.stream;
+  SideStream* side = side_stream();
+  GRAB_REQUIRE(side, "insert: could not create the side stream");
   StageTimer tm("insert_opt batch");
   // pooled scratch: thousands of batches must not pay cudaMalloc / cudaFree each
   Buf ig{pool_get(kPoolInsIdsG, sizeof(int64_t) * num_new * search_k, false)};
@@ -115,35 +142,79 @@ int insert_opt_impl(const float* d_dataset, uint32_t* d_graph, const uint64_t* d
   Buf dl{pool_get(kPoolInsDistL, sizeof(float) * num_new * search_k, false)};
   const size_t ws_bytes = grab_graph_search_workspace_bytes(num_new, params.hash_bitlen);
   void* ws = pool_get(kPoolSearchWs, ws_bytes, false);
-  if (!ig.ptr || !dg.ptr || !il.ptr || !dl.ptr || !ws) {
+  void* ws2 = pool_get(kPoolSearchWs2, ws_bytes, false);
+  if (!ig.ptr || !dg.ptr || !il.ptr || !dl.ptr || !ws || !ws2) {
     set_last_error("insert: out of device memory for the batch scratch");
     return GRAB_ERR_CUDA;
   }
+  uint32_t* seeds_g = nullptr;
+  uint32_t* seeds_l = nullptr;
+  void* rws = nullptr;
+  void* rws2 = nullptr;
+  size_t rws_bytes = 0;
+  if (o.router) {
+    rws_bytes = grab_route_seeds_workspace_bytes(num_new, o.probes);
+    seeds_g = static_cast<uint32_t*>(pool_get(kPoolInsSeedsG, sizeof(uint32_t) * num_new * o.routed_seeds, false));
+    seeds_l = static_cast<uint32_t*>(pool_get(kPoolInsSeedsL, sizeof(uint32_t) * num_new * o.routed_seeds, false));
+    rws = pool_get(kPoolRouteWs, rws_bytes, false);
+    rws2 = pool_get(kPoolRouteWs2, rws_bytes, false);
+    if (!seeds_g || !seeds_l || !rws || !rws2) {
+      set_last_error("insert: out of device memory for the routing scratch");
+      return GRAB_ERR_CUDA;
+    }
+  }
   const uint64_t total = num_new * search_k;
-  // global search over the old nodes, all columns, self-drawn seeds (cagra_opt.cu:1725-1740)
+  const uint64_t seed = 0x51ED270B3A4D9C35ull + num_existing;
+  // the bucket search runs on the side stream, next to the global search
+  GRAB_CUDA_TRY(cudaEventRecord(side->fork, st));
+  GRAB_CUDA_TRY(cudaStreamWaitEvent(side->st, side->fork, 0));
+  // global search over the old nodes, all columns (cagra_opt.cu:1725-1740); seeds: the router's, else self-drawn
   {
     grab_search_args a = insert_search_args(d_dataset, dim, num_existing, d_graph, total_degree, d_queries, num_new,
                                             search_k, params, ig.as<int64_t>(), dg.as<float>(), metric);
     a.filter.kind = GRAB_FILTER_NONE;
-    a.d_ws = ws; a.ws_bytes = ws_bytes;
+    a.d_ws = ws; a.ws_bytes = ws_bytes; a.stream = st;
+    if (o.router) {
+      GRAB_TRY(route_seeds_impl(o.router, d_queries, num_new, num_existing, nullptr, o.probes, o.routed_seeds, seed,
+                                seeds_g, rws, rws_bytes, st));
+      a.d_seeds = seeds_g;
+      a.seeds_per_query = o.routed_seeds;
+    }
     GRAB_TRY(graph_search_impl(&a));
   }
-  tm.mark("global search");
   // bucket search from in-bucket seeds, local columns only (cagra_opt.cu:1779-1795)
-  if (d_seeds && num_seeds_per_query > 0) {
+  const bool routed_bucket = o.router && o.bucket_has_old_members;
+  if (routed_bucket || (d_seeds && num_seeds_per_query > 0)) {
     grab_search_args a = insert_search_args(d_dataset, dim, num_existing, d_graph, total_degree, d_queries, num_new,
                                             search_k, params, il.as<int64_t>(), dl.as<float>(), metric);
     a.filter.kind = GRAB_FILTER_PREFIX;
     a.filter.active_degree = local_degree;
     a.d_seeds = d_seeds;
     a.seeds_per_query = num_seeds_per_query;
-    a.d_ws = ws; a.ws_bytes = ws_bytes;
+    a.d_ws = ws2; a.ws_bytes = ws_bytes; a.stream = side->st;
+    if (routed_bucket) {
+      // members of the nearest centroids that lie in the target bucket (bucket ids are non-decreasing in the id,
+      // so the bucket is one id window)
+      grab_filter bf;
+      memset(&bf, 0, sizeof(bf));
+      bf.kind = GRAB_FILTER_TS_RANGE;
+      bf.d_ts = d_bucket;
+      bf.lo = target_bucket;
+      bf.hi = target_bucket + 1;
+      bf.ts_sorted = 1;
+      GRAB_TRY(route_seeds_impl(o.router, d_queries, num_new, num_existing, &bf, o.probes, o.routed_seeds, seed + 1,
+                                seeds_l, rws2, rws_bytes, side->st));
+      a.d_seeds = seeds_l;
+      a.seeds_per_query = o.routed_seeds;
+    }
     GRAB_TRY(graph_search_impl(&a));
   } else {
-    fill_empty_kernel<<<(unsigned)((total + 255) / 256), 256>>>(il.as<int64_t>(), dl.as<float>(), total);
+    fill_empty_kernel<<<(unsigned)((total + 255) / 256), 256, 0, side->st>>>(il.as<int64_t>(), dl.as<float>(), total);
     GRAB_CUDA_TRY(cudaGetLastError());
   }
-  tm.mark("bucket search");
+  GRAB_CUDA_TRY(cudaEventRecord(side->join, side->st));
+  GRAB_CUDA_TRY(cudaStreamWaitEvent(st, side->join, 0));
+  tm.mark("global + bucket search");
   // exact kNN inside the batch, tmp = min(n, search_k/2) wide (cagra_opt.cu:1877-1928)
   const uint32_t tmp = static_cast<uint32_t>(num_new < search_k / 2 ? num_new : search_k / 2);
   if (num_new >= 2 && tmp >= 1) {
@@ -154,17 +225,16 @@ int insert_opt_impl(const float* d_dataset, uint32_t* d_graph, const uint64_t* d
       return GRAB_ERR_CUDA;
     }
     const uint64_t offs[2] = {0, num_new};
-    GRAB_TRY(knn_blocks_impl(d_queries, num_new, dim, metric, offs, 1, tmp, 0, bi.as<uint32_t>(), bd.as<float>(), nullptr));
+    GRAB_TRY(knn_blocks_impl(d_queries, num_new, dim, metric, offs, 1, tmp, 0, bi.as<uint32_t>(), bd.as<float>(), st));
     const uint32_t padded = next_pow2(search_k + tmp);
-    merge_two_lists_kernel<<<(unsigned)num_new, 128, sizeof(uint64_t) * padded>>>(
+    merge_two_lists_kernel<<<(unsigned)num_new, 128, sizeof(uint64_t) * padded, st>>>(
         il.as<int64_t>(), dl.as<float>(), search_k, bi.as<uint32_t>(), bd.as<float>(), tmp, num_existing, padded);
     GRAB_CUDA_TRY(cudaGetLastError());
-    GRAB_CUDA_TRY(cudaDeviceSynchronize());
   }
   tm.mark("batch kNN + merge");
   GRAB_TRY(update_topology_opt_impl(d_graph, d_bucket, il.as<int64_t>(), ig.as<int64_t>(), num_existing, num_new,
-                                    target_bucket, total_degree, local_degree, search_k, search_k, nullptr));
-  GRAB_CUDA_TRY(cudaDeviceSynchronize());
+                                    target_bucket, total_degree, local_degree, search_k, search_k, st,
+                                    o.repair_by_distance ? d_dataset : nullptr, dim, metric, o.sync));
   tm.mark("topology update");
   return GRAB_OK;
 }
@@ -199,7 +269,7 @@ int grab_insert_opt(const float* d_dataset, uint32_t* d_graph, const uint64_t* d
                     grab_search_params params, uint32_t num_seeds_per_query) {
   (void)use_heuristic;  // the reference compiles a heuristic variant but never runs it (insert.cu:1425)
   return insert_opt_impl(d_dataset, d_graph, d_ts, d_seeds, num_existing, num_new, target_ts, d_queries, dim,
-                         total_degree, local_degree, params, num_seeds_per_query, GRAB_METRIC_L2);
+                         total_degree, local_degree, params, num_seeds_per_query, GRAB_METRIC_L2, nullptr);
 }
 
 }  // extern "C"

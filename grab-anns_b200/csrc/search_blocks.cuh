@@ -235,4 +235,51 @@ __device__ __forceinline__ void warp_merge_runs_regs(const uint64_t* top, const 
   RegBitonicLevel<R, LOGM>::run(t, M, lane);
 }
 
+// ---------------------------------------------------------------------------------------
+// Merge by rank, for the common late-iteration case of a handful of kept keys: no sort at all.
+// The list top[0, 32*R) is sorted, the K <= 32 candidate keys are NOT (lane j holds candidate j).
+// All keys are distinct (ids are unique), so every key's position in the merged order is
+//   list entry e    : e + #{candidates below it}
+//   candidate j     : #{list entries below it} + #{candidates below it}
+// and each key is written straight to that slot (if it is still inside the list).  One pass over
+// the candidates by shuffle serves both counts.  The list is left sorted in shared memory AND in
+// t (element e in register e/32 of lane e%32).
+// ---------------------------------------------------------------------------------------
+template <int R>
+__device__ __forceinline__ void warp_merge_by_rank(uint64_t* top, uint64_t cand, uint32_t K, uint32_t lane,
+                                                   uint64_t (&t)[R]) {
+  constexpr uint32_t M = 32u * R;
+#pragma unroll
+  for (int r = 0; r < R; ++r) t[r] = top[lane + 32u * r];
+  // candidates below each list entry / below my candidate
+  uint32_t below_t[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) below_t[r] = 0;
+  uint32_t below_c = 0;
+  for (uint32_t j = 0; j < K; ++j) {
+    const uint64_t cj = __shfl_sync(0xFFFFFFFFu, cand, j);
+    below_c += cj < cand;
+#pragma unroll
+    for (int r = 0; r < R; ++r) below_t[r] += cj < t[r];
+  }
+  // list entries below my candidate: lower bound in the sorted list
+  uint32_t lo = 0, hi = M;
+  if (lane < K) {
+    while (lo < hi) {
+      const uint32_t mid = (lo + hi) >> 1;
+      if (top[mid] < cand) lo = mid + 1; else hi = mid;
+    }
+  }
+  __syncwarp();  // every read of the old list is done
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const uint32_t pos = lane + 32u * r + below_t[r];
+    if (pos < M) top[pos] = t[r];
+  }
+  if (lane < K && lo + below_c < M) top[lo + below_c] = cand;
+  __syncwarp();
+#pragma unroll
+  for (int r = 0; r < R; ++r) t[r] = top[lane + 32u * r];
+}
+
 }  // namespace grab

@@ -11,7 +11,8 @@ namespace grab {
 
 // One warp per list: fold `ncand` unsorted candidate keys into the sorted list of m keys with the routine the
 // search kernel would pick for this m (64: registers x2, 128: registers x4, else shared memory).
-// variant 0 = as the kernel dispatches, 1 = force the shared-memory version.
+// variant 0 = as the shared-list kernel dispatches, 1 = force the shared-memory version, 2 = merge by rank
+// (ncand <= 32, m 64 / 128), 3 = two register-sorted runs folded in (ncand <= 256, m 64 / 128).
 __global__ void selftest_sort_merge_kernel(const uint64_t* __restrict__ top_in, const uint64_t* __restrict__ cand_in,
                                            uint32_t m, uint32_t ncand, uint32_t cand_stride, int variant,
                                            uint64_t* __restrict__ top_out) {
@@ -23,7 +24,38 @@ __global__ void selftest_sort_merge_kernel(const uint64_t* __restrict__ top_in, 
   for (uint32_t i = lane; i < m; i += 32) top[i] = top_in[list * m + i];
   for (uint32_t i = lane; i < ncand; i += 32) cand[i] = cand_in[list * cand_stride + i];
   __syncwarp();
-  if (ncand > 0) {
+  if (ncand > 0 && variant == 2) {
+    // merge by rank (the warp-split kernel's path for a handful of kept keys): ncand <= 32, m = 64 or 128
+    const uint64_t c = lane < ncand ? cand[lane] : kMaxKey;
+    if (m == 64) { uint64_t t[2]; warp_merge_by_rank<2>(top, c, ncand, lane, t); }
+    else { uint64_t t[4]; warp_merge_by_rank<4>(top, c, ncand, lane, t); }
+  } else if (ncand > 0 && variant == 3) {
+    // the warp-split kernel's path for many kept keys: the candidates are cut in two runs, each sorted in
+    // registers as its warp would, then both are folded into the list
+    const uint32_t n0 = ncand / 2, n1 = ncand - n0;
+    uint64_t* run1 = cand + n0;
+    auto sort_run = [&](uint64_t* keys, uint32_t n) {
+      if (n <= 1) return;
+      if (n <= 32) warp_sort_regs<1>(keys, n, lane);
+      else if (n <= 64) warp_sort_regs<2>(keys, n, lane);
+      else warp_sort_regs_128(keys, n, lane);
+    };
+    sort_run(cand, n0);
+    __syncwarp();
+    sort_run(run1, n1);
+    __syncwarp();
+    if (m == 64) {
+      uint64_t t[2];
+      warp_merge_runs_regs<2>(top, cand, n0 < m ? n0 : m, run1, n1 < m ? n1 : m, lane, t);
+      __syncwarp();
+      for (int r = 0; r < 2; ++r) top[lane + 32 * r] = t[r];
+    } else {
+      uint64_t t[4];
+      warp_merge_runs_regs<4>(top, cand, n0 < m ? n0 : m, run1, n1 < m ? n1 : m, lane, t);
+      __syncwarp();
+      for (int r = 0; r < 4; ++r) top[lane + 32 * r] = t[r];
+    }
+  } else if (ncand > 0) {
     if (variant == 0 && m == 64 && ncand <= 64) {
       warp_sort_merge_regs<2>(top, cand, ncand, lane);
     } else if (variant == 0 && m == 128 && ncand <= 128) {
@@ -69,6 +101,8 @@ extern "C" int grab_selftest_sort_merge(const uint64_t* d_top, const uint64_t* d
   GRAB_REQUIRE(m >= 64 && m <= 1024 && (m & (m - 1)) == 0, "selftest_sort_merge: m %u must be a power of two in [64,1024]", m);
   GRAB_REQUIRE(ncand <= cand_stride && cand_stride <= 2048, "selftest_sort_merge: ncand %u > stride %u or stride > 2048",
                ncand, cand_stride);
+  GRAB_REQUIRE(variant < 2 || ((m == 64 || m == 128) && ncand <= (variant == 2 ? 32u : 256u)),
+               "selftest_sort_merge: variant %d needs m 64 or 128 and fewer candidates", variant);
   if (lists == 0) return GRAB_OK;
   uint32_t padded = 32;
   while (padded < ncand) padded <<= 1;

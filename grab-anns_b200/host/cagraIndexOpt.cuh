@@ -60,7 +60,19 @@ class CagraIndexOpt {
   void setMetric(int metric) { metric_ = metric; }
   void setKnnPrecision(int precision) { knn_precision_ = precision; }
   void setSeed(uint64_t seed) { seed_ = seed; }
-  void setInsertBatch(size_t batch) { insert_batch_ = batch ? batch : 1024; }
+  void setInsertBatch(size_t batch) { insert_batch_ = batch ? batch : 4096; }
+  // Insert behaviour beyond the reference's.  routed: seeds of the insert searches come from the entry-point
+  // router (needs setRouter != 0 and sorted timestamps; otherwise the reference's seed rule applies).
+  // repair_by_distance: a new node replaces the FARTHEST neighbour of an old node it links back to, and only when
+  // it is closer, instead of the reference's pseudo-random slot (src/index/insert.cu:693-712); false restores the
+  // reference's rule.
+  void setInsertMode(bool routed, bool repair_by_distance) {
+    insert_routed_ = routed;
+    insert_repair_by_distance_ = repair_by_distance;
+  }
+  void setInsertSearchParams(uint32_t itopk, uint32_t width, uint32_t max_iterations, uint32_t hash_bitlen) {
+    insert_params_routed_ = {itopk, width, 0, max_iterations, hash_bitlen};
+  }
   // Entry-point router: searches that get no seeds from the caller start from members of the
   // query's nearest k-means centroids that pass the filter, instead of uniformly drawn ids.
   // centroids = 0 switches it off (the reference's behaviour), kRouterAuto picks about sqrt(n).
@@ -94,7 +106,10 @@ class CagraIndexOpt {
   std::unique_ptr<grab::QueryArena, grab::QueryArenaDeleter> arena_;
   // the reference inserts 32 at a time (src/cagraIndexOpt.cu:590); the sparse mailboxes and the
   // exact kNN inside the batch make four-digit batches as good and far faster
-  size_t insert_batch_ = 1024;
+  size_t insert_batch_ = 4096;
+  bool insert_routed_ = true, insert_repair_by_distance_ = true;
+  grab_search_params insert_params_ = {128, 4, 0, 100, 13};         // src/cagraIndexOpt.cu:596-602
+  grab_search_params insert_params_routed_ = {128, 4, 0, 16, 12};   // from routed seeds
   struct RouterState;
   struct RouterDeleter { void operator()(RouterState*) const; };
   const grab_router* ensure_router();  // nullptr when switched off or the index is too small

@@ -41,6 +41,13 @@ class DeviceBuffer {
   std::vector<std::pair<CUmemGenericAllocationHandle, size_t>> chunks_;
 };
 
+// Exception that carries the grab_status the C handles return for it (plain std::runtime_error maps to
+// GRAB_ERR_INVALID_ARGUMENT there).
+struct StatusError : std::runtime_error {
+  int status;
+  StatusError(int status_, const std::string& message) : std::runtime_error(message), status(status_) {}
+};
+
 // Query scratch an index keeps across calls (defined with the classes, index_classes.cu).
 struct QueryArena;
 struct QueryArenaDeleter { void operator()(QueryArena*) const; };

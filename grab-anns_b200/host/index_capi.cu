@@ -14,6 +14,9 @@ int guarded(F&& f) {
   try {
     f();
     return GRAB_OK;
+  } catch (const grab::StatusError& e) {  // CUDA failures, out of memory, file errors, device-side timeouts
+    grab::set_last_error("%s", e.what());
+    return e.status;
   } catch (const std::exception& e) {
     grab::set_last_error("%s", e.what());
     return GRAB_ERR_INVALID_ARGUMENT;
@@ -48,6 +51,13 @@ int grab_index_opt_set_query_params(void* h, uint32_t itopk, uint32_t width, uin
 }
 int grab_index_opt_set_router(void* h, uint32_t centroids, uint32_t probes, uint32_t seeds_per_query) {
   return guarded([&] { O(h)->setRouter(centroids, probes, seeds_per_query); });
+}
+int grab_index_opt_set_insert_mode(void* h, int routed, int repair_by_distance) {
+  return guarded([&] { O(h)->setInsertMode(routed != 0, repair_by_distance != 0); });
+}
+int grab_index_opt_set_insert_search_params(void* h, uint32_t itopk, uint32_t width, uint32_t max_iter,
+                                            uint32_t hash_bitlen) {
+  return guarded([&] { O(h)->setInsertSearchParams(itopk, width, max_iter, hash_bitlen); });
 }
 int grab_index_opt_add(void* h, size_t n, const float* v, const uint64_t* ts) { return guarded([&] { O(h)->add(n, v, ts); }); }
 int grab_index_opt_build(void* h) { return guarded([&] { O(h)->build(); }); }

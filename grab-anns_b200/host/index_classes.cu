@@ -15,16 +15,16 @@
 namespace grab {
 int insert_v1_impl(const float*, uint64_t, uint64_t, const float*, uint32_t*, uint32_t, uint32_t, grab_search_params, int);
 int insert_opt_impl(const float*, uint32_t*, const uint64_t*, const uint32_t*, uint64_t, uint64_t, uint64_t, const float*,
-                    uint32_t, uint32_t, uint32_t, grab_search_params, uint32_t, int);
+                    uint32_t, uint32_t, uint32_t, grab_search_params, uint32_t, int, const InsertOptions*);
 }  // namespace grab
 
 namespace {
 
 void ok(int rc, const char* what) {
-  if (rc != GRAB_OK) throw std::runtime_error(std::string(what) + ": " + grab_last_error());
+  if (rc != GRAB_OK) throw grab::StatusError(rc, std::string(what) + ": " + grab_last_error());
 }
 void cu(cudaError_t e, const char* what) {
-  if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+  if (e != cudaSuccess) throw grab::StatusError(GRAB_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
 }
 
 struct Scratch {
@@ -318,7 +318,7 @@ void CagraIndex::query_range(const float* host_queries, size_t num_queries, int 
 
 void CagraIndex::save(const std::string& filepath) {  // src/cagraIndex.cu:352-368: dim, degree, size, data, graph
   std::ofstream out(filepath, std::ios::binary);
-  if (!out) throw std::runtime_error("Cannot open file for save");
+  if (!out) throw grab::StatusError(GRAB_ERR_IO, "Cannot open file for save");
   get_graph();
   out.write(reinterpret_cast<const char*>(&dim_), sizeof(dim_));
   out.write(reinterpret_cast<const char*>(&graph_degree_), sizeof(graph_degree_));
@@ -331,11 +331,11 @@ void CagraIndex::save(const std::string& filepath) {  // src/cagraIndex.cu:352-3
 
 void CagraIndex::load(const std::string& filepath) {  // src/cagraIndex.cu:370-395
   std::ifstream in(filepath, std::ios::binary);
-  if (!in) throw std::runtime_error("Cannot open file for load");
+  if (!in) throw grab::StatusError(GRAB_ERR_IO, "Cannot open file for load");
   in.read(reinterpret_cast<char*>(&dim_), sizeof(dim_));
   in.read(reinterpret_cast<char*>(&graph_degree_), sizeof(graph_degree_));
   in.read(reinterpret_cast<char*>(&current_size_), sizeof(current_size_));
-  if (!in) throw std::runtime_error("load: truncated header");
+  if (!in) throw grab::StatusError(GRAB_ERR_IO, "load: truncated header");
   h_data_.resize(current_size_ * dim_);
   h_graph_.resize(current_size_ * graph_degree_);
   h_timestamps_.clear();
@@ -343,7 +343,7 @@ void CagraIndex::load(const std::string& filepath) {  // src/cagraIndex.cu:370-3
   if (current_size_ > 0) {
     in.read(reinterpret_cast<char*>(h_data_.data()), h_data_.size() * sizeof(float));
     in.read(reinterpret_cast<char*>(h_graph_.data()), h_graph_.size() * sizeof(uint32_t));
-    if (!in) throw std::runtime_error("load: truncated body");
+    if (!in) throw grab::StatusError(GRAB_ERR_IO, "load: truncated body");
     d_data_->resize(h_data_.size() * sizeof(float));
     d_graph_->resize(h_graph_.size() * sizeof(uint32_t));
     cu(cudaMemcpy(d_data_->data(), h_data_.data(), h_data_.size() * sizeof(float), cudaMemcpyHostToDevice), "H2D dataset");
@@ -451,6 +451,7 @@ const grab_router* CagraIndexOpt::ensure_router() {
 void CagraIndexOpt::build() {
   const size_t n = h_data_.size() / dim_;
   if (n == 0) return;
+  router_.reset();  // centroids and member lists of the previous contents must not outlive them
   current_size_ = n;
   d_data_->resize(n * dim_ * sizeof(float));
   cu(cudaMemcpy(d_data_->data(), h_data_.data(), n * dim_ * sizeof(float), cudaMemcpyHostToDevice), "H2D dataset");
@@ -589,58 +590,87 @@ void CagraIndexOpt::insert(size_t new_vectors, const float* insert_vectors, cons
     return;
   }
   const size_t first_new = current_size_, new_total = first_new + new_vectors;
+  // The router (when it is on and the timestamps are sorted) covers the nodes present before this call; both
+  // insert searches then start from routed seeds -- members of the new vector's nearest centroids, for the bucket
+  // search those inside the target bucket -- instead of random ids / a host-sampled list shared by the whole batch,
+  // and need a fraction of the iterations.
+  const grab_router* router = (insert_routed_ && ts_sorted_) ? ensure_router() : nullptr;
   add(new_vectors, insert_vectors, insert_timestamps);
-  d_data_->resize(new_total * dim_ * sizeof(float));
-  d_graph_->resize(new_total * graph_degree_ * sizeof(uint32_t));
-  float* d_data = static_cast<float*>(d_data_->data());
-  uint32_t* d_graph = static_cast<uint32_t*>(d_graph_->data());
-  cu(cudaMemcpy(d_data + first_new * dim_, insert_vectors, new_vectors * dim_ * sizeof(float), cudaMemcpyHostToDevice),
-     "H2D new vectors");
-  // search parameters of the insert path (src/cagraIndexOpt.cu:596-602; kept apart from the
-  // user's query parameters, which the reference overwrites here)
-  const grab_search_params ip = {128, 4, 0, 100, 13};
-  const uint32_t spq = std::max(32u, ip.itopk_size);
-  size_t old_size = first_new;
-  size_t off = 0;
-  while (off < new_vectors) {
-    // the reference assumes one bucket per call (src/cagraIndexOpt.cu:560); runs of equal
-    // bucket ids are inserted one after the other here
-    const uint64_t target = bucket_of(insert_timestamps[off]);
-    size_t run = 1;
-    while (off + run < new_vectors && bucket_of(insert_timestamps[off + run]) == target) ++run;
-    for (size_t b = 0; b < run; b += insert_batch_) {
-      const size_t cur = std::min(insert_batch_, run - b);
-      std::vector<uint32_t> in_bucket;
-      auto it = ts_to_ids_.find(target);
-      if (it != ts_to_ids_.end())
-        for (uint32_t id : it->second) {
-          if (id >= old_size) break;  // ids are appended in ascending order
-          in_bucket.push_back(id);
+  if (!ts_sorted_) router = nullptr;
+  try {
+    d_data_->resize(new_total * dim_ * sizeof(float));
+    d_graph_->resize(new_total * graph_degree_ * sizeof(uint32_t));
+    float* d_data = static_cast<float*>(d_data_->data());
+    uint32_t* d_graph = static_cast<uint32_t*>(d_graph_->data());
+    cu(cudaMemcpy(d_data + first_new * dim_, insert_vectors, new_vectors * dim_ * sizeof(float), cudaMemcpyHostToDevice),
+       "H2D new vectors");
+    // search parameters of the insert path (src/cagraIndexOpt.cu:596-602: itopk 128, width 4, up to 100 iterations,
+    // hash 2^13; kept apart from the user's query parameters, which the reference overwrites here).  Routed seeds
+    // start next to the answer: a dozen iterations settle the 128 nearest.
+    const grab_search_params ip = router ? insert_params_routed_ : insert_params_;
+    const uint32_t spq = std::max(32u, ip.itopk_size);
+    grab::InsertOptions io;
+    io.router = router;
+    io.probes = router_probes_;
+    io.routed_seeds = 32;
+    io.repair_by_distance = insert_repair_by_distance_;
+    io.sync = false;  // batches are stream-ordered; one wait at the end of the call
+    size_t old_size = first_new;
+    size_t off = 0;
+    while (off < new_vectors) {
+      // the reference assumes one bucket per call (src/cagraIndexOpt.cu:560); runs of equal
+      // bucket ids are inserted one after the other here
+      const uint64_t target = bucket_of(insert_timestamps[off]);
+      size_t run = 1;
+      while (off + run < new_vectors && bucket_of(insert_timestamps[off + run]) == target) ++run;
+      for (size_t b = 0; b < run; b += insert_batch_) {
+        const size_t cur = std::min(insert_batch_, run - b);
+        auto it = ts_to_ids_.find(target);
+        const bool has_old = it != ts_to_ids_.end() && !it->second.empty() && it->second.front() < old_size;
+        std::unique_ptr<Scratch> d_seeds;
+        if (!router && has_old) {
+          // host seed sampling as in the reference (src/cagraIndexOpt.cu:604-640): one list for the batch
+          std::vector<uint32_t> in_bucket;
+          for (uint32_t id : it->second) {
+            if (id >= old_size) break;  // ids are appended in ascending order
+            in_bucket.push_back(id);
+          }
+          std::vector<uint32_t> one = sample_ids(in_bucket, spq, seed_ + old_size);
+          one.resize(spq, 0xFFFFFFFFu);
+          std::vector<uint32_t> all(cur * spq);
+          for (size_t i = 0; i < cur; ++i) memcpy(all.data() + i * spq, one.data(), spq * 4);
+          d_seeds.reset(new Scratch(all.size() * 4));
+          cu(cudaMemcpy(d_seeds->p, all.data(), all.size() * 4, cudaMemcpyHostToDevice), "H2D seeds");
         }
-      std::unique_ptr<Scratch> d_seeds;
-      if (!in_bucket.empty()) {
-        std::vector<uint32_t> one = sample_ids(in_bucket, spq, seed_ + old_size);
-        one.resize(spq, 0xFFFFFFFFu);
-        std::vector<uint32_t> all(cur * spq);
-        for (size_t i = 0; i < cur; ++i) memcpy(all.data() + i * spq, one.data(), spq * 4);
-        d_seeds.reset(new Scratch(all.size() * 4));
-        cu(cudaMemcpy(d_seeds->p, all.data(), all.size() * 4, cudaMemcpyHostToDevice), "H2D seeds");
+        io.bucket_has_old_members = has_old;
+        ok(grab::insert_opt_impl(d_data, d_graph, static_cast<uint64_t*>(d_bucket_->data()),
+                                 d_seeds ? d_seeds->as<uint32_t>() : nullptr, old_size, cur, target,
+                                 d_data + old_size * dim_, dim_, graph_degree_, static_cast<uint32_t>(local_degree_), ip,
+                                 d_seeds ? spq : 0, metric_, &io),
+           "insert");
+        if (d_seeds) cu(cudaDeviceSynchronize(), "insert batch");  // the seed list is freed on scope exit
+        old_size += cur;
       }
-      ok(grab::insert_opt_impl(d_data, d_graph, static_cast<uint64_t*>(d_bucket_->data()),
-                               d_seeds ? d_seeds->as<uint32_t>() : nullptr, old_size, cur, target,
-                               d_data + old_size * dim_, dim_, graph_degree_, static_cast<uint32_t>(local_degree_), ip,
-                               d_seeds ? spq : 0, metric_),
-         "insert");
-      old_size += cur;
+      off += run;
     }
-    off += run;
+    cu(cudaDeviceSynchronize(), "insert");
+  } catch (...) {
+    // leave the index as it was before the call: the host mirrors must not run ahead of current_size_
+    h_data_.resize(first_new * dim_);
+    h_timestamps_.resize(first_new);
+    for (auto it = ts_to_ids_.begin(); it != ts_to_ids_.end();) {
+      while (!it->second.empty() && it->second.back() >= first_new) it->second.pop_back();
+      it = it->second.empty() ? ts_to_ids_.erase(it) : std::next(it);
+    }
+    cudaDeviceSynchronize();
+    throw;
   }
   current_size_ = new_total;
 }
 
 void CagraIndexOpt::save(const std::string& filepath) {  // "MCAG" v1, src/cagraIndexOpt.cu:725-794
   std::ofstream ofs(filepath, std::ios::binary);
-  if (!ofs.is_open()) throw std::runtime_error("Failed to open file for writing: " + filepath);
+  if (!ofs.is_open()) throw grab::StatusError(GRAB_ERR_IO, "Failed to open file for writing: " + filepath);
   get_graph();
   auto put = [&](const void* p, size_t b) { ofs.write(reinterpret_cast<const char*>(p), b); };
   const char magic[4] = {'M', 'C', 'A', 'G'};
@@ -662,17 +692,18 @@ void CagraIndexOpt::save(const std::string& filepath) {  // "MCAG" v1, src/cagra
 
 void CagraIndexOpt::load(const std::string& filepath) {  // src/cagraIndexOpt.cu:796-898
   std::ifstream ifs(filepath, std::ios::binary);
-  if (!ifs.is_open()) throw std::runtime_error("Failed to open file for reading: " + filepath);
+  if (!ifs.is_open()) throw grab::StatusError(GRAB_ERR_IO, "Failed to open file for reading: " + filepath);
+  router_.reset();  // a file of the same size would otherwise keep the old index's centroids and member lists
   auto get = [&](void* p, size_t b) {
     ifs.read(reinterpret_cast<char*>(p), b);
-    if (!ifs) throw std::runtime_error("load: truncated file " + filepath);
+    if (!ifs) throw grab::StatusError(GRAB_ERR_IO, "load: truncated file " + filepath);
   };
   char magic[4];
   uint32_t version = 0;
   get(magic, 4);
-  if (memcmp(magic, "MCAG", 4) != 0) throw std::runtime_error("load: bad magic in " + filepath);
+  if (memcmp(magic, "MCAG", 4) != 0) throw grab::StatusError(GRAB_ERR_IO, "load: bad magic in " + filepath);
   get(&version, 4);
-  if (version != 1) throw std::runtime_error("load: unsupported version");
+  if (version != 1) throw grab::StatusError(GRAB_ERR_IO, "load: unsupported version");
   get(&dim_, 4); get(&graph_degree_, 4); get(&local_degree_, sizeof(size_t)); get(&current_size_, sizeof(size_t));
   size_t ts_size = 0, nb = 0, dsz = 0, gsz = 0;
   get(&ts_size, sizeof(size_t));

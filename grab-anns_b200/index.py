@@ -70,7 +70,7 @@ class CagraIndexOpt(_Base):
     _prefix = "grab_index_opt_"
 
     def __init__(self, dim, graph_degree=32, local_degree=16, vmm_max_bytes=4 << 30, bucket_width=1, metric=0,
-                 knn_precision=2, seed=0x9E3779B97F4A7C15, insert_batch=1024):
+                 knn_precision=2, seed=0x9E3779B97F4A7C15, insert_batch=4096):
         self.dim, self.graph_degree = dim, graph_degree
         self.h = _lib().grab_index_opt_create(C.c_uint32(dim), C.c_uint32(graph_degree), C.c_uint32(local_degree),
                                               C.c_size_t(vmm_max_bytes))
@@ -99,6 +99,14 @@ class CagraIndexOpt(_Base):
     def set_router(self, centroids=0xFFFFFFFF, probes=2, seeds_per_query=64):
         """Entry-point router for searches without caller seeds: 0 = off, 0xFFFFFFFF = about sqrt(n)."""
         self._call("set_router", C.c_uint32(centroids), C.c_uint32(probes), C.c_uint32(seeds_per_query))
+
+    def set_insert_mode(self, routed=True, repair_by_distance=True):
+        """Routed insert searches / distance-aware reverse-edge repair (False, False = the reference's rules)."""
+        self._call("set_insert_mode", C.c_int(int(routed)), C.c_int(int(repair_by_distance)))
+
+    def set_insert_search_params(self, itopk=128, width=4, max_iter=16, hash_bitlen=12):
+        self._call("set_insert_search_params", C.c_uint32(itopk), C.c_uint32(width), C.c_uint32(max_iter),
+                   C.c_uint32(hash_bitlen))
 
     def query_local(self, queries, k, target_timestamp):
         q = _f32(queries)

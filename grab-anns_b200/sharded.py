@@ -46,6 +46,66 @@ def gather_and_merge(dists, ids, k: int, merge_fn, dist_mod=None, group=None):
     return merge_fn(all_d.transpose(0, 1).contiguous(), all_i.transpose(0, 1).contiguous(), k)
 
 
+class HostSync:
+    """Stream / event operations of run_pipelined for hosts without streams (CPU ranks in the tests): every call
+    runs in program order, so there is nothing to wait for."""
+
+    def searched(self, i):
+        pass
+
+    def wait_exchanged(self, i):
+        pass
+
+    def on_exchange_stream(self, fn, i):
+        fn(i)
+
+    def drain(self):
+        pass
+
+    def begin(self):
+        import time
+        self.t0 = time.perf_counter()
+
+    def end(self):
+        import time
+        return (time.perf_counter() - self.t0) * 1e3
+
+
+def run_pipelined(n_sets: int, steps: int, warmup: int, search, exchange, sync, barrier=None):
+    """The step loop of the sharded search.  Step i searches into buffer set i % n_sets (search(set)) and hands the
+    set to the exchange stream (exchange(set): the all-gather + merge); a set is searched into again only after its
+    previous exchange has finished, so with two sets the exchange of step i overlaps the search of step i+1.
+    Every rank issues exactly warmup + steps exchanges, whatever its timing -- the number of collectives must not
+    depend on anything a rank measures locally.  Returns milliseconds per timed step (sync.end() / steps)."""
+    used = [False] * n_sets
+    count = 0
+
+    def one():
+        nonlocal count
+        i = count % n_sets
+        count += 1
+        if used[i]:
+            sync.wait_exchanged(i)
+        search(i)
+        sync.searched(i)
+        sync.on_exchange_stream(exchange, i)
+        used[i] = True
+
+    for _ in range(warmup):
+        one()
+    sync.drain()
+    if barrier is not None:
+        barrier()
+    sync.begin()
+    for _ in range(steps):
+        one()
+    sync.drain()
+    ms = sync.end()
+    if barrier is not None:
+        barrier()
+    return ms / max(steps, 1)
+
+
 def sharded_search(search_fn, merge_fn, k: int, rank: int, world: int, dist_mod=None, group=None):
     """search_fn() -> (ids [nq,k] GLOBAL int64, dists [nq,k]) on this rank's shard."""
     ids, dists = search_fn()

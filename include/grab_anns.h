@@ -389,8 +389,11 @@ int grab_route_status(const void* d_ws, void* stream);
 /* ------------------------------------------------------------------------------------ */
 /* Per list (one warp each): the m sorted keys d_top[list] and ncand unsorted keys            */
 /* d_cand[list, 0..ncand) -> the m smallest of their union, ascending, in d_out[list].        */
-/* m: power of two in [64,1024].  variant 0 = the routine the search kernel picks for this m  */
-/* (registers for 64 and 128, shared memory above), 1 = the shared-memory routine.            */
+/* m: power of two in [64,1024].  variant 0 = the routine the shared-list kernel picks for     */
+/* this m (registers for 64 and 128, shared memory above), 1 = the shared-memory routine,     */
+/* 2 = merge by rank (ncand <= 32, m 64 / 128), 3 = the candidates as two register-sorted     */
+/* runs folded into the list (ncand <= 256, m 64 / 128) -- the two paths of the warp-split    */
+/* kernel.                                                                                    */
 int grab_selftest_sort_merge(const uint64_t* d_top, const uint64_t* d_cand, uint64_t lists, uint32_t m,
                              uint32_t ncand, uint32_t cand_stride, int variant, uint64_t* d_out,
                              void* stream);

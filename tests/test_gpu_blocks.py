@@ -36,7 +36,7 @@ def sort_merge(grab, top, cand, variant=0):
     return out.cpu().numpy().view(np.uint64)
 
 
-@pytest.mark.parametrize("m,variant", [(64, 0), (128, 0), (64, 1), (256, 0), (512, 0)])
+@pytest.mark.parametrize("m,variant", [(64, 0), (128, 0), (64, 1), (256, 0), (512, 0), (64, 3), (128, 3)])
 @pytest.mark.parametrize("n_per_lane", [2, 4, 8])
 def test_sort_merge_reference_kat(grab, m, variant, n_per_lane):
     """test_bitonic.cu inputs: 32*N keys U(0,100), seed 42, value = index.  The merge of those candidates into an
@@ -97,6 +97,27 @@ def test_sort_merge_random_lists(grab, m):
         cand = skeys(rng.random((lists, ncand)).astype(np.float32), 100000 + np.arange(lists * ncand).reshape(lists, -1))
         got = sort_merge(grab, top, cand)
         assert np.array_equal(got, np.sort(np.concatenate([top, cand], axis=1), axis=1)[:, :m])
+
+
+@pytest.mark.parametrize("m", [64, 128])
+def test_split_kernel_merges_random_lists(grab, m):
+    """The two merge paths of the warp-split kernel on random lists: by rank (up to 32 unsorted candidates) and two
+    register-sorted runs (up to 256), lists partially filled and with expanded flags: result == the m smallest of
+    the union.  Keys are distinct, as ids in a search are."""
+    rng = np.random.default_rng(50 + m)
+    lists = 300
+    for variant, counts in [(2, [1, 2, 3, 7, 16, 31, 32]), (3, [2, 3, 17, 33, 64, 65, 128, 200, 256])]:
+        for ncand in counts:
+            ids = rng.permutation(lists * (m + ncand)).reshape(lists, m + ncand)
+            d = np.round(rng.random((lists, m + ncand)) * 60).astype(np.float32)      # equal distances, distinct ids
+            keys = skeys(d, ids)
+            top = np.sort(keys[:, :m] | (rng.random((lists, m)) < 0.3).astype(np.uint64), axis=1)
+            fill = rng.integers(0, m + 1, size=lists)
+            top[np.arange(m)[None, :] >= fill[:, None]] = MAXKEY
+            cand = keys[:, m:]
+            got = sort_merge(grab, top, cand, variant)
+            want = np.sort(np.concatenate([top, cand], axis=1), axis=1)[:, :m]
+            assert np.array_equal(got, want), (m, variant, ncand)
 
 
 def hash_run(grab, bitlen, keys, threads=64):

@@ -61,13 +61,16 @@ def test_opt_bucket_and_range_search(grab, oracle, index_mod):
     assert (ids == -1).all() and (d == -1.0).all()
 
 
-def test_opt_insert_then_search(grab, oracle, index_mod, tmp_path):
+@pytest.mark.parametrize("repair_by_distance", [False, True])
+def test_opt_insert_then_search(grab, oracle, index_mod, tmp_path, repair_by_distance):
     # tests/test_cagra_opt_insert.cu: build on the first half of every bucket, insert the second
-    # half; global recall > 90 %, local > 95 %, 0 bound errors (:359-360)
+    # half; global recall > 90 %, local > 95 %, 0 bound errors (:359-360).  Both reverse-edge rules: the
+    # reference's slot rule and the distance-aware repair.
     nb, per, dim, k = 4, 6000, 64, 10
     data = clustered(nb * per, dim, 24, 1.0, 73).reshape(nb, per, dim)
     half = per // 2
     idx = index_mod.CagraIndexOpt(dim, 32, 24, insert_batch=256)
+    idx.set_insert_mode(routed=False, repair_by_distance=repair_by_distance)
     first = data[:, :half].reshape(-1, dim)
     idx.add(first, np.repeat(np.arange(nb, dtype=np.uint64), half))
     idx.build()
@@ -102,6 +105,44 @@ def test_opt_insert_then_search(grab, oracle, index_mod, tmp_path):
     assert np.array_equal(idx2.get_graph(), g)
     ids2, _ = idx2.query_local(q, k, 0)
     assert np.array_equal(ids2, idx.query_local(q, k, 0)[0])
+
+
+@pytest.mark.parametrize("reference_rules", [False, True])
+def test_opt_streaming_insert_holds_recall(grab, oracle, index_mod, reference_rules):
+    """The streaming shape of tests/test_cagra_opt_insert_auto.cu:199-204 in small: build, then batches with
+    increasing timestamps, after each batch range queries over the newest 20 %.  Thresholds of
+    tests/test_cagra_opt_insert.cu:359-360 (0 bound errors, recall floors); with routed inserts and the
+    distance-aware repair (the class default) recall@10 must stay >= 0.95 after every batch."""
+    import torch
+    n0, nb, bn, dim, k = 24000, 4, 6000, 96, 10
+    total = n0 + nb * bn
+    data = clustered(total, dim, 40, 0.6, 81)
+    ts = np.arange(total, dtype=np.uint64)
+    idx = index_mod.CagraIndexOpt(dim, 32, 24, bucket_width=3000, insert_batch=2048)
+    idx.set_router(128, 2, 64)
+    idx.set_query_params(64, 3, 0, 8, 11)
+    if reference_rules:
+        idx.set_insert_mode(routed=False, repair_by_distance=False)
+    idx.add(data[:n0], ts[:n0])
+    idx.build()
+    rng = np.random.default_rng(82)
+    size = n0
+    for b in range(nb):
+        idx.insert(data[size:size + bn], ts[size:size + bn])
+        size += bn
+        assert idx.size() == size
+        q = data[rng.integers(0, size, 400)] + 0.05 * rng.standard_normal((400, dim)).astype(np.float32)
+        lo = np.full(400, size - size // 5, dtype=np.uint64)
+        hi = np.full(400, size, dtype=np.uint64)
+        ids, _ = idx.query_range_batch(q, k, lo, hi)
+        assert (((ids >= int(lo[0])) & (ids < size)) | (ids < 0)).all()                  # 0 bound errors
+        gt = _gt(grab, data[:size], q, k, ts[:size], int(lo[0]), size)
+        rec = oracle.recall(ids, gt)
+        assert rec > (0.90 if reference_rules else 0.95), (b, rec)
+    g = idx.get_graph()
+    assert not (g == np.arange(size, dtype=np.uint32)[:, None]).any()                   # no self loops
+    assert (g[n0:, 0] != 0xFFFFFFFF).all()                                              # inserted rows are linked
+    assert int(g[g != 0xFFFFFFFF].max()) < size
 
 
 def test_opt_per_query_ranges_with_bucket_width(grab, oracle, index_mod):

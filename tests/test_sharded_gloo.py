@@ -203,3 +203,57 @@ def test_manifest_validation(tmp_path):
     os.remove(sharded.shard_file(d, 2))
     with pytest.raises(FileNotFoundError):
         sharded.read_manifest(d, 3)
+
+
+# ------------------------------------------------------------------ step loop of the sharded benchmark
+def _loop_worker(rank, world, port, out_dir):
+    """Walks the step structure bench.py uses for the sharded path (sharded.run_pipelined) with a counting stub:
+    a rank-dependent number of collective-free load steps first (the clock-sampling loop), then warm-up + timed
+    pipelined steps with one all_gather each.  Every rank must issue the same number of collectives."""
+    sys.path.insert(0, ROOT)
+    import torch
+    import torch.distributed as dist
+    sharded = importlib.import_module("grab-anns_b200.sharded")
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    nq, kp, steps, warmup = 16, 4, 5, 3
+    counts = {"search": 0, "collectives": 0}
+    keys = [torch.zeros((nq, kp), dtype=torch.int64) for _ in range(2)]
+    merged = [None, None]
+
+    def search(i):
+        counts["search"] += 1
+        # ascending runs whose content depends on the step and the rank
+        keys[i] = (torch.arange(nq * kp, dtype=torch.int64).reshape(nq, kp) * world + rank) + 1000 * counts["search"]
+
+    def exchange(i):
+        counts["collectives"] += 1
+        out = [torch.empty_like(keys[i]) for _ in range(world)]
+        dist.all_gather(out, keys[i])
+        merged[i] = torch.sort(torch.cat(out, dim=1), dim=1)[0][:, :kp]
+
+    for _ in range(1 + 3 * rank):        # the load loop runs a rank-dependent number of times: no collective in it
+        search(0)
+    counts["search"] = 0
+    ms = sharded.run_pipelined(2, steps, warmup, search, exchange, sharded.HostSync(), barrier=dist.barrier)
+    mine = torch.tensor([counts["collectives"], counts["search"]], dtype=torch.int64)
+    every = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(every, mine)
+    same_counts = all(torch.equal(e, every[0]) for e in every)
+    last = merged[(steps + warmup - 1) % 2]
+    ref = [torch.empty_like(last) for _ in range(world)]
+    dist.all_gather(ref, last)
+    same_result = all(torch.equal(r_, ref[0]) for r_ in ref)
+    ok = same_counts and same_result and counts["collectives"] == steps + warmup and ms >= 0
+    with open(os.path.join(out_dir, f"loop{rank}.txt"), "w") as fh:
+        fh.write("ok" if ok else f"mismatch {counts} {same_counts} {same_result}")
+    dist.destroy_process_group()
+
+
+def test_two_rank_pipelined_loop_issues_equal_collectives(tmp_path):
+    import torch.multiprocessing as mp
+    port = _free_port()
+    mp.spawn(_loop_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    for r in range(2):
+        assert (tmp_path / f"loop{r}.txt").read_text() == "ok"
