@@ -17,8 +17,11 @@
 // are never observed.
 //
 // The first call on each device looks up the device address of the array (one
-// cudaGetSymbolAddress, no allocation).  Make that first call before starting any stream
-// capture.  No counterpart in the reference.
+// cudaGetSymbolAddress).  With CUDA's default lazy module loading that lookup is also the moment
+// the driver places this library's image -- and with it the array -- in the device's memory, so
+// it is the one point at which device memory is taken: make that first call (any small request
+// will do) before the host's memory pool claims the rest of the GPU, and before starting any
+// stream capture.  Later calls take nothing.  No counterpart in the reference.
 #include <mutex>
 
 #include "common.cuh"

@@ -165,16 +165,15 @@ struct SharedCtl {
   uint64_t full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2];
   uint32_t tmem_base;
   int abort_flag;
-  alignas(16) float ynorm[4][BN];  // one staging row per epilogue warp, read as float4
   uint32_t hist[4][256];    // radix-select histogram per epilogue warp
 };
 
 template <int KC>
 __global__ void __launch_bounds__(THREADS, CTAS_PER_SM)
 knn_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-              const float* __restrict__ ynorm, const ScanWindow* __restrict__ windows, uint64_t n,
-              uint32_t kblocks, uint32_t num_row_tiles, uint64_t* __restrict__ scratch,
-              uint64_t* __restrict__ out_keys, int* __restrict__ status) {
+              const ScanWindow* __restrict__ windows, uint64_t n, uint32_t kblocks, uint32_t last_kk,
+              uint32_t num_row_tiles, uint64_t* __restrict__ scratch, uint64_t* __restrict__ out_keys,
+              int* __restrict__ status) {
   constexpr uint32_t CAP = 2 * KC;
   constexpr int NREG = CAP / 32;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -258,10 +257,12 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             const uint32_t a_addr = smem_u32(ring + s * STAGE_BYTES);
             const uint64_t da = smem_desc_sw128(a_addr);
             const uint64_t db = smem_desc_sw128(a_addr + BM * BK * 2);
+            // the last K block holds operand columns only in its first last_kk slices of 16 (the rest is zero padding)
+            const uint32_t nkk = kb + 1 == kblocks ? last_kk : BK / 16;
 #pragma unroll
             for (uint32_t kk = 0; kk < BK / 16; ++kk) {
               // 16 bf16 = 32 bytes further along K inside the swizzled row: +2 in 16-byte units
-              tc_mma_bf16(d_tmem, da + 2 * kk, db + 2 * kk, kIdesc, (kb | kk) != 0 ? 1u : 0u);
+              if (kk < nkk) tc_mma_bf16(d_tmem, da + 2 * kk, db + 2 * kk, kIdesc, (kb | kk) != 0 ? 1u : 0u);
             }
             tc_commit(smem_u32(&ctl->empty[s]));  // stage reusable once these MMAs have read it
           }
@@ -289,71 +290,46 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
       if (row_valid) w = windows[t.row0 + r_local];
       uint32_t cnt = 0;
       float thr = __int_as_float(0x7f800000);  // +inf
-      float ynext[BN / 32];
-      {
-        uint32_t j0 = t.jb;
-        while (j0 < t.je && tile_skipped(t, j0)) ++j0;
-#pragma unroll
-        for (int i = 0; i < BN / 32; ++i) {
-          const uint64_t c = static_cast<uint64_t>(j0) * BN + i * 32 + lane;
-          ynext[i] = (j0 < t.je && c < n) ? __ldg(ynorm + c) : 0.0f;
-        }
-      }
       for (uint32_t j = t.jb; j < t.je && ok; ++j) {
         if (tile_skipped(t, j)) continue;
         const uint32_t acc = tile & 1, acc_phase = (tile >> 1) & 1;
         const uint32_t c0 = j * BN;
-        // column norms of this tile: prefetched into registers while the previous tile was
-        // processed, staged per warp in shared memory (no cross-warp barrier in the epilogue)
-        float* yn = ctl->ynorm[warp - 2];
-        __syncwarp();
-#pragma unroll
-        for (int i = 0; i < BN / 32; ++i) yn[i * 32 + lane] = ynext[i];
-        __syncwarp();
-        {
-          uint32_t jn = j + 1;  // next tile this CTA will visit in this row tile
-          while (jn < t.je && tile_skipped(t, jn)) ++jn;
-          if (jn < t.je) {
-#pragma unroll
-            for (int i = 0; i < BN / 32; ++i) {
-              const uint64_t c = static_cast<uint64_t>(jn) * BN + i * 32 + lane;
-              ynext[i] = c < n ? __ldg(ynorm + c) : 0.0f;
-            }
-          }
-        }
         if (!mbar_wait(smem_u32(&ctl->tmem_full[acc]), acc_phase, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const bool need_mask = !(c0 >= t.safe_lo && c0 + BN <= t.safe_hi && (c0 + BN <= t.ex_lo || c0 >= t.ex_hi));
         const uint32_t taddr = tmem_base + ((quarter * 32) << 16) + acc * BN;
 
-        // one 32-column chunk: branch-free threshold mask, then the (rare) appends
+        // One 32-column chunk.  The accumulator already IS the ranking distance |y|^2 - 2 x.y (the column norm rides
+        // along the contraction as three extra K columns against ones), so the common case costs one min per value:
+        // a min tree over the chunk, one compare with the row's threshold, one warp vote.  Only chunks in which some
+        // row has a value below its threshold build the per-element mask and append.
         auto process = [&](uint32_t (&v)[32], uint32_t chunk) {
-          const uint32_t cbase = c0 + chunk * 32;
-          const float4* yn4 = reinterpret_cast<const float4*>(yn + chunk * 32);
-          uint32_t m = 0;
+          float m8[8];
 #pragma unroll
-          for (int i4 = 0; i4 < 8; ++i4) {
-            const float4 y = yn4[i4];
-            const float d0 = __fmaf_rn(-2.0f, __uint_as_float(v[4 * i4 + 0]), y.x);
-            const float d1 = __fmaf_rn(-2.0f, __uint_as_float(v[4 * i4 + 1]), y.y);
-            const float d2 = __fmaf_rn(-2.0f, __uint_as_float(v[4 * i4 + 2]), y.z);
-            const float d3 = __fmaf_rn(-2.0f, __uint_as_float(v[4 * i4 + 3]), y.w);
-            v[4 * i4 + 0] = __float_as_uint(d0);
-            v[4 * i4 + 1] = __float_as_uint(d1);
-            v[4 * i4 + 2] = __float_as_uint(d2);
-            v[4 * i4 + 3] = __float_as_uint(d3);
-            m |= (d0 < thr ? 1u : 0u) << (4 * i4 + 0);
-            m |= (d1 < thr ? 1u : 0u) << (4 * i4 + 1);
-            m |= (d2 < thr ? 1u : 0u) << (4 * i4 + 2);
-            m |= (d3 < thr ? 1u : 0u) << (4 * i4 + 3);
-          }
-          uint32_t allowed = row_valid ? 0xFFFFFFFFu : 0u;
-          if (need_mask) allowed &= range_bits(cbase, w.begin, w.end) & ~range_bits(cbase, w.xbegin, w.xend);
-          m &= allowed;
-          while (m) {  // rare once the threshold has tightened
-            const uint32_t i = __ffs(m) - 1;
-            m &= m - 1;
-            my_buf[cnt++] = make_key(__uint_as_float(pick32(v, i)), cbase + i);
+          for (int i = 0; i < 8; ++i)
+            m8[i] = fminf(fminf(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1])),
+                          fminf(__uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3])));
+          const float mn = fminf(fminf(fminf(m8[0], m8[1]), fminf(m8[2], m8[3])),
+                                 fminf(fminf(m8[4], m8[5]), fminf(m8[6], m8[7])));
+          const bool hit = row_valid && mn < thr;
+          if (!__any_sync(0xFFFFFFFFu, hit)) return;
+          if (hit) {
+            const uint32_t cbase = c0 + chunk * 32;
+            uint32_t m0 = 0, m1 = 0, m2 = 0, m3 = 0;  // four independent accumulators: no serial chain through one mask
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              m0 |= (__uint_as_float(v[i]) < thr ? 1u : 0u) << i;
+              m1 |= (__uint_as_float(v[8 + i]) < thr ? 1u : 0u) << (8 + i);
+              m2 |= (__uint_as_float(v[16 + i]) < thr ? 1u : 0u) << (16 + i);
+              m3 |= (__uint_as_float(v[24 + i]) < thr ? 1u : 0u) << (24 + i);
+            }
+            uint32_t m = (m0 | m1) | (m2 | m3);
+            if (need_mask) m &= range_bits(cbase, w.begin, w.end) & ~range_bits(cbase, w.xbegin, w.xend);
+            while (m) {
+              const uint32_t i = __ffs(m) - 1;
+              m &= m - 1;
+              my_buf[cnt++] = make_key(__uint_as_float(pick32(v, i)), cbase + i);
+            }
           }
           if (__any_sync(0xFFFFFFFFu, cnt > CAP - 32)) {
             const uint2 r = compress_rows<KC>(warp_buf, hist, lane, cnt, thr, false);
@@ -426,12 +402,15 @@ __global__ void mean_final_kernel(const float* __restrict__ partial, uint32_t nc
   mean[d] = s / static_cast<float>(n);
 }
 
-// fp32 rows -> bf16 operands.  split == 0: A = B = bf16(x - mean), K = dim.
-// split == 1: hi = bf16(v), lo = bf16(v - hi); A = [hi, lo, hi], B = [hi, hi, lo], K = 3*dim.
-// norm[r] = sum (x - mean)^2 (L2) or 0 (inner product).  One warp per row.
+// fp32 rows -> bf16 operands of  acc(x, y) = |y|^2 - 2 x.y  (the ranking distance itself; inner product: -2 x.y).
+// With v = x - mean:  split == 0: A = [bf16(v), 1, 1, 1], B = [-2 bf16(v), n0, n1, n2], K = dim + 3;
+// split == 1: hi = bf16(v), lo = bf16(v - hi): A = [hi, lo, hi, 1, 1, 1], B = -2 [hi, hi, lo] then n0, n1, n2,
+// K = 3 dim + 3.  n0 + n1 + n2 = |v|^2 to 24 bits (three bf16 terms), carried through the contraction against the
+// ones, so that the epilogue has no arithmetic left to do; -2 x is exact in bf16.  Columns up to kp are zero.
+// One warp per row.
 __global__ void prep_operands_kernel(const float* __restrict__ x, uint64_t n, uint32_t dim, const float* __restrict__ mean,
                                      int split, int metric, uint32_t kp, __nv_bfloat16* __restrict__ a,
-                                     __nv_bfloat16* __restrict__ b, float* __restrict__ norm) {
+                                     __nv_bfloat16* __restrict__ b) {
   const uint64_t r = (blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x) >> 5;
   const uint32_t lane = threadIdx.x & 31;
   if (r >= n) return;
@@ -440,21 +419,34 @@ __global__ void prep_operands_kernel(const float* __restrict__ x, uint64_t n, ui
     const float v = x[r * dim + d] - (mean ? mean[d] : 0.0f);
     s = __fmaf_rn(v, v, s);
     const __nv_bfloat16 hi = __float2bfloat16_rn(v);
+    const __nv_bfloat16 hi2 = __float2bfloat16_rn(-2.0f * __bfloat162float(hi));
     if (!split) {
       a[r * kp + d] = hi;
+      b[r * kp + d] = hi2;
     } else {
       const __nv_bfloat16 lo = __float2bfloat16_rn(v - __bfloat162float(hi));
+      const __nv_bfloat16 lo2 = __float2bfloat16_rn(-2.0f * __bfloat162float(lo));
       a[r * kp + d] = hi; a[r * kp + dim + d] = lo; a[r * kp + 2 * dim + d] = hi;
-      b[r * kp + d] = hi; b[r * kp + dim + d] = hi; b[r * kp + 2 * dim + d] = lo;
+      b[r * kp + d] = hi2; b[r * kp + dim + d] = hi2; b[r * kp + 2 * dim + d] = lo2;
     }
   }
+  for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, off);
   const uint32_t used = split ? 3 * dim : dim;
   for (uint32_t d = used + lane; d < kp; d += 32) {
-    a[r * kp + d] = __float2bfloat16_rn(0.0f);
-    if (split) b[r * kp + d] = __float2bfloat16_rn(0.0f);
+    a[r * kp + d] = __float2bfloat16_rn(d < used + 3 ? 1.0f : 0.0f);
+    b[r * kp + d] = __float2bfloat16_rn(0.0f);
   }
-  for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, off);
-  if (lane == 0) norm[r] = metric == GRAB_METRIC_L2 ? s : 0.0f;
+  __syncwarp();
+  if (lane == 0) {
+    const float nrm = metric == GRAB_METRIC_L2 ? s : 0.0f;
+    const __nv_bfloat16 n0 = __float2bfloat16_rn(nrm);
+    const float r1 = nrm - __bfloat162float(n0);
+    const __nv_bfloat16 n1 = __float2bfloat16_rn(r1);
+    const __nv_bfloat16 n2 = __float2bfloat16_rn(r1 - __bfloat162float(n1));
+    b[r * kp + used] = n0;
+    b[r * kp + used + 1] = n1;
+    b[r * kp + used + 2] = n2;
+  }
 }
 
 // ------------------------------------------------------------------ exact re-rank
@@ -530,9 +522,10 @@ int knn_tc_impl(const float* d_dataset, uint64_t n, uint32_t dim, int metric, co
   GRAB_REQUIRE(k >= 1 && want <= 256, "knn_tc: k %u too large for the tensor-core path (max 204)", k);
   const uint32_t kc = want <= 128 ? 128 : 256;
   const int split = precision == 2;
-  const uint32_t kused = split ? 3 * dim : dim;
+  const uint32_t kused = (split ? 3 * dim : dim) + 3;  // + the three column-norm terms
   const uint32_t kp = (kused + BK - 1) / BK * BK;
   const uint32_t kblocks = kp / BK;
+  const uint32_t last_kk = (kused - (kblocks - 1) * BK + 15) / 16;  // 16-wide MMA slices of the last K block in use
   const uint32_t num_row_tiles = static_cast<uint32_t>((n + BM - 1) / BM);
   int dev = 0, sms = 0;
   GRAB_CUDA_TRY(cudaGetDevice(&dev));
@@ -541,12 +534,11 @@ int knn_tc_impl(const float* d_dataset, uint64_t n, uint32_t dim, int metric, co
   const uint32_t grid = num_row_tiles < max_ctas ? num_row_tiles : max_ctas;
 
   StageTimer tm(mode == 0 ? "knn_tc (own block)" : "knn_tc (other blocks)");
-  ScopedDeviceBuffer offs, wins, a_op, b_op, norm, mean, partial, scratch, keys, status;
+  ScopedDeviceBuffer offs, wins, a_op, b_op, mean, partial, scratch, keys, status;
   GRAB_CUDA_TRY(offs.alloc(sizeof(uint64_t) * (num_blocks + 1)));
   GRAB_CUDA_TRY(wins.alloc(sizeof(ScanWindow) * n));
   GRAB_CUDA_TRY(a_op.alloc(sizeof(__nv_bfloat16) * n * kp));
-  if (split) GRAB_CUDA_TRY(b_op.alloc(sizeof(__nv_bfloat16) * n * kp));
-  GRAB_CUDA_TRY(norm.alloc(sizeof(float) * n));
+  GRAB_CUDA_TRY(b_op.alloc(sizeof(__nv_bfloat16) * n * kp));
   GRAB_CUDA_TRY(scratch.alloc(sizeof(uint64_t) * static_cast<uint64_t>(grid) * BM * 2 * kc));
   GRAB_CUDA_TRY(keys.alloc(sizeof(uint64_t) * n * kc));
   GRAB_CUDA_TRY(status.alloc(sizeof(int)));
@@ -566,9 +558,9 @@ int knn_tc_impl(const float* d_dataset, uint64_t n, uint32_t dim, int metric, co
     d_mean = mean.as<float>();
   }
   __nv_bfloat16* pa = a_op.as<__nv_bfloat16>();
-  __nv_bfloat16* pb = split ? b_op.as<__nv_bfloat16>() : pa;
+  __nv_bfloat16* pb = b_op.as<__nv_bfloat16>();
   prep_operands_kernel<<<(unsigned)((n * 32 + 255) / 256), 256, 0, st>>>(d_dataset, n, dim, d_mean, split, metric, kp, pa,
-                                                                      pb, norm.as<float>());
+                                                                      pb);
   GRAB_CUDA_TRY(cudaGetLastError());
 
   tm.mark("alloc + operands");
@@ -581,12 +573,12 @@ int knn_tc_impl(const float* d_dataset, uint64_t n, uint32_t dim, int metric, co
   const size_t smem = STAGES * STAGE_BYTES + sizeof(SharedCtl) + 1024;
   if (kc == 128) {
     GRAB_CUDA_TRY(cudaFuncSetAttribute(knn_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    knn_tc_kernel<128><<<grid, THREADS, smem, st>>>(map_a, map_b, norm.as<float>(), wins.as<ScanWindow>(), n, kblocks,
+    knn_tc_kernel<128><<<grid, THREADS, smem, st>>>(map_a, map_b, wins.as<ScanWindow>(), n, kblocks, last_kk,
                                                    num_row_tiles, scratch.as<uint64_t>(), keys.as<uint64_t>(),
                                                    status.as<int>());
   } else {
     GRAB_CUDA_TRY(cudaFuncSetAttribute(knn_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    knn_tc_kernel<256><<<grid, THREADS, smem, st>>>(map_a, map_b, norm.as<float>(), wins.as<ScanWindow>(), n, kblocks,
+    knn_tc_kernel<256><<<grid, THREADS, smem, st>>>(map_a, map_b, wins.as<ScanWindow>(), n, kblocks, last_kk,
                                                    num_row_tiles, scratch.as<uint64_t>(), keys.as<uint64_t>(),
                                                    status.as<int>());
   }

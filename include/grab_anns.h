@@ -115,8 +115,10 @@ int grab_exact_search(const float* d_dataset, uint64_t n, uint32_t dim, int metr
  * scratch is a fixed GRAB_NOALLOC_SCRATCH_BYTES array inside the library, held by every GPU that
  * loads it.  Requests needing more (grab_exact_search_workspace_bytes) fail with
  * GRAB_ERR_WORKSPACE.  All calls on a device share the array: calls that overlap on the GPU
- * race.  The first call on a device resolves the array's address; make it before any stream
- * capture.  This entry point has no counterpart in the reference. */
+ * race.  The first call on a device resolves the array's address; with lazy module loading that
+ * is also when the array is placed in device memory, so make that call before the host's pool
+ * claims the GPU and before any stream capture.  This entry point has no counterpart in the
+ * reference. */
 #define GRAB_NOALLOC_SCRATCH_BYTES (8u << 20)
 int grab_exact_search_noalloc(const float* d_dataset, uint64_t n, uint32_t dim, int metric,
                               const grab_filter* filter, const float* d_queries, uint64_t nq,

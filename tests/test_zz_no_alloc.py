@@ -27,9 +27,13 @@ def _noalloc(grab, data, queries, k, flt, metric=0):
     ids = torch.full((nq, k), -7, dtype=torch.int64, device="cuda")
     dists = torch.full((nq, k), -7.0, dtype=torch.float32, device="cuda")
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]        # device-wide figure, taken around the C call alone
     rc = grab.lib().grab_exact_search_noalloc(grab._p(data), C.c_uint64(n), C.c_uint32(dim), C.c_int(metric),
                                                C.byref(flt) if flt is not None else None, grab._p(queries),
                                                C.c_uint64(nq), C.c_uint32(k), grab._p(ids), grab._p(dists), stream)
+    torch.cuda.synchronize()
+    _noalloc.taken = free_before - torch.cuda.mem_get_info()[0]
     return rc, ids, dists
 
 
@@ -49,11 +53,19 @@ def test_noalloc_matches_allocating_entry_point_twice(grab):
     lo2 = _t(rng.integers(0, n - 3000, 300).astype(np.int64))
     hi2 = lo2 + 3000
     f2 = grab.make_filter(grab.FILTER_TS_RANGE, ts=ts, lo=lo2, hi=hi2, ts_sorted=False)
-    for q, k, f in [(q1, 10, f1), (q2, 50, f2)]:
-        want_ids, want_d = grab.exact_search(data, q, k, flt=f)
-        rc, got_ids, got_d = _noalloc(grab, data, q, k, f)
+    # call 3: enough queries that every query is one CTA (no partial lists), inner product, label masks
+    q3 = _t(rng.standard_normal((1300, dim)).astype(np.float32))
+    labels = _t(rng.integers(0, 8, n).astype(np.uint8))
+    masks = _t(rng.integers(1, 256, 1300).astype(np.int32))
+    f3 = grab.make_filter(grab.FILTER_LABELS, labels=labels, masks=masks)
+    for call, (q, k, f, metric) in enumerate([(q1, 10, f1, 0), (q2, 50, f2, 0), (q3, 10, f3, 1)]):
+        want_ids, want_d = grab.exact_search(data, q, k, metric=metric, flt=f)
+        rc, got_ids, got_d = _noalloc(grab, data, q, k, f, metric)
         assert rc == 0, grab.lib().grab_last_error()
-        torch.cuda.synchronize()
+        if call > 0:
+            # the call took no device memory (only the very first call on a device may: that is when the driver
+            # places the library image with the scratch array, see the entry point's notes)
+            assert _noalloc.taken <= 0, _noalloc.taken
         assert torch.equal(got_ids, want_ids)          # same tolerance as the exact-path tests: bit-exact
         assert torch.equal(got_d, want_d)
         assert (got_ids >= 0).all()
