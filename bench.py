@@ -92,6 +92,8 @@ def parse():
     ap.add_argument("--insert-reference-rules", action="store_true",
                     help="C4: the reference's insert rules (random seeds, pseudo-random reverse-edge slots) instead of "
                          "routed inserts with the distance-aware repair")
+    ap.add_argument("--insert-routed", type=int, default=-1, help="C4: 1/0 routed insert searches (-1 = class default)")
+    ap.add_argument("--insert-repair", type=int, default=-1, help="C4: reverse-edge repair mode 0/1/2 (-1 = class default)")
     ap.add_argument("--insert-iters", type=int, default=0, help="C4: iterations of the routed insert searches (0 = 16)")
     a = ap.parse_args()
     return a
@@ -100,6 +102,25 @@ def parse():
 def resolve_defaults(args, w):
     """Workload-dependent defaults (the swept operating points recorded in the design notes)."""
     big_k = w["k"] >= 100
+    if args.workload == "C4":
+        # 96-d isotropic clusters: all cluster mates are nearly equidistant, so recall is the fraction of the query's
+        # cluster (inside the window) that the walk looks at, and that population grows with every batch -- a long
+        # walk over a 128-entry list (swept: 64 / 4 / 32 iterations loses 12 points over ten batches)
+        if args.itopk == 0:
+            args.itopk = 128
+        if args.width == 0:
+            args.width = 4
+        if args.max_iter == 0:
+            args.max_iter = 48
+        if args.hash_bitlen == 0:
+            args.hash_bitlen = 13
+    if w["degree"] <= 32:   # degree-32 graphs (C1, C4) reach fewer nodes per iteration: wider and longer walks
+        if args.width == 0:
+            args.width = 4
+        if args.max_iter == 0 and args.router_centroids != 0:
+            args.max_iter = 10
+        if args.hash_bitlen == 0:
+            args.hash_bitlen = 12
     if args.itopk == 0:
         args.itopk = max(64, w.get("itopk", 64))
     if args.width == 0:
@@ -619,19 +640,20 @@ def recall_of(res, gt):
 
 def shard_schedule(args, G, k, centroids, probes):
     """Per-shard search effort of a G-way id-striped index.  A stripe holds 1/G of every neighbourhood, so of the
-    global top-k it owns Binomial(k, 1/G) -- its own nearest few, the first entries a graph search settles: the run
-    it sends is k/G + 4 sigma + 1 long, and routing / iterations shrink with G (swept so that the MERGED recall
-    stays at the single index's)."""
+    global top-k it owns Binomial(k, 1/G): the run it sends is k/G + 4.5 sigma + 2 long instead of k.  The search
+    effort itself shrinks only a little with G -- a stripe's graph walk still has to reach the query's neighbourhood
+    and look at a few hundred vectors there (swept on one GPU with --emulate-shards so that the MERGED recall stays
+    at the single index's: 4 iterations from 48 seeds instead of 5 from 64 hold recall@10 0.97 at G = 2, 4, 8;
+    3 iterations drop it to 0.94, 2 to 0.83)."""
     p = 1.0 / G
-    run = k if G == 1 else min(k, int(math.ceil(k * p + 4.0 * math.sqrt(k * p * (1 - p)) + 1)))
+    run = k if G == 1 else min(k, int(math.ceil(k * p + 4.5 * math.sqrt(k * p * (1 - p)) + 2)))
     big_k = k >= 100
-    iters = {1: args.max_iter, 2: max(3, args.max_iter - 1), 4: max(3, args.max_iter - 2),
-             8: max(2, args.max_iter - 3)}.get(G, max(2, args.max_iter - 3))
-    if big_k:
-        iters = {1: args.max_iter, 2: max(6, args.max_iter * 3 // 4), 4: max(5, args.max_iter * 7 // 12),
-                 8: max(4, args.max_iter // 2)}.get(G, max(4, args.max_iter // 2))
-    seeds = {1: args.seeds, 2: max(16, args.seeds * 3 // 4), 4: max(16, args.seeds // 2),
-             8: max(16, args.seeds * 3 // 8)}.get(G, max(16, args.seeds // 2))
+    if G == 1:
+        iters, seeds = args.max_iter, args.seeds
+    elif big_k:
+        iters, seeds = max(6, args.max_iter * 3 // 4), args.seeds
+    else:
+        iters, seeds = max(3, args.max_iter - 1), max(16, args.seeds * 3 // 4)
     return {"run_length": args.shard_run or run, "iterations": args.shard_iters or iters,
             "seeds": args.shard_seeds or seeds,
             "centroids": args.shard_centroids or (max(64, centroids // G) if centroids else 0),
@@ -897,7 +919,9 @@ def run_c4(args):
     ix.set_query_params(args.itopk, args.width, 0, args.max_iter, args.hash_bitlen)
     ix.set_router(args.router_centroids, args.probes, args.seeds)
     if args.insert_reference_rules:
-        ix.set_insert_mode(routed=False, repair_by_distance=False)
+        ix.set_insert_mode(routed=False, repair_mode=0)
+    elif args.insert_routed >= 0 or args.insert_repair >= 0:
+        ix.set_insert_mode(routed=args.insert_routed != 0, repair_mode=max(args.insert_repair, 0) if args.insert_repair >= 0 else 1)
     if args.insert_iters:
         ix.set_insert_search_params(128, 4, args.insert_iters, 12)
     t0 = time.perf_counter()
@@ -954,7 +978,8 @@ def run_c4(args):
                        "router_centroids": args.router_centroids, "probes": args.probes, "routed_seeds": args.seeds,
                        "insert_rules": "reference (random seeds, pseudo-random reverse-edge slots)"
                                        if args.insert_reference_rules else
-                                       "routed insert searches, distance-aware reverse-edge repair",
+                                       f"routed={args.insert_routed} repair_mode={args.insert_repair} (-1 = class "
+                                       "default: routed insert searches, every request takes the farthest weak-half slot)",
                        "insert_batch": args.insert_batch_size or 4096},
             "build": {"seconds": build_s, "mvec_per_s": n0 / build_s / 1e6},
             "batches": per_batch,

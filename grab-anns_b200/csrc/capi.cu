@@ -108,7 +108,7 @@ int inject_reverse_impl(uint32_t*, uint64_t, uint32_t, uint32_t, uint32_t, cudaS
 int update_topology_v1_impl(uint32_t*, const int64_t*, uint64_t, uint64_t, uint32_t, uint32_t, cudaStream_t);
 int update_topology_opt_impl(uint32_t*, const uint64_t*, int64_t*, int64_t*, uint64_t, uint64_t, uint64_t,
                              uint32_t, uint32_t, uint32_t, uint32_t, cudaStream_t, const float* = nullptr, uint32_t = 0,
-                             int = 0, bool = true);
+                             int = 0, bool = true, int = 1);
 
 #define GRAB_TRY(expr)            \
   do {                            \

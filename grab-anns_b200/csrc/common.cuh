@@ -223,7 +223,13 @@ struct InsertOptions {
   const grab_router* router = nullptr;  // seeds of both searches from the entry-point router (old nodes only)
   uint32_t probes = 2, routed_seeds = 32;
   bool bucket_has_old_members = false;  // with a router: whether the bucket search can be seeded at all
-  bool repair_by_distance = false;      // reverse edges replace the farthest neighbour instead of a random slot
+  // id range of the target bucket's members among the old nodes (contiguous: bucket ids are non-decreasing in the
+  // id) and the number of leading ids the router's member lists cover.  A bucket the router does not cover
+  // completely (nodes inserted after its last assignment) gets uniform seeds from its id range instead.
+  uint64_t bucket_begin = 0, bucket_end = 0, router_covers = 0;
+  // reverse edges: 0 = the reference's pseudo-random slot; 1 = every request takes the slot of the farthest old
+  // neighbour in the weak half; 2 = a request replaces the farthest neighbour only when it is closer
+  int repair_mode = 0;
   bool sync = true;                     // false: only enqueue on `stream`
   cudaStream_t stream = nullptr;
 };

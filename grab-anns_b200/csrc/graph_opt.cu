@@ -835,18 +835,23 @@ mail_apply_kernel(uint32_t* __restrict__ graph, const uint64_t* __restrict__ buc
   }
 }
 
-// Distance-aware reverse-edge repair (an alternative to the reference's rule above, which overwrites a
-// pseudo-random slot -- 10 % strong half / 90 % weak half, insert.cu:693-712 -- whether or not the new node is any
-// closer than the neighbour it evicts; over many batches that erodes the rows of old nodes and recall drifts).
-// One warp per touched node t and column region [c0, c1): distances from t to the region's current neighbours and
-// to every new node that asked to be linked (up to 256 requests), then the requests are taken nearest first and
-// each replaces the FARTHEST current neighbour as long as it is closer than that one.  Empty slots count as
-// infinitely far, a request already present is skipped.  Ties go to the lower id / lower slot, so the result does
-// not depend on the order in which the requests were posted.
+// Distance-aware reverse-edge repair (alternatives to the reference's rule above, which overwrites a pseudo-random
+// slot -- 10 % strong half / 90 % weak half, insert.cu:693-712 -- whatever it holds).  One warp per touched node t
+// and column region [c0, c1): distances from t to the region's current neighbours and to every new node that asked
+// to be linked (up to 256 requests); the requests are then taken nearest first.
+//   ALWAYS = 1 (the class default): like the reference, every request up to the mailbox capacity (half the region)
+//     gets a slot, so that every new node receives the in-edges that make it reachable -- but the slot it takes is
+//     the FARTHEST old neighbour in the weak half of the region, not a random one; slots given to new nodes in this
+//     pass are not evicted again.
+//   ALWAYS = 0: a request replaces the farthest neighbour of the whole region only when it is closer (rows stay
+//     "the nearest seen so far"; on data whose neighbourhoods are crowded few new nodes earn an in-edge, which
+//     costs recall over the new region -- kept for comparison).
+// Empty slots count as infinitely far, a request already present is skipped.  Ties go to the lower id / lower
+// slot, so the result does not depend on the order in which the requests were posted.
 constexpr int kRepairMaxRegion = 256;
 constexpr int kRepairMaxReq = 256;
 
-template <int METRIC, int REMOTE>
+template <int METRIC, int REMOTE, int ALWAYS>
 __global__ void __launch_bounds__(kSelWarps * 32)
 mail_apply_dist_kernel(uint32_t* __restrict__ graph, const float* __restrict__ data, uint32_t dim,
                        const uint32_t* __restrict__ touched, const MailMeta* __restrict__ meta,
@@ -902,7 +907,10 @@ mail_apply_dist_kernel(uint32_t* __restrict__ graph, const float* __restrict__ d
     if (dup) reqd[j] = kFltMax;
   }
   __syncwarp();
-  for (uint32_t round = 0; round < nreq; ++round) {
+  // ALWAYS: victims come from the weak half only, at most as many as the reference's mailbox holds
+  const uint32_t v0 = ALWAYS ? rlen / 2 : 0;
+  const uint32_t max_rounds = ALWAYS ? (rlen / 2 < nreq ? rlen / 2 : nreq) : nreq;
+  for (uint32_t round = 0; round < max_rounds; ++round) {
     // nearest remaining request, by (distance, id)
     uint64_t best = kMaxKey;
     uint32_t best_j = 0;
@@ -919,9 +927,10 @@ mail_apply_dist_kernel(uint32_t* __restrict__ graph, const float* __restrict__ d
       if (ok < best) { best = ok; best_j = oj; }
     }
     if (best == kMaxKey) break;
-    // farthest current neighbour of the region, by (distance, slot) descending
+    // farthest current neighbour among the candidate victims, by (distance, slot) descending; slots handed to a
+    // new node in this pass carry -FLT_MAX and are never picked while an old neighbour is left
     uint64_t worst = 0;
-    for (uint32_t x = lane; x < rlen; x += 32) {
+    for (uint32_t x = v0 + lane; x < rlen; x += 32) {
       const uint64_t key = (static_cast<uint64_t>(float_to_ordered(rowd[x])) << 32) | (rlen - 1 - x);
       if (key >= worst) worst = key;
     }
@@ -931,10 +940,14 @@ mail_apply_dist_kernel(uint32_t* __restrict__ graph, const float* __restrict__ d
     }
     const uint32_t slot = rlen - 1 - static_cast<uint32_t>(worst & 0xFFFFFFFFull);
     const float dnew = key_dist(best);
-    if (!(float_to_ordered(dnew) < static_cast<uint32_t>(worst >> 32))) break;  // every remaining request is farther still
+    if (ALWAYS) {
+      if (static_cast<uint32_t>(worst >> 32) == float_to_ordered(-kFltMax)) break;  // only new nodes left in the weak half
+    } else {
+      if (!(float_to_ordered(dnew) < static_cast<uint32_t>(worst >> 32))) break;  // every remaining request is farther still
+    }
     if (lane == 0) {
       row[slot] = key_id(best);
-      rowd[slot] = dnew;
+      rowd[slot] = ALWAYS ? -kFltMax : dnew;
       reqd[best_j] = kFltMax;
     }
     __syncwarp();
@@ -951,13 +964,14 @@ __global__ void mail_clear_kernel(const uint32_t* __restrict__ touched, const Ma
   if (i < meta->n_touched) counts[touched[i]] = 0;
 }
 
-// d_dataset == NULL: the reference's slot rule.  Otherwise the distance-aware repair (regions of up to 256 columns).
+// d_dataset == NULL: the reference's slot rule.  Otherwise the distance-aware repair (regions of up to 256 columns),
+// repair_mode 1 = every request takes the farthest weak-half slot, 2 = only requests closer than the farthest.
 // sync: wait for the stream before returning (the stateless entry points do, the batched class insert does not).
 int update_topology_opt_impl(uint32_t* d_graph, const uint64_t* d_bucket, int64_t* d_local_knn,
                              int64_t* d_global_knn, uint64_t num_existing, uint64_t num_new,
                              uint64_t target_bucket, uint32_t total_deg, uint32_t local_deg,
                              uint32_t k_local, uint32_t k_global, cudaStream_t st, const float* d_dataset,
-                             uint32_t dim, int metric, bool sync) {
+                             uint32_t dim, int metric, bool sync, int repair_mode) {
   GRAB_REQUIRE(d_graph && d_bucket && d_local_knn && d_global_knn, "update_topology_opt: null pointer");
   GRAB_REQUIRE(local_deg >= 2 && local_deg < total_deg && total_deg - local_deg >= 2 && total_deg <= 512,
                "update_topology_opt: bad degrees %u/%u", local_deg, total_deg);
@@ -1009,11 +1023,17 @@ int update_topology_opt_impl(uint32_t* d_graph, const uint64_t* d_bucket, int64_
     group_fill_kernel<<<eg, 256, 0, st>>>(e, total, offsets, cursor, csr);
     const unsigned ag = (unsigned)((total + kSelWarps - 1) / kSelWarps);  // upper bound on touched nodes
     if (d_dataset && e.c1 - e.c0 <= kRepairMaxRegion) {
-#define GRAB_REPAIR(M, R)                                                                                        \
-  mail_apply_dist_kernel<M, R><<<ag, kSelWarps * 32, 0, st>>>(d_graph, d_dataset, dim, tl, meta + pass, counts, \
-                                                             offsets, cursor, csr, e.c0, e.c1, total_deg)
-      if (metric == GRAB_METRIC_L2) { if (pass == 0) GRAB_REPAIR(GRAB_METRIC_L2, 0); else GRAB_REPAIR(GRAB_METRIC_L2, 1); }
-      else { if (pass == 0) GRAB_REPAIR(GRAB_METRIC_IP, 0); else GRAB_REPAIR(GRAB_METRIC_IP, 1); }
+#define GRAB_REPAIR(M, R, A)                                                                                       \
+  mail_apply_dist_kernel<M, R, A><<<ag, kSelWarps * 32, 0, st>>>(d_graph, d_dataset, dim, tl, meta + pass, counts, \
+                                                                offsets, cursor, csr, e.c0, e.c1, total_deg)
+#define GRAB_REPAIR_M(M)                                                    \
+  do {                                                                      \
+    if (repair_mode == 2) { if (pass == 0) GRAB_REPAIR(M, 0, 0); else GRAB_REPAIR(M, 1, 0); } \
+    else { if (pass == 0) GRAB_REPAIR(M, 0, 1); else GRAB_REPAIR(M, 1, 1); }                  \
+  } while (0)
+      if (metric == GRAB_METRIC_L2) GRAB_REPAIR_M(GRAB_METRIC_L2);
+      else GRAB_REPAIR_M(GRAB_METRIC_IP);
+#undef GRAB_REPAIR_M
 #undef GRAB_REPAIR
     } else if (pass == 0)
       mail_apply_kernel<0><<<ag, kSelWarps * 32, 0, st>>>(d_graph, d_bucket, tl, meta + pass, counts, counts_l, offsets,

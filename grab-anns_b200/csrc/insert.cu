@@ -19,7 +19,7 @@ int knn_blocks_impl(const float*, uint64_t, uint32_t, int, const uint64_t*, uint
 int update_topology_v1_impl(uint32_t*, const int64_t*, uint64_t, uint64_t, uint32_t, uint32_t, cudaStream_t);
 int update_topology_opt_impl(uint32_t*, const uint64_t*, int64_t*, int64_t*, uint64_t, uint64_t, uint64_t,
                              uint32_t, uint32_t, uint32_t, uint32_t, cudaStream_t, const float* = nullptr, uint32_t = 0,
-                             int = 0, bool = true);
+                             int = 0, bool = true, int = 1);
 
 #define GRAB_TRY(expr)              \
   do {                              \
@@ -97,6 +97,18 @@ int insert_v1_impl(const float* d_dataset, uint64_t num_existing, uint64_t num_n
   GRAB_TRY(update_topology_v1_impl(d_graph, ids.as<int64_t>(), num_existing, num_new, degree, search_k, nullptr));
   GRAB_CUDA_TRY(cudaDeviceSynchronize());
   return GRAB_OK;
+}
+
+// Uniform pseudo-random seeds inside an id range, one list per query (splitmix64 of (seed, query, slot)).
+__global__ void uniform_seeds_kernel(uint32_t* __restrict__ seeds, uint64_t nq, uint32_t spq, uint32_t begin,
+                                     uint32_t len, uint64_t seed) {
+  const uint64_t i = blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x;
+  if (i >= nq * spq) return;
+  uint64_t x = seed ^ (i * 0x9e3779b97f4a7c15ull + 0x632be59bd9b4e019ull);
+  x ^= x >> 30; x *= 0xbf58476d1ce4e5b9ull;
+  x ^= x >> 27; x *= 0x94d049bb133111ebull;
+  x ^= x >> 31;
+  seeds[i] = len ? begin + static_cast<uint32_t>(x % len) : kInvalid;
 }
 
 // A second stream and two events per device, so that the global and the bucket search of a batch overlap.
@@ -192,7 +204,17 @@ int insert_opt_impl(const float* d_dataset, uint32_t* d_graph, const uint64_t* d
     a.d_seeds = d_seeds;
     a.seeds_per_query = num_seeds_per_query;
     a.d_ws = ws2; a.ws_bytes = ws_bytes; a.stream = side->st;
-    if (routed_bucket) {
+    if (routed_bucket && o.bucket_end > o.router_covers) {
+      // the bucket holds nodes the router has not been told about (inserted after its last assignment): uniform
+      // seeds from the bucket's id range, one list per new vector
+      const uint64_t cnt = num_new * o.routed_seeds;
+      uniform_seeds_kernel<<<(unsigned)((cnt + 255) / 256), 256, 0, side->st>>>(
+          seeds_l, num_new, o.routed_seeds, static_cast<uint32_t>(o.bucket_begin),
+          static_cast<uint32_t>(o.bucket_end - o.bucket_begin), seed + 2);
+      GRAB_CUDA_TRY(cudaGetLastError());
+      a.d_seeds = seeds_l;
+      a.seeds_per_query = o.routed_seeds;
+    } else if (routed_bucket) {
       // members of the nearest centroids that lie in the target bucket (bucket ids are non-decreasing in the id,
       // so the bucket is one id window)
       grab_filter bf;
@@ -234,7 +256,7 @@ int insert_opt_impl(const float* d_dataset, uint32_t* d_graph, const uint64_t* d
   tm.mark("batch kNN + merge");
   GRAB_TRY(update_topology_opt_impl(d_graph, d_bucket, il.as<int64_t>(), ig.as<int64_t>(), num_existing, num_new,
                                     target_bucket, total_degree, local_degree, search_k, search_k, st,
-                                    o.repair_by_distance ? d_dataset : nullptr, dim, metric, o.sync));
+                                    o.repair_mode ? d_dataset : nullptr, dim, metric, o.sync, o.repair_mode));
   tm.mark("topology update");
   return GRAB_OK;
 }

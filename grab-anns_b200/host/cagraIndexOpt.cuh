@@ -63,12 +63,13 @@ class CagraIndexOpt {
   void setInsertBatch(size_t batch) { insert_batch_ = batch ? batch : 4096; }
   // Insert behaviour beyond the reference's.  routed: seeds of the insert searches come from the entry-point
   // router (needs setRouter != 0 and sorted timestamps; otherwise the reference's seed rule applies).
-  // repair_by_distance: a new node replaces the FARTHEST neighbour of an old node it links back to, and only when
-  // it is closer, instead of the reference's pseudo-random slot (src/index/insert.cu:693-712); false restores the
-  // reference's rule.
-  void setInsertMode(bool routed, bool repair_by_distance) {
+  // repair_mode: how a new node is linked back into the rows of the old nodes it points to --
+  //   0  the reference's rule: a pseudo-random slot, 10 % strong / 90 % weak half (src/index/insert.cu:693-712);
+  //   1  (default) every request still gets a slot, but the one of the FARTHEST old neighbour in the weak half;
+  //   2  a request replaces the farthest neighbour of the region only when it is closer.
+  void setInsertMode(bool routed, int repair_mode) {
     insert_routed_ = routed;
-    insert_repair_by_distance_ = repair_by_distance;
+    insert_repair_mode_ = repair_mode;
   }
   void setInsertSearchParams(uint32_t itopk, uint32_t width, uint32_t max_iterations, uint32_t hash_bitlen) {
     insert_params_routed_ = {itopk, width, 0, max_iterations, hash_bitlen};
@@ -107,7 +108,8 @@ class CagraIndexOpt {
   // the reference inserts 32 at a time (src/cagraIndexOpt.cu:590); the sparse mailboxes and the
   // exact kNN inside the batch make four-digit batches as good and far faster
   size_t insert_batch_ = 4096;
-  bool insert_routed_ = true, insert_repair_by_distance_ = true;
+  bool insert_routed_ = true;
+  int insert_repair_mode_ = 1;
   grab_search_params insert_params_ = {128, 4, 0, 100, 13};         // src/cagraIndexOpt.cu:596-602
   grab_search_params insert_params_routed_ = {128, 4, 0, 16, 12};   // from routed seeds
   struct RouterState;

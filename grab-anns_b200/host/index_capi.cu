@@ -52,8 +52,8 @@ int grab_index_opt_set_query_params(void* h, uint32_t itopk, uint32_t width, uin
 int grab_index_opt_set_router(void* h, uint32_t centroids, uint32_t probes, uint32_t seeds_per_query) {
   return guarded([&] { O(h)->setRouter(centroids, probes, seeds_per_query); });
 }
-int grab_index_opt_set_insert_mode(void* h, int routed, int repair_by_distance) {
-  return guarded([&] { O(h)->setInsertMode(routed != 0, repair_by_distance != 0); });
+int grab_index_opt_set_insert_mode(void* h, int routed, int repair_mode) {
+  return guarded([&] { O(h)->setInsertMode(routed != 0, repair_mode); });
 }
 int grab_index_opt_set_insert_search_params(void* h, uint32_t itopk, uint32_t width, uint32_t max_iter,
                                             uint32_t hash_bitlen) {

@@ -612,8 +612,8 @@ void CagraIndexOpt::insert(size_t new_vectors, const float* insert_vectors, cons
     grab::InsertOptions io;
     io.router = router;
     io.probes = router_probes_;
-    io.routed_seeds = 32;
-    io.repair_by_distance = insert_repair_by_distance_;
+    io.routed_seeds = 64;
+    io.repair_mode = insert_repair_mode_;
     io.sync = false;  // batches are stream-ordered; one wait at the end of the call
     size_t old_size = first_new;
     size_t off = 0;
@@ -643,6 +643,12 @@ void CagraIndexOpt::insert(size_t new_vectors, const float* insert_vectors, cons
           cu(cudaMemcpy(d_seeds->p, all.data(), all.size() * 4, cudaMemcpyHostToDevice), "H2D seeds");
         }
         io.bucket_has_old_members = has_old;
+        if (has_old) {  // sorted timestamps: the bucket's old members are the id run [front, old_size) or [front, next bucket)
+          io.bucket_begin = it->second.front();
+          auto last_old = std::lower_bound(it->second.begin(), it->second.end(), static_cast<uint32_t>(old_size));
+          io.bucket_end = static_cast<uint64_t>(*(last_old - 1)) + 1;
+        }
+        io.router_covers = first_new;  // ensure_router() ran at the start of this call
         ok(grab::insert_opt_impl(d_data, d_graph, static_cast<uint64_t*>(d_bucket_->data()),
                                  d_seeds ? d_seeds->as<uint32_t>() : nullptr, old_size, cur, target,
                                  d_data + old_size * dim_, dim_, graph_degree_, static_cast<uint32_t>(local_degree_), ip,

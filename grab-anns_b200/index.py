@@ -100,9 +100,11 @@ class CagraIndexOpt(_Base):
         """Entry-point router for searches without caller seeds: 0 = off, 0xFFFFFFFF = about sqrt(n)."""
         self._call("set_router", C.c_uint32(centroids), C.c_uint32(probes), C.c_uint32(seeds_per_query))
 
-    def set_insert_mode(self, routed=True, repair_by_distance=True):
-        """Routed insert searches / distance-aware reverse-edge repair (False, False = the reference's rules)."""
-        self._call("set_insert_mode", C.c_int(int(routed)), C.c_int(int(repair_by_distance)))
+    def set_insert_mode(self, routed=True, repair_mode=1):
+        """Routed insert searches; repair_mode 0 = the reference's pseudo-random slot, 1 = every request takes the
+        farthest weak-half slot, 2 = only closer requests replace the farthest neighbour.  (False, 0) = the
+        reference's rules."""
+        self._call("set_insert_mode", C.c_int(int(routed)), C.c_int(int(repair_mode)))
 
     def set_insert_search_params(self, itopk=128, width=4, max_iter=16, hash_bitlen=12):
         self._call("set_insert_search_params", C.c_uint32(itopk), C.c_uint32(width), C.c_uint32(max_iter),

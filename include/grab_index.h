@@ -23,11 +23,12 @@ int grab_index_opt_set_query_params(void* h, uint32_t itopk, uint32_t width, uin
 /* Entry-point router of the searches that get no seeds from the caller: centroids = 0 off,
  * 0xFFFFFFFF (default) about sqrt(n); probes / seeds_per_query = 0 keep 2 / 64. */
 int grab_index_opt_set_router(void* h, uint32_t centroids, uint32_t probes, uint32_t seeds_per_query);
-/* Insert behaviour beyond the reference's (both on by default): routed = the insert searches start from the
- * router's seeds (needs a router and sorted timestamps); repair_by_distance = a new node replaces the farthest
- * neighbour of an old node, and only when it is closer, instead of the reference's pseudo-random slot
- * (src/index/insert.cu:693-712).  0 / 0 restores the reference's rules. */
-int grab_index_opt_set_insert_mode(void* h, int routed, int repair_by_distance);
+/* Insert behaviour beyond the reference's.  routed (default 1) = the insert searches start from the router's
+ * seeds (needs a router and sorted timestamps).  repair_mode = how a new node is linked back into the rows of the
+ * old nodes it points to: 0 the reference's pseudo-random slot (src/index/insert.cu:693-712); 1 (default) every
+ * request still gets a slot, the one of the farthest old neighbour in the weak half; 2 only requests closer than
+ * the region's farthest neighbour replace it.  0 / 0 restores the reference's rules. */
+int grab_index_opt_set_insert_mode(void* h, int routed, int repair_mode);
 /* Search parameters of routed inserts (default itopk 128, width 4, 16 iterations, hash 2^12). */
 int grab_index_opt_set_insert_search_params(void* h, uint32_t itopk, uint32_t width, uint32_t max_iter,
                                             uint32_t hash_bitlen);

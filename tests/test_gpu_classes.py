@@ -61,8 +61,8 @@ def test_opt_bucket_and_range_search(grab, oracle, index_mod):
     assert (ids == -1).all() and (d == -1.0).all()
 
 
-@pytest.mark.parametrize("repair_by_distance", [False, True])
-def test_opt_insert_then_search(grab, oracle, index_mod, tmp_path, repair_by_distance):
+@pytest.mark.parametrize("repair_mode", [0, 1, 2])
+def test_opt_insert_then_search(grab, oracle, index_mod, tmp_path, repair_mode):
     # tests/test_cagra_opt_insert.cu: build on the first half of every bucket, insert the second
     # half; global recall > 90 %, local > 95 %, 0 bound errors (:359-360).  Both reverse-edge rules: the
     # reference's slot rule and the distance-aware repair.
@@ -70,7 +70,7 @@ def test_opt_insert_then_search(grab, oracle, index_mod, tmp_path, repair_by_dis
     data = clustered(nb * per, dim, 24, 1.0, 73).reshape(nb, per, dim)
     half = per // 2
     idx = index_mod.CagraIndexOpt(dim, 32, 24, insert_batch=256)
-    idx.set_insert_mode(routed=False, repair_by_distance=repair_by_distance)
+    idx.set_insert_mode(routed=False, repair_mode=repair_mode)
     first = data[:, :half].reshape(-1, dim)
     idx.add(first, np.repeat(np.arange(nb, dtype=np.uint64), half))
     idx.build()
@@ -122,7 +122,7 @@ def test_opt_streaming_insert_holds_recall(grab, oracle, index_mod, reference_ru
     idx.set_router(128, 2, 64)
     idx.set_query_params(64, 3, 0, 8, 11)
     if reference_rules:
-        idx.set_insert_mode(routed=False, repair_by_distance=False)
+        idx.set_insert_mode(routed=False, repair_mode=0)
     idx.add(data[:n0], ts[:n0])
     idx.build()
     rng = np.random.default_rng(82)
