@@ -128,7 +128,7 @@ def resolve_defaults(args, w):
     if args.probes == 0:
         args.probes = 4 if big_k else 2
     if args.hash_bitlen == 0:
-        args.hash_bitlen = 12 if big_k else 11
+        args.hash_bitlen = 11   # 2 048 slots: a query visits 350-550 ids; a larger table only costs resident CTAs
     if args.local_degree == 0:
         args.local_degree = w["degree"] * 3 // 4
     if args.router_centroids < 0:
@@ -1321,7 +1321,7 @@ def main():
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one search launch, per algorithmic byte, from the ncu capture of
 # the default configuration summarised in profiles/graph_search_kernel_C2.md (traffic grows with the work done)
-DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = 0.7305
+DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = 0.7300
 
 
 def roofline_traffic(args, w, alg_bytes):

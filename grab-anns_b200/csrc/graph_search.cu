@@ -382,6 +382,9 @@ graph_search_kernel(const SearchKernelArgs a) {
 #ifndef GRAB_SEARCH2_CTAS_PER_SM
 #define GRAB_SEARCH2_CTAS_PER_SM 14
 #endif
+#ifndef GRAB_SEARCH_UNROLL_96
+#define GRAB_SEARCH_UNROLL_96 2
+#endif
 #ifndef GRAB_RANK_MERGE_HALF
 #define GRAB_RANK_MERGE_HALF 16
 #endif
@@ -391,6 +394,9 @@ template <int METRIC, int CPL, int R>
 __global__ void __launch_bounds__(kSearchThreads, GRAB_SEARCH2_CTAS_PER_SM)
 graph_search_split_kernel(const SearchKernelArgs a) {
   static_assert(kSearchThreads == 64, "two warps per query");
+  // vectors in flight per team: a 96-d row is three float4 per lane, so three of them cost the registers two 128-d
+  // rows do, and a warp's survivors take a third fewer round trips to memory
+  constexpr int U = CPL == 3 ? GRAB_SEARCH_UNROLL_96 : kSearchUnroll;
   constexpr uint32_t M = 32u * R;  // list length
   extern __shared__ __align__(16) unsigned char smem_raw[];
   uint64_t* queue = reinterpret_cast<uint64_t*>(smem_raw);                 // [M] sorted itopk list
@@ -499,26 +505,26 @@ graph_search_split_kernel(const SearchKernelArgs a) {
     //      the current worst entry of the list ----
     const uint64_t worst = queue[M - 1];
     uint32_t nkeep = 0;  // warp-uniform
-    for (uint32_t j0 = 0; j0 < ncand; j0 += 4 * kSearchUnroll) {
-      uint32_t id[kSearchUnroll];
-      bool ok[kSearchUnroll];
-      float acc[kSearchUnroll];
+    for (uint32_t j0 = 0; j0 < ncand; j0 += 4 * U) {
+      uint32_t id[U];
+      bool ok[U];
+      float acc[U];
 #pragma unroll
-      for (int u = 0; u < kSearchUnroll; ++u) {
+      for (int u = 0; u < U; ++u) {
         const uint32_t j = j0 + u * 4 + wteam;
         ok[u] = j < ncand;
         id[u] = ok[u] ? my_cand[j] : 0;
         acc[u] = 0.0f;
       }
       if (CPL > 0) {
-        float4 x[kSearchUnroll][CPL > 0 ? CPL : 1];
+        float4 x[U][CPL > 0 ? CPL : 1];
 #pragma unroll
-        for (int u = 0; u < kSearchUnroll; ++u)
+        for (int u = 0; u < U; ++u)
 #pragma unroll
           for (int c = 0; c < CPL; ++c)
             if (ok[u]) x[u][c] = ldg_f4(a.data + static_cast<size_t>(id[u]) * a.dim + 4 * (lane8 + kTeam * c));
 #pragma unroll
-        for (int u = 0; u < kSearchUnroll; ++u)
+        for (int u = 0; u < U; ++u)
 #pragma unroll
           for (int c = 0; c < CPL; ++c)
             if (ok[u])
@@ -526,9 +532,9 @@ graph_search_split_kernel(const SearchKernelArgs a) {
       } else {
         const uint32_t nchunk = a.dim / 4;
         for (uint32_t c0 = lane8; c0 < nchunk; c0 += 4 * kTeam) {
-          float4 x[kSearchUnroll][4];
+          float4 x[U][4];
 #pragma unroll
-          for (int u = 0; u < kSearchUnroll; ++u)
+          for (int u = 0; u < U; ++u)
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               const uint32_t c = c0 + i * kTeam;
@@ -540,14 +546,14 @@ graph_search_split_kernel(const SearchKernelArgs a) {
             if (c < nchunk) {
               const float4 qv = *reinterpret_cast<const float4*>(q_smem + 4 * c);
 #pragma unroll
-              for (int u = 0; u < kSearchUnroll; ++u)
+              for (int u = 0; u < U; ++u)
                 if (ok[u]) acc[u] = accum4<METRIC>(acc[u], qv, x[u][i]);
             }
           }
         }
       }
 #pragma unroll
-      for (int u = 0; u < kSearchUnroll; ++u) {
+      for (int u = 0; u < U; ++u) {
         const float d = team_reduce<METRIC>(acc[u]);
         const uint64_t key = make_skey(d, id[u]);
         const bool keep = lane8 == 0 && ok[u] && key < worst;
