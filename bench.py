@@ -137,7 +137,9 @@ def resolve_defaults(args, w):
     if args.max_iter == 0:
         args.max_iter = (12 if big_k else 5) if args.router_centroids else 20
     if args.knn_precision < 0:
-        args.knn_precision = 1 if args.workload == "C2" else 2
+        # bf16 candidates (+ exact re-rank) where they are exact or cheap enough to matter: integer-valued C2, and the
+        # 768-d C3 whose split-precision all-pairs stage would take 3x the tensor work; split bf16 elsewhere
+        args.knn_precision = 1 if args.workload in ("C2", "C3") else 2
     return args
 
 
@@ -638,7 +640,7 @@ def recall_of(res, gt):
     return hit / max(denom, 1)
 
 
-def shard_schedule(args, G, k, centroids, probes):
+def shard_schedule(args, G, k, centroids, probes, shard_is_fraction=True):
     """Per-shard search effort of a G-way id-striped index.  A stripe holds 1/G of every neighbourhood, so of the
     global top-k it owns Binomial(k, 1/G): the run it sends is k/G + 4.5 sigma + 2 long instead of k.  The search
     effort itself shrinks only a little with G -- a stripe's graph walk still has to reach the query's neighbourhood
@@ -651,12 +653,15 @@ def shard_schedule(args, G, k, centroids, probes):
     if G == 1:
         iters, seeds = args.max_iter, args.seeds
     elif big_k:
-        iters, seeds = max(6, args.max_iter * 3 // 4), args.seeds
+        iters, seeds = max(6, args.max_iter * 5 // 6), args.seeds
     else:
         iters, seeds = max(3, args.max_iter - 1), max(16, args.seeds * 3 // 4)
     return {"run_length": args.shard_run or run, "iterations": args.shard_iters or iters,
             "seeds": args.shard_seeds or seeds,
-            "centroids": args.shard_centroids or (max(64, centroids // G) if centroids else 0),
+            # a stripe of a fixed total holds 1/G of it: as many members per centroid with 1/G of the centroids;
+            # shards of a fixed size (C5: 12.5M per GPU whatever G) keep theirs
+            "centroids": args.shard_centroids or ((max(64, centroids // G) if shard_is_fraction else centroids)
+                                                  if centroids else 0),
             "probes": args.shard_probes or probes}
 
 
@@ -687,22 +692,31 @@ def sharded_record(args, grab, torch, dist, w, rank, world, steps, warmup, d_bas
     effort, ONE all-gather of the key runs (NCCL inside the C library) + G-way device merge, pipelined over two
     buffer sets so that the exchange of step i overlaps the search of step i+1."""
     k = w["k"]
-    if shard is None:
-        base = np.ascontiguousarray(w["base"][rank::world])
-        ts = np.ascontiguousarray(w["ts"][rank::world])
-        d_base = torch.from_numpy(base).cuda()
-        n_total = w["n"]
-    else:
-        d_base, ts, n_total = shard["base"], shard["ts"], shard["n_total"]
-    sch = shard_schedule(args, world, k, args.router_centroids, args.probes)
-    ix = Index(grab, args, w, d_base, ts=ts, n_total=n_total, centroids=sch["centroids"], id_scale=world,
-               id_offset=rank)
+    by_labels = "labels" in w
+    sch = shard_schedule(args, world, k, args.router_centroids, args.probes, shard_is_fraction=shard is None)
     nq = w["queries"].shape[0]
-    kp = sch["run_length"]
     d_q = torch.from_numpy(w["queries"]).cuda()
-    d_lo = torch.from_numpy(w["lo"].view(np.int64)).cuda()
-    d_hi = torch.from_numpy(w["hi"].view(np.int64)).cuda()
-    flt = ix.filter(d_lo, d_hi)
+    if by_labels:
+        # the vectors are grouped by label; a stripe of a grouped array is grouped too
+        d_base = torch.from_numpy(np.ascontiguousarray(w["base"][rank::world])).cuda()
+        labels = np.ascontiguousarray(w["labels"][rank::world])
+        offs = np.searchsorted(labels, np.arange(33), side="left").astype(np.uint32)
+        ix = Index(grab, args, w, d_base, labels=labels, label_offsets=offs, centroids=sch["centroids"],
+                   id_scale=world, id_offset=rank)
+        flt = ix.filter(torch.from_numpy(w["masks"].view(np.int32)).cuda())
+    else:
+        if shard is None:
+            d_base = torch.from_numpy(np.ascontiguousarray(w["base"][rank::world])).cuda()
+            ts = np.ascontiguousarray(w["ts"][rank::world])
+            n_total = w["n"]
+        else:
+            d_base, ts, n_total = shard["base"], shard["ts"], shard["n_total"]
+        ix = Index(grab, args, w, d_base, ts=ts, n_total=n_total, centroids=sch["centroids"], id_scale=world,
+                   id_offset=rank)
+        d_lo = torch.from_numpy(w["lo"].view(np.int64)).cuda()
+        d_hi = torch.from_numpy(w["hi"].view(np.int64)).cuda()
+        flt = ix.filter(d_lo, d_hi)
+    kp = sch["run_length"]
     comm = None
     if world > 1:
         comm = grab.Comm(world, rank, grab.torch_broadcast_bytes)
@@ -740,8 +754,12 @@ def sharded_record(args, grab, torch, dist, w, rank, world, steps, warmup, d_bas
     torch.cuda.synchronize()
     res = s0.out[0].cpu().numpy()
     recall = recall_of(res, gt)
-    lo_i, hi_i = w["lo"][:, None].astype(np.int64), w["hi"][:, None].astype(np.int64)
-    in_range = bool(np.all(((res >= lo_i) & (res < hi_i)) | (res < 0)))
+    if by_labels:   # global id -> label through the grouped global array
+        lab = w["labels"][np.clip(res, 0, w["n"] - 1)]
+        in_range = bool(np.all((((w["masks"][:, None] >> lab) & 1) == 1) | (res < 0)))
+    else:
+        lo_i, hi_i = w["lo"][:, None].astype(np.int64), w["hi"][:, None].astype(np.int64)
+        in_range = bool(np.all(((res >= lo_i) & (res < hi_i)) | (res < 0)))
 
     class CudaSync:
         """Stream / event operations of sharded.run_pipelined on this device."""
@@ -798,7 +816,7 @@ def sharded_record(args, grab, torch, dist, w, rank, world, steps, warmup, d_bas
                                                                  out=s0.out), steps, warmup, dist)
     st = torch.tensor([stats.iterations, stats.parents, stats.edges, stats.distances, stats.seeds, stats.hash_resets],
                       device="cuda", dtype=torch.int64)
-    alg = grab.search_bytes(stats, nq, ix.dim, ix.deg, kp, 0)
+    alg = grab.search_bytes(stats, nq, ix.dim, ix.deg, kp, 1 if by_labels else 0)
     peak = measured_peak()[0]
     rec = {"world": world, "striping": "gid % world == rank", "shard_vectors": int(ix.n), "queries": int(nq),
            "value": nq / (ms_pipe / 1e3), "unit": "queries/s", "ms_per_step": ms_pipe,
@@ -1057,8 +1075,6 @@ def main():
         return
 
     if args.sharded:
-        if by_labels:
-            raise SystemExit("--sharded is implemented for the timestamp workloads")
         sampler = ClockSampler(local_rank)
         sampler.start()
         rec = sharded_record(args, grab, torch, dist, w, rank, world, steps, warmup)
@@ -1261,7 +1277,7 @@ def main():
     ms_search = timed(search_only, steps, warmup) if ix.router is not None else ms
 
     sharded = None
-    if world > 1 and not by_labels and not args.no_sharded_record:
+    if world > 1 and not args.no_sharded_record:
         del S
         torch.cuda.empty_cache()
         sharded = sharded_record(args, grab, torch, dist, w, rank, world, steps, warmup)

@@ -315,15 +315,18 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
           if (!__any_sync(0xFFFFFFFFu, hit)) return;
           if (hit) {
             const uint32_t cbase = c0 + chunk * 32;
-            uint32_t m0 = 0, m1 = 0, m2 = 0, m3 = 0;  // four independent accumulators: no serial chain through one mask
+            // the min tree's first level already says which groups of four hold a value below the threshold
+            // (usually one): only those are looked at element by element
+            uint32_t m = 0;
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-              m0 |= (__uint_as_float(v[i]) < thr ? 1u : 0u) << i;
-              m1 |= (__uint_as_float(v[8 + i]) < thr ? 1u : 0u) << (8 + i);
-              m2 |= (__uint_as_float(v[16 + i]) < thr ? 1u : 0u) << (16 + i);
-              m3 |= (__uint_as_float(v[24 + i]) < thr ? 1u : 0u) << (24 + i);
+              if (m8[i] < thr) {
+                m |= (__uint_as_float(v[4 * i]) < thr ? 1u : 0u) << (4 * i);
+                m |= (__uint_as_float(v[4 * i + 1]) < thr ? 1u : 0u) << (4 * i + 1);
+                m |= (__uint_as_float(v[4 * i + 2]) < thr ? 1u : 0u) << (4 * i + 2);
+                m |= (__uint_as_float(v[4 * i + 3]) < thr ? 1u : 0u) << (4 * i + 3);
+              }
             }
-            uint32_t m = (m0 | m1) | (m2 | m3);
             if (need_mask) m &= range_bits(cbase, w.begin, w.end) & ~range_bits(cbase, w.xbegin, w.xend);
             while (m) {
               const uint32_t i = __ffs(m) - 1;

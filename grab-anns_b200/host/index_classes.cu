@@ -59,12 +59,14 @@ grab_search_args make_args(const float* d_data, uint64_t n, uint32_t dim, int me
 }  // namespace
 
 // Per-index query scratch that survives across calls (grow-only): device copies of the queries, per-query
-// ranges, seeds and results, the routing and search workspaces, and two streams.  The reference allocates and
+// ranges, seeds and results, the routing and search workspaces, page-locked staging for the caller's pageable
+// arrays (filled and drained by a few host threads, so that the PCIe copies themselves are asynchronous and run
+// at link speed), and two streams.  The reference allocates and
 // frees all of this inside every query call (src/index/cagra_opt.cu:1136-1206: cudaMalloc / cudaFree plus two
 // device-wide synchronisations per call); here a query performs no allocation once the largest batch has been
-// seen.  Batches of 4096 queries and more are cut in two halves on two streams, so that the host-to-device copy
-// of the second half overlaps the search of the first and the result copy of the first the search of the
-// second.  One caller at a time per index (the mutex serialises others), as in the reference.
+// seen.  Batches of 4096 queries and more are cut in two (8192 and more: four) parts on as many streams, so that
+// the host-to-device copy of one part overlaps the search of the part before it and the result copy of that part
+// the search of the next.  One caller at a time per index (the mutex serialises others), as in the reference.
 namespace grab {
 struct QueryArena {
   struct Buf {
@@ -82,12 +84,29 @@ struct QueryArena {
     ~Buf() { if (p) cudaFree(p); }
     template <class T> T* as() { return static_cast<T*>(p); }
   };
+  struct Pinned {  // page-locked host staging, grow-only
+    void* p = nullptr;
+    size_t cap = 0;
+    void need(size_t bytes) {
+      if (bytes <= cap) return;
+      if (p) cudaFreeHost(p);
+      p = nullptr;
+      cap = 0;
+      const size_t want = bytes + bytes / 4 + 256;
+      cu(cudaHostAlloc(&p, want, cudaHostAllocDefault), "cudaHostAlloc (query staging)");
+      cap = want;
+    }
+    ~Pinned() { if (p) cudaFreeHost(p); }
+    template <class T> T* as() { return static_cast<T*>(p); }
+  };
   struct Slot {
     cudaStream_t st = nullptr;
     Buf q, lo, hi, ids, dists, seeds, search_ws, route_ws;
+    Pinned h_in, h_out;  // [queries | lo | hi | seeds] and [ids | dists] of this half-batch
     ~Slot() { if (st) cudaStreamDestroy(st); }
   };
-  Slot slot[2];
+  static constexpr int kSlots = 4;
+  Slot slot[kSlots];
   std::mutex mu;
 };
 void QueryArenaDeleter::operator()(QueryArena* a) const { delete a; }
@@ -98,6 +117,18 @@ namespace {
 grab::QueryArena& arena_of(std::unique_ptr<grab::QueryArena, grab::QueryArenaDeleter>& holder) {
   if (!holder) holder.reset(new grab::QueryArena());
   return *holder;
+}
+
+// memcpy by up to 8 host threads (a single thread moves ~10 GB/s, the PCIe link five times that)
+void parallel_copy(void* dst, const void* src, size_t bytes) {
+  constexpr size_t kPiece = 256 << 10;
+  const long pieces = static_cast<long>((bytes + kPiece - 1) / kPiece);
+  if (pieces <= 2) { memcpy(dst, src, bytes); return; }
+#pragma omp parallel for num_threads(8) schedule(static)
+  for (long i = 0; i < pieces; ++i) {
+    const size_t off = static_cast<size_t>(i) * kPiece;
+    memcpy(static_cast<char*>(dst) + off, static_cast<const char*>(src) + off, std::min(kPiece, bytes - off));
+  }
 }
 
 // queries up, one filtered search (routed seeds, caller's seeds, or the kernel's own draws), results down.
@@ -114,9 +145,9 @@ void run_search(grab::QueryArena& A, grab_search_args a, const float* host_q, si
     for (size_t i = 0; i < nq; ++i) memcpy(expanded.data() + i * seeds_per_query, host_seeds, seeds_per_query * 4);
     host_seeds = expanded.data();
   }
-  const size_t chunks = nq >= 4096 ? 2 : 1;
+  const size_t chunks = nq >= 8192 ? 4 : (nq >= 4096 ? 2 : 1);
   const size_t per = (nq + chunks - 1) / chunks;
-  size_t count[2] = {0, 0};
+  size_t count[grab::QueryArena::kSlots] = {0, 0, 0, 0};
   for (size_t c = 0; c < chunks; ++c) {
     grab::QueryArena::Slot& s = A.slot[c];
     const size_t q0 = c * per, m = std::min(per, nq - q0);
@@ -127,13 +158,21 @@ void run_search(grab::QueryArena& A, grab_search_args a, const float* host_q, si
     s.dists.need(m * k * sizeof(float));
     const size_t sws = grab_graph_search_workspace_bytes(m, a.params.hash_bitlen);
     s.search_ws.need(sws);
-    cu(cudaMemcpyAsync(s.q.p, host_q + q0 * dim, m * dim * sizeof(float), cudaMemcpyHostToDevice, s.st), "H2D queries");
+    // stage this half-batch in page-locked memory: [queries | lo | hi | seeds]
+    const size_t qb = m * dim * sizeof(float), rb = host_lo ? m * sizeof(uint64_t) : 0;
+    const size_t sb = own_seeds ? m * seeds_per_query * sizeof(uint32_t) : 0;
+    s.h_in.need(qb + 2 * rb + sb);
+    char* hin = s.h_in.as<char>();
+    parallel_copy(hin, host_q + q0 * dim, qb);
+    cu(cudaMemcpyAsync(s.q.p, hin, qb, cudaMemcpyHostToDevice, s.st), "H2D queries");
     grab_search_args ac = a;
     if (host_lo) {
-      s.lo.need(m * sizeof(uint64_t));
-      s.hi.need(m * sizeof(uint64_t));
-      cu(cudaMemcpyAsync(s.lo.p, host_lo + q0, m * sizeof(uint64_t), cudaMemcpyHostToDevice, s.st), "H2D range");
-      cu(cudaMemcpyAsync(s.hi.p, host_hi + q0, m * sizeof(uint64_t), cudaMemcpyHostToDevice, s.st), "H2D range");
+      s.lo.need(rb);
+      s.hi.need(rb);
+      memcpy(hin + qb, host_lo + q0, rb);
+      memcpy(hin + qb + rb, host_hi + q0, rb);
+      cu(cudaMemcpyAsync(s.lo.p, hin + qb, rb, cudaMemcpyHostToDevice, s.st), "H2D range");
+      cu(cudaMemcpyAsync(s.hi.p, hin + qb + rb, rb, cudaMemcpyHostToDevice, s.st), "H2D range");
       ac.filter.d_lo = s.lo.as<uint64_t>();
       ac.filter.d_hi = s.hi.as<uint64_t>();
     }
@@ -154,24 +193,27 @@ void run_search(grab::QueryArena& A, grab_search_args a, const float* host_q, si
       ac.d_seeds = s.seeds.as<uint32_t>();
       ac.seeds_per_query = routed_seeds;
     } else if (own_seeds) {
-      s.seeds.need(m * seeds_per_query * sizeof(uint32_t));
-      cu(cudaMemcpyAsync(s.seeds.p, host_seeds + q0 * seeds_per_query, m * seeds_per_query * 4, cudaMemcpyHostToDevice,
-                         s.st), "H2D seeds");
+      s.seeds.need(sb);
+      parallel_copy(hin + qb + 2 * rb, host_seeds + q0 * seeds_per_query, sb);
+      cu(cudaMemcpyAsync(s.seeds.p, hin + qb + 2 * rb, sb, cudaMemcpyHostToDevice, s.st), "H2D seeds");
       ac.d_seeds = s.seeds.as<uint32_t>();
       ac.seeds_per_query = static_cast<uint32_t>(seeds_per_query);
     }
     ok(grab_graph_search(&ac), "graph search");
+    // results of this half leave as soon as its search is done, while the other half is staged and searched
+    const size_t ib = m * k * sizeof(int64_t), db = m * k * sizeof(float);
+    s.h_out.need(ib + db);
+    cu(cudaMemcpyAsync(s.h_out.p, s.ids.p, ib, cudaMemcpyDeviceToHost, s.st), "D2H ids");
+    cu(cudaMemcpyAsync(s.h_out.as<char>() + ib, s.dists.p, db, cudaMemcpyDeviceToHost, s.st), "D2H dists");
   }
   for (size_t c = 0; c < chunks; ++c) {
     grab::QueryArena::Slot& s = A.slot[c];
     const size_t q0 = c * per, m = count[c];
-    cu(cudaMemcpyAsync(host_ids + q0 * k, s.ids.p, m * k * sizeof(int64_t), cudaMemcpyDeviceToHost, s.st), "D2H ids");
-    cu(cudaMemcpyAsync(host_dists + q0 * k, s.dists.p, m * k * sizeof(float), cudaMemcpyDeviceToHost, s.st),
-       "D2H dists");
-  }
-  for (size_t c = 0; c < chunks; ++c) {
-    cu(cudaStreamSynchronize(A.slot[c].st), "query stream");
-    if (router && !own_seeds) ok(grab_route_status(A.slot[c].route_ws.p, A.slot[c].st), "seed routing");
+    cu(cudaStreamSynchronize(s.st), "query stream");
+    if (router && !own_seeds) ok(grab_route_status(s.route_ws.p, s.st), "seed routing");
+    const size_t ib = m * k * sizeof(int64_t), db = m * k * sizeof(float);
+    parallel_copy(host_ids + q0 * k, s.h_out.p, ib);
+    parallel_copy(host_dists + q0 * k, s.h_out.as<char>() + ib, db);
   }
 }
 

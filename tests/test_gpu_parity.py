@@ -292,6 +292,42 @@ def test_merge_sorted_keys_bit_exact(grab, oracle):
         assert np.array_equal(gd.cpu().numpy(), od), (parts, kp, k)
 
 
+def test_search_keys_output_and_single_shard_exchange(grab, oracle):
+    """grab_search_args.d_out_keys carries the same results as the id / distance outputs (global ids through
+    id_scale / id_offset), and the exchange entry point with no communicator (one shard) returns them unchanged;
+    two emulated stripes merged by grab_merge_sorted_keys give the exact search's ids when both stripes are searched
+    exactly (the sharded result is the unsharded one)."""
+    import torch
+    rng = np.random.default_rng(31)
+    n, dim, nq, k = 6000, 64, 64, 10
+    data = rng.standard_normal((n, dim)).astype(np.float32)
+    q = rng.standard_normal((nq, dim)).astype(np.float32)
+    knn = oracle.knn_block(data, 32)
+    g = oracle.prune(knn, 16)
+    d_data, d_g, d_q = _t(data), _t(g.view(np.int32)), _t(q)
+    keys = torch.empty((nq, k), dtype=torch.int64, device="cuda")
+    ids, dists = grab.graph_search(d_data, d_g, d_q, k, grab.SearchParams(64, 4, 0, 20, 11), id_scale=3, id_offset=2,
+                                   out_keys=keys)
+    out = (torch.empty_like(ids), torch.empty_like(dists))
+    grab.check(grab.lib().grab_sharded_gather_merge(None, grab._p(keys), grab.C.c_uint64(nq), k, k, None,
+                                                    grab.C.c_size_t(0), grab._p(out[0]), grab._p(out[1]), None))
+    torch.cuda.synchronize()
+    assert torch.equal(out[0], ids) and torch.equal(out[1], dists)
+    assert ((ids % 3 == 2) | (ids < 0)).all()
+    # two stripes, exact per-stripe results as keys -> merged == exact over the whole set
+    want, wd = oracle.exact_search(data, q, k)
+    parts = []
+    for r in range(2):
+        gi, gd = grab.exact_search(_t(data[r::2]), d_q, k)
+        gi = gi.cpu().numpy() * 2 + r
+        o = gd.cpu().numpy().view(np.uint32)
+        o = np.where(o & 0x80000000, ~o, o | 0x80000000).astype(np.uint64)
+        parts.append((o << np.uint64(32)) | gi.astype(np.uint64))
+    mi, md = grab.merge_sorted_keys(_t(np.stack(parts).view(np.int64)), k)
+    assert np.array_equal(mi.cpu().numpy(), want)
+    assert np.array_equal(md.cpu().numpy(), wd)
+
+
 # ------------------------------------------------------------------ filtered graph search
 def _graph_fixture(oracle, n=20000, dim=64, deg=32, seed=31):
     data = clustered(n, dim, 40, 1.0, seed)
