@@ -126,3 +126,30 @@ def test_router_argument_checks(lib):
     assert lib.grab_build_time_partitioned_graph_ex(one, C.c_uint64(10), 8, 0, one, one, C.c_void_p(offs.ctypes.data),
                                                     2, 4, 2, C.byref(opt)) == 1
     assert "global_candidates" in _err(lib)
+
+
+def test_sharded_and_selftest_entry_points_validate_on_the_host(lib):
+    """The exchange step, the communicator and the device-level test entry points reject bad arguments with a
+    status before any GPU work; a communicator is never created from a null id."""
+    null = None
+    one = C.c_void_p(16)
+    assert lib.grab_merge_sorted_keys(null, C.c_uint64(4), 2, 10, 10, one, one, null) == 1
+    assert "null pointer" in _err(lib)
+    assert lib.grab_merge_sorted_keys(one, C.c_uint64(4), 0, 10, 10, one, one, null) == 1      # no runs
+    assert lib.grab_merge_sorted_keys(one, C.c_uint64(4), 2, 5000, 10, one, one, null) == 1     # run too long
+    assert lib.grab_merge_sorted_keys(one, C.c_uint64(0), 2, 10, 10, one, one, null) == 0       # nothing to do
+    assert lib.grab_sharded_gather_merge(null, null, C.c_uint64(4), 10, 10, null, C.c_size_t(0), one, one, null) == 1
+    buf = (C.c_uint8 * 64)()
+    assert lib.grab_comm_unique_id(buf, C.c_size_t(64)) == 1                                    # needs 128 bytes
+    assert "128" in _err(lib)
+    h = C.c_void_p()
+    assert lib.grab_comm_create(null, 2, 0, C.byref(h)) == 1
+    uid = (C.c_uint8 * 128)()
+    assert lib.grab_comm_create(uid, 2, 5, C.byref(h)) == 1                                     # rank outside the world
+    assert lib.grab_comm_destroy(null) == 0
+    assert lib.grab_comm_world(null) == 1 and lib.grab_comm_rank(null) == 0
+    assert lib.grab_route_status(null, null) == 1
+    assert lib.grab_selftest_sort_merge(one, one, C.c_uint64(1), 48, 4, 4, 0, one, null) == 1   # m not a power of two
+    assert lib.grab_selftest_sort_merge(one, one, C.c_uint64(1), 64, 40, 40, 2, one, null) == 1  # rank merge: <= 32
+    assert lib.grab_selftest_hash_insert(one, 2, one, 4, 64, one, null) == 1
+    assert lib.grab_selftest_hash_insert(one, 8, one, 4, 48, one, null) == 1                    # threads % 32
