@@ -69,6 +69,9 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the GPU-exact-vs-CPU-oracle check at config shape")
     ap.add_argument("--no-class-e2e", action="store_true", help="skip the timing of the class call")
+    ap.add_argument("--small-batch", action="store_true",
+                    help="latency report for batches of 1..512 queries: one CTA per query against several "
+                         "co-operating CTAs per query (ctas_per_query), instead of the throughput line")
     ap.add_argument("--no-overlap", action="store_true",
                     help="end-to-end steps on one stream only (no overlap of the copies with the search)")
     ap.add_argument("--no-hnsw", action="store_true", help="reference arm: skip the CPU HNSW harness")
@@ -619,16 +622,56 @@ class Searcher:
                                      seeds_per_query=self.nseeds, out=self.seeds, ws=self.route_ws)
         return self.seeds
 
-    def search(self, d_q, flt, out=None, stats=False, keys_only=False):
+    def search(self, d_q, flt, out=None, stats=False, keys_only=False, ws=None, ctas_per_query=0):
         ix = self.ix
         o = (None, None) if keys_only else (out or (self.ids, self.d))
         return ix.grab.graph_search(ix.d_base, ix.graph, d_q, self.k, self.params, metric=ix.metric, flt=flt,
-                                    stats=stats, seeds=self.seeds, out=o, ws=self.ws, id_scale=ix.id_scale,
-                                    id_offset=ix.id_offset, out_keys=self.keys)
+                                    stats=stats, seeds=self.seeds, out=o, ws=self.ws if ws is None else ws,
+                                    id_scale=ix.id_scale, id_offset=ix.id_offset, out_keys=self.keys,
+                                    ctas_per_query=ctas_per_query)
+
+    def search_args(self, d_q, flt, ctas_per_query):
+        """The argument struct of search() (for the workspace-size query)."""
+        ix = self.ix
+        return ix.grab.search_args(ix.d_base, ix.graph, d_q, self.k, self.params, metric=ix.metric, flt=flt,
+                                   seeds=self.seeds, ctas_per_query=ctas_per_query)
 
     def step(self, d_q, flt, keys_only=False):
         self.route(d_q, flt)
         self.search(d_q, flt, keys_only=keys_only)
+
+
+def small_batch_report(args, grab, torch, ix, w, d_q, d_lo, d_hi, gt, steps, warmup):
+    """Latency of route + search for small batches, one CTA per query against several per query, on the workload's
+    index.  Two parameter sets: the workload's own and the reference classes' defaults (itopk 256, width 6, up to 50
+    iterations: src/cagraIndexOpt.cu:32-37), whose long single-CTA walks are what small batches of a reference user
+    pay for."""
+    k, by_labels = w["k"], "ts" not in w
+    rows = []
+    sets = [("workload", args.itopk, args.width, args.max_iter, args.hash_bitlen),
+            ("reference class defaults", 256, 6, 50, 13)]
+    for name, itopk, width, iters, bitlen in sets:
+        for nq in (1, 8, 64, 512):
+            q = d_q[:nq].contiguous()
+            flt = ix.filter(d_lo[:nq].contiguous(), None if by_labels else d_hi[:nq].contiguous())
+            S = Searcher(ix, nq, k, itopk, width, iters, bitlen, args.probes, args.seeds)
+            for ctas in (1, 4, 16, grab.CTAS_AUTO):
+                a = S.search_args(q, flt, ctas)
+                ws = torch.empty(grab.search_workspace_bytes(a), dtype=torch.uint8, device="cuda")
+
+                def step():
+                    S.route(q, flt)
+                    S.search(q, flt, ws=ws, ctas_per_query=ctas)
+                try:
+                    ms = time_events(torch, step, steps, warmup)
+                except RuntimeError as e:       # a request the kernel refuses (k above the per-CTA list)
+                    rows.append({"params": name, "queries": nq, "ctas_per_query": ctas, "refused": str(e)[:120]})
+                    continue
+                res = S.ids.cpu().numpy()
+                rows.append({"params": name, "itopk": itopk, "width": width, "iterations": iters, "queries": nq,
+                             "ctas_per_query": "auto" if ctas == grab.CTAS_AUTO else ctas,
+                             "ms": ms, "us_per_query": 1e3 * ms / nq, "recall": recall_of(res, gt[:nq])})
+    return rows
 
 
 def recall_of(res, gt):
@@ -1135,6 +1178,11 @@ def main():
     else:  # timestamps equal ids in this workload
         in_range = bool(np.all(((res >= w_lo[:, None].astype(np.int64)) &
                                 (res < w_hi[:, None].astype(np.int64))) | (res < 0)))
+    if args.small_batch:
+        rows = small_batch_report(args, grab, torch, ix, w, d_q, d_lo, d_hi, gt, steps, warmup)
+        print(json.dumps({"small_batch": rows, "config": workload_config(args, w), "recall_full_batch": recall,
+                          "unit": "ms per call (route + search, CUDA events), inputs resident"}), flush=True)
+        return
     # sorted timestamps: id-window predicate, no gather (f = 0); labels: one byte per examined edge
     alg_bytes = grab.search_bytes(stats, nq, dim, deg, k, 1 if by_labels else 0)
 

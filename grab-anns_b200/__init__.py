@@ -63,7 +63,10 @@ class SearchArgs(C.Structure):
                 ("seeds_per_query", C.c_uint32), ("seed", C.c_uint64), ("d_out_ids", C.c_void_p),
                 ("d_out_dists", C.c_void_p), ("id_scale", C.c_uint64), ("id_offset", C.c_uint64),
                 ("d_stats", C.c_void_p), ("d_ws", C.c_void_p), ("ws_bytes", C.c_size_t),
-                ("stream", C.c_void_p), ("d_out_keys", C.c_void_p)]
+                ("stream", C.c_void_p), ("d_out_keys", C.c_void_p), ("ctas_per_query", C.c_uint32)]
+
+
+CTAS_AUTO = 0xFFFFFFFF
 
 
 class RouterStruct(C.Structure):
@@ -98,6 +101,8 @@ def lib() -> C.CDLL:
         _lib.grab_exact_search_workspace_bytes.argtypes = [C.c_uint64, C.c_uint64, C.c_uint32]
         _lib.grab_graph_search_workspace_bytes.restype = C.c_size_t
         _lib.grab_graph_search_workspace_bytes.argtypes = [C.c_uint64, C.c_uint32]
+        _lib.grab_graph_search_workspace_bytes_for.restype = C.c_size_t
+        _lib.grab_graph_search_workspace_bytes_for.argtypes = [C.c_void_p]
         _lib.grab_route_seeds_workspace_bytes.restype = C.c_size_t
         _lib.grab_route_seeds_workspace_bytes.argtypes = [C.c_uint64, C.c_uint32]
     return _lib
@@ -161,12 +166,35 @@ def exact_search(dataset, queries, k, metric=METRIC_L2, flt: Filter | None = Non
     return ids, dists
 
 
+def search_args(dataset, graph, queries, k, params: SearchParams, metric=METRIC_L2, flt: Filter | None = None,
+                seeds=None, ctas_per_query=0) -> SearchArgs:
+    """A grab_search_args with the inputs filled in (no outputs, no workspace): what
+    grab_graph_search_workspace_bytes_for() needs."""
+    a = SearchArgs()
+    a.d_dataset, a.n, a.dim, a.metric = _p(dataset), dataset.shape[0], dataset.shape[1], metric
+    a.d_graph, a.graph_degree = _p(graph), graph.shape[1]
+    a.d_queries, a.nq, a.k = _p(queries), queries.shape[0], k
+    a.params = params
+    if flt is not None:
+        a.filter = flt
+    if seeds is not None:
+        a.d_seeds, a.seeds_per_query = _p(seeds), seeds.shape[1]
+    a.ctas_per_query = ctas_per_query
+    return a
+
+
+def search_workspace_bytes(args: SearchArgs) -> int:
+    """grab_graph_search_workspace_bytes_for: bytes of d_ws this request needs (covers ctas_per_query > 1)."""
+    return lib().grab_graph_search_workspace_bytes_for(C.byref(args))
+
+
 def graph_search(dataset, graph, queries, k, params: SearchParams, metric=METRIC_L2,
                  flt: Filter | None = None, seeds=None, seed=0x1234ABCD, id_scale=1, id_offset=0,
-                 stats=False, out=None, ws=None, out_keys=None):
+                 stats=False, out=None, ws=None, out_keys=None, ctas_per_query=0):
     """Filtered graph search; returns (ids, dists[, SearchStats]).  out_keys: optional int64 tensor [nq, k] that
     receives the results as (ordered distance << 32 | result id) keys for the sharded exchange step; with
-    out=(None, None) only the keys are written."""
+    out=(None, None) only the keys are written.  ctas_per_query: 0/1 = one CTA per query (the reference's walk),
+    n >= 2 = n co-operating CTAs per query, CTAS_AUTO = as many as fill the GPU (small batches)."""
     import torch
     n, dim = dataset.shape
     nq = queries.shape[0]
@@ -192,8 +220,9 @@ def graph_search(dataset, graph, queries, k, params: SearchParams, metric=METRIC
     if stats:
         st = torch.zeros(6, dtype=torch.int64, device=dataset.device)
         a.d_stats = _p(st)
+    a.ctas_per_query = ctas_per_query
     if ws is None:
-        ws_bytes = lib().grab_graph_search_workspace_bytes(nq, params.hash_bitlen)
+        ws_bytes = search_workspace_bytes(a)
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dataset.device)
     a.d_ws, a.ws_bytes = _p(ws), ws.numel()
     a.stream = _stream()

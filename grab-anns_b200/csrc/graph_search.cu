@@ -80,6 +80,7 @@ struct SearchKernelArgs {
   uint32_t ckeys_cap;
   uint32_t cand_cap, sort_cap;  // survivor list capacity; sort_cap = itopk rounded up to a power of two
   uint32_t inv_active_deg;      // ceil(2^32 / active_deg) (0 when active_deg == 1): e / active_deg = umulhi(e, inv)
+  uint32_t parts;               // CTAs that co-operate on one query (warp-split kernel only); 1 = the plain search
 };
 
 template <int METRIC, int CPL>
@@ -391,10 +392,42 @@ graph_search_kernel(const SearchKernelArgs a) {
 #ifndef GRAB_SEARCH_PREFETCH
 #define GRAB_SEARCH_PREFETCH 0
 #endif
+// 1: the lane that admits a survivor (seed or neighbour) prefetches its vector into L2 at once, so that by the time
+// the gather loop reaches it only the first round of loads still waits for DRAM.
+#ifndef GRAB_SEARCH_PREFETCH_VEC
+#define GRAB_SEARCH_PREFETCH_VEC 0
+#endif
+// 1: the lane that keeps a key (a possible future parent) prefetches that node's graph row into L2.
+#ifndef GRAB_SEARCH_PREFETCH_ROW
+#define GRAB_SEARCH_PREFETCH_ROW 0
+#endif
 #ifndef GRAB_RANK_MERGE_HALF
 #define GRAB_RANK_MERGE_HALF 16
 #endif
 constexpr uint32_t kRankMergeHalf = GRAB_RANK_MERGE_HALF;  // per-warp kept keys up to which the merge is by rank (<= 16)
+
+// Profiling build only (-DGRAB_SEARCH_PHASE_CLOCKS=1): SM cycles every warp spends in each phase of the loop, summed
+// over all launches; read with grab_debug_search_phase_cycles(). Slots (warp 0: 0-7, warp 1: 8-15): start + seeds,
+// gather, sort, first barrier, merge + pick, second barrier, table reset + expand, results.
+#ifndef GRAB_SEARCH_PHASE_CLOCKS
+#define GRAB_SEARCH_PHASE_CLOCKS 0
+#endif
+#if GRAB_SEARCH_PHASE_CLOCKS
+__device__ unsigned long long g_phase_cycles[16];
+#define GRAB_PHASE(i)                                                    \
+  do {                                                                   \
+    const long long now_ = clock64();                                    \
+    if (lane == 0) s_phase[(i) + 8 * warp] += static_cast<uint32_t>(now_ - t_phase); \
+    t_phase = now_;                                                      \
+  } while (0)
+#else
+#define GRAB_PHASE(i)
+#endif
+
+__device__ __forceinline__ void prefetch_l2(const void* p, uint32_t bytes) {
+  const char* c = static_cast<const char*>(p);
+  for (uint32_t b = 0; b < bytes; b += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(c + b));
+}
 
 template <int METRIC, int CPL, int R>
 __global__ void __launch_bounds__(kSearchThreads, GRAB_SEARCH2_CTAS_PER_SM)
@@ -414,10 +447,20 @@ graph_search_split_kernel(const SearchKernelArgs a) {
   __shared__ uint32_t s_nparents, s_kept[2], s_inserted[2];
   __shared__ uint32_t s_stat[6];  // iterations, parents, edges, distances, seeds, resets (this query)
 
-  const uint64_t qi = blockIdx.x;
+  // several CTAs per query: CTA `part` of query qi walks from its own share of the seeds with its own list; all of
+  // them share ONE visited table in global memory, so a node is evaluated by exactly one of them and the lists are
+  // disjoint; a merge of the sorted lists follows the launch
+  const uint32_t parts = a.parts;
+  const uint64_t qi = parts > 1 ? blockIdx.x / parts : blockIdx.x;
+  const uint32_t part = parts > 1 ? static_cast<uint32_t>(blockIdx.x - qi * parts) : 0u;
   if (qi >= a.nq) return;
   const uint32_t tid = threadIdx.x;
   const uint32_t warp = tid >> 5, lane = tid & 31u;
+#if GRAB_SEARCH_PHASE_CLOCKS
+  __shared__ uint32_t s_phase[16];
+  if (tid < 16) s_phase[tid] = 0;
+  long long t_phase = clock64();
+#endif
   const int lane8 = tid & (kTeam - 1);
   const uint32_t wteam = lane / kTeam;  // team inside the warp, 0..3
   const uint32_t wcap = a.ckeys_cap;
@@ -429,8 +472,9 @@ graph_search_split_kernel(const SearchKernelArgs a) {
   for (uint32_t i = tid; i < a.dim / 4; i += kSearchThreads)
     reinterpret_cast<float4*>(q_smem)[i] = __ldg(reinterpret_cast<const float4*>(a.queries + qi * a.dim) + i);
   for (uint32_t i = tid; i < M; i += kSearchThreads) queue[i] = kMaxKey;
-  for (uint32_t i = tid; i < hsize / 4; i += kSearchThreads)
-    reinterpret_cast<uint4*>(hash)[i] = make_uint4(kInvalid, kInvalid, kInvalid, kInvalid);
+  if (parts == 1)  // a shared table is cleared by the host before the launch
+    for (uint32_t i = tid; i < hsize / 4; i += kSearchThreads)
+      reinterpret_cast<uint4*>(hash)[i] = make_uint4(kInvalid, kInvalid, kInvalid, kInvalid);
   if (tid == 0) s_nparents = 0;
   if (tid < 6) s_stat[tid] = 0;
 
@@ -473,8 +517,9 @@ graph_search_split_kernel(const SearchKernelArgs a) {
                                a.filter_kind != GRAB_FILTER_PREFIX) ? 4 * a.num_seeds : a.num_seeds;
     // every provided / window-drawn attempt may be taken; blind draws (4 attempts per seed) stop at the quota
     const uint32_t my_quota = attempts == a.num_seeds ? wcap : (a.num_seeds + 1 - warp) / 2;
-    for (uint32_t i0 = 0; i0 < attempts; i0 += kSearchThreads) {
-      const uint32_t i = i0 + tid;
+    const uint32_t my_attempts = (attempts + parts - 1 - part) / parts;  // attempts part, part + parts, ...
+    for (uint32_t i0 = 0; i0 < my_attempts; i0 += kSearchThreads) {
+      const uint32_t i = i0 + tid < my_attempts ? (i0 + tid) * parts + part : attempts;
       uint32_t id = kInvalid;
       if (i < attempts) {
         if (a.seeds && i < a.seeds_per_query) id = a.seeds[qi * a.seeds_per_query + i];
@@ -496,7 +541,10 @@ graph_search_split_kernel(const SearchKernelArgs a) {
       const bool take = id < a.n && passes(id) && hash_insert(hash, a.hash_bitlen, id);
       const uint32_t vote = __ballot_sync(0xFFFFFFFFu, take);
       const uint32_t pos = ncand + __popc(vote & lt_mask);
-      if (take && pos < my_quota) my_cand[pos] = id;
+      if (take && pos < my_quota) {
+        my_cand[pos] = id;
+        if (GRAB_SEARCH_PREFETCH_VEC) prefetch_l2(a.data + static_cast<size_t>(id) * a.dim, a.dim * 4);
+      }
       ncand += __popc(vote);
     }
     inserted_total = ncand;
@@ -504,6 +552,7 @@ graph_search_split_kernel(const SearchKernelArgs a) {
     if (a.stats && lane == 0) atomicAdd(&s_stat[4], ncand);
   }
   __syncwarp();
+  GRAB_PHASE(0);
 
   uint32_t iter = 0;
   for (;;) {
@@ -564,11 +613,15 @@ graph_search_split_kernel(const SearchKernelArgs a) {
         const uint64_t key = make_skey(d, id[u]);
         const bool keep = lane8 == 0 && ok[u] && key < worst;
         const uint32_t vote = __ballot_sync(0xFFFFFFFFu, keep);
-        if (keep) my_keys[nkeep + __popc(vote & lt_mask)] = key;
+        if (keep) {
+          my_keys[nkeep + __popc(vote & lt_mask)] = key;
+          if (GRAB_SEARCH_PREFETCH_ROW) prefetch_l2(a.graph + static_cast<size_t>(id[u]) * a.deg, a.active_deg * 4);
+        }
         nkeep += __popc(vote);
       }
     }
     __syncwarp();
+    GRAB_PHASE(1);
     // ---- a handful of kept keys (the usual case after the first iterations) is merged by rank and needs no
     //      sort; more are sorted here, by this warp, in registers ----
     if (nkeep > kRankMergeHalf) {
@@ -580,7 +633,9 @@ graph_search_split_kernel(const SearchKernelArgs a) {
       s_kept[warp] = nkeep < M ? nkeep : M;
       s_inserted[warp] = inserted_total;
     }
+    GRAB_PHASE(2);
     __syncthreads();
+    GRAB_PHASE(3);
 
     // ---- warp 0: fold both runs into the list, pick up to `width` unexpanded parents, best first
     //      (search.cu:38-107), while the list is in registers ----
@@ -629,10 +684,12 @@ graph_search_split_kernel(const SearchKernelArgs a) {
       for (int r = 0; r < R; ++r) queue[lane + 32u * r] = t[r];
       if (lane == 0) s_nparents = found;
     }
+    GRAB_PHASE(4);
     __syncthreads();
+    GRAB_PHASE(5);
 
     // ---- visited table half full: clear and re-seed from the current list ----
-    if (s_inserted[0] + s_inserted[1] > hsize / 2) {  // uniform
+    if (parts == 1 && s_inserted[0] + s_inserted[1] > hsize / 2) {  // uniform (a shared table is sized never to fill)
       for (uint32_t i = tid; i < hsize; i += kSearchThreads) hash[i] = kInvalid;
       __syncthreads();
       uint32_t kept = 0;
@@ -673,7 +730,10 @@ graph_search_split_kernel(const SearchKernelArgs a) {
         my_edges += valid;
         const bool take = valid && passes(nb) && hash_insert(hash, a.hash_bitlen, nb);
         const uint32_t vote = __ballot_sync(0xFFFFFFFFu, take);
-        if (take) my_cand[ncand + __popc(vote & lt_mask)] = nb;
+        if (take) {
+          my_cand[ncand + __popc(vote & lt_mask)] = nb;
+          if (GRAB_SEARCH_PREFETCH_VEC) prefetch_l2(a.data + static_cast<size_t>(nb) * a.dim, a.dim * 4);
+        }
         ncand += __popc(vote);
       }
     }
@@ -685,6 +745,7 @@ graph_search_split_kernel(const SearchKernelArgs a) {
     }
     ++iter;
     __syncwarp();
+    GRAB_PHASE(6);
   }
 
   // ---- results: ascending (dist,id); id = local*scale + offset; empty slots are -1 ----
@@ -694,13 +755,30 @@ graph_search_split_kernel(const SearchKernelArgs a) {
     const uint64_t gid = static_cast<uint64_t>(skey_id(key)) * a.id_scale + a.id_offset;
     if (a.out_ids) a.out_ids[qi * a.k + i] = empty ? -1 : static_cast<int64_t>(gid);
     if (a.out_dists) a.out_dists[qi * a.k + i] = empty ? kFltMax : key_dist(key);
-    if (a.out_keys) a.out_keys[qi * a.k + i] = empty ? kMaxKey : ((key & 0xFFFFFFFF00000000ull) | gid);
+    // several CTAs per query: run `part` of query qi, laid out [part][query][k] for the merge of sorted runs
+    if (a.out_keys) a.out_keys[(part * a.nq + qi) * a.k + i] = empty ? kMaxKey : ((key & 0xFFFFFFFF00000000ull) | gid);
   }
   if (a.stats) {
     __syncthreads();
     if (tid < 6) atomicAdd(&a.stats[tid], static_cast<unsigned long long>(s_stat[tid]));
   }
+#if GRAB_SEARCH_PHASE_CLOCKS
+  GRAB_PHASE(7);
+  __syncthreads();
+  if (tid < 16) atomicAdd(&g_phase_cycles[tid], static_cast<unsigned long long>(s_phase[tid]));
+#endif
 }
+
+#if GRAB_SEARCH_PHASE_CLOCKS
+extern "C" int grab_debug_search_phase_cycles(unsigned long long* out16, int reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(out16, g_phase_cycles, sizeof(unsigned long long) * 16);
+  if (e == cudaSuccess && reset) {
+    unsigned long long zero[16] = {};
+    e = cudaMemcpyToSymbol(g_phase_cycles, zero, sizeof(zero));
+  }
+  return e == cudaSuccess ? 0 : -1;
+}
+#endif
 
 template <int METRIC, int R>
 static cudaError_t launch_search_split(const SearchKernelArgs& a, size_t smem, cudaStream_t st) {
@@ -709,7 +787,7 @@ static cudaError_t launch_search_split(const SearchKernelArgs& a, size_t smem, c
     cudaError_t e = cudaFuncSetAttribute(graph_search_split_kernel<METRIC, CPL, R>,                   \
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
     if (e != cudaSuccess) return e;                                                                   \
-    graph_search_split_kernel<METRIC, CPL, R><<<(unsigned)a.nq, kSearchThreads, smem, st>>>(a);       \
+    graph_search_split_kernel<METRIC, CPL, R><<<(unsigned)(a.nq * a.parts), kSearchThreads, smem, st>>>(a);       \
   } while (0)
   if (a.dim == 96) GRAB_SPLIT_LAUNCH(3);
   else if (a.dim == 128) GRAB_SPLIT_LAUNCH(4);
@@ -756,6 +834,74 @@ __global__ void ts_window4_kernel(const uint64_t* __restrict__ ts, uint64_t n,
   if (lane_id() == 0) *reinterpret_cast<uint4*>(windows + qi * 4) = make_uint4(wb, we, 0u, 0u);
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Several CTAs per query (for batches that would leave most of the GPU idle with one CTA each).  The caller's
+// (itopk, search_width, max_iterations) describe the single-CTA search; its budget of search_width * max_iterations
+// expansions is spread over `parts` CTAs that each keep a short list (64 or 128 entries), expand
+// max(1, search_width / parts) parents per iteration and share one visited table in global memory, sized so that
+// it never fills (no reset).  The merge of the parts' sorted lists is the result.  Not the reference's algorithm
+// (it has one CTA per query only, cagra_opt.cu:1394): results are valid top-k lists of evaluated nodes, checked
+// on recall, not bit for bit.
+// ---------------------------------------------------------------------------------------------------------
+int merge_sorted_keys_impl(const uint64_t* d_keys, uint64_t nq, uint32_t parts, uint32_t kp, uint32_t k,
+                           int64_t* d_out_ids, float* d_out_dists, uint64_t* d_out_keys, cudaStream_t st);
+
+struct MultiPlan {
+  uint32_t parts = 1, width = 0, iters = 0, list = 0, nseeds = 0, hash_bitlen = 0;
+  size_t hash_off = 0, keys_off = 0, bytes = 0;  // workspace layout (after the id windows)
+};
+
+static uint32_t base_itopk(const grab_search_args* g) {
+  uint32_t itopk = g->k > g->params.itopk_size ? g->k : g->params.itopk_size;
+  const uint32_t floor_ = g->filter.kind == GRAB_FILTER_PREFIX ? 128u : 64u;
+  return itopk < floor_ ? floor_ : itopk;
+}
+
+static uint32_t base_nseeds(const grab_search_args* g, uint32_t itopk) {
+  const uint32_t spq = g->d_seeds ? g->seeds_per_query : 0;
+  uint32_t nseeds;
+  if (g->filter.kind == GRAB_FILTER_NONE) nseeds = spq > 32 ? spq : 32;
+  else if (g->d_seeds) nseeds = spq;
+  else nseeds = itopk / 4 > 32 ? itopk / 4 : 32;
+  return nseeds > itopk ? itopk : nseeds;
+}
+
+static size_t windows_bytes(uint64_t nq) { return ((sizeof(uint32_t) * 4 * nq + 255) / 256) * 256; }
+
+static MultiPlan plan_multi(const grab_search_args* g) {
+  MultiPlan p;
+  uint32_t parts = g->ctas_per_query;
+  const uint32_t W = g->params.search_width ? g->params.search_width : 1;
+  const uint32_t budget = W * (g->params.max_iterations ? g->params.max_iterations : 1);  // expansions per query
+  if (parts == GRAB_CTAS_AUTO) {
+    // fill about one wave of the GPU (148 SMs x 14 resident CTAs) and keep >= 8 iterations per CTA; beyond 16 CTAs
+    // the walks get too short to pay for their share of the merge (measured: 1 query, 300 expansions: 0.75 ms with
+    // one CTA, 0.26 / 0.15 / 0.40 ms with 4 / 16 / 64)
+    const uint64_t room = g->nq ? 2072 / g->nq : 1;
+    parts = static_cast<uint32_t>(room < 16 ? room : 16);
+    if (parts > budget / 8) parts = budget / 8;
+  }
+  if (parts > 64) parts = 64;  // the merge takes up to 64 runs
+  if (parts < 2 || g->k > 128 || search_kernel_choice() != 1) return p;
+  p.parts = parts;
+  p.width = W / parts ? W / parts : 1;
+  p.iters = (budget + parts * p.width - 1) / (parts * p.width);
+  if (p.iters < 2) p.iters = 2;
+  p.list = g->k <= 64 ? 64 : 128;
+  const uint32_t deg = g->filter.kind == GRAB_FILTER_PREFIX ? g->filter.active_degree : g->graph_degree;
+  uint32_t nseeds = base_nseeds(g, base_itopk(g));
+  if (!g->d_seeds && nseeds < 8 * parts) nseeds = 8 * parts;  // generated seeds: at least 8 per CTA
+  p.nseeds = nseeds;
+  const uint64_t inserts = 4ull * nseeds + static_cast<uint64_t>(parts) * p.iters * p.width * deg;
+  uint32_t bits = 11;
+  while (bits < 22 && (1ull << bits) < 2 * inserts) ++bits;
+  p.hash_bitlen = bits;
+  p.hash_off = windows_bytes(g->nq);
+  p.keys_off = p.hash_off + sizeof(uint32_t) * (size_t(1) << bits) * g->nq;
+  p.bytes = p.keys_off + sizeof(uint64_t) * parts * g->nq * g->k + 256;
+  return p;
+}
+
 // Launcher rules restated from the reference: itopk = max(k, itopk) with floor 64
 // (cagra_opt.cu:1126-1129, :1352-1355) or 128 for the bucket search (:1242-1243); seeds
 // evaluated = clamp(max(32, provided), itopk) unfiltered (:1150-1151) or min(provided, itopk)
@@ -793,6 +939,9 @@ int graph_search_impl(const grab_search_args* g) {
                "graph_search: d_out_keys holds 32-bit result ids, (n-1)*id_scale+id_offset does not fit");
   a.stats = reinterpret_cast<unsigned long long*>(g->d_stats);
 
+  const MultiPlan mp = plan_multi(g);
+  GRAB_REQUIRE(mp.parts > 1 || g->ctas_per_query < 2 || g->ctas_per_query == GRAB_CTAS_AUTO,
+               "graph_search: ctas_per_query %u needs k <= 128 (k = %u) and the warp-split kernel", g->ctas_per_query, g->k);
   uint32_t itopk = g->k > g->params.itopk_size ? g->k : g->params.itopk_size;
   uint32_t floor_ = 64;
   bool need_window = false;
@@ -827,6 +976,12 @@ int graph_search_impl(const grab_search_args* g) {
   else if (g->d_seeds) nseeds = a.seeds_per_query;
   else nseeds = itopk / 4 > 32 ? itopk / 4 : 32;
   if (nseeds > itopk) nseeds = itopk;
+  a.parts = mp.parts;
+  if (mp.parts > 1) {
+    a.width = mp.width; a.max_iter = mp.iters; a.hash_bitlen = mp.hash_bitlen;
+    itopk = a.itopk = mp.list;
+    nseeds = mp.nseeds;
+  }
   a.num_seeds = nseeds;
   a.cand_cap = a.width * a.deg > itopk ? a.width * a.deg : itopk;
   a.cand_cap = (a.cand_cap + 3) & ~3u;
@@ -835,13 +990,14 @@ int graph_search_impl(const grab_search_args* g) {
   a.ckeys_cap = next_pow2(a.cand_cap);
   if (a.ckeys_cap < 32) a.ckeys_cap = 32;
 
-  const bool local_hash = a.hash_bitlen <= 13;
+  const bool local_hash = a.hash_bitlen <= 13 && mp.parts == 1;
   const size_t hash_bytes = sizeof(uint32_t) * (size_t(1) << a.hash_bitlen);
   // warp-split kernel: lists of 64 / 128 entries, at most 128 candidates per warp and iteration
   const uint32_t blind = (!g->d_seeds && !need_window && !(f.kind == GRAB_FILTER_LABELS && f.d_label_offsets) &&
                           f.kind != GRAB_FILTER_NONE && f.kind != GRAB_FILTER_PREFIX) ? 1u : 0u;
   const uint32_t warp_edges = (a.width * a.active_deg + kSearchThreads - 1) / kSearchThreads * 32;
-  const uint32_t warp_seeds = blind ? (nseeds + 1) / 2 : (nseeds + kSearchThreads - 1) / kSearchThreads * 32;
+  const uint32_t part_seeds = (nseeds + mp.parts - 1) / mp.parts;  // attempts of one CTA
+  const uint32_t warp_seeds = blind ? (nseeds + 1) / 2 : (part_seeds + kSearchThreads - 1) / kSearchThreads * 32;
   uint32_t wcap = next_pow2(warp_edges > warp_seeds ? warp_edges : warp_seeds);
   if (wcap < 32) wcap = 32;
   const bool split = search_kernel_choice() == 1 && (a.sort_cap == 64 || a.sort_cap == 128) && wcap <= 128;
@@ -858,7 +1014,9 @@ int graph_search_impl(const grab_search_args* g) {
                    itopk, a.width, a.deg, a.dim, smem);
     return GRAB_ERR_UNSUPPORTED;
   }
-  const size_t need = grab_graph_search_workspace_bytes(g->nq, a.hash_bitlen);
+  GRAB_REQUIRE(mp.parts == 1 || split, "graph_search: ctas_per_query %u: width %u x degree %u does not fit the "
+               "warp-split kernel", mp.parts, a.width, a.active_deg);
+  const size_t need = mp.parts > 1 ? mp.bytes : grab_graph_search_workspace_bytes(g->nq, a.hash_bitlen);
   ScopedDeviceBuffer own;
   void* ws = g->d_ws;
   if (!ws) {
@@ -875,9 +1033,14 @@ int graph_search_impl(const grab_search_args* g) {
     GRAB_CUDA_TRY(cudaGetLastError());
     a.windows = windows;
   }
-  if (!local_hash)
-    a.global_hash = reinterpret_cast<uint32_t*>(static_cast<char*>(ws) +
-                                                ((sizeof(uint32_t) * 4 * g->nq + 255) / 256) * 256);
+  if (!local_hash) a.global_hash = reinterpret_cast<uint32_t*>(static_cast<char*>(ws) + windows_bytes(g->nq));
+  uint64_t* part_keys = nullptr;
+  if (mp.parts > 1) {
+    // the shared visited tables start empty; every CTA leaves its sorted top-k as packed keys for the merge
+    GRAB_CUDA_TRY(cudaMemsetAsync(a.global_hash, 0xFF, mp.keys_off - mp.hash_off, st));
+    part_keys = reinterpret_cast<uint64_t*>(static_cast<char*>(ws) + mp.keys_off);
+    a.out_keys = part_keys; a.out_ids = nullptr; a.out_dists = nullptr;
+  }
   cudaError_t e;
   if (split && a.sort_cap == 64)
     e = g->metric == GRAB_METRIC_L2 ? launch_search_split<GRAB_METRIC_L2, 2>(a, smem, st)
@@ -889,11 +1052,25 @@ int graph_search_impl(const grab_search_args* g) {
     e = g->metric == GRAB_METRIC_L2 ? launch_search<GRAB_METRIC_L2>(a, smem, st)
                                     : launch_search<GRAB_METRIC_IP>(a, smem, st);
   GRAB_CUDA_TRY(e);
+  if (mp.parts > 1) {
+    const int rc = merge_sorted_keys_impl(part_keys, g->nq, mp.parts, g->k, g->k, g->d_out_ids, g->d_out_dists,
+                                          g->d_out_keys, st);
+    if (rc != GRAB_OK) return rc;
+  }
   if (own.ptr) GRAB_CUDA_TRY(cudaStreamSynchronize(st));
   return GRAB_OK;
 }
 
+size_t graph_search_workspace_bytes_for(const grab_search_args* g) {
+  const MultiPlan mp = plan_multi(g);
+  return mp.parts > 1 ? mp.bytes : grab_graph_search_workspace_bytes(g->nq, g->params.hash_bitlen);
+}
+
 }  // namespace grab
+
+extern "C" size_t grab_graph_search_workspace_bytes_for(const grab_search_args* args) {
+  return args ? grab::graph_search_workspace_bytes_for(args) : 0;
+}
 
 extern "C" size_t grab_graph_search_workspace_bytes(uint64_t nq, uint32_t hash_bitlen) {
   size_t b = ((sizeof(uint32_t) * 4 * nq + 255) / 256) * 256 + 256;

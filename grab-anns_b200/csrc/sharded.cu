@@ -25,7 +25,7 @@ constexpr int kMergeWarps = 4;
 // keys: [parts][nq][kp], every run ascending, empty slots = all ones at the tail.
 __global__ void __launch_bounds__(32 * kMergeWarps)
 merge_runs_kernel(const uint64_t* __restrict__ keys, uint64_t nq, uint32_t parts, uint32_t kp, uint32_t k,
-                  int64_t* __restrict__ out_ids, float* __restrict__ out_dists) {
+                  int64_t* __restrict__ out_ids, float* __restrict__ out_dists, uint64_t* __restrict__ out_keys) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
   const uint64_t qi = blockIdx.x * static_cast<uint64_t>(blockDim.x >> 5) + warp;
@@ -55,20 +55,22 @@ merge_runs_kernel(const uint64_t* __restrict__ keys, uint64_t nq, uint32_t parts
       rank += lo;
     }
     if (rank < k) {
-      out_ids[qi * k + rank] = static_cast<int64_t>(key & 0xFFFFFFFFull);
-      out_dists[qi * k + rank] = key_dist(key);
+      if (out_ids) out_ids[qi * k + rank] = static_cast<int64_t>(key & 0xFFFFFFFFull);
+      if (out_dists) out_dists[qi * k + rank] = key_dist(key);
+      if (out_keys) out_keys[qi * k + rank] = key;
     }
   }
   valid = __reduce_add_sync(0xFFFFFFFFu, valid);
   for (uint32_t i = valid + lane; i < k; i += 32) {
-    out_ids[qi * k + i] = -1;
-    out_dists[qi * k + i] = kFltMax;
+    if (out_ids) out_ids[qi * k + i] = -1;
+    if (out_dists) out_dists[qi * k + i] = kFltMax;
+    if (out_keys) out_keys[qi * k + i] = kMaxKey;
   }
 }
 
 int merge_sorted_keys_impl(const uint64_t* d_keys, uint64_t nq, uint32_t parts, uint32_t kp, uint32_t k,
-                           int64_t* d_out_ids, float* d_out_dists, cudaStream_t st) {
-  GRAB_REQUIRE(d_keys && d_out_ids && d_out_dists, "merge_sorted_keys: null pointer");
+                           int64_t* d_out_ids, float* d_out_dists, uint64_t* d_out_keys, cudaStream_t st) {
+  GRAB_REQUIRE(d_keys && ((d_out_ids && d_out_dists) || d_out_keys), "merge_sorted_keys: null pointer");
   GRAB_REQUIRE(parts >= 1 && parts <= 64 && kp >= 1 && kp <= 1024 && k >= 1 && k <= 1024,
                "merge_sorted_keys: parts %u / run length %u / k %u outside [1,64] / [1,1024] / [1,1024]", parts, kp, k);
   if (nq == 0) return GRAB_OK;
@@ -84,7 +86,7 @@ int merge_sorted_keys_impl(const uint64_t* d_keys, uint64_t nq, uint32_t parts, 
                                      static_cast<int>(smem)));
   const uint64_t blocks = (nq + warps - 1) / warps;
   merge_runs_kernel<<<static_cast<unsigned>(blocks), 32 * warps, smem, st>>>(d_keys, nq, parts, kp, k, d_out_ids,
-                                                                              d_out_dists);
+                                                                              d_out_dists, d_out_keys);
   GRAB_CUDA_TRY(cudaGetLastError());
   return GRAB_OK;
 }
@@ -139,7 +141,7 @@ extern "C" {
 
 int grab_merge_sorted_keys(const uint64_t* d_keys, uint64_t nq, uint32_t parts, uint32_t run_length, uint32_t k,
                            int64_t* d_out_ids, float* d_out_dists, void* stream) {
-  return grab::merge_sorted_keys_impl(d_keys, nq, parts, run_length, k, d_out_ids, d_out_dists,
+  return grab::merge_sorted_keys_impl(d_keys, nq, parts, run_length, k, d_out_ids, d_out_dists, nullptr,
                                       static_cast<cudaStream_t>(stream));
 }
 
@@ -200,7 +202,7 @@ int grab_sharded_gather_merge(grab_comm* comm, const uint64_t* d_keys, uint64_t 
   GRAB_REQUIRE(d_keys && d_out_ids && d_out_dists, "sharded_gather_merge: null pointer");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int world = comm ? comm->world : 1;
-  if (world == 1) return merge_sorted_keys_impl(d_keys, nq, 1, run_length, k, d_out_ids, d_out_dists, st);
+  if (world == 1) return merge_sorted_keys_impl(d_keys, nq, 1, run_length, k, d_out_ids, d_out_dists, nullptr, st);
   const size_t need = sizeof(uint64_t) * nq * run_length * world;
   if (!d_gather || gather_bytes < need) {
     set_last_error("sharded_gather_merge: gather buffer %zu < %zu bytes", gather_bytes, need);
@@ -215,7 +217,7 @@ int grab_sharded_gather_merge(grab_comm* comm, const uint64_t* d_keys, uint64_t 
     const ncclResult_t r = a.all_gather(d_keys, d_gather, nq * run_length, ncclUint64, comm->comm, st);
     if (r != ncclSuccess) return nccl_fail("ncclAllGather", r);
   }
-  return merge_sorted_keys_impl(d_gather, nq, static_cast<uint32_t>(world), run_length, k, d_out_ids, d_out_dists, st);
+  return merge_sorted_keys_impl(d_gather, nq, static_cast<uint32_t>(world), run_length, k, d_out_ids, d_out_dists, nullptr, st);
 }
 
 }  // extern "C"

@@ -10,13 +10,11 @@
 #include <string>
 #include <vector>
 
+#include "cagra.cuh"
 #include "device_buffer.hpp"
 #include "grab_anns.h"
 
 namespace cagra {
-
-using BuildParams = grab_build_params;
-using SearchParams = grab_search_params;
 
 class CagraIndex {
  public:
@@ -93,6 +91,15 @@ class CagraIndex {
   void setKnnPrecision(int precision) { knn_precision_ = precision; }
   void setSeed(uint64_t seed) { seed_ = seed; }
   void setInsertBatch(size_t batch) { insert_batch_ = batch ? batch : 64; }
+  // Small requests.  ctas_per_query: CTAs that co-operate on one query when the batch would leave most of the GPU
+  // idle (GRAB_CTAS_AUTO = as many as fill it, the default; 1 = the reference's one CTA per query, bit-compatible
+  // with the stateless search).  exact_below: a single-range query whose range holds at most this many vectors is
+  // answered by an exact scan of the range instead of a graph walk (0 = never): with so few vectors in range the
+  // filtered graph has no paths left between them, and the scan is both exact and cheaper.
+  void setSmallBatchMode(uint32_t ctas_per_query, size_t exact_below) {
+    ctas_per_query_ = ctas_per_query;
+    exact_below_ = exact_below;
+  }
 
  private:
   void upload_timestamps();
@@ -110,6 +117,8 @@ class CagraIndex {
   uint64_t seed_ = 0x9E3779B97F4A7C15ull;
   std::unique_ptr<grab::QueryArena, grab::QueryArenaDeleter> arena_;
   size_t insert_batch_ = 64;  // the reference's batch (src/cagraIndex.cu:165)
+  uint32_t ctas_per_query_ = GRAB_CTAS_AUTO;
+  size_t exact_below_ = 1024;
 };
 
 }  // namespace cagra

@@ -14,6 +14,7 @@
 #include <string>
 #include <vector>
 
+#include "cagra.cuh"
 #include "device_buffer.hpp"
 #include "grab_anns.h"
 
@@ -61,6 +62,15 @@ class CagraIndexOpt {
   void setKnnPrecision(int precision) { knn_precision_ = precision; }
   void setSeed(uint64_t seed) { seed_ = seed; }
   void setInsertBatch(size_t batch) { insert_batch_ = batch ? batch : 4096; }
+  // Small requests.  ctas_per_query: CTAs that co-operate on one query when the batch would leave most of the GPU
+  // idle (GRAB_CTAS_AUTO = as many as fill it, the default; 1 = the reference's one CTA per query, bit-compatible
+  // with the stateless search).  exact_below: a single-range query whose range holds at most this many vectors is
+  // answered by an exact scan of the range instead of a graph walk (0 = never): with so few vectors in range the
+  // filtered graph has no paths left between them, and the scan is both exact and cheaper.
+  void setSmallBatchMode(uint32_t ctas_per_query, size_t exact_below) {
+    ctas_per_query_ = ctas_per_query;
+    exact_below_ = exact_below;
+  }
   // Insert behaviour beyond the reference's.  routed: seeds of the insert searches come from the entry-point
   // router (needs setRouter != 0 and sorted timestamps; otherwise the reference's seed rule applies).
   // repair_mode: how a new node is linked back into the rows of the old nodes it points to --
@@ -89,7 +99,7 @@ class CagraIndexOpt {
  private:
   uint64_t bucket_of(uint64_t ts) const { return ts / bucket_width_; }
   void range_search(const float* host_queries, size_t nq, int k, const uint64_t* lo, const uint64_t* hi,
-                    uint64_t lo1, uint64_t hi1, int64_t* ids, float* dists);
+                    uint64_t lo1, uint64_t hi1, int64_t* ids, float* dists, bool exact = false);
   uint32_t dim_, graph_degree_;
   size_t current_size_ = 0;
   std::vector<float> h_data_;
@@ -108,6 +118,8 @@ class CagraIndexOpt {
   // the reference inserts 32 at a time (src/cagraIndexOpt.cu:590); the sparse mailboxes and the
   // exact kNN inside the batch make four-digit batches as good and far faster
   size_t insert_batch_ = 4096;
+  uint32_t ctas_per_query_ = GRAB_CTAS_AUTO;
+  size_t exact_below_ = 1024;
   bool insert_routed_ = true;
   int insert_repair_mode_ = 1;
   grab_search_params insert_params_ = {128, 4, 0, 100, 13};         // src/cagraIndexOpt.cu:596-602

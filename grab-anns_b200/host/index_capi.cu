@@ -4,7 +4,7 @@
 
 #include "cagraIndex.hpp"
 #include "cagraIndexOpt.cuh"
-#include "common.cuh"
+#include "../csrc/common.cuh"
 #include "grab_index.h"
 #include "timeStampIndex.cuh"
 
@@ -59,6 +59,9 @@ int grab_index_opt_set_insert_search_params(void* h, uint32_t itopk, uint32_t wi
                                             uint32_t hash_bitlen) {
   return guarded([&] { O(h)->setInsertSearchParams(itopk, width, max_iter, hash_bitlen); });
 }
+int grab_index_opt_set_small_batch_mode(void* h, uint32_t ctas_per_query, size_t exact_below) {
+  return guarded([&] { O(h)->setSmallBatchMode(ctas_per_query, exact_below); });
+}
 int grab_index_opt_add(void* h, size_t n, const float* v, const uint64_t* ts) { return guarded([&] { O(h)->add(n, v, ts); }); }
 int grab_index_opt_build(void* h) { return guarded([&] { O(h)->build(); }); }
 int grab_index_opt_insert(void* h, size_t n, const float* v, const uint64_t* ts) { return guarded([&] { O(h)->insert(n, v, ts); }); }
@@ -95,6 +98,9 @@ void* grab_index_create(uint32_t dim, uint32_t graph_degree, size_t vmm_max_byte
 void grab_index_destroy(void* h) { delete I(h); }
 int grab_index_configure(void* h, int metric, int knn_precision, uint64_t seed, size_t insert_batch) {
   return guarded([&] { I(h)->setMetric(metric); I(h)->setKnnPrecision(knn_precision); I(h)->setSeed(seed); I(h)->setInsertBatch(insert_batch); });
+}
+int grab_index_set_small_batch_mode(void* h, uint32_t ctas_per_query, size_t exact_below) {
+  return guarded([&] { I(h)->setSmallBatchMode(ctas_per_query, exact_below); });
 }
 int grab_index_set_query_params(void* h, uint32_t itopk, uint32_t width, uint32_t min_iter, uint32_t max_iter,
                                 uint32_t hash_bitlen) {

@@ -9,7 +9,7 @@
 
 #include "cagraIndex.hpp"
 #include "cagraIndexOpt.cuh"
-#include "common.cuh"
+#include "../csrc/common.cuh"
 #include "timeStampIndex.cuh"
 
 namespace grab {
@@ -136,8 +136,9 @@ void parallel_copy(void* dst, const void* src, size_t bytes) {
 void run_search(grab::QueryArena& A, grab_search_args a, const float* host_q, size_t nq, uint32_t dim, int k,
                 const uint32_t* host_seeds, size_t seeds_per_query, bool broadcast_seeds, const uint64_t* host_lo,
                 const uint64_t* host_hi, int64_t* host_ids, float* host_dists, const grab_router* router = nullptr,
-                uint32_t probes = 0, uint32_t routed_seeds = 0) {
+                uint32_t probes = 0, uint32_t routed_seeds = 0, bool exact_scan = false) {
   std::lock_guard<std::mutex> lock(A.mu);
+  if (exact_scan) { router = nullptr; host_seeds = nullptr; seeds_per_query = 0; }
   const bool own_seeds = host_seeds && seeds_per_query;
   std::vector<uint32_t> expanded;
   if (own_seeds && broadcast_seeds) {
@@ -156,8 +157,6 @@ void run_search(grab::QueryArena& A, grab_search_args a, const float* host_q, si
     s.q.need(m * dim * sizeof(float));
     s.ids.need(m * k * sizeof(int64_t));
     s.dists.need(m * k * sizeof(float));
-    const size_t sws = grab_graph_search_workspace_bytes(m, a.params.hash_bitlen);
-    s.search_ws.need(sws);
     // stage this half-batch in page-locked memory: [queries | lo | hi | seeds]
     const size_t qb = m * dim * sizeof(float), rb = host_lo ? m * sizeof(uint64_t) : 0;
     const size_t sb = own_seeds ? m * seeds_per_query * sizeof(uint32_t) : 0;
@@ -180,8 +179,6 @@ void run_search(grab::QueryArena& A, grab_search_args a, const float* host_q, si
     ac.nq = m;
     ac.d_out_ids = s.ids.as<int64_t>();
     ac.d_out_dists = s.dists.as<float>();
-    ac.d_ws = s.search_ws.p;
-    ac.ws_bytes = sws;
     ac.stream = s.st;
     if (router && !own_seeds) {
       // seeds from the entry-point router: members of the nearest centroids that pass the filter
@@ -199,7 +196,19 @@ void run_search(grab::QueryArena& A, grab_search_args a, const float* host_q, si
       ac.d_seeds = s.seeds.as<uint32_t>();
       ac.seeds_per_query = static_cast<uint32_t>(seeds_per_query);
     }
-    ok(grab_graph_search(&ac), "graph search");
+    if (exact_scan) {
+      // a range this narrow holds fewer vectors than a walk would visit: scan it (exact, and cheaper)
+      const size_t sws = grab_exact_search_workspace_bytes(a.n, m, static_cast<uint32_t>(k));
+      s.search_ws.need(sws);
+      ok(grab_exact_search(ac.d_dataset, ac.n, ac.dim, ac.metric, &ac.filter, ac.d_queries, m, static_cast<uint32_t>(k),
+                           ac.d_out_ids, ac.d_out_dists, s.search_ws.p, sws, s.st), "exact scan");
+    } else {
+      const size_t sws = grab_graph_search_workspace_bytes_for(&ac);
+      s.search_ws.need(sws);
+      ac.d_ws = s.search_ws.p;
+      ac.ws_bytes = sws;
+      ok(grab_graph_search(&ac), "graph search");
+    }
     // results of this half leave as soon as its search is done, while the other half is staged and searched
     const size_t ib = m * k * sizeof(int64_t), db = m * k * sizeof(float);
     s.h_out.need(ib + db);
@@ -323,6 +332,7 @@ void CagraIndex::query(const float* host_queries, size_t num_queries, int k, int
   grab_search_args a = make_args(static_cast<float*>(d_data_->data()), current_size_, dim_, metric_,
                                  static_cast<uint32_t*>(d_graph_->data()), graph_degree_, nullptr, num_queries, k,
                                  search_params_, nullptr, nullptr, seed_);
+  a.ctas_per_query = ctas_per_query_;
   a.filter.kind = GRAB_FILTER_NONE;
   run_search(arena_of(arena_), a, host_queries, num_queries, dim_, k, seeds, num_seeds_per_query, false, nullptr,
              nullptr, host_indices, host_dists);
@@ -340,11 +350,24 @@ void CagraIndex::query_range(const float* host_queries, size_t num_queries, int 
   grab_search_args a = make_args(static_cast<float*>(d_data_->data()), current_size_, dim_, metric_,
                                  static_cast<uint32_t*>(d_graph_->data()), graph_degree_, nullptr, num_queries, k,
                                  search_params_, nullptr, nullptr, seed_);
+  a.ctas_per_query = ctas_per_query_;
   a.filter.kind = GRAB_FILTER_TS_RANGE;
   a.filter.d_ts = static_cast<uint64_t*>(d_ts_->data());
   a.filter.lo = start_ts;
   a.filter.hi = end_ts;
   a.filter.ts_sorted = ts_sorted_;
+  // vectors inside the range (each map entry is one timestamp here)
+  size_t in_range_count = 0;
+  for (auto it = ts_to_ids_.lower_bound(start_ts); it != ts_to_ids_.end() && it->first < end_ts; ++it) {
+    in_range_count += it->second.size();
+    if (in_range_count > exact_below_) break;
+  }
+  if (in_range_count == 0) { fill_no_data(host_indices, host_dists, num_queries * k); return; }
+  if (in_range_count <= exact_below_) {
+    run_search(arena_of(arena_), a, host_queries, num_queries, dim_, k, nullptr, 0, false, nullptr, nullptr, host_indices,
+               host_dists, nullptr, 0, 0, true);
+    return;
+  }
   std::vector<uint32_t> sampled;
   if (!ts_sorted_) {
     // one seed list for all queries, drawn from the ids inside the range (src/cagraIndex.cu:267-296)
@@ -529,6 +552,7 @@ void CagraIndexOpt::query(const float* host_queries, size_t num_queries, int k, 
   grab_search_args a = make_args(static_cast<float*>(d_data_->data()), current_size_, dim_, metric_,
                                  static_cast<uint32_t*>(d_graph_->data()), graph_degree_, nullptr, num_queries, k,
                                  search_params_, nullptr, nullptr, seed_);
+  a.ctas_per_query = ctas_per_query_;
   a.filter.kind = GRAB_FILTER_NONE;
   run_search(arena_of(arena_), a, host_queries, num_queries, dim_, k, seeds, num_seeds_per_query, false, nullptr,
              nullptr, host_indices, host_dists, ensure_router(), router_probes_, router_seeds_);
@@ -548,6 +572,7 @@ void CagraIndexOpt::query_local(const float* host_queries, size_t num_queries, i
   grab_search_args a = make_args(static_cast<float*>(d_data_->data()), current_size_, dim_, metric_,
                                  static_cast<uint32_t*>(d_graph_->data()), graph_degree_, nullptr, num_queries, k,
                                  search_params_, nullptr, nullptr, seed_);
+  a.ctas_per_query = ctas_per_query_;
   a.filter.kind = GRAB_FILTER_PREFIX;
   a.filter.active_degree = static_cast<uint32_t>(local_degree_);
   run_search(arena_of(arena_), a, host_queries, num_queries, dim_, k, seeds.data(), seeds.size(), true, nullptr,
@@ -555,16 +580,22 @@ void CagraIndexOpt::query_local(const float* host_queries, size_t num_queries, i
 }
 
 void CagraIndexOpt::range_search(const float* host_queries, size_t nq, int k, const uint64_t* lo, const uint64_t* hi,
-                                 uint64_t lo1, uint64_t hi1, int64_t* ids, float* dists) {
+                                 uint64_t lo1, uint64_t hi1, int64_t* ids, float* dists, bool exact) {
   grab_search_args a = make_args(static_cast<float*>(d_data_->data()), current_size_, dim_, metric_,
                                  static_cast<uint32_t*>(d_graph_->data()), graph_degree_, nullptr, nq, k, search_params_,
                                  nullptr, nullptr, seed_);
+  a.ctas_per_query = ctas_per_query_;
   a.filter.kind = GRAB_FILTER_TS_RANGE;
   a.filter.d_ts = static_cast<uint64_t*>(d_ts_->data());
   a.filter.ts_sorted = ts_sorted_;
   if (!lo) {
     a.filter.lo = lo1;
     a.filter.hi = hi1;
+    if (exact) {
+      run_search(arena_of(arena_), a, host_queries, nq, dim_, k, nullptr, 0, false, nullptr, nullptr, ids, dists, nullptr,
+                 0, 0, true);
+      return;
+    }
   }
   std::vector<uint32_t> seeds;
   size_t spq = 0;
@@ -606,15 +637,18 @@ void CagraIndexOpt::range_search(const float* host_queries, size_t nq, int k, co
 void CagraIndexOpt::query_range(const float* host_queries, size_t num_queries, int k, uint64_t start_bucket,
                                 uint64_t end_bucket, int64_t* host_indices, float* host_dists, uint32_t) {
   if (current_size_ == 0 || num_queries == 0) return;
-  // "no data in the range" early-out (src/cagraIndexOpt.cu:479-485)
-  bool any = false;
-  for (auto it = ts_to_ids_.lower_bound(bucket_of(start_bucket)); it != ts_to_ids_.end() && !any; ++it) {
+  // "no data in the range" early-out (src/cagraIndexOpt.cu:479-485); the same pass counts the vectors inside the
+  // range up to the exact-scan threshold
+  size_t inside = 0;
+  for (auto it = ts_to_ids_.lower_bound(bucket_of(start_bucket)); it != ts_to_ids_.end() && inside <= exact_below_; ++it) {
     if (end_bucket == 0 || it->first > bucket_of(end_bucket - 1)) break;
     for (uint32_t id : it->second)
-      if (id < current_size_ && h_timestamps_[id] >= start_bucket && h_timestamps_[id] < end_bucket) { any = true; break; }
+      if (id < current_size_ && h_timestamps_[id] >= start_bucket && h_timestamps_[id] < end_bucket && ++inside > exact_below_)
+        break;
   }
-  if (!any) { fill_no_data(host_indices, host_dists, num_queries * k); return; }
-  range_search(host_queries, num_queries, k, nullptr, nullptr, start_bucket, end_bucket, host_indices, host_dists);
+  if (inside == 0) { fill_no_data(host_indices, host_dists, num_queries * k); return; }
+  range_search(host_queries, num_queries, k, nullptr, nullptr, start_bucket, end_bucket, host_indices, host_dists,
+               inside <= exact_below_);
 }
 
 void CagraIndexOpt::query_range_batch(const float* host_queries, size_t num_queries, int k, const uint64_t* start_ts,

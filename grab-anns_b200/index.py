@@ -60,6 +60,11 @@ class _Base:
     def load(self, path):
         self._call("load", C.c_char_p(str(path).encode()))
 
+    def set_small_batch_mode(self, ctas_per_query=0xFFFFFFFF, exact_below=1024):
+        """ctas_per_query: CTAs co-operating on one query (0xFFFFFFFF = as many as fill the GPU, 1 = the reference's
+        one per query); single-range queries over at most exact_below vectors are answered by an exact scan."""
+        self._call("set_small_batch_mode", C.c_uint32(ctas_per_query), C.c_size_t(exact_below))
+
     def set_query_params(self, itopk=256, width=6, min_iter=1, max_iter=50, hash_bitlen=13):
         self._call("set_query_params", C.c_uint32(itopk), C.c_uint32(width), C.c_uint32(min_iter),
                    C.c_uint32(max_iter), C.c_uint32(hash_bitlen))

@@ -24,7 +24,7 @@
 extern "C" {
 #endif
 
-#define GRAB_ABI_VERSION 2
+#define GRAB_ABI_VERSION 3
 
 enum grab_status {
   GRAB_OK = 0,
@@ -135,7 +135,16 @@ int grab_exact_search_noalloc(const float* d_dataset, uint64_t n, uint32_t dim, 
 /* [nq,k] uint64): the results once more as ascending keys [ordered fp32 distance : 32 |  */
 /* result id : 32] (all ones = empty) -- the form the sharded exchange step gathers; needs */
 /* result ids < 2^32.  With d_out_keys given, d_out_ids / d_out_dists may be NULL.         */
+/* ctas_per_query: 0 or 1 = one CTA per query, the reference's algorithm (grid = queries, */
+/* cagra_opt.cu:1394).  n >= 2 = n CTAs co-operate on every query (for batches too small   */
+/* to fill the GPU): the budget of search_width * max_iterations expansions is spread over  */
+/* n CTAs with short lists of their own, disjoint shares of the seeds and ONE visited table */
+/* per query in global memory; their sorted lists are merged.  Same result FORMAT, not the  */
+/* same walk: judged on recall.  GRAB_CTAS_AUTO = as many as fill the GPU (1 for batches of */
+/* about a thousand queries and more).  Needs k <= 128; workspace size from                 */
+/* grab_graph_search_workspace_bytes_for().                                                  */
 /* ------------------------------------------------------------------------------------ */
+#define GRAB_CTAS_AUTO 0xFFFFFFFFu
 typedef struct grab_search_args {
   const float* d_dataset;
   uint64_t n;
@@ -159,9 +168,12 @@ typedef struct grab_search_args {
   size_t ws_bytes;
   void* stream;
   uint64_t* d_out_keys;
+  uint32_t ctas_per_query;
 } grab_search_args;
 
 size_t grab_graph_search_workspace_bytes(uint64_t nq, uint32_t hash_bitlen);
+/* the same for a filled-in argument struct (d_ws / ws_bytes ignored): covers ctas_per_query > 1 */
+size_t grab_graph_search_workspace_bytes_for(const grab_search_args* args);
 int grab_graph_search(const grab_search_args* args);
 
 /* Reference-shaped wrappers (same argument order as the functions they replace, int

@@ -32,6 +32,10 @@ int grab_index_opt_set_insert_mode(void* h, int routed, int repair_mode);
 /* Search parameters of routed inserts (default itopk 128, width 4, 16 iterations, hash 2^12). */
 int grab_index_opt_set_insert_search_params(void* h, uint32_t itopk, uint32_t width, uint32_t max_iter,
                                             uint32_t hash_bitlen);
+/* Small requests: ctas_per_query as in grab_search_args (GRAB_CTAS_AUTO is the default of the classes); a
+ * single-range query whose range holds at most exact_below vectors (default 1024, 0 = never) is answered by an
+ * exact scan of the range.  No counterpart in the reference. */
+int grab_index_opt_set_small_batch_mode(void* h, uint32_t ctas_per_query, size_t exact_below);
 int grab_index_opt_add(void* h, size_t n, const float* vectors, const uint64_t* timestamps);
 int grab_index_opt_build(void* h);
 int grab_index_opt_insert(void* h, size_t n, const float* vectors, const uint64_t* timestamps);
@@ -51,6 +55,7 @@ int grab_index_opt_load(void* h, const char* path);
 void* grab_index_create(uint32_t dim, uint32_t graph_degree, size_t vmm_max_bytes);
 void grab_index_destroy(void* h);
 int grab_index_configure(void* h, int metric, int knn_precision, uint64_t seed, size_t insert_batch);
+int grab_index_set_small_batch_mode(void* h, uint32_t ctas_per_query, size_t exact_below);
 int grab_index_set_query_params(void* h, uint32_t itopk, uint32_t width, uint32_t min_iter, uint32_t max_iter,
                                 uint32_t hash_bitlen);
 int grab_index_add(void* h, size_t n, const float* vectors, const uint64_t* timestamps_or_null);

@@ -31,7 +31,7 @@ def test_header_symbols_exported():
 def test_status_strings_and_version():
     grab = importlib.import_module("grab-anns_b200")
     lib = grab.lib()
-    assert lib.grab_abi_version() == 2
+    assert lib.grab_abi_version() == 3
     assert lib.grab_status_string(0) == b"ok"
     assert lib.grab_status_string(1) == b"invalid argument"
 

@@ -1,0 +1,97 @@
+"""Several CTAs per query (grab_search_args.ctas_per_query): for batches too small to fill the GPU.  Not the
+reference's walk (it launches one CTA per query, src/index/cagra_opt.cu:1394), so the check is the result
+contract -- valid ids inside the filter, no duplicates, ascending canonical fp32 distances of exactly those ids --
+and recall against the exact filtered ground truth at least that of the one-CTA search minus one point."""
+import numpy as np
+import pytest
+
+from conftest import clustered
+
+pytestmark = pytest.mark.gpu
+
+
+def _t(a):
+    import torch
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+@pytest.fixture(scope="module")
+def index(oracle):
+    n, dim, deg = 20000, 64, 32
+    data = clustered(n, dim, 40, 1.0, 41)
+    knn = oracle.knn_block(data, 2 * deg)
+    g = oracle.prune(knn, deg)
+    rev, cnt = oracle.reverse_graph(g)
+    return data, oracle.merge_graphs(g, rev, cnt)
+
+
+def _contract(oracle, data, q, ids, dists, lo=None, hi=None):
+    ids, dists = ids.cpu().numpy(), dists.cpu().numpy()
+    for i in range(ids.shape[0]):
+        row = ids[i][ids[i] >= 0]
+        assert len(set(row.tolist())) == len(row)                       # no node twice
+        if lo is not None:
+            assert np.all((row >= lo[i]) & (row < hi[i]))                # inside the range
+        assert np.all(np.diff(dists[i][: len(row)]) >= 0)               # ascending
+        for j in range(0, len(row), 3):
+            assert dists[i, j] == oracle.dist(q[i], data[row[j]])       # canonical fp32 bits
+        assert np.all(ids[i][len(row):] == -1)
+
+
+@pytest.mark.parametrize("nq,ctas", [(1, 16), (7, 8), (64, 4), (33, 0xFFFFFFFF)])
+def test_multi_cta_unfiltered(grab, oracle, index, nq, ctas):
+    data, g = index
+    n, dim = data.shape
+    rng = np.random.default_rng(100 + nq)
+    k = 10
+    q = data[rng.integers(0, n, nq)] + 0.1 * rng.standard_normal((nq, dim)).astype(np.float32)
+    gt, _ = oracle.exact_search(data, q, k)
+    p = grab.SearchParams(128, 4, 0, 32, 13)
+    one, _ = grab.graph_search(_t(data), _t(g.view(np.int32)), _t(q), k, p)
+    ids, dists, st = grab.graph_search(_t(data), _t(g.view(np.int32)), _t(q), k, p, ctas_per_query=ctas, stats=True)
+    _contract(oracle, data, q, ids, dists)
+    r1, rm = oracle.recall(one.cpu().numpy(), gt), oracle.recall(ids.cpu().numpy(), gt)
+    assert rm >= r1 - 0.01 and rm > 0.9, (rm, r1)
+    assert st.hash_resets == 0 and st.parents > 0
+
+
+def test_multi_cta_range_filter_and_seeds(grab, oracle, index):
+    data, g = index
+    n, dim = data.shape
+    rng = np.random.default_rng(7)
+    nq, k = 24, 10
+    q = data[rng.integers(0, n, nq)] + 0.1 * rng.standard_normal((nq, dim)).astype(np.float32)
+    ts = np.arange(n, dtype=np.uint64)
+    lo = rng.integers(0, n - n // 2, nq).astype(np.uint64)
+    hi = lo + np.uint64(n // 2)
+    gt, _ = oracle.exact_search(data, q, k, ts=ts, lo=lo, hi=hi)
+    f = grab.make_filter(grab.FILTER_TS_RANGE, ts=_t(ts.view(np.int64)), lo=_t(lo.view(np.int64)),
+                         hi=_t(hi.view(np.int64)), ts_sorted=True)
+    p = grab.SearchParams(64, 4, 0, 40, 13)
+    # seeds drawn by the kernel inside each query's id window
+    ids, dists = grab.graph_search(_t(data), _t(g.view(np.int32)), _t(q), k, p, flt=f, ctas_per_query=8)
+    _contract(oracle, data, q, ids, dists, lo, hi)
+    assert oracle.recall(ids.cpu().numpy(), gt) > 0.85
+    # seeds provided: each CTA takes every eighth one
+    seeds = np.stack([rng.integers(int(lo[i]), int(hi[i]), 64) for i in range(nq)]).astype(np.uint32)
+    import torch
+    keys = torch.empty((nq, k), dtype=torch.int64, device="cuda")
+    ids2, dists2 = grab.graph_search(_t(data), _t(g.view(np.int32)), _t(q), k, p, flt=f,
+                                     seeds=_t(seeds.view(np.int32)), ctas_per_query=8, out_keys=keys)
+    _contract(oracle, data, q, ids2, dists2, lo, hi)
+    assert oracle.recall(ids2.cpu().numpy(), gt) > 0.85
+    kk = keys.cpu().numpy().view(np.uint64)
+    valid = ids2.cpu().numpy() >= 0
+    assert np.array_equal((kk & np.uint64(0xFFFFFFFF))[valid].astype(np.int64), ids2.cpu().numpy()[valid])
+
+
+def test_multi_cta_refusals(grab, index):
+    data, g = index
+    q = data[:4]
+    with pytest.raises(Exception):   # k above the per-CTA list length
+        grab.graph_search(_t(data), _t(g.view(np.int32)), _t(q), 200, grab.SearchParams(256, 4, 0, 32, 13),
+                          ctas_per_query=4)
+    # AUTO on the same request falls back to one CTA per query
+    ids, _ = grab.graph_search(_t(data), _t(g.view(np.int32)), _t(q), 200, grab.SearchParams(256, 4, 0, 32, 13),
+                               ctas_per_query=0xFFFFFFFF)
+    assert ids.shape == (4, 200)
