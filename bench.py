@@ -591,10 +591,14 @@ class Index:
         self.centroids = centroids
 
     def filter(self, lo, hi=None):
+        """With a router, the filter carries an id-window scratch: route_seeds leaves every query's window there and
+        the search of the same step reads it (one search of the timestamp column per step instead of two)."""
+        import torch
         g = self.grab
         if self.by_labels:
             return g.make_filter(g.FILTER_LABELS, labels=self.d_labels, masks=lo, label_offsets=self.d_offs)
-        return g.make_filter(g.FILTER_TS_RANGE, ts=self.d_ts, lo=lo, hi=hi, ts_sorted=True)
+        win = torch.empty((lo.shape[0], 4), dtype=torch.int32, device="cuda") if self.router is not None else None
+        return g.make_filter(g.FILTER_TS_RANGE, ts=self.d_ts, lo=lo, hi=hi, ts_sorted=True, id_windows=win)
 
 
 class Searcher:

@@ -47,7 +47,7 @@ class Filter(C.Structure):
     _fields_ = [("kind", C.c_int32), ("ts_sorted", C.c_int32), ("d_ts", C.c_void_p),
                 ("d_lo", C.c_void_p), ("d_hi", C.c_void_p), ("lo", C.c_uint64), ("hi", C.c_uint64),
                 ("d_labels", C.c_void_p), ("d_masks", C.c_void_p), ("mask", C.c_uint32),
-                ("active_degree", C.c_uint32), ("d_label_offsets", C.c_void_p)]
+                ("active_degree", C.c_uint32), ("d_label_offsets", C.c_void_p), ("d_id_windows", C.c_void_p)]
 
 
 class SearchStats(C.Structure):
@@ -129,7 +129,9 @@ def _stream():
 
 
 def make_filter(kind=FILTER_NONE, ts=None, lo=None, hi=None, ts_sorted=False, labels=None,
-                masks=None, active_degree=0, label_offsets=None) -> Filter:
+                masks=None, active_degree=0, label_offsets=None, id_windows=None) -> Filter:
+    """id_windows: optional int32 tensor [nq, 4] shared by route_seeds (writes every query's id window) and a
+    graph_search with the same queries and ranges (reads it instead of searching the timestamps again)."""
     f = Filter()
     f.kind = kind
     f.ts_sorted = int(ts_sorted)
@@ -145,8 +147,9 @@ def make_filter(kind=FILTER_NONE, ts=None, lo=None, hi=None, ts_sorted=False, la
         f.mask = int(masks)
     f.active_degree = active_degree
     f.d_label_offsets = _p(label_offsets)
+    f.d_id_windows = _p(id_windows)
     # the struct only holds raw pointers: keep the tensors alive as long as the filter is
-    f._keepalive = (ts, lo, hi, labels, masks, label_offsets)
+    f._keepalive = (ts, lo, hi, labels, masks, label_offsets, id_windows)
     return f
 
 

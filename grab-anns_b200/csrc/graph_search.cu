@@ -1027,7 +1027,9 @@ int graph_search_impl(const grab_search_args* g) {
     return GRAB_ERR_WORKSPACE;
   }
   uint32_t* windows = static_cast<uint32_t*>(ws);
-  if (need_window) {
+  if (need_window && f.d_id_windows) {
+    a.windows = f.d_id_windows;  // left there by grab_route_seeds for these queries and this filter
+  } else if (need_window) {
     ts_window4_kernel<<<(unsigned)((g->nq * 32 + 255) / 256), 256, 0, st>>>(f.d_ts, g->n, f.d_lo, f.d_hi,
                                                                            f.lo, f.hi, g->nq, windows);
     GRAB_CUDA_TRY(cudaGetLastError());

@@ -327,6 +327,7 @@ struct RouteArgs {
   const uint64_t* ts; const uint64_t* lo; const uint64_t* hi; uint64_t lo1, hi1;
   const uint8_t* labels; const uint32_t* masks; uint32_t mask1; const uint32_t* label_offsets;
   uint32_t* seeds;  // [nq, S]
+  uint32_t* id_windows;  // [nq, 4] or NULL: the id window of every query's range is left here for the search
 };
 
 __device__ __forceinline__ uint32_t lower_bound_u32(const uint32_t* a, uint32_t b, uint32_t e, uint32_t x) {
@@ -411,6 +412,8 @@ __global__ void __launch_bounds__(256) route_seeds_kernel(RouteArgs a) {
     if (a.ts_sorted) {
       wlo = warp_lower_bound_u64(a.ts, n32, tlo);
       whi = warp_lower_bound_u64(a.ts, n32, thi);
+      if (a.id_windows && lane == 0 && a.filter_kind == GRAB_FILTER_TS_RANGE)
+        *reinterpret_cast<uint4*>(a.id_windows + q * 4) = make_uint4(wlo, whi, 0u, 0u);
       if (whi <= wlo) nwin = 0;
     } else {
       check = true;
@@ -648,6 +651,7 @@ int route_seeds_impl(const grab_router* r, const float* d_queries, uint64_t nq, 
         GRAB_REQUIRE((f->d_lo == nullptr) == (f->d_hi == nullptr),
                      "route_seeds: d_lo and d_hi must both be given or both NULL");
         a.ts = f->d_ts; a.lo = f->d_lo; a.hi = f->d_hi; a.lo1 = f->lo; a.hi1 = f->hi; a.ts_sorted = f->ts_sorted;
+        a.id_windows = f->d_id_windows;
         break;
       case GRAB_FILTER_LABELS:
         GRAB_REQUIRE(f->d_labels, "route_seeds: label filter without d_labels");

@@ -101,7 +101,7 @@ struct QueryArena {
   };
   struct Slot {
     cudaStream_t st = nullptr;
-    Buf q, lo, hi, ids, dists, seeds, search_ws, route_ws;
+    Buf q, lo, hi, ids, dists, seeds, search_ws, route_ws, windows;
     Pinned h_in, h_out;  // [queries | lo | hi | seeds] and [ids | dists] of this half-batch
     ~Slot() { if (st) cudaStreamDestroy(st); }
   };
@@ -185,6 +185,11 @@ void run_search(grab::QueryArena& A, grab_search_args a, const float* host_q, si
       const size_t rws = grab_route_seeds_workspace_bytes(m, probes);
       s.route_ws.need(rws);
       s.seeds.need(m * routed_seeds * sizeof(uint32_t));
+      if (ac.filter.kind == GRAB_FILTER_TS_RANGE && ac.filter.ts_sorted) {
+        // the router leaves every query's id window here and the search reads it
+        s.windows.need(m * 4 * sizeof(uint32_t));
+        ac.filter.d_id_windows = s.windows.as<uint32_t>();
+      }
       ok(grab_route_seeds(router, s.q.as<float>(), m, a.n, &ac.filter, probes, routed_seeds, a.seed,
                           s.seeds.as<uint32_t>(), s.route_ws.p, rws, s.st), "seed routing");
       ac.d_seeds = s.seeds.as<uint32_t>();

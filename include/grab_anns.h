@@ -77,6 +77,11 @@ typedef struct grab_filter {
    * [d_label_offsets[l], d_label_offsets[l+1])), 33 offsets on the device let the search draw its
    * own seeds inside the query's labels */
   const uint32_t* d_label_offsets;
+  /* kind TS_RANGE with ts_sorted, optional: [nq,4] uint32 scratch shared by the two calls of a routed search.
+   * grab_route_seeds WRITES every query's id window (first id with ts >= lo, first id with ts >= hi, 0, 0)
+   * here; grab_graph_search, given the same pointer with the same queries and ranges, READS it instead of
+   * searching the timestamp column again.  NULL: each call computes what it needs. */
+  uint32_t* d_id_windows;
 } grab_filter;
 
 /* Per-launch counters of the graph search (all queries summed), the inputs of the

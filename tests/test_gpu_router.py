@@ -129,6 +129,18 @@ def test_routed_seeds_reach_separated_clusters(grab, oracle):
     assert ((routed >= lo[:, None].astype(np.int64)) & (routed < hi[:, None].astype(np.int64)) | (routed < 0)).all()
     r_plain, r_routed = oracle.recall(plain.cpu().numpy(), gt), oracle.recall(routed, gt)
     assert r_routed > 0.95 and r_routed > r_plain + 0.1, (r_plain, r_routed)
+    # the id windows handed from the router to the search: the windows themselves, and the same results bit for bit
+    import torch
+    win = torch.full((nq, 4), -1, dtype=torch.int32, device="cuda")
+    fw = grab.make_filter(grab.FILTER_TS_RANGE, ts=d_ts, lo=d_lo, hi=d_hi, ts_sorted=True, id_windows=win)
+    seeds_w = grab.route_seeds(r, d_q, n, fw, probes=4, seeds_per_query=32)
+    assert torch.equal(seeds_w, seeds)
+    w = win.cpu().numpy()
+    assert np.array_equal(w[:, 0], np.searchsorted(ts, lo, side="left"))
+    assert np.array_equal(w[:, 1], np.searchsorted(ts, hi, side="left"))
+    shared, shared_d = grab.graph_search(d_data, graph, d_q, k, p, flt=fw, seeds=seeds_w)
+    again, again_d = grab.graph_search(d_data, graph, d_q, k, p, flt=f, seeds=seeds)
+    assert torch.equal(shared, again) and torch.equal(shared_d, again_d)
 
 
 @pytest.mark.parametrize("dim,metric,nc,nq", [(128, 0, 256, 1000), (100, 0, 200, 300), (768, 1, 384, 513)])
