@@ -1098,7 +1098,7 @@ def main():
                     "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
                     "data": "synthetic", "config": cfg, "recall_at_100": rec["recall_at_k_merged"],
                     "results_in_range": rec["results_in_range"], "sharded": rec,
-                    "gpu_launches": (5 if world > 1 else 5) * steps,
+                    "gpu_launches": 4 * steps,  # centroid ranking, seed kernel, search, merge of the gathered runs
                     "roofline": {"bound": "hbm", "achieved": rec["search_kernel_roofline_frac"] * peak, "peak": peak,
                                  "unit": "GB/s", "frac": rec["search_kernel_roofline_frac"], "traffic": None,
                                  "peak_source": peak_source},
@@ -1132,7 +1132,7 @@ def main():
                     "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                     "config": workload_config(args, w, sharded=True), "recall_at_10": rec["recall_at_k_merged"],
                     "results_in_range": rec["results_in_range"], "sharded": rec,
-                    "gpu_launches": (5 if world > 1 else 4) * steps, "cpu_baseline": None, "clocks": clocks}
+                    "gpu_launches": 4 * steps, "cpu_baseline": None, "clocks": clocks}
             print(json.dumps(line), flush=True)
         if dist is not None:
             dist.destroy_process_group()
@@ -1369,8 +1369,9 @@ def main():
                     "d2h_bytes_per_step": int(12 * nq * k), "mode": e2e_mode,
                     "one_stream_value": world * nq / (ms_e2e_seq / 1e3)},
             "e2e_class": e2e_cls,
-            # per step: centroid ranking + seed kernel (router), id windows (sorted timestamps), search
-            "gpu_launches": ((2 if ix.router is not None else 0) + (1 if by_labels else 2)) * steps,
+            # per step: centroid ranking + seed kernel (router; it leaves the id windows for the search), search;
+            # without a router the search computes the id windows of sorted timestamps itself
+            "gpu_launches": ((2 if ix.router is not None else (0 if by_labels else 1)) + 1) * steps,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": roofline_traffic(args, w, alg_bytes),
                          "peak_source": peak_source,
