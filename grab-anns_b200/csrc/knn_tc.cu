@@ -35,24 +35,64 @@ namespace grab {
 namespace tc {
 
 constexpr int BM = 128, BN = 128, BK = 64;  // BK bf16 = one 128-byte swizzle row
-constexpr int STAGES = 3;
+#ifndef GRAB_KNN_STAGES
+#define GRAB_KNN_STAGES 3
+#endif
+constexpr int STAGES = GRAB_KNN_STAGES;
 constexpr int CTAS_PER_SM = 2;
 constexpr int STAGE_BYTES = (BM + BN) * BK * 2;  // 32 KB
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;  // one K block of either operand: 16 KB
+// "A resident": when the whole K extent of a row tile fits kAresBlocks K blocks, the row tile's A operand is loaded
+// ONCE per row tile and stays in shared memory for the sweep over the column tiles; only B streams through the ring
+// (kAresStages stages of 16 KB).  Per 128 x 128 tile the SM then reads 48 KB instead of 96 KB through its L2 port,
+// which is what bounds the MMA side of this kernel (measured: 0.28 s of the 0.37 s at 1M x 128 with no epilogue
+// work at all, i.e. 72 bytes per clock and SM).
+constexpr int kAresBlocks = 3;
+constexpr int kAresStages = (STAGES * STAGE_BYTES - kAresBlocks * A_BYTES) / B_BYTES;  // same footprint: 3
 constexpr int THREADS = 192;
 // Instruction descriptor: D fp32, A/B bf16, both K-major, N=128, M=128.
 constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((BN >> 3) << 17) | ((BM >> 4) << 24);
 
+// Profiling build only (-DGRAB_KNN_PHASE_CLOCKS=1): SM cycles the epilogue warps spend waiting for an accumulator,
+// waiting for TMEM loads, in chunks without / with a value below a threshold, and in buffer cuts; summed over all
+// launches, read with grab_debug_knn_phase_cycles().  Slots: 0 accumulator wait, 1 TMEM load wait, 2 chunks without a
+// hit, 3 chunks with a hit, 4 cuts, 5 rest; 8-13 the event counts of slots 0-5.
+#ifndef GRAB_KNN_PHASE_CLOCKS
+#define GRAB_KNN_PHASE_CLOCKS 0
+#endif
+#if GRAB_KNN_PHASE_CLOCKS
+__device__ unsigned long long g_knn_phase[16];
+#define KNN_PHASE(i)                                                           \
+  do {                                                                         \
+    const long long now_ = clock64();                                          \
+    if (lane == 0) { ph[i] += static_cast<unsigned long long>(now_ - t_ph); ++ph[8 + (i)]; } \
+    t_ph = now_;                                                               \
+  } while (0)
+#else
+#define KNN_PHASE(i)
+#endif
+
 // ------------------------------------------------------------------ epilogue helpers
+__device__ __forceinline__ float fmin3(float a, float b, float c) {  // one instruction on sm_100
+  float d;
+  asm("min.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 // Cut the candidate buffers of the rows that are (nearly) full back to their KC smallest keys
 // and tighten the rows' thresholds.  Warp-cooperative, one row at a time: the row's keys sit in
 // registers (element g = j*32 + lane), a 4-pass radix select on the ordered distance finds the
 // KC-th smallest value, a ballot compaction writes the survivors back.  No ordering is produced:
 // the exact re-rank sorts later.  Kept out of line: it runs rarely and would otherwise bloat
 // the hot loop's instruction footprint.
+// Capacity of a row's candidate buffer: a cut happens when fewer than 32 free slots are left and brings the row back to
+// KC entries, so CAP - 32 - KC appends lie between two cuts of a row (96 / 160 / 96 / 224 for KC 32 / 64 / 128 / 256).
+__host__ __device__ constexpr uint32_t cap_of(uint32_t kc) { return kc < 128 ? 4 * kc + (kc == 32 ? 32 : 0) : 2 * kc; }
+
 template <int KC>
 __device__ __noinline__ uint2 compress_rows(uint64_t* warp_buf, uint32_t* hist, uint32_t lane, uint32_t cnt,
                                             float thr, bool force) {
-  constexpr uint32_t CAP = 2 * KC;
+  constexpr uint32_t CAP = cap_of(KC);
   constexpr int NREG = CAP / 32;
   const uint32_t lt_mask = (1u << lane) - 1u;
   __syncwarp();
@@ -162,20 +202,19 @@ __device__ __forceinline__ bool tile_skipped(const TileRange& t, uint32_t j) {
 }
 
 struct SharedCtl {
-  uint64_t full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2];
+  uint64_t full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], a_full, a_empty;
   uint32_t tmem_base;
   int abort_flag;
   uint32_t hist[4][256];    // radix-select histogram per epilogue warp
 };
 
-template <int KC>
+template <int KC, bool ARES>
 __global__ void __launch_bounds__(THREADS, CTAS_PER_SM)
 knn_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
               const ScanWindow* __restrict__ windows, uint64_t n, uint32_t kblocks, uint32_t last_kk,
               uint32_t num_row_tiles, uint64_t* __restrict__ scratch, uint64_t* __restrict__ out_keys,
-              int* __restrict__ status) {
-  constexpr uint32_t CAP = 2 * KC;
-  constexpr int NREG = CAP / 32;
+              const float* __restrict__ thr0, int* __restrict__ status) {
+  constexpr uint32_t CAP = cap_of(KC);
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // stage s: A tile at s*STAGE_BYTES, B tile 16 KB after it; control block after the ring
   unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -192,6 +231,8 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
       mbar_init(smem_u32(&ctl->tmem_full[a]), 1);
       mbar_init(smem_u32(&ctl->tmem_empty[a]), 4);
     }
+    mbar_init(smem_u32(&ctl->a_full), 1);
+    mbar_init(smem_u32(&ctl->a_empty), 1);
     ctl->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -207,23 +248,45 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
   if (warp == 0) {
     // ============================ TMA producer ============================
     if (lane == 0) {
-      uint32_t it = 0;
+      uint32_t it = 0, nrt = 0;
       uint32_t issued_phase[STAGES];
       bool issued[STAGES];
       for (int s = 0; s < STAGES; ++s) { issued[s] = false; issued_phase[s] = 0; }
+      bool a_issued = false;
+      uint32_t a_phase = 0;
+      constexpr uint32_t NST = ARES ? kAresStages : STAGES;
+      unsigned char* b_ring = ring + kAresBlocks * A_BYTES;  // ARES: the B ring behind the resident A blocks
       bool ok = true;
       for (uint32_t rt = blockIdx.x; rt < num_row_tiles && ok; rt += gridDim.x) {
         const TileRange t = tile_range(windows, n, rt);
+        if (ARES) {
+          // the MMAs of the previous row tile must be done with A before it is overwritten
+          if (!mbar_wait(smem_u32(&ctl->a_empty), (nrt & 1) ^ 1, abort_flag)) { ok = false; break; }
+          const uint32_t bar = smem_u32(&ctl->a_full);
+          mbar_expect_tx(bar, kblocks * A_BYTES);
+          for (uint32_t kb = 0; kb < kblocks; ++kb)
+            tma_load_2d(smem_u32(ring + kb * A_BYTES), &map_a, bar, static_cast<int32_t>(kb * BK),
+                        static_cast<int32_t>(t.row0));
+          a_issued = true;
+          a_phase = nrt & 1;
+          ++nrt;
+        }
         for (uint32_t j = t.jb; j < t.je && ok; ++j) {
           if (tile_skipped(t, j)) continue;
           for (uint32_t kb = 0; kb < kblocks; ++kb, ++it) {
-            const uint32_t s = it % STAGES, phase = (it / STAGES) & 1;
+            const uint32_t s = it % NST, phase = (it / NST) & 1;
             if (!mbar_wait(smem_u32(&ctl->empty[s]), phase ^ 1, abort_flag)) { ok = false; break; }
             const uint32_t bar = smem_u32(&ctl->full[s]);
-            mbar_expect_tx(bar, STAGE_BYTES);
-            const uint32_t dst = smem_u32(ring + s * STAGE_BYTES);
-            tma_load_2d(dst, &map_a, bar, static_cast<int32_t>(kb * BK), static_cast<int32_t>(t.row0));
-            tma_load_2d(dst + BM * BK * 2, &map_b, bar, static_cast<int32_t>(kb * BK), static_cast<int32_t>(j * BN));
+            if (ARES) {
+              mbar_expect_tx(bar, B_BYTES);
+              tma_load_2d(smem_u32(b_ring + s * B_BYTES), &map_b, bar, static_cast<int32_t>(kb * BK),
+                          static_cast<int32_t>(j * BN));
+            } else {
+              mbar_expect_tx(bar, STAGE_BYTES);
+              const uint32_t dst = smem_u32(ring + s * STAGE_BYTES);
+              tma_load_2d(dst, &map_a, bar, static_cast<int32_t>(kb * BK), static_cast<int32_t>(t.row0));
+              tma_load_2d(dst + A_BYTES, &map_b, bar, static_cast<int32_t>(kb * BK), static_cast<int32_t>(j * BN));
+            }
             issued[s] = true;
             issued_phase[s] = phase;
           }
@@ -235,15 +298,24 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
           if (issued[s])
             for (uint32_t i = 0; i < (1u << 16); ++i)
               if (mbar_try_wait(smem_u32(&ctl->full[s]), issued_phase[s])) break;
+        if (a_issued)
+          for (uint32_t i = 0; i < (1u << 16); ++i)
+            if (mbar_try_wait(smem_u32(&ctl->a_full), a_phase)) break;
       }
     }
   } else if (warp == 1) {
     // ============================ MMA issuer ============================
     if (lane == 0) {
-      uint32_t it = 0, tile = 0;
+      uint32_t it = 0, tile = 0, nrt = 0;
+      constexpr uint32_t NST = ARES ? kAresStages : STAGES;
+      unsigned char* b_ring = ring + kAresBlocks * A_BYTES;
       bool ok = true;
       for (uint32_t rt = blockIdx.x; rt < num_row_tiles && ok; rt += gridDim.x) {
         const TileRange t = tile_range(windows, n, rt);
+        if (ARES) {
+          if (!mbar_wait(smem_u32(&ctl->a_full), nrt & 1, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+        }
         for (uint32_t j = t.jb; j < t.je && ok; ++j) {
           if (tile_skipped(t, j)) continue;
           const uint32_t acc = tile & 1, acc_phase = (tile >> 1) & 1;
@@ -251,12 +323,13 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + acc * BN;
           for (uint32_t kb = 0; kb < kblocks; ++kb, ++it) {
-            const uint32_t s = it % STAGES, phase = (it / STAGES) & 1;
+            const uint32_t s = it % NST, phase = (it / NST) & 1;
             if (!mbar_wait(smem_u32(&ctl->full[s]), phase, abort_flag)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t a_addr = smem_u32(ring + s * STAGE_BYTES);
+            const uint32_t a_addr = smem_u32(ARES ? ring + kb * A_BYTES : ring + s * STAGE_BYTES);
+            const uint32_t b_addr = ARES ? smem_u32(b_ring + s * B_BYTES) : a_addr + A_BYTES;
             const uint64_t da = smem_desc_sw128(a_addr);
-            const uint64_t db = smem_desc_sw128(a_addr + BM * BK * 2);
+            const uint64_t db = smem_desc_sw128(b_addr);
             // the last K block holds operand columns only in its first last_kk slices of 16 (the rest is zero padding)
             const uint32_t nkk = kb + 1 == kblocks ? last_kk : BK / 16;
 #pragma unroll
@@ -270,6 +343,10 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
           tc_commit(smem_u32(&ctl->tmem_full[acc]));  // accumulator complete
           ++tile;
         }
+        if (ARES && ok) {
+          tc_commit(smem_u32(&ctl->a_empty));  // arrives once every MMA of this row tile has read A
+          ++nrt;
+        }
       }
     }
   } else {
@@ -282,6 +359,10 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     bool ok = true;
 
     uint32_t* hist = ctl->hist[warp - 2];
+#if GRAB_KNN_PHASE_CLOCKS
+    unsigned long long ph[16] = {};
+    long long t_ph = clock64();
+#endif
 
     for (uint32_t rt = blockIdx.x; rt < num_row_tiles && ok; rt += gridDim.x) {
       const TileRange t = tile_range(windows, n, rt);
@@ -289,13 +370,16 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
       ScanWindow w{0, 0, 0, 0};
       if (row_valid) w = windows[t.row0 + r_local];
       uint32_t cnt = 0;
-      float thr = __int_as_float(0x7f800000);  // +inf
+      // the row's threshold starts at +inf, or at the bound a pass over a sample of the columns found for it
+      float thr = thr0 != nullptr && row_valid ? thr0[t.row0 + r_local] : __int_as_float(0x7f800000);
       for (uint32_t j = t.jb; j < t.je && ok; ++j) {
         if (tile_skipped(t, j)) continue;
         const uint32_t acc = tile & 1, acc_phase = (tile >> 1) & 1;
         const uint32_t c0 = j * BN;
+        KNN_PHASE(5);
         if (!mbar_wait(smem_u32(&ctl->tmem_full[acc]), acc_phase, abort_flag)) { ok = false; break; }
         tc_fence_after();
+        KNN_PHASE(0);
         const bool need_mask = !(c0 >= t.safe_lo && c0 + BN <= t.safe_hi && (c0 + BN <= t.ex_lo || c0 >= t.ex_hi));
         const uint32_t taddr = tmem_base + ((quarter * 32) << 16) + acc * BN;
 
@@ -304,19 +388,25 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         // a min tree over the chunk, one compare with the row's threshold, one warp vote.  Only chunks in which some
         // row has a value below its threshold build the per-element mask and append.
         auto process = [&](uint32_t (&v)[32], uint32_t chunk) {
-          float m8[8];
+#if defined(GRAB_KNN_PROBE_NO_EPILOGUE)  // timing probe only: results are wrong
+          if (v[0] == 0x7fc12345u) my_buf[cnt++] = chunk;
+          return;
+#endif
+          float m8[8];  // three-input minima: 16 instead of 24 operations for the groups of four, 4 instead of 7 above
 #pragma unroll
           for (int i = 0; i < 8; ++i)
-            m8[i] = fminf(fminf(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1])),
-                          fminf(__uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3])));
-          const float mn = fminf(fminf(fminf(m8[0], m8[1]), fminf(m8[2], m8[3])),
-                                 fminf(fminf(m8[4], m8[5]), fminf(m8[6], m8[7])));
+            m8[i] = fminf(fmin3(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]), __uint_as_float(v[4 * i + 2])),
+                          __uint_as_float(v[4 * i + 3]));
+          const float mn = fmin3(fmin3(m8[0], m8[1], m8[2]), fmin3(m8[3], m8[4], m8[5]), fminf(m8[6], m8[7]));
           const bool hit = row_valid && mn < thr;
-          if (!__any_sync(0xFFFFFFFFu, hit)) return;
+          if (!__any_sync(0xFFFFFFFFu, hit)) { KNN_PHASE(2); return; }
           if (hit) {
             const uint32_t cbase = c0 + chunk * 32;
             // the min tree's first level already says which groups of four hold a value below the threshold
-            // (usually one): only those are looked at element by element
+            // (usually one): only those are looked at element by element.  Measured and slower (full sweeps of the
+            // 1M x 128 build, own block / other blocks): a warp-uniform loop over the union of the rows' group masks
+            // with a switch per group 135 / 495 ms, appends straight from the registers of each flagged group without
+            // the mask word 64 / 358 ms, against 55 / 339 ms for this form.
             uint32_t m = 0;
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
@@ -334,24 +424,33 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
               my_buf[cnt++] = make_key(__uint_as_float(pick32(v, i)), cbase + i);
             }
           }
+          KNN_PHASE(3);
           if (__any_sync(0xFFFFFFFFu, cnt > CAP - 32)) {
             const uint2 r = compress_rows<KC>(warp_buf, hist, lane, cnt, thr, false);
             cnt = r.x;
             thr = __uint_as_float(r.y);
+            KNN_PHASE(4);
           }
         };
 
         uint32_t va[32], vb[32];
+#if defined(GRAB_KNN_PROBE_NO_TMEM_LOAD)  // timing probe only: the accumulator is never read
+        if (false)
+#endif
+        {
         tmem_ld32_issue(taddr, va);
         tmem_ld_wait(va);
+        KNN_PHASE(1);
 #pragma unroll 1
         for (uint32_t pair = 0; pair < BN / 64; ++pair) {
           tmem_ld32_issue(taddr + pair * 64 + 32, vb);
           process(va, 2 * pair);
           tmem_ld_wait(vb);
+          KNN_PHASE(1);
           if (pair + 1 < BN / 64) tmem_ld32_issue(taddr + pair * 64 + 64, va);
           process(vb, 2 * pair + 1);
-          if (pair + 1 < BN / 64) tmem_ld_wait(va);
+          if (pair + 1 < BN / 64) { tmem_ld_wait(va); KNN_PHASE(1); }
+        }
         }
 
         tc_fence_before();
@@ -375,6 +474,11 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
       }
       __syncwarp();
     }
+#if GRAB_KNN_PHASE_CLOCKS
+    KNN_PHASE(5);
+    if (lane == 0 && thr0 != nullptr)  // the seeded full sweeps only
+      for (int i = 0; i < 16; ++i) atomicAdd(&g_knn_phase[i], ph[i]);
+#endif
   }
 
   tc_fence_before();
@@ -383,6 +487,21 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
   if (warp == 1) tmem_dealloc(tmem_base, 2 * BN);
   if (threadIdx.x == 0 && ctl->abort_flag) *status = GRAB_ERR_TIMEOUT;
 }
+
+#if GRAB_KNN_PHASE_CLOCKS
+}  // namespace tc
+}  // namespace grab
+extern "C" int grab_debug_knn_phase_cycles(unsigned long long* out16, int reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(out16, grab::tc::g_knn_phase, sizeof(unsigned long long) * 16);
+  if (e == cudaSuccess && reset) {
+    unsigned long long zero[16] = {};
+    e = cudaMemcpyToSymbol(grab::tc::g_knn_phase, zero, sizeof(zero));
+  }
+  return e == cudaSuccess ? 0 : -1;
+}
+namespace grab {
+namespace tc {
+#endif
 
 // ------------------------------------------------------------------ operand preparation
 // Deterministic column means: fixed row chunks, fixed summation order.
@@ -487,15 +606,53 @@ rerank_kernel(const float* __restrict__ data, uint32_t dim, const uint64_t* __re
   }
 }
 
+// ------------------------------------------------------------------ threshold seeding
+// A first pass over every `stride`-th column gives each row a bound on its final threshold: the kSeedKC-th
+// smallest ranking distance among the sampled columns of the row's window.  About kSeedKC * stride columns of the
+// full sweep lie below it, far more than the `want` the row keeps (it falls short only if kSeedKC of the row's
+// true top-`want` columns are sampled: Binomial(want, 1/stride) >= kSeedKC, below 1e-9 for the sizes used), so the
+// full sweep starts with a threshold that rejects all but a few hundred columns instead of tightening it from
+// +inf over the first hundred thousand.  Windows in sample space: column c = stride * c'.
+constexpr uint32_t kSeedKC = 32;
+
+__global__ void sample_window_kernel(const ScanWindow* __restrict__ w, uint64_t n, uint32_t stride,
+                                     ScanWindow* __restrict__ ws) {
+  const uint64_t r = blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x;
+  if (r >= n) return;
+  const ScanWindow a = w[r];
+  ScanWindow b;
+  b.begin = (a.begin + stride - 1) / stride;
+  b.end = (a.end + stride - 1) / stride;
+  b.xbegin = (a.xbegin + stride - 1) / stride;
+  b.xend = (a.xend + stride - 1) / stride;
+  ws[r] = b;
+}
+
+// thr0[r] = largest of the row's kSeedKC sample keys; +inf when the sample held fewer (the row's window is small)
+__global__ void seed_threshold_kernel(const uint64_t* __restrict__ keys, uint64_t n, float* __restrict__ thr0) {
+  const uint64_t r = (blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x) >> 5;
+  const uint32_t lane = threadIdx.x & 31;
+  if (r >= n) return;
+  static_assert(kSeedKC == 32, "one key per lane");
+  uint64_t key = keys[r * kSeedKC + lane];
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const uint64_t o = __shfl_xor_sync(0xFFFFFFFFu, key, off);
+    key = o > key ? o : key;
+  }
+  if (lane == 0) thr0[r] = key == kMaxKey ? __int_as_float(0x7f800000) : key_dist(key);
+}
+
 // ------------------------------------------------------------------ host side
-static int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint32_t kp) {
+// row_stride: the map views every row_stride-th row of the operand (`rows` of them)
+static int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint32_t kp, uint32_t row_stride = 1) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) {
     set_last_error("knn_tc: cuTensorMapEncodeTiled is not available from the driver");
     return GRAB_ERR_CUDA;
   }
   const cuuint64_t dims[2] = {kp, rows};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(kp) * 2};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(kp) * 2 * row_stride};
   const cuuint32_t box[2] = {BK, BM};
   const cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
@@ -510,6 +667,23 @@ static int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint32_t 
 
 }  // namespace tc
 
+// GRAB_KNN_SEED=0 in the environment switches the threshold seeding off (for comparisons).
+static bool seed_thresholds_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("GRAB_KNN_SEED");
+    return !(v && v[0] == '0');
+  }();
+  return on;
+}
+
+static bool a_resident_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("GRAB_KNN_ARES");
+    return !(v && v[0] == '0');
+  }();
+  return on;
+}
+
 // precision 1: bf16 operands; 2: split bf16 (hi+lo), close to fp32 products.
 int knn_tc_impl(const float* d_dataset, uint64_t n, uint32_t dim, int metric, const uint64_t* h_block_offsets,
                 uint32_t num_blocks, uint32_t k, int mode, int precision, uint32_t* d_out_knn,
@@ -523,7 +697,7 @@ int knn_tc_impl(const float* d_dataset, uint64_t n, uint32_t dim, int metric, co
   GRAB_REQUIRE(precision == 1 || precision == 2, "knn_tc: precision must be 1 (bf16) or 2 (split bf16)");
   const uint32_t want = k + k / 4 + 1;  // over-fetch: the exact re-rank picks the final k
   GRAB_REQUIRE(k >= 1 && want <= 256, "knn_tc: k %u too large for the tensor-core path (max 204)", k);
-  const uint32_t kc = want <= 128 ? 128 : 256;
+  const uint32_t kc = want <= 64 ? 64 : (want <= 128 ? 128 : 256);
   const int split = precision == 2;
   const uint32_t kused = (split ? 3 * dim : dim) + 3;  // + the three column-norm terms
   const uint32_t kp = (kused + BK - 1) / BK * BK;
@@ -542,7 +716,7 @@ int knn_tc_impl(const float* d_dataset, uint64_t n, uint32_t dim, int metric, co
   GRAB_CUDA_TRY(wins.alloc(sizeof(ScanWindow) * n));
   GRAB_CUDA_TRY(a_op.alloc(sizeof(__nv_bfloat16) * n * kp));
   GRAB_CUDA_TRY(b_op.alloc(sizeof(__nv_bfloat16) * n * kp));
-  GRAB_CUDA_TRY(scratch.alloc(sizeof(uint64_t) * static_cast<uint64_t>(grid) * BM * 2 * kc));
+  GRAB_CUDA_TRY(scratch.alloc(sizeof(uint64_t) * static_cast<uint64_t>(grid) * BM * cap_of(kc)));
   GRAB_CUDA_TRY(keys.alloc(sizeof(uint64_t) * n * kc));
   GRAB_CUDA_TRY(status.alloc(sizeof(int)));
   GRAB_CUDA_TRY(cudaMemsetAsync(status.ptr, 0, sizeof(int), st));
@@ -574,17 +748,63 @@ int knn_tc_impl(const float* d_dataset, uint64_t n, uint32_t dim, int metric, co
   if (rc != GRAB_OK) return rc;
 
   const size_t smem = STAGES * STAGE_BYTES + sizeof(SharedCtl) + 1024;
-  if (kc == 128) {
-    GRAB_CUDA_TRY(cudaFuncSetAttribute(knn_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    knn_tc_kernel<128><<<grid, THREADS, smem, st>>>(map_a, map_b, wins.as<ScanWindow>(), n, kblocks, last_kk,
-                                                   num_row_tiles, scratch.as<uint64_t>(), keys.as<uint64_t>(),
-                                                   status.as<int>());
-  } else {
-    GRAB_CUDA_TRY(cudaFuncSetAttribute(knn_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    knn_tc_kernel<256><<<grid, THREADS, smem, st>>>(map_a, map_b, wins.as<ScanWindow>(), n, kblocks, last_kk,
-                                                   num_row_tiles, scratch.as<uint64_t>(), keys.as<uint64_t>(),
-                                                   status.as<int>());
+  // the A operand of a row tile stays in shared memory when its K extent fits (GRAB_KNN_ARES=0 switches it off)
+  const bool ares = kblocks <= static_cast<uint32_t>(kAresBlocks) && a_resident_enabled();
+  // threshold seeding from every stride-th column (see above); skipped when the sweeps are short anyway
+  const uint32_t stride = want <= 170 ? 16 : 32;
+  uint64_t widest = 0;  // columns the widest row window sweeps
+  for (uint32_t b = 0; b < num_blocks; ++b) {
+    const uint64_t own = h_block_offsets[b + 1] - h_block_offsets[b];
+    const uint64_t sweep = mode == 0 ? own : n - own;
+    widest = sweep > widest ? sweep : widest;
   }
+  const float* d_thr0 = nullptr;
+  ScopedDeviceBuffer wins_s, keys_s, thr0;
+  if (seed_thresholds_enabled() && widest >= static_cast<uint64_t>(stride) * kSeedKC * 8) {
+    const uint64_t n_s = (n + stride - 1) / stride;
+    GRAB_CUDA_TRY(wins_s.alloc(sizeof(ScanWindow) * n));
+    GRAB_CUDA_TRY(keys_s.alloc(sizeof(uint64_t) * n * kSeedKC));
+    GRAB_CUDA_TRY(thr0.alloc(sizeof(float) * n));
+    sample_window_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(wins.as<ScanWindow>(), n, stride,
+                                                                      wins_s.as<ScanWindow>());
+    GRAB_CUDA_TRY(cudaGetLastError());
+    CUtensorMap map_bs;
+    rc = make_map(&map_bs, pb, n_s, kp, stride);
+    if (rc != GRAB_OK) return rc;
+    if (ares) {
+      GRAB_CUDA_TRY(cudaFuncSetAttribute(knn_tc_kernel<kSeedKC, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      knn_tc_kernel<kSeedKC, true><<<grid, THREADS, smem, st>>>(map_a, map_bs, wins_s.as<ScanWindow>(), n, kblocks, last_kk,
+                                                               num_row_tiles, scratch.as<uint64_t>(), keys_s.as<uint64_t>(),
+                                                               nullptr, status.as<int>());
+    } else {
+      GRAB_CUDA_TRY(cudaFuncSetAttribute(knn_tc_kernel<kSeedKC, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      knn_tc_kernel<kSeedKC, false><<<grid, THREADS, smem, st>>>(map_a, map_bs, wins_s.as<ScanWindow>(), n, kblocks, last_kk,
+                                                                num_row_tiles, scratch.as<uint64_t>(), keys_s.as<uint64_t>(),
+                                                                nullptr, status.as<int>());
+    }
+    GRAB_CUDA_TRY(cudaGetLastError());
+    seed_threshold_kernel<<<(unsigned)((n * 32 + 255) / 256), 256, 0, st>>>(keys_s.as<uint64_t>(), n, thr0.as<float>());
+    GRAB_CUDA_TRY(cudaGetLastError());
+    d_thr0 = thr0.as<float>();
+    tm.mark("threshold seeding (sampled columns)");
+  }
+#define GRAB_KNN_TC_LAUNCH(KC, AR)                                                                                        \
+  do {                                                                                                                    \
+    GRAB_CUDA_TRY(cudaFuncSetAttribute(knn_tc_kernel<KC, AR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));   \
+    knn_tc_kernel<KC, AR><<<grid, THREADS, smem, st>>>(map_a, map_b, wins.as<ScanWindow>(), n, kblocks, last_kk,          \
+                                                      num_row_tiles, scratch.as<uint64_t>(), keys.as<uint64_t>(), d_thr0, \
+                                                      status.as<int>());                                                  \
+  } while (0)
+  if (ares) {
+    if (kc == 64) GRAB_KNN_TC_LAUNCH(64, true);
+    else if (kc == 128) GRAB_KNN_TC_LAUNCH(128, true);
+    else GRAB_KNN_TC_LAUNCH(256, true);
+  } else {
+    if (kc == 64) GRAB_KNN_TC_LAUNCH(64, false);
+    else if (kc == 128) GRAB_KNN_TC_LAUNCH(128, false);
+    else GRAB_KNN_TC_LAUNCH(256, false);
+  }
+#undef GRAB_KNN_TC_LAUNCH
   GRAB_CUDA_TRY(cudaGetLastError());
   tm.mark("tcgen05 all-pairs + top-k");
   const size_t rsmem = sizeof(uint64_t) * kc + sizeof(float) * dim;
