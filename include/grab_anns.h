@@ -57,7 +57,11 @@ typedef struct grab_search_params {
   uint32_t search_width;   /* 5  */
   uint32_t min_iterations; /* 0 (carried, unused, as in the reference) */
   uint32_t max_iterations; /* 20 */
-  uint32_t hash_bitlen;    /* 12 */
+  uint32_t hash_bitlen;    /* 12: log2 of the visited table of a query.  An upper bound up to 13: the per-CTA table
+                            * in shared memory holds max(2^11, 8 * itopk) slots at most (it is cleared and re-seeded
+                            * from the list when half full, so a smaller table costs repeated evaluations, not
+                            * results, and keeps more queries resident per SM); above 13 the table lives in global
+                            * memory at the size asked for */
 } grab_search_params;
 
 /* Filter of one search call.  One [lo,hi) / mask per call (the reference's form) when
