@@ -153,3 +153,32 @@ def test_sharded_and_selftest_entry_points_validate_on_the_host(lib):
     assert lib.grab_selftest_sort_merge(one, one, C.c_uint64(1), 64, 40, 40, 2, one, null) == 1  # rank merge: <= 32
     assert lib.grab_selftest_hash_insert(one, 2, one, 4, 64, one, null) == 1
     assert lib.grab_selftest_hash_insert(one, 8, one, 4, 48, one, null) == 1                    # threads % 32
+
+
+def test_search_workspace_plan_is_host_arithmetic(lib):
+    """grab_graph_search_workspace_bytes_for() plans a request without touching the GPU: one CTA per query needs the
+    id windows only (plus a global table above 2^13), several CTAs per query add the shared table and the per-CTA
+    result runs, and AUTO falls back to one CTA for batches that fill the GPU or walks too short to split."""
+    grab = importlib.import_module("grab-anns_b200")
+    lib.grab_graph_search_workspace_bytes_for.restype = C.c_size_t
+    lib.grab_graph_search_workspace_bytes.restype = C.c_size_t
+
+    def need(nq, k, itopk, width, iters, bitlen, ctas):
+        a = grab.SearchArgs()
+        a.n, a.dim, a.graph_degree, a.nq, a.k = 100000, 128, 32, nq, k
+        a.params = grab.SearchParams(itopk, width, 0, iters, bitlen)
+        a.ctas_per_query = ctas
+        return lib.grab_graph_search_workspace_bytes_for(C.byref(a))
+
+    single = lib.grab_graph_search_workspace_bytes(C.c_uint64(64), C.c_uint32(13))
+    assert need(64, 10, 256, 6, 50, 13, 0) == single == need(64, 10, 256, 6, 50, 13, 1)
+    multi = need(64, 10, 256, 6, 50, 13, 8)
+    # 8 runs of k keys per query + a shared table of at least 2 x (seeds + 8 CTAs x iterations x width x degree) slots
+    assert multi >= single + 8 * 64 * 10 * 8 + 4 * 64 * 2 * (8 * 38 * 1 * 32)
+    assert need(64, 10, 256, 6, 50, 13, grab.CTAS_AUTO) > single          # small batch, long walk: split
+    assert need(10000, 10, 256, 6, 50, 13, grab.CTAS_AUTO) == lib.grab_graph_search_workspace_bytes(
+        C.c_uint64(10000), C.c_uint32(13))                                  # the batch fills the GPU: one CTA each
+    assert need(64, 10, 64, 3, 5, 11, grab.CTAS_AUTO) == lib.grab_graph_search_workspace_bytes(
+        C.c_uint64(64), C.c_uint32(11))                                     # 15 expansions: nothing to split
+    assert need(64, 200, 256, 6, 50, 13, grab.CTAS_AUTO) == single          # k above the per-CTA list: one CTA each
+    assert lib.grab_graph_search_workspace_bytes_for(None) == 0
