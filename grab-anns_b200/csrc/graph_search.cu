@@ -372,7 +372,7 @@ graph_search_kernel(const SearchKernelArgs a) {
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// Warp-split variant of the same search loop (lists of 64 or 128 entries, at most 128 candidates per warp and
+// Warp-split variant of the same search loop (lists of 64 or 128 entries, at most 256 candidates per warp and
 // iteration).  The two warps of a CTA no longer share a survivor list: each expands its own half of the
 // parents' edges, compacts its survivors by ballot (no shared counters), gathers THEIR vectors, keeps the keys
 // that beat the list's worst entry and sorts them in registers; then warp 0 folds both sorted runs into the
@@ -627,7 +627,8 @@ graph_search_split_kernel(const SearchKernelArgs a) {
     if (nkeep > kRankMergeHalf) {
       if (nkeep <= 32) warp_sort_regs<1>(my_keys, nkeep, lane);
       else if (nkeep <= 64) warp_sort_regs<2>(my_keys, nkeep, lane);
-      else warp_sort_regs_128(my_keys, nkeep, lane);
+      else if (nkeep <= 128) warp_sort_regs_128(my_keys, nkeep, lane);
+      else warp_sort_regs_256(my_keys, nkeep, lane);
     }
     if (lane == 0) {
       s_kept[warp] = nkeep < M ? nkeep : M;
@@ -1011,7 +1012,7 @@ int graph_search_impl(const grab_search_args* g) {
   }
   const bool local_hash = a.hash_bitlen <= 13 && mp.parts == 1;
   const size_t hash_bytes = sizeof(uint32_t) * (size_t(1) << a.hash_bitlen);
-  // warp-split kernel: lists of 64 / 128 entries, at most 128 candidates per warp and iteration
+  // warp-split kernel: lists of 64 / 128 entries, at most 256 candidates per warp and iteration
   const uint32_t blind = (!g->d_seeds && !need_window && !(f.kind == GRAB_FILTER_LABELS && f.d_label_offsets) &&
                           f.kind != GRAB_FILTER_NONE && f.kind != GRAB_FILTER_PREFIX) ? 1u : 0u;
   const uint32_t warp_edges = (a.width * a.active_deg + kSearchThreads - 1) / kSearchThreads * 32;
@@ -1019,7 +1020,9 @@ int graph_search_impl(const grab_search_args* g) {
   const uint32_t warp_seeds = blind ? (nseeds + 1) / 2 : (part_seeds + kSearchThreads - 1) / kSearchThreads * 32;
   uint32_t wcap = next_pow2(warp_edges > warp_seeds ? warp_edges : warp_seeds);
   if (wcap < 32) wcap = 32;
-  const bool split = search_kernel_choice() == 1 && (a.sort_cap == 64 || a.sort_cap == 128) && wcap <= 128;
+  // (a 256-entry list on this kernel -- 8 list registers per lane, 8 CTAs per SM -- was measured level with the
+  // shared-list kernel, 7.69 against 7.57 ms at itopk 256 / width 6 / 50 iterations, and is left to the latter)
+  const bool split = search_kernel_choice() == 1 && (a.sort_cap == 64 || a.sort_cap == 128) && wcap <= 256;
   a.inv_active_deg = a.active_deg > 1 ? static_cast<uint32_t>(((1ull << 32) + a.active_deg - 1) / a.active_deg) : 0;
   size_t smem = sizeof(uint64_t) * (a.sort_cap + a.ckeys_cap) + sizeof(float) * a.dim + sizeof(uint32_t) * a.cand_cap +
                 sizeof(uint32_t) * ((a.width + 3) & ~3u) + (local_hash ? hash_bytes : 0);

@@ -145,6 +145,7 @@ template <int R> struct Log2Of32R;
 template <> struct Log2Of32R<1> { static constexpr int value = 5; };
 template <> struct Log2Of32R<2> { static constexpr int value = 6; };
 template <> struct Log2Of32R<4> { static constexpr int value = 7; };
+template <> struct Log2Of32R<8> { static constexpr int value = 8; };
 
 // Sorts the nkeep (<= 32*R) candidate keys and folds them into the sorted list top[0..32*R).
 template <int R>
@@ -207,6 +208,9 @@ __device__ __forceinline__ void warp_sort_regs(uint64_t* keys, uint32_t count, u
 }
 static __device__ __noinline__ void warp_sort_regs_128(uint64_t* keys, uint32_t count, uint32_t lane) {
   warp_sort_regs<4>(keys, count, lane);
+}
+static __device__ __noinline__ void warp_sort_regs_256(uint64_t* keys, uint32_t count, uint32_t lane) {
+  warp_sort_regs<8>(keys, count, lane);
 }
 
 // top[0, 32*R) sorted; run0[0, n0) and run1[0, n1) ascending.  Leaves the 32*R smallest of the union,

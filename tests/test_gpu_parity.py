@@ -355,7 +355,8 @@ def test_graph_search_range_recall_parity(grab, oracle, small_graph):
     hi = lo + np.uint64(n // 2)
     gt, _ = oracle.exact_search(data, q, k, ts=ts, lo=lo, hi=hi)
     seeds = np.stack([rng.integers(int(lo[i]), int(hi[i]), 32) for i in range(nq)]).astype(np.uint32)
-    for itopk, width in [(64, 4), (128, 2)]:
+    # (256, 4): the 256-entry list; (128, 12): 384 edges per iteration, 192 candidates per warp
+    for itopk, width in [(64, 4), (128, 2), (256, 4), (128, 12)]:
         oi, _ = oracle.graph_search(data, g, q, k, itopk, width, 40, 13, mode=2, ts=ts, lo=lo, hi=hi, seeds=seeds)
         f = grab.make_filter(grab.FILTER_TS_RANGE, ts=_t(ts.view(np.int64)), lo=_t(lo.view(np.int64)),
                              hi=_t(hi.view(np.int64)))
