@@ -49,7 +49,17 @@ constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;  // one K block of e
 // work at all, i.e. 72 bytes per clock and SM).
 constexpr int kAresBlocks = 3;
 constexpr int kAresStages = (STAGES * STAGE_BYTES - kAresBlocks * A_BYTES) / B_BYTES;  // same footprint: 3
-constexpr int THREADS = 192;
+// Epilogue warpgroups per CTA.  With two, warps 2-5 take the tiles of accumulator 0 and warps 6-9 those of
+// accumulator 1 (consecutive column tiles), each group with candidate buffers and thresholds of its own, so that
+// twice as many warps hide the epilogue's latencies; a row then leaves two candidate lists for the re-rank.
+// Measured at 1M x 128 (96 registers, one TMEM buffer per thread): own-block sweep 53 -> 36 ms, but the cross-bucket
+// sweep 333 -> 358 ms and the re-rank of two lists 29 -> 56 ms: whole build 0.60 -> 0.64 s.  Off.
+#ifndef GRAB_KNN_EPI_WGS
+#define GRAB_KNN_EPI_WGS 1
+#endif
+constexpr int EPI_WGS = GRAB_KNN_EPI_WGS;
+static_assert(EPI_WGS == 1 || EPI_WGS == 2, "one epilogue warpgroup per accumulator at most");
+constexpr int THREADS = 64 + 128 * EPI_WGS;
 // Instruction descriptor: D fp32, A/B bf16, both K-major, N=128, M=128.
 constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((BN >> 3) << 17) | ((BM >> 4) << 24);
 
@@ -205,7 +215,7 @@ struct SharedCtl {
   uint64_t full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], a_full, a_empty;
   uint32_t tmem_base;
   int abort_flag;
-  uint32_t hist[4][256];    // radix-select histogram per epilogue warp
+  uint32_t hist[4 * EPI_WGS][256];    // radix-select histogram per epilogue warp
 };
 
 template <int KC, bool ARES>
@@ -350,10 +360,11 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
       }
     }
   } else {
-    // ============================ epilogue (warps 2..5) ============================
+    // ============================ epilogue (warps 2..5, and 6..9 with two groups) ============================
     const uint32_t quarter = warp & 3;          // TMEM lane quarter this warp may read
+    const uint32_t wg = (warp - 2) >> 2;        // epilogue warpgroup = the accumulator it serves when there are two
     const uint32_t r_local = quarter * 32 + lane;
-    uint64_t* warp_buf = scratch + (static_cast<uint64_t>(blockIdx.x) * BM + quarter * 32) * CAP;
+    uint64_t* warp_buf = scratch + ((static_cast<uint64_t>(blockIdx.x) * EPI_WGS + wg) * BM + quarter * 32) * CAP;
     uint64_t* my_buf = warp_buf + static_cast<uint64_t>(lane) * CAP;
     uint32_t tile = 0;
     bool ok = true;
@@ -375,6 +386,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
       for (uint32_t j = t.jb; j < t.je && ok; ++j) {
         if (tile_skipped(t, j)) continue;
         const uint32_t acc = tile & 1, acc_phase = (tile >> 1) & 1;
+        if (EPI_WGS == 2 && acc != wg) { ++tile; continue; }  // the other group's tile
         const uint32_t c0 = j * BN;
         KNN_PHASE(5);
         if (!mbar_wait(smem_u32(&ctl->tmem_full[acc]), acc_phase, abort_flag)) { ok = false; break; }
@@ -433,24 +445,36 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
           }
         };
 
-        uint32_t va[32], vb[32];
 #if defined(GRAB_KNN_PROBE_NO_TMEM_LOAD)  // timing probe only: the accumulator is never read
         if (false)
 #endif
-        {
-        tmem_ld32_issue(taddr, va);
-        tmem_ld_wait(va);
-        KNN_PHASE(1);
-#pragma unroll 1
-        for (uint32_t pair = 0; pair < BN / 64; ++pair) {
-          tmem_ld32_issue(taddr + pair * 64 + 32, vb);
-          process(va, 2 * pair);
-          tmem_ld_wait(vb);
+        if (EPI_WGS == 1) {
+          // one group: the next 32 columns are in flight while the current 32 are tested
+          uint32_t va[32], vb[32];
+          tmem_ld32_issue(taddr, va);
+          tmem_ld_wait(va);
           KNN_PHASE(1);
-          if (pair + 1 < BN / 64) tmem_ld32_issue(taddr + pair * 64 + 64, va);
-          process(vb, 2 * pair + 1);
-          if (pair + 1 < BN / 64) { tmem_ld_wait(va); KNN_PHASE(1); }
-        }
+#pragma unroll 1
+          for (uint32_t pair = 0; pair < BN / 64; ++pair) {
+            tmem_ld32_issue(taddr + pair * 64 + 32, vb);
+            process(va, 2 * pair);
+            tmem_ld_wait(vb);
+            KNN_PHASE(1);
+            if (pair + 1 < BN / 64) tmem_ld32_issue(taddr + pair * 64 + 64, va);
+            process(vb, 2 * pair + 1);
+            if (pair + 1 < BN / 64) { tmem_ld_wait(va); KNN_PHASE(1); }
+          }
+        } else {
+          // two groups: one buffer per thread (the register budget of 640 threads per SM); the other group's warps
+          // cover the load latency
+          uint32_t va[32];
+#pragma unroll 1
+          for (uint32_t chunk = 0; chunk < BN / 32; ++chunk) {
+            tmem_ld32_issue(taddr + chunk * 32, va);
+            tmem_ld_wait(va);
+            KNN_PHASE(1);
+            process(va, chunk);
+          }
         }
 
         tc_fence_before();
@@ -470,7 +494,8 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         const uint32_t row = t.row0 + quarter * 32 + r;
         if (row >= n) continue;  // uniform across the warp
         const uint64_t* rb = warp_buf + static_cast<uint64_t>(r) * CAP;
-        for (uint32_t i = lane; i < KC; i += 32) out_keys[static_cast<uint64_t>(row) * KC + i] = i < c_r ? rb[i] : kMaxKey;
+        for (uint32_t i = lane; i < KC; i += 32)
+          out_keys[(static_cast<uint64_t>(row) * EPI_WGS + wg) * KC + i] = i < c_r ? rb[i] : kMaxKey;
       }
       __syncwarp();
     }
@@ -628,19 +653,33 @@ __global__ void sample_window_kernel(const ScanWindow* __restrict__ w, uint64_t 
   ws[r] = b;
 }
 
-// thr0[r] = largest of the row's kSeedKC sample keys; +inf when the sample held fewer (the row's window is small)
+// thr0[r] = the kSeedKC-th smallest of the row's sample keys (one list of kSeedKC per epilogue warpgroup); +inf when
+// the sample held fewer (the row's window is small).  One warp per row; keys are distinct, so a key's rank is the
+// number of keys below it.
 __global__ void seed_threshold_kernel(const uint64_t* __restrict__ keys, uint64_t n, float* __restrict__ thr0) {
   const uint64_t r = (blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x) >> 5;
   const uint32_t lane = threadIdx.x & 31;
   if (r >= n) return;
-  static_assert(kSeedKC == 32, "one key per lane");
-  uint64_t key = keys[r * kSeedKC + lane];
+  static_assert(kSeedKC == 32, "one key per lane and list");
+  uint64_t mine[EPI_WGS];
+  uint32_t below[EPI_WGS];
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) {
-    const uint64_t o = __shfl_xor_sync(0xFFFFFFFFu, key, off);
-    key = o > key ? o : key;
-  }
-  if (lane == 0) thr0[r] = key == kMaxKey ? __int_as_float(0x7f800000) : key_dist(key);
+  for (int g = 0; g < EPI_WGS; ++g) { mine[g] = keys[(r * EPI_WGS + g) * kSeedKC + lane]; below[g] = 0; }
+#pragma unroll
+  for (int h = 0; h < EPI_WGS; ++h)
+    for (uint32_t j = 0; j < 32; ++j) {
+      const uint64_t o = __shfl_sync(0xFFFFFFFFu, mine[h], j);
+#pragma unroll
+      for (int g = 0; g < EPI_WGS; ++g) below[g] += o < mine[g];
+    }
+  float t = __int_as_float(0x7f800000);
+  bool found = false;
+#pragma unroll
+  for (int g = 0; g < EPI_WGS; ++g)
+    if (below[g] == kSeedKC - 1 && mine[g] != kMaxKey) { t = key_dist(mine[g]); found = true; }
+  const uint32_t who = __ballot_sync(0xFFFFFFFFu, found);
+  if (who == 0) { if (lane == 0) thr0[r] = t; }
+  else if (lane == static_cast<uint32_t>(__ffs(who) - 1)) thr0[r] = t;
 }
 
 // ------------------------------------------------------------------ host side
@@ -716,8 +755,8 @@ int knn_tc_impl(const float* d_dataset, uint64_t n, uint32_t dim, int metric, co
   GRAB_CUDA_TRY(wins.alloc(sizeof(ScanWindow) * n));
   GRAB_CUDA_TRY(a_op.alloc(sizeof(__nv_bfloat16) * n * kp));
   GRAB_CUDA_TRY(b_op.alloc(sizeof(__nv_bfloat16) * n * kp));
-  GRAB_CUDA_TRY(scratch.alloc(sizeof(uint64_t) * static_cast<uint64_t>(grid) * BM * cap_of(kc)));
-  GRAB_CUDA_TRY(keys.alloc(sizeof(uint64_t) * n * kc));
+  GRAB_CUDA_TRY(scratch.alloc(sizeof(uint64_t) * static_cast<uint64_t>(grid) * EPI_WGS * BM * cap_of(kc)));
+  GRAB_CUDA_TRY(keys.alloc(sizeof(uint64_t) * n * kc * EPI_WGS));
   GRAB_CUDA_TRY(status.alloc(sizeof(int)));
   GRAB_CUDA_TRY(cudaMemsetAsync(status.ptr, 0, sizeof(int), st));
   GRAB_CUDA_TRY(cudaMemcpyAsync(offs.ptr, h_block_offsets, sizeof(uint64_t) * (num_blocks + 1), cudaMemcpyHostToDevice, st));
@@ -763,7 +802,7 @@ int knn_tc_impl(const float* d_dataset, uint64_t n, uint32_t dim, int metric, co
   if (seed_thresholds_enabled() && widest >= static_cast<uint64_t>(stride) * kSeedKC * 8) {
     const uint64_t n_s = (n + stride - 1) / stride;
     GRAB_CUDA_TRY(wins_s.alloc(sizeof(ScanWindow) * n));
-    GRAB_CUDA_TRY(keys_s.alloc(sizeof(uint64_t) * n * kSeedKC));
+    GRAB_CUDA_TRY(keys_s.alloc(sizeof(uint64_t) * n * kSeedKC * EPI_WGS));
     GRAB_CUDA_TRY(thr0.alloc(sizeof(float) * n));
     sample_window_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(wins.as<ScanWindow>(), n, stride,
                                                                       wins_s.as<ScanWindow>());
@@ -807,13 +846,14 @@ int knn_tc_impl(const float* d_dataset, uint64_t n, uint32_t dim, int metric, co
 #undef GRAB_KNN_TC_LAUNCH
   GRAB_CUDA_TRY(cudaGetLastError());
   tm.mark("tcgen05 all-pairs + top-k");
-  const size_t rsmem = sizeof(uint64_t) * kc + sizeof(float) * dim;
+  const uint32_t kc_all = kc * EPI_WGS;  // candidates per row handed to the re-rank
+  const size_t rsmem = sizeof(uint64_t) * kc_all + sizeof(float) * dim;
   if (metric == GRAB_METRIC_L2)
-    rerank_kernel<GRAB_METRIC_L2><<<(unsigned)n, kRerankThreads, rsmem, st>>>(d_dataset, dim, keys.as<uint64_t>(), kc, k,
-                                                                           d_out_knn, d_out_dists);
+    rerank_kernel<GRAB_METRIC_L2><<<(unsigned)n, kRerankThreads, rsmem, st>>>(d_dataset, dim, keys.as<uint64_t>(), kc_all,
+                                                                           k, d_out_knn, d_out_dists);
   else
-    rerank_kernel<GRAB_METRIC_IP><<<(unsigned)n, kRerankThreads, rsmem, st>>>(d_dataset, dim, keys.as<uint64_t>(), kc, k,
-                                                                           d_out_knn, d_out_dists);
+    rerank_kernel<GRAB_METRIC_IP><<<(unsigned)n, kRerankThreads, rsmem, st>>>(d_dataset, dim, keys.as<uint64_t>(), kc_all,
+                                                                           k, d_out_knn, d_out_dists);
   GRAB_CUDA_TRY(cudaGetLastError());
   tm.mark("exact re-rank");
   int h_status = 0;
