@@ -2,7 +2,8 @@
 // oracle/_ref/libgrab_ref.so from the reference sources where they lie, never shipped).
 //
 // src/index/insert.cu compiles stand-alone except for one symbol, cagra::search (the base
-// launcher, src/index/cagra.cu:844-935, whose file needs FAISS).  Its parameter arithmetic is
+// launcher, src/index/cagra.cu:844-935).  When cagra.cu is part of the build (GRAB_REF_WITH_CAGRA_CU, see
+// ref_build_harness.cu) that launcher is the reference's own; otherwise its parameter arithmetic is
 // restated below so that the reference's find_near_nodes links.  The topology functions
 // update_topology_gpu_v1 (insert.cu:372-440) and update_topology_gpu_opt (:1398-1573) are called
 // as they are; the three kernels of the latter (:448, :579, :653) are also launched one by one,
@@ -44,6 +45,7 @@ __global__ void widen_ids_kernel(const uint32_t* src, int64_t* dst, size_t count
 }
 }  // namespace
 
+#ifndef GRAB_REF_WITH_CAGRA_CU  // with cagra.cu compiled in, the reference's own launcher is linked instead
 // cagra.cu:844-935 restated: itopk = max(k, itopk, 64); queue = max(256, pow2(itopk + W*deg)); seed
 // target itopk/4; the xor mask is fixed here (the reference draws std::random_device).  Only the
 // shared-memory visited table (hash_bitlen <= 13) is supported: the reference's global-table branch
@@ -72,6 +74,7 @@ void search(const float* d_dataset, size_t num_dataset, uint32_t dim, const uint
   cudaDeviceSynchronize();
   cudaFree(d_ids32);
 }
+#endif  // GRAB_REF_WITH_CAGRA_CU
 
 }  // namespace cagra
 

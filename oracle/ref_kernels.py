@@ -134,3 +134,59 @@ def find_near_nodes(data, num_existing, new, graph, search_k, itopk, width, max_
                                      C.c_uint32(max_iter), C.c_uint32(hash_bitlen), _ptr(ids), _ptr(dists)),
            "find_near_nodes")
     return ids, dists
+
+
+# ---------------------------------------------------------------------------------------------------------
+# Graph optimisation (src/index/cagra.cu compiled with the FAISS declaration shim, oracle/ref_build_harness.cu).
+# Host numpy arrays in and out, as the reference's functions take them; they launch their own kernels.
+# ---------------------------------------------------------------------------------------------------------
+def _np_u32(a):
+    import numpy as np
+    return np.ascontiguousarray(a, dtype=np.uint32)
+
+
+def optimize_prune(knn, out_deg):
+    """optimize_prune (src/index/cagra.cu:286-401): [n, in_deg] uint32 kNN graph -> [n, out_deg] pruned graph."""
+    import numpy as np
+    knn = _np_u32(knn)
+    n, in_deg = knn.shape
+    out = np.empty((n, out_deg), dtype=np.uint32)
+    _check(lib().ref_optimize_prune(knn.ctypes.data_as(C.c_void_p), out.ctypes.data_as(C.c_void_p), C.c_uint64(n),
+                                    C.c_uint32(in_deg), C.c_uint32(out_deg)), "optimize_prune")
+    return out
+
+
+def optimize_reverse(graph):
+    """optimize_create_reverse_graph (src/index/cagra.cu:455-548): -> (rev [n, deg], counts [n])."""
+    import numpy as np
+    graph = _np_u32(graph)
+    n, deg = graph.shape
+    rev = np.full((n, deg), 0xFFFFFFFF, dtype=np.uint32)
+    cnt = np.zeros(n, dtype=np.uint32)
+    _check(lib().ref_optimize_reverse(graph.ctypes.data_as(C.c_void_p), rev.ctypes.data_as(C.c_void_p),
+                                      cnt.ctypes.data_as(C.c_void_p), C.c_uint64(n), C.c_uint32(deg)),
+           "optimize_create_reverse_graph")
+    return rev, cnt
+
+
+def optimize_merge(graph, rev, counts):
+    """optimize_merge_graphs (src/index/cagra.cu:574-650): returns the merged copy of `graph`."""
+    graph = _np_u32(graph).copy()
+    rev, counts = _np_u32(rev), _np_u32(counts)
+    n, deg = graph.shape
+    _check(lib().ref_optimize_merge(graph.ctypes.data_as(C.c_void_p), rev.ctypes.data_as(C.c_void_p),
+                                    counts.ctypes.data_as(C.c_void_p), C.c_uint64(n), C.c_uint32(deg)),
+           "optimize_merge_graphs")
+    return graph
+
+
+def build(data, raw_knn, deg):
+    """build (src/index/cagra.cu:665-711): device dataset [n, dim] and raw kNN graph (int32 CUDA tensor [n, inter]
+    holding uint32 bits) -> final graph, int32 CUDA tensor [n, deg]."""
+    import torch
+    n, inter = raw_knn.shape
+    out = torch.empty((n, deg), dtype=torch.int32, device=raw_knn.device)
+    torch.cuda.synchronize()
+    _check(lib().ref_build(_ptr(data), C.c_uint64(n), _ptr(raw_knn), C.c_uint32(inter), C.c_uint32(deg), _ptr(out)),
+           "build")
+    return out
