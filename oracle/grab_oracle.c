@@ -16,9 +16,12 @@
  * Pinning: the reference ships no stored golden outputs; what it does ship are
  * known-answer tests (bitonic sort == std::sort of pairs, hashmap success
  * counts, constant-vector kNN ideal neighbours, exact brute force).  The test
- * suite runs this file against those known answers.  Parts whose reference
- * behaviour comes from libraries that are not in the reference tree (FAISS
- * IVF-PQ candidate sets, RAFT brute force, FAISS HNSW) are "parity unpinned".
+ * suite runs this file against those known answers, and against outputs of the
+ * reference's own code compiled for the GPU (search, insert, prune / reverse /
+ * merge, remote edges / reverse injection: tests/golden/reference_*.npz and the
+ * live three-way tests).  Parts whose reference behaviour comes from libraries
+ * that are not in the reference tree (FAISS IVF-PQ candidate sets, RAFT brute
+ * force, FAISS HNSW) are "parity unpinned".
  */
 #include <math.h>
 #include <stdint.h>

@@ -190,3 +190,60 @@ def build(data, raw_knn, deg):
     _check(lib().ref_build(_ptr(data), C.c_uint64(n), _ptr(raw_knn), C.c_uint32(inter), C.c_uint32(deg), _ptr(out)),
            "build")
     return out
+
+
+# ---------------------------------------------------------------------------------------------------------
+# Remote edges, reverse injection and the reference's own launchers (src/index/cagra_opt.cu compiled with the
+# FAISS / RAFT / RMM declaration shims, oracle/ref_opt_harness.cu).  torch CUDA tensors (int32 holding uint32 bits).
+# ---------------------------------------------------------------------------------------------------------
+def update_remote_edges(graph, ts, cand, local_deg):
+    """update_remote_edges_kernel (cagra_opt.cu:209-303) in place on `graph` [n, total]; `cand` [n, gk] is consumed."""
+    n, total = graph.shape
+    _check(lib().ref_update_remote_edges(_ptr(graph), _ptr(ts), _ptr(cand), C.c_uint64(n), C.c_uint32(total),
+                                         C.c_uint32(local_deg), C.c_uint32(cand.shape[1])), "update_remote_edges_kernel")
+
+
+def make_global_rev(graph, local_deg, max_rev=32):
+    """kern_make_global_rev_graph (cagra_opt.cu:457-482) -> (rev [n, max_rev], counts [n]); racy order inside a list."""
+    import torch
+    n, total = graph.shape
+    rev = torch.full((n, max_rev), -1, dtype=torch.int32, device=graph.device)
+    cnt = torch.zeros(n, dtype=torch.int32, device=graph.device)
+    _check(lib().ref_make_global_rev(_ptr(graph), _ptr(rev), _ptr(cnt), C.c_uint64(n), C.c_uint32(total),
+                                     C.c_uint32(local_deg), C.c_uint32(max_rev)), "kern_make_global_rev_graph")
+    return rev, cnt
+
+
+def inject_global_rev(graph, rev, cnt, local_deg):
+    """kern_inject_global_reverse_edges (cagra_opt.cu:487-600) in place on `graph`."""
+    n, total = graph.shape
+    _check(lib().ref_inject_global_rev(_ptr(graph), _ptr(rev), _ptr(cnt), C.c_uint64(n), C.c_uint32(total),
+                                       C.c_uint32(local_deg), C.c_uint32(rev.shape[1])),
+           "kern_inject_global_reverse_edges")
+
+
+def enhance_global_connectivity(graph, local_deg):
+    """enhance_global_connectivity (cagra_opt.cu:739-793): both kernels in a row, in place (racy through the lists)."""
+    n, total = graph.shape
+    _check(lib().ref_enhance_global_connectivity(C.c_uint64(n), _ptr(graph), C.c_uint32(total), C.c_uint32(local_deg)),
+           "enhance_global_connectivity")
+
+
+def search_launcher(mode, dataset, graph, queries, k, itopk, width, max_iter, hash_bitlen, local_deg=None, ts=None,
+                    lo=0, hi=0, seeds=None):
+    """The reference's own launchers: mode 0 search_opt, 1 search_bucket_opt, 2 search_bucket_range."""
+    import torch
+    n, dim = dataset.shape
+    nq = queries.shape[0]
+    total = graph.shape[1]
+    ids = torch.empty((nq, k), dtype=torch.int64, device=dataset.device)
+    dists = torch.empty((nq, k), dtype=torch.float32, device=dataset.device)
+    torch.cuda.synchronize()
+    _check(lib().ref_search_launcher(C.c_int(mode), _ptr(dataset), C.c_uint32(dim), C.c_uint64(n), _ptr(graph),
+                                     C.c_uint32(total), C.c_uint32(local_deg if local_deg is not None else total),
+                                     _ptr(ts), C.c_uint64(lo), C.c_uint64(hi), _ptr(queries), C.c_int64(nq),
+                                     C.c_int64(k), C.c_uint32(itopk), C.c_uint32(width), C.c_uint32(max_iter),
+                                     C.c_uint32(hash_bitlen), _ptr(seeds),
+                                     C.c_uint32(seeds.shape[1] if seeds is not None else 0), _ptr(ids), _ptr(dists)),
+           "search launcher")
+    return ids, dists
