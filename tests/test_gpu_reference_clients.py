@@ -1,8 +1,9 @@
 """The reference's own test programs as clients of this library.
 
-`make -C oracle clients REF=<reference root>` compiles tests/test_knn_build.cu, tests/test_cagra_build.cu and
-tests/test_cagra_auto.cu of the reference, unmodified and from where they lie, against the stand-in headers in
-grab-anns_b200/host (cagra.cuh, cagraIndex.hpp) and links them with libgrab_anns.so.  The binaries travel
+`make -C oracle clients REF=<reference root>` compiles tests/test_knn_build.cu, test_cagra_build.cu,
+test_cagra_auto.cu, test_cagra_opt.cu and test_cagra_opt_search_bucket.cu of the reference, unmodified and from
+where they lie, against the stand-in headers in grab-anns_b200/host (cagra.cuh, cagraIndex.hpp, cagraIndexOpt.cuh)
+and links them with libgrab_anns.so.  The binaries travel
 prebuilt; here they run on the GPU and their own pass criteria (and, where a program only prints, the recall it
 prints) are checked.
 """
@@ -90,3 +91,42 @@ def test_reference_class_range_program(tmp_path):
     floor = {"1": 0.99, "10": 0.70, "20": 0.90, "100": 0.99}
     for itopk, iters, pct, recall in rows:
         assert float(recall) >= floor[pct], (itopk, iters, pct, recall)
+
+
+def _sift_like(n, dim, seed, centres=200):
+    rng = np.random.default_rng(seed)
+    c = rng.standard_normal((centres, dim)).astype(np.float32)
+    a = rng.standard_normal((12, dim)).astype(np.float32)
+    return (c[rng.integers(0, centres, n)] + rng.standard_normal((n, 12)).astype(np.float32) @ a
+            + 0.05 * rng.standard_normal((n, dim)).astype(np.float32)).astype(np.float32)
+
+
+def _hotpot_stand_in(tmp_path, n, dim, seed):
+    """../data/hotpotqa_fullwiki_train.{meta.json,bin} as the programs read them: a JSON with "dim" and "total", and
+    the vectors as raw float32 rows (a seeded synthetic stand-in; the data set itself is not part of the reference)."""
+    (tmp_path / "data").mkdir()
+    (tmp_path / "run").mkdir()
+    _sift_like(n, dim, seed).tofile(tmp_path / "data" / "hotpotqa_fullwiki_train.bin")
+    # one key per line: one of the programs parses the file line by line
+    (tmp_path / "data" / "hotpotqa_fullwiki_train.meta.json").write_text('{\n  "dim": %d,\n  "total": %d\n}\n' % (dim, n))
+    return tmp_path / "run"
+
+
+def test_reference_opt_class_program(tmp_path):
+    # tests/test_cagra_opt.cu: CagraIndexOpt(dim) (degree 32, 16 local), 40 timestamp buckets, add + build, then the
+    # global query with itopk 512, width 6, 100 iterations, hash 2^16; its own criterion: recall@10 > 90 % against
+    # its CPU ground truth ("graph is well-connected") -> exit code 0
+    rc, out = run(client("test_cagra_opt"), _hotpot_stand_in(tmp_path, 80000, 128, 11))
+    assert rc == 0, out[-2000:]
+    assert "PASSED" in out
+    m = re.search(r"Recall@10:\s+([0-9.]+)%", out)
+    assert m and float(m.group(1)) > 90.0
+
+
+def test_reference_opt_bucket_search_program(tmp_path):
+    # tests/test_cagra_opt_search_bucket.cu: CagraIndexOpt(dim, 64), 4 buckets of 10 000, query_local in random
+    # buckets; its own criterion: 0 results outside the bucket and average recall@10 > 95 % -> exit code 0
+    rc, out = run(client("test_cagra_opt_search_bucket"), _hotpot_stand_in(tmp_path, 40000, 128, 12))
+    assert rc == 0, out[-2500:]
+    m = re.search(r"Avg Recall@\d+:\s+([0-9.]+)%", out)
+    assert m and float(m.group(1)) > 95.0
