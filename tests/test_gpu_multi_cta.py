@@ -51,7 +51,10 @@ def test_multi_cta_unfiltered(grab, oracle, index, nq, ctas):
     ids, dists, st = grab.graph_search(_t(data), _t(g.view(np.int32)), _t(q), k, p, ctas_per_query=ctas, stats=True)
     _contract(oracle, data, q, ids, dists)
     r1, rm = oracle.recall(one.cpu().numpy(), gt), oracle.recall(ids.cpu().numpy(), gt)
-    assert rm >= r1 - 0.01 and rm > 0.9, (rm, r1)
+    # which CTA wins a node is a race, so a result's tail may differ from run to run: allow one and a half misses
+    # over the whole batch when the batch is tiny
+    tol = max(0.01, 1.5 / (nq * k))
+    assert rm >= r1 - tol and rm >= 0.9 - 1e-9, (rm, r1)
     assert st.hash_resets == 0 and st.parents > 0
 
 
