@@ -2,6 +2,7 @@
 #include <algorithm>
 #include <cmath>
 #include <cstring>
+#include <exception>
 #include <fstream>
 #include <mutex>
 #include <random>
@@ -942,18 +943,33 @@ void TimeStampIndex::query(const float* query, size_t topk, int64_t* out_indices
   std::stable_sort(ranked.begin(), ranked.end());
   std::vector<std::pair<float, int64_t>> all;
   const size_t probes = std::min<size_t>(probe_buckets, ranked.size());
-  for (size_t r = 0; r < probes; ++r) {
-    const uint64_t ts = ranked[r].second;
-    cagra::CagraIndex* bucket = buckets_.at(ts).get();
-    const BucketContext& ctx = bucket_contexts_.at(ts);
-    std::vector<uint32_t>& seeds = votes[ts].second;
-    std::vector<int64_t> bi(topk);
-    std::vector<float> bd(topk);
-    bucket->query(query, 1, static_cast<int>(topk), bi.data(), bd.data(), seeds.data(), seeds.size());
-    for (size_t k = 0; k < topk; ++k)
-      if (bi[k] >= 0 && static_cast<size_t>(bi[k]) < ctx.local_to_global.size())
-        all.push_back({bd[k], static_cast<int64_t>(ctx.local_to_global[bi[k]])});
+  // the probed buckets are independent indexes with query scratch and streams of their own: search them side by
+  // side, as the reference does (src/timeStampIndex.cu:318-372, an OpenMP loop over the buckets)
+  std::vector<std::vector<std::pair<float, int64_t>>> found(probes);
+  std::exception_ptr failure;
+  int device = 0;
+  cu(cudaGetDevice(&device), "cudaGetDevice");  // worker threads start on device 0: hand them the caller's device
+#pragma omp parallel for schedule(dynamic) num_threads(8)
+  for (long r = 0; r < static_cast<long>(probes); ++r) {
+    try {
+      cu(cudaSetDevice(device), "cudaSetDevice");
+      const uint64_t ts = ranked[r].second;
+      cagra::CagraIndex* bucket = buckets_.at(ts).get();
+      const BucketContext& ctx = bucket_contexts_.at(ts);
+      std::vector<uint32_t>& seeds = votes.at(ts).second;
+      std::vector<int64_t> bi(topk);
+      std::vector<float> bd(topk);
+      bucket->query(query, 1, static_cast<int>(topk), bi.data(), bd.data(), seeds.data(), seeds.size());
+      for (size_t k = 0; k < topk; ++k)
+        if (bi[k] >= 0 && static_cast<size_t>(bi[k]) < ctx.local_to_global.size())
+          found[r].push_back({bd[k], static_cast<int64_t>(ctx.local_to_global[bi[k]])});
+    } catch (...) {
+#pragma omp critical
+      if (!failure) failure = std::current_exception();
+    }
   }
+  if (failure) std::rethrow_exception(failure);
+  for (const auto& f : found) all.insert(all.end(), f.begin(), f.end());
   std::sort(all.begin(), all.end());
   for (size_t k = 0; k < topk; ++k) {
     out_indices[k] = k < all.size() ? all[k].second : -1;
