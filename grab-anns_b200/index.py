@@ -129,9 +129,11 @@ class CagraIndexOpt(_Base):
                    _ptr(ids), _ptr(d))
         return ids, d
 
-    def query_range_batch(self, queries, k, start, end):
+    def query_range_batch(self, queries, k, start, end, out=None):
+        """out: optional (ids int64 [nq, k], dists float32 [nq, k]) arrays of the caller's, as the C call takes them;
+        fresh arrays are allocated otherwise."""
         q, s, e = _f32(queries), _u64(start), _u64(end)
-        ids, d = self._out(q.shape[0], k)
+        ids, d = out if out is not None else self._out(q.shape[0], k)
         self._call("query_range_batch", _ptr(q), C.c_size_t(q.shape[0]), C.c_int(k), _ptr(s), _ptr(e), _ptr(ids),
                    _ptr(d))
         return ids, d
