@@ -13,7 +13,8 @@ _g = importlib.import_module("grab-anns_b200")
 def _lib():
     lib = _g.lib()
     if not getattr(lib, "_index_api_ready", False):
-        for name in ("grab_index_opt_create", "grab_index_create", "grab_tsindex_create"):
+        for name in ("grab_index_opt_create", "grab_index_create", "grab_tsindex_create",
+                     "grab_index_opt_create_on", "grab_index_create_on", "grab_tsindex_create_on"):
             getattr(lib, name).restype = C.c_void_p
         for name in ("grab_index_opt_size", "grab_index_size", "grab_tsindex_size"):
             getattr(lib, name).restype = C.c_size_t
@@ -75,10 +76,12 @@ class CagraIndexOpt(_Base):
     _prefix = "grab_index_opt_"
 
     def __init__(self, dim, graph_degree=32, local_degree=16, vmm_max_bytes=4 << 30, bucket_width=1, metric=0,
-                 knn_precision=2, seed=0x9E3779B97F4A7C15, insert_batch=4096):
+                 knn_precision=2, seed=0x9E3779B97F4A7C15, insert_batch=4096, device=-1):
+        """device: the GPU the index lives on (-1 = the calling thread's current device); every later call runs
+        there whatever the current device is."""
         self.dim, self.graph_degree = dim, graph_degree
-        self.h = _lib().grab_index_opt_create(C.c_uint32(dim), C.c_uint32(graph_degree), C.c_uint32(local_degree),
-                                              C.c_size_t(vmm_max_bytes))
+        self.h = _lib().grab_index_opt_create_on(C.c_int(device), C.c_uint32(dim), C.c_uint32(graph_degree),
+                                                 C.c_uint32(local_degree), C.c_size_t(vmm_max_bytes))
         if not self.h:
             raise _g.GrabError(1, _lib().grab_last_error().decode())
         self._call("configure", C.c_uint64(bucket_width), C.c_int(metric), C.c_int(knn_precision), C.c_uint64(seed),
@@ -149,9 +152,10 @@ class CagraIndex(_Base):
     _prefix = "grab_index_"
 
     def __init__(self, dim, graph_degree=64, vmm_max_bytes=4 << 30, metric=0, knn_precision=2,
-                 seed=0x9E3779B97F4A7C15, insert_batch=64):
+                 seed=0x9E3779B97F4A7C15, insert_batch=64, device=-1):
         self.dim, self.graph_degree = dim, graph_degree
-        self.h = _lib().grab_index_create(C.c_uint32(dim), C.c_uint32(graph_degree), C.c_size_t(vmm_max_bytes))
+        self.h = _lib().grab_index_create_on(C.c_int(device), C.c_uint32(dim), C.c_uint32(graph_degree),
+                                             C.c_size_t(vmm_max_bytes))
         if not self.h:
             raise _g.GrabError(1, _lib().grab_last_error().decode())
         self._call("configure", C.c_int(metric), C.c_int(knn_precision), C.c_uint64(seed), C.c_size_t(insert_batch))
@@ -190,9 +194,10 @@ class TimeStampIndex(_Base):
     """timestamp::TimeStampIndex (reference: src/timeStampIndex.cuh:39-95)."""
     _prefix = "grab_tsindex_"
 
-    def __init__(self, dim, degree=32, cluster_ratio=1000):
+    def __init__(self, dim, degree=32, cluster_ratio=1000, device=-1):
         self.dim = dim
-        self.h = _lib().grab_tsindex_create(C.c_uint32(dim), C.c_uint32(degree), C.c_size_t(cluster_ratio))
+        self.h = _lib().grab_tsindex_create_on(C.c_int(device), C.c_uint32(dim), C.c_uint32(degree),
+                                               C.c_size_t(cluster_ratio))
 
     def insert(self, vectors, timestamps):
         v, t = _f32(vectors), _u64(timestamps)

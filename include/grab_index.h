@@ -15,6 +15,12 @@ extern "C" {
 
 /* cagra::CagraIndexOpt */
 void* grab_index_opt_create(uint32_t dim, uint32_t graph_degree, uint32_t local_degree, size_t vmm_max_bytes);
+/* The same on a named GPU.  A handle belongs to the device it was made on (the calling thread's current one for the
+ * plain *_create): every call through it runs there whatever the caller's current device is, and leaves the
+ * caller's device as it was -- one host thread can drive indexes on several GPUs.  The reference compiles one
+ * device id in (src/index/common.cuh:5-7). */
+void* grab_index_opt_create_on(int device, uint32_t dim, uint32_t graph_degree, uint32_t local_degree,
+                               size_t vmm_max_bytes);
 void grab_index_opt_destroy(void* h);
 int grab_index_opt_configure(void* h, uint64_t bucket_width, int metric, int knn_precision, uint64_t seed,
                              size_t insert_batch);
@@ -53,6 +59,7 @@ int grab_index_opt_load(void* h, const char* path);
 
 /* cagra::CagraIndex */
 void* grab_index_create(uint32_t dim, uint32_t graph_degree, size_t vmm_max_bytes);
+void* grab_index_create_on(int device, uint32_t dim, uint32_t graph_degree, size_t vmm_max_bytes);
 void grab_index_destroy(void* h);
 int grab_index_configure(void* h, int metric, int knn_precision, uint64_t seed, size_t insert_batch);
 int grab_index_set_small_batch_mode(void* h, uint32_t ctas_per_query, size_t exact_below);
@@ -71,6 +78,7 @@ int grab_index_load(void* h, const char* path);
 
 /* timestamp::TimeStampIndex */
 void* grab_tsindex_create(uint32_t dim, uint32_t degree, size_t cluster_ratio);
+void* grab_tsindex_create_on(int device, uint32_t dim, uint32_t degree, size_t cluster_ratio);
 void grab_tsindex_destroy(void* h);
 int grab_tsindex_insert(void* h, const float* vectors, const uint64_t* timestamps, size_t n, uint64_t* first_id);
 int grab_tsindex_build_virtual_index(void* h);

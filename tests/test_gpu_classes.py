@@ -265,3 +265,33 @@ def test_timestamp_index_routed_search(grab, oracle, index_mod):
     assert ((ids >= 2 * per) & (ids < 3 * per)).all()
     ids, d = tsi.query_by_timestamp(qs[0], topk, 999)
     assert (ids == -1).all()
+
+
+def test_handles_are_bound_to_their_device(grab, oracle, index_mod):
+    """A handle made with *_create_on(device) runs every call on that GPU and leaves the caller's current device
+    alone; with two GPUs the index lives on the second while the first stays current."""
+    import torch
+    ngpu = torch.cuda.device_count()
+    target = 1 if ngpu >= 2 else 0
+    torch.cuda.set_device(0)
+    n, dim, nb, k = 12000, 64, 4, 10
+    data = clustered(n, dim, 24, 1.0, 81)
+    ts = np.repeat(np.arange(nb, dtype=np.uint64), n // nb)
+    torch.cuda.synchronize()
+    free0 = torch.cuda.mem_get_info(0)[0]
+    idx = index_mod.CagraIndexOpt(dim, 32, 24, device=target)
+    idx.add(data, ts)
+    idx.build()
+    assert torch.cuda.current_device() == 0
+    if ngpu >= 2:   # the index's memory is on the second GPU: the first one holds none of it
+        assert free0 - torch.cuda.mem_get_info(0)[0] < (32 << 20)
+    rng = np.random.default_rng(82)
+    q = data[rng.integers(0, n, 128)] + 0.1 * rng.standard_normal((128, dim)).astype(np.float32)
+    idx.set_query_params(128, 4, 0, 50, 13)
+    ids, _ = idx.query_range(q, k, 1, 3)
+    assert torch.cuda.current_device() == 0
+    assert ((ts[ids] >= 1) & (ts[ids] < 3)).all()
+    gt, _ = oracle.exact_search(data, q, k, ts=ts, lo=np.full(128, 1, np.uint64), hi=np.full(128, 3, np.uint64))
+    assert oracle.recall(ids, gt) > 0.95
+    with pytest.raises(Exception):
+        index_mod.CagraIndexOpt(dim, 32, 24, device=ngpu + 7)   # no such GPU: a status, not a crash
