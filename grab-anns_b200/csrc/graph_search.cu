@@ -883,12 +883,13 @@ static MultiPlan plan_multi(const grab_search_args* g) {
   const uint32_t W = g->params.search_width ? g->params.search_width : 1;
   const uint32_t budget = W * (g->params.max_iterations ? g->params.max_iterations : 1);  // expansions per query
   if (parts == GRAB_CTAS_AUTO) {
-    // fill about one wave of the GPU (148 SMs x 14 resident CTAs) and keep >= 8 iterations per CTA; beyond 16 CTAs
-    // the walks get too short to pay for their share of the merge (measured: 1 query, 300 expansions: 0.75 ms with
-    // one CTA, 0.26 / 0.15 / 0.40 ms with 4 / 16 / 64)
+    // Only long walks are split (a shared table in global memory, its clearing and the merge of the runs cost more
+    // than a short walk gains: 1 000 queries of 40 expansions take 0.097 ms with one CTA each, 0.118 ms with two), over
+    // at most 16 CTAs with at least 16 expansions each (1 query, 300 expansions: 0.75 ms with one CTA, 0.26 / 0.15 /
+    // 0.40 ms with 4 / 16 / 64), and only while the batch leaves room on the GPU (148 SMs x 14 resident CTAs).
     const uint64_t room = g->nq ? 2072 / g->nq : 1;
-    parts = static_cast<uint32_t>(room < 16 ? room : 16);
-    if (parts > budget / 8) parts = budget / 8;
+    parts = budget < 64 ? 1u : static_cast<uint32_t>(room < 16 ? room : 16);
+    if (parts > budget / 16) parts = budget / 16;
   }
   if (parts > 64) parts = 64;  // the merge takes up to 64 runs
   if (parts < 2 || g->k > 128 || search_kernel_choice() != 1) return p;

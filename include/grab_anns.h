@@ -149,9 +149,9 @@ int grab_exact_search_noalloc(const float* d_dataset, uint64_t n, uint32_t dim, 
 /* to fill the GPU): the budget of search_width * max_iterations expansions is spread over  */
 /* n CTAs with short lists of their own, disjoint shares of the seeds and ONE visited table */
 /* per query in global memory; their sorted lists are merged.  Same result FORMAT, not the  */
-/* same walk: judged on recall.  GRAB_CTAS_AUTO = as many as fill the GPU (1 for batches of */
-/* about a thousand queries and more).  Needs k <= 128; workspace size from                 */
-/* grab_graph_search_workspace_bytes_for().                                                  */
+/* same walk: judged on recall.  GRAB_CTAS_AUTO = as many as fill the GPU, for walks of 64   */
+/* expansions and more (1 for shorter walks and for batches of about a thousand queries).  */
+/* Needs k <= 128; workspace size from grab_graph_search_workspace_bytes_for().             */
 /* ------------------------------------------------------------------------------------ */
 #define GRAB_CTAS_AUTO 0xFFFFFFFFu
 typedef struct grab_search_args {
