@@ -40,8 +40,10 @@ struct DeviceGuard {
     if (device < 0) return;
     if (cudaGetDevice(&prev) != cudaSuccess) throw grab::StatusError(GRAB_ERR_CUDA, "cudaGetDevice failed");
     if (prev != device) {
-      if (cudaSetDevice(device) != cudaSuccess)
+      if (cudaSetDevice(device) != cudaSuccess) {
+        cudaGetLastError();  // a refused device id must not linger as the thread's "last error" for other CUDA users
         throw grab::StatusError(GRAB_ERR_CUDA, "cudaSetDevice(" + std::to_string(device) + ") failed");
+      }
       switched = true;
     }
   }
