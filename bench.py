@@ -742,10 +742,26 @@ def time_events(torch, fn, steps, warmup, dist=None):
     return float(t.item()) / steps
 
 
-def sharded_record(args, grab, torch, dist, w, rank, world, steps, warmup, d_base_full=None, shard=None):
+def sharded_record(args, grab, torch, dist, w, rank, world, steps, warmup, d_base_full=None, shard=None, shards=None):
     """The id-sharded path on `world` ranks: build this rank's stripe, search every query on it with the per-shard
     effort, ONE all-gather of the key runs (NCCL inside the C library) + G-way device merge, pipelined over two
-    buffer sets so that the exchange of step i overlaps the search of step i+1."""
+    buffer sets so that the exchange of step i overlaps the search of step i+1.
+
+    shards (S < world): shard GROUPS -- the ranks form world / S groups of S; every group holds the whole index
+    striped over its S ranks and answers its own slice of the query stream (a communicator per group, no traffic
+    between groups): capacity S x one GPU, throughput (world / S) x one group."""
+    all_ranks, my_rank = world, rank
+    groups, group = 1, 0
+    if shards and shards < world:
+        assert world % shards == 0 and shard is None
+        groups, group = world // shards, rank // shards
+        world, rank = shards, rank % shards
+        if group:   # every group answers different queries (same count)
+            w = dict(w)
+            w["queries"] = np.roll(w["queries"], group * 997, axis=0)
+            for key in ("lo", "hi", "masks"):
+                if key in w:
+                    w[key] = np.roll(w[key], group * 997)
     k = w["k"]
     by_labels = "labels" in w
     sch = shard_schedule(args, world, k, args.router_centroids, args.probes, shard_is_fraction=shard is None)
@@ -773,8 +789,18 @@ def sharded_record(args, grab, torch, dist, w, rank, world, steps, warmup, d_bas
         flt = ix.filter(d_lo, d_hi)
     kp = sch["run_length"]
     comm = None
-    if world > 1:
+    if world > 1 and groups == 1:
         comm = grab.Comm(world, rank, grab.torch_broadcast_bytes)
+    elif world > 1:
+        # one process group per shard group (every rank creates all of them, in the same order); the group's first
+        # rank hands its unique id to the others
+        pgs = [dist.new_group(ranks=list(range(g * world, (g + 1) * world))) for g in range(groups)]
+
+        def bcast(buf, pg=pgs[group], src=group * world):
+            t = torch.from_numpy(buf.copy()).cuda()
+            dist.broadcast(t, src=src, group=pg)
+            return t.cpu().numpy()
+        comm = grab.Comm(world, rank, bcast)
     # exact sharded ground truth: per-stripe exact top-k with global ids, gathered and merged the same way
     gi, gd = grab.exact_search(d_base, d_q, k, metric=w["metric"], flt=flt)
     gi = torch.where(gi >= 0, gi * world + rank, gi)
@@ -873,10 +899,20 @@ def sharded_record(args, grab, torch, dist, w, rank, world, steps, warmup, d_bas
                       device="cuda", dtype=torch.int64)
     alg = grab.search_bytes(stats, nq, ix.dim, ix.deg, kp, 1 if by_labels else 0)
     peak = measured_peak()[0]
-    rec = {"world": world, "striping": "gid % world == rank", "shard_vectors": int(ix.n), "queries": int(nq),
-           "value": nq / (ms_pipe / 1e3), "unit": "queries/s", "ms_per_step": ms_pipe,
+    if groups > 1:   # mean recall over the groups (every group answered its own queries)
+        t = torch.tensor([recall], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t)
+        recall = float(t.item()) / all_ranks
+        t = torch.tensor([1.0 if in_range else 0.0], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        in_range = bool(t.item() > 0.5)
+    rec = {"world": all_ranks, "shards": world, "shard_groups": groups,
+           "striping": "gid % shards == rank % shards" + ("; every group of `shards` ranks holds the whole index and "
+                                                           "answers its own queries" if groups > 1 else ""),
+           "shard_vectors": int(ix.n), "queries": int(nq * groups),
+           "value": groups * nq / (ms_pipe / 1e3), "unit": "queries/s", "ms_per_step": ms_pipe,
            "pipelining": "two buffer sets: the exchange of step i (high-priority stream) overlaps the search of step i+1",
-           "qps_unpipelined": nq / (ms_serial / 1e3), "ms_per_step_unpipelined": ms_serial,
+           "qps_unpipelined": groups * nq / (ms_serial / 1e3), "ms_per_step_unpipelined": ms_serial,
            "recall_at_k_merged": recall, "k": int(k), "results_in_range": in_range,
            "ground_truth": "exact filtered kernel per stripe, gathered and merged (the exact sharded result)",
            "per_shard_effort": sch, "ms_route": ms_route, "ms_search": ms_search,
@@ -1337,11 +1373,16 @@ def main():
     # the dominant kernel alone (the search launch with the routed seeds already written), for the roofline
     ms_search = timed(search_only, steps, warmup) if ix.router is not None else ms
 
-    sharded = None
+    sharded = sharded_groups = None
     if world > 1 and not args.no_sharded_record:
         del S
         torch.cuda.empty_cache()
         sharded = sharded_record(args, grab, torch, dist, w, rank, world, steps, warmup)
+        if world >= 4 and world % 2 == 0:
+            # the same path as shard groups: pairs of ranks hold the index between them, every pair answers its own
+            # queries -- half the index per GPU, throughput that grows with the number of pairs
+            torch.cuda.empty_cache()
+            sharded_groups = sharded_record(args, grab, torch, dist, w, rank, world, steps, warmup, shards=2)
 
     cpu = parity = e2e_cls = None
     if rank == 0 and world == 1:
@@ -1392,6 +1433,8 @@ def main():
         }
         if sharded is not None:
             line["sharded"] = sharded
+        if sharded_groups is not None:
+            line["sharded_groups"] = sharded_groups
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
