@@ -65,6 +65,8 @@ def parse():
                          "C2, 2 otherwise")
     ap.add_argument("--global-candidates", type=int, default=0,
                     help="cross-bucket candidates of the build: 0 auto, 1 all-pairs, 2 routed graph search")
+    ap.add_argument("--gc-iterations", type=int, default=0, help="routed candidate search: iterations (0 = library default)")
+    ap.add_argument("--gc-width", type=int, default=0, help="routed candidate search: parents per iteration (0 = library default)")
     ap.add_argument("--cpu-sample", type=int, default=0, help="queries in the CPU sample (0 = auto)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the GPU-exact-vs-CPU-oracle check at config shape")
@@ -384,7 +386,8 @@ def reference_kernel_bar(args, w):
         sizes = np.bincount(h_bucket.astype(np.int64)).tolist()
         graph = grab.build_time_partitioned_graph(d_base, torch.from_numpy(h_bucket.view(np.int64)).cuda(), sizes, deg,
                                                   args.local_degree, metric=0, knn_precision=args.knn_precision,
-                                                  global_candidates=args.global_candidates)
+                                                  global_candidates=args.global_candidates,
+                                                  search_iterations=args.gc_iterations, search_width=args.gc_width)
         nq = w["queries"].shape[0]
         d_q = torch.from_numpy(w["queries"]).cuda()
         width = max(1, int(n * args.selectivity))
@@ -580,13 +583,15 @@ class Index:
             wb = torch.arange(m, device="cuda") // (m // 2)
             grab.build_time_partitioned_graph(d_base[:m].contiguous(), wb.contiguous(), [m // 2, m // 2], self.deg,
                                               args.local_degree, metric=self.metric, knn_precision=args.knn_precision,
-                                              global_candidates=args.global_candidates)
+                                              global_candidates=args.global_candidates,
+                                                  search_iterations=args.gc_iterations, search_width=args.gc_width)
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         self.graph = grab.build_time_partitioned_graph(d_base, d_bucket.contiguous(), sizes, self.deg,
                                                        args.local_degree, metric=self.metric,
                                                        knn_precision=args.knn_precision,
-                                                       global_candidates=args.global_candidates)
+                                                       global_candidates=args.global_candidates,
+                                                  search_iterations=args.gc_iterations, search_width=args.gc_width)
         torch.cuda.synchronize()
         self.build_s = time.perf_counter() - t0
         self.router, self.router_s = None, 0.0

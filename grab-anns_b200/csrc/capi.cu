@@ -442,18 +442,26 @@ int grab_build_time_partitioned_graph_ex(const float* d_dataset, uint64_t total_
   gk = (gk + 32) - (gk % 32);
   if (gk < 64) gk = 64;
   if (gk > 256) gk = 256;
-  // all-pairs is exact but quadratic (0.5 s at 1M x 128, 75 s at 12.5M x 96): from 2^21 vectors on the
-  // routed search takes over (within 1 pp of the all-pairs graph in range-search recall)
-  if (global_mode == GRAB_GLOBAL_AUTO)
-    global_mode = total_num >= (1ull << 21) ? GRAB_GLOBAL_ROUTED_SEARCH : GRAB_GLOBAL_ALL_PAIRS;
+  // all-pairs is exact but quadratic (0.4 s at 1M x 128, 75 s at 12.5M x 96); the reference itself takes these
+  // candidates from an approximate index (IVF-PQ, cagra_opt.cu:813-847).  From 2^19 vectors on the routed search
+  // takes over: at 1M x 128 with 6 parents x 12 iterations it needs 0.21 s instead of 0.40 s and the finished
+  // graph answers 10 % range queries at recall 0.970 instead of 0.973; from 2^21 vectors on, where the candidates
+  // dominate the build, 4 x 10 (within 1 pp of the all-pairs graph).
+  uint32_t gc_iterations = options ? options->search_iterations : 0, gc_width = options ? options->search_width : 0;
+  if (global_mode == GRAB_GLOBAL_AUTO) {
+    global_mode = total_num >= (1ull << 19) ? GRAB_GLOBAL_ROUTED_SEARCH : GRAB_GLOBAL_ALL_PAIRS;
+    if (total_num < (1ull << 21)) {
+      if (!gc_iterations) gc_iterations = 12;
+      if (!gc_width) gc_width = 6;
+    }
+  }
   if (total_num < 4096) global_mode = GRAB_GLOBAL_ALL_PAIRS;
   {
     ScopedDeviceBuffer cand;
     GRAB_CUDA_TRY(cand.alloc(sizeof(uint32_t) * total_num * gk));
     if (global_mode == GRAB_GLOBAL_ROUTED_SEARCH) {
       GRAB_TRY(global_candidates_by_search(d_dataset, total_num, dim, metric, d_graph, total_degree, local_degree, gk,
-                                           options ? options->search_iterations : 0,
-                                           options ? options->search_width : 0, cand.as<uint32_t>()));
+                                           gc_iterations, gc_width, cand.as<uint32_t>()));
     } else {
       GRAB_TRY(knn_dispatch(d_dataset, total_num, dim, metric, offs.data(), num_buckets, gk, 1,
                             gk <= 204 ? knn_precision : GRAB_KNN_EXACT_SCAN, cand.as<uint32_t>(), nullptr, nullptr));

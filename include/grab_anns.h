@@ -271,13 +271,14 @@ int grab_build_time_partitioned_graph(const float* d_dataset, uint64_t total_num
 /* The same build with its choices spelled out.  Cross-bucket candidates (the reference's
  * IVF-PQ search over the whole dataset, cagra_opt.cu:813-847) come either from the all-pairs
  * tensor-core kernel (exact top candidates, quadratic in N) or from a routed graph search over
- * the local edges (approximate, linear in N); AUTO takes all-pairs below 2^21 vectors. */
+ * the local edges (approximate, linear in N); AUTO takes all-pairs below 2^19 vectors, the routed search
+ * with 6 parents x 12 iterations below 2^21 and with 4 x 10 from there on. */
 enum grab_global_candidates { GRAB_GLOBAL_AUTO = 0, GRAB_GLOBAL_ALL_PAIRS = 1, GRAB_GLOBAL_ROUTED_SEARCH = 2 };
 typedef struct grab_tp_build_options {
   int knn_precision;      /* grab_knn_precision */
   int global_candidates;  /* grab_global_candidates */
-  uint32_t search_iterations; /* routed search: iterations per vector (0 = 10) */
-  uint32_t search_width;      /* routed search: parents per iteration (0 = 4) */
+  uint32_t search_iterations; /* routed search: iterations per vector (0 = 10; AUTO: see above) */
+  uint32_t search_width;      /* routed search: parents per iteration (0 = 4; AUTO: see above) */
 } grab_tp_build_options;
 int grab_build_time_partitioned_graph_ex(const float* d_dataset, uint64_t total_num, uint32_t dim,
                                          int metric, uint32_t* d_graph, const uint64_t* d_bucket,
